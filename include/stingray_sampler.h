@@ -1,0 +1,265 @@
+/*
+ * stingray_sampler.h - C ABI of the B200 (sm_100a) token-sampling library.
+ *
+ * The library replaces, for batched [rows, vocab] logits that already live in device memory, the
+ * managed per-row loop of the reference host:
+ *     Filter -> Sampler.Greedy | Sampler.Sample -> (speculative accept / residual resampling)
+ * Each entry point below names the reference interface it stands in for (paths are relative to
+ * the reference project's root).
+ *
+ * Binding conventions follow the reference's own native bindings
+ * (src/OpenTail.Stingray.Cuda/CuBlasInterop.cs:37-41, NvrtcInterop.cs:371-380): every call returns
+ * an int status with 0 = success, handles and device pointers are pointer-sized integers created
+ * through an out parameter, structs are sequential-layout PODs, strings are UTF-8 copied into a
+ * caller buffer.  No C++ or framework types cross this boundary.
+ *
+ * Threading: a handle is not re-entrant (the reference drives the backend from one batcher
+ * thread, src/OpenTail.Stingray.Engine/ContinuousBatchingEngine.cs:495-500); distinct handles are
+ * independent.  Work is enqueued on the caller's stream; a call blocks only when it has to hand
+ * results back in host memory (STG_MEM_HOST_OUTPUTS) or is documented as blocking.
+ */
+#ifndef STINGRAY_SAMPLER_H
+#define STINGRAY_SAMPLER_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define STG_API __declspec(dllexport)
+#else
+#define STG_API __attribute__((visibility("default")))
+#endif
+
+#define STG_ABI_VERSION 1
+
+/* ---- status codes --------------------------------------------------------------------------- */
+enum {
+    STG_OK = 0,
+    STG_ERR_INVALID_ARGUMENT = 1, /* null pointer, negative size, size beyond the handle's limits */
+    STG_ERR_CUDA = 2,             /* a CUDA runtime call failed; stg_last_error has the text */
+    STG_ERR_CAPACITY = 3,         /* request exceeds the capacities given at stg_create */
+    STG_ERR_UNSUPPORTED = 4,      /* combination of options this build does not implement */
+    STG_ERR_TIMEOUT = 5,          /* a bounded device-side wait gave up */
+    STG_ERR_NCCL = 6,             /* NCCL could not be loaded or a collective failed */
+    STG_ERR_NO_DEVICE = 7         /* no usable CUDA device: there is no CPU fallback */
+};
+
+/* ---- element types of a logits buffer --------------------------------------------------------- */
+enum {
+    STG_DTYPE_F32 = 0,
+    STG_DTYPE_BF16 = 1 /* widened exactly to fp32 on load; the reference has fp32 logits only */
+};
+
+/* ---- where a caller array lives (bit set = host memory) ------------------------------------- */
+enum {
+    STG_MEM_HOST_LOGITS = 1u << 0,
+    STG_MEM_HOST_HISTORY = 1u << 1,  /* history_ids */
+    STG_MEM_HOST_MASK = 1u << 2,
+    STG_MEM_HOST_BIAS = 1u << 3,     /* bias_ids, bias_values */
+    STG_MEM_HOST_UNIFORMS = 1u << 4,
+    STG_MEM_HOST_OUTPUTS = 1u << 5,  /* every output array; makes the call blocking */
+    STG_MEM_HOST_DRAFT = 1u << 6     /* stg_spec_verify: draft_tokens */
+};
+
+/* ---- per-row flags written to StgSampleBatch.row_flags -------------------------------------- */
+enum {
+    STG_ROW_PATH_MASK = 0x7u,        /* 0 greedy, 1 greedy with penalties, 2 top-k path,
+                                        3 full-vocabulary path, 4 top-k path found no finite logit */
+    STG_ROW_TIE_AT_CUTOFF = 1u << 4, /* the top-p cut fell inside a group of equal probabilities */
+    STG_ROW_CDF_FALLBACK = 1u << 5,  /* the draw ran past the end of the CDF (rounding fallback) */
+    STG_ROW_FULLY_MASKED = 1u << 6,  /* no finite logit in the row */
+    STG_ROW_WIDE_NUCLEUS = 1u << 7   /* top-p candidates did not fit on chip; global-memory sort */
+};
+
+typedef struct StgSampler_ *StgHandle;
+
+/* Capacities fixed at creation; all device workspace is allocated once from them, so that no
+ * entry point allocates on the per-step path (the reference's own rule for this path,
+ * src/OpenTail.Stingray.Core/Grammar/ITokenConstraint.cs:22-23). */
+typedef struct StgConfig {
+    int32_t struct_size;  /* = sizeof(StgConfig) */
+    int32_t device;       /* CUDA device ordinal */
+    int32_t max_rows;     /* rows per call */
+    int32_t max_vocab;    /* vocabulary size per row */
+    int32_t max_history;  /* history entries per row; max_top_k + max_history <= 8192 */
+    int32_t max_top_k;
+    int32_t max_bias;     /* logit-bias entries per row */
+    int32_t max_spec_draft; /* draft length of stg_spec_verify (0 = entry point unused) */
+    uint32_t flags;       /* reserved, 0 */
+} StgConfig;
+
+/* SamplingParams of the reference (src/OpenTail.Stingray.Engine/Sampler.cs:648-686), the fields
+ * the sampler reads.  Defaults there: temperature 1, top_k 0 (off), top_p 1 (off), min_p 0 (off),
+ * repetition_penalty 1 (off), repeat_last_n 64 (0 = whole history), penalties 0. */
+typedef struct StgRowParams {
+    float temperature;
+    float top_p;
+    float min_p;
+    float repetition_penalty;
+    float presence_penalty;
+    float frequency_penalty;
+    int32_t top_k;
+    int32_t repeat_last_n;
+} StgRowParams;
+
+/* One batched sampling step.  `params`, `history_offsets` and `bias_offsets` are always HOST
+ * arrays (they are what the managed host builds per step, ContinuousBatchingEngine.cs:638-640);
+ * the location of every other array is given by `mem_flags` (bit clear = device memory). */
+typedef struct StgSampleBatch {
+    int32_t struct_size;            /* = sizeof(StgSampleBatch) */
+    int32_t rows;
+    int32_t vocab;
+    int32_t logits_dtype;           /* STG_DTYPE_* */
+    const void *logits;             /* [rows, row_stride] */
+    int64_t row_stride;             /* elements between rows (>= vocab) */
+    const StgRowParams *params;     /* host [rows] */
+    const int32_t *history_ids;     /* CSR values: PreviousTokens of each row, oldest first */
+    const int32_t *history_offsets; /* host [rows + 1], or NULL: no row has a history */
+    const uint32_t *mask;           /* allowed-token bitmask [rows, mask_row_stride] or NULL:
+                                       bit (i & 31) of word (i >> 5) set <=> token i untouched,
+                                       clear <=> -infinity (ITokenConstraint.Filter contract,
+                                       ITokenConstraint.cs:31-43) */
+    int64_t mask_row_stride;        /* 32-bit words between mask rows */
+    const uint8_t *row_uses_mask;   /* host [rows] or NULL (= every row when mask != NULL):
+                                       0 = this row is unconstrained (IsConstraining false) */
+    const int32_t *bias_ids;        /* CSR values of LogitBias (Sampler.cs:50-56) */
+    const float *bias_values;
+    const int32_t *bias_offsets;    /* host [rows + 1] or NULL */
+    const float *uniforms;          /* [rows]: (float)rng.NextDouble() of each non-greedy row */
+    int32_t *tokens;                /* out [rows] */
+    float *token_probs;             /* out [rows] or NULL: normalised probability of the token */
+    uint32_t *row_flags;            /* out [rows] or NULL: STG_ROW_* */
+    int32_t *topk_ids;              /* out [rows, topk_stride] or NULL: candidates of the top-k
+                                       path after the penalty re-sort (-1 = unused slot) */
+    float *topk_logits;             /* out, same shape or NULL: their penalised logits */
+    float *topk_probs;              /* out, same shape or NULL: softmax over the k candidates */
+    int32_t topk_stride;
+    uint32_t mem_flags;             /* STG_MEM_HOST_* */
+} StgSampleBatch;
+
+/* One speculative verification step over `n_seq` sequences with `n_draft` draft tokens each
+ * (SpeculativeDecoder.StepSampled, src/OpenTail.Stingray.Engine/SpeculativeDecoder.cs:529-559).
+ * target_logits: [n_seq, n_draft + 1, vocab] (row i predicts the slot of draft token i, the last
+ * row is the bonus position); draft_logits: [n_seq, n_draft, vocab] (row i is what draft token i
+ * was drawn from); both built into distributions with the same `params`. */
+typedef struct StgSpecBatch {
+    int32_t struct_size;
+    int32_t n_seq;
+    int32_t n_draft;
+    int32_t vocab;
+    int32_t logits_dtype;
+    int32_t mode;                   /* 0: accept with min(1, p/q), residual resampling;
+                                       1: looser accept p >= p_min || draft == argmax, draw from p */
+    const void *target_logits;
+    const void *draft_logits;       /* may be NULL when mode == 1 */
+    const int32_t *draft_tokens;    /* [n_seq, n_draft] */
+    const StgRowParams *params;     /* host [n_seq]; histories and bias do not apply here (the
+                                       reference turns speculation off when they are set,
+                                       src/OpenTail.Stingray.Cli/RunCommand.cs:1651-1678) */
+    const double *uniforms;         /* [n_seq, n_draft + 2]: rng.NextDouble() of each accept test,
+                                       then the two draws the correction/bonus may consume */
+    float p_min;                    /* SpecDraftPMin for mode 1 */
+    int32_t *accepted;              /* out [n_seq]: number of accepted draft tokens */
+    int32_t *correction;            /* out [n_seq]: residual / bonus token */
+    float *accept_probs;            /* out [n_seq, n_draft] or NULL: the ratio a (mode 0) or p(x) */
+    uint32_t *seq_flags;            /* out [n_seq] or NULL: STG_ROW_CDF_FALLBACK etc. */
+    uint32_t mem_flags;             /* STG_MEM_HOST_LOGITS | _DRAFT | _UNIFORMS | _OUTPUTS */
+} StgSpecBatch;
+
+typedef struct StgStats {
+    uint64_t calls;
+    uint64_t rows_sampled;
+    uint64_t rows_greedy;
+    uint64_t rows_topk_path;
+    uint64_t rows_full_path;
+    uint64_t sequences_verified;
+    uint64_t kernel_launches;
+    uint64_t plan_uploads;
+} StgStats;
+
+/* ---- lifetime ---------------------------------------------------------------------------------- */
+
+/* Allocates the workspace on `config->device`.  There is no counterpart in the reference (its
+ * sampler is managed code); the shape follows cublasCreate_v2's, CuBlasInterop.cs:37-38.
+ * Returns STG_ERR_NO_DEVICE when no CUDA device can be used: nothing falls back to the CPU. */
+STG_API int stg_create(const StgConfig *config, StgHandle *out_handle);
+STG_API int stg_destroy(StgHandle handle);
+STG_API int stg_abi_version(void);
+
+/* Copies the NUL-terminated text of the last failure on `handle` (or of the last stg_create
+ * failure when handle is NULL) into buf; returns the length needed, like
+ * nvrtcGetProgramLogSize + nvrtcGetProgramLog (NvrtcInterop.cs:268-272). */
+STG_API size_t stg_last_error(StgHandle handle, char *buf, size_t buf_len);
+STG_API int stg_get_stats(StgHandle handle, StgStats *out);
+
+/* ---- the hot path ------------------------------------------------------------------------------- */
+
+/* Per-row greedy argmax over device logits [rows, row_stride], valid length `vocab`.
+ * Replaces CudaBackend.ArgmaxRowsToDevice / ArgmaxRows (src/OpenTail.Stingray.Cuda/
+ * CudaBackend.cs:4141-4190) and the kernel llm_argmax_rows (CudaTextKernels.cs:465-492): out_pairs
+ * holds rows x {int32 index bits, float value}; the highest value wins, the lowest index on ties
+ * (Sampler.Greedy, Sampler.cs:442-446). */
+STG_API int stg_argmax_rows(StgHandle handle, const void *logits, int32_t logits_dtype,
+                            int32_t rows, int32_t vocab, int64_t row_stride, void *out_pairs,
+                            void *stream);
+
+/* One sampling step for every row of the batch: mask, logit bias, history penalties, temperature,
+ * top-k, min-p, top-p and the inverse-CDF draw.  Replaces the serial loop
+ *   ctr.Filter(row) -> Sampler.Greedy(row) | Sampler.Sample(row, spWithHistory, seq.Rng)
+ * of ContinuousBatchingEngine.cs:609-644 (and InferenceEngine.cs:1245-1253,
+ * InferenceSession.cs:494-510) after the logits download it makes unnecessary
+ * (CudaForwardPass.cs:5209-5217).  Row r consumes uniforms[r] only when its temperature > 0. */
+STG_API int stg_sample_rows(StgHandle handle, const StgSampleBatch *batch, void *stream);
+
+/* Materialises the post-filter distribution of each row into `probs` [rows, vocab] (device, or
+ * host with STG_MEM_HOST_OUTPUTS): Sampler.BuildFilteredDistribution, Sampler.cs:118-163.  Uses
+ * the same batch description; `uniforms`, `tokens` and the top-k outputs are ignored. */
+STG_API int stg_build_distribution(StgHandle handle, const StgSampleBatch *batch, float *probs,
+                                   void *stream);
+
+/* Speculative accept / reject with residual resampling for a batch of sequences: the loop of
+ * SpeculativeDecoder.StepSampled (SpeculativeDecoder.cs:529-559) with Sampler.ResampleResidual
+ * (Sampler.cs:587-618) and the bonus draw.  temperature <= 0 rows use the greedy accept of
+ * SpeculativeDecoder.Step (SpeculativeDecoder.cs:400-405): `correction` is then the target
+ * argmax at the first mismatch (or at the bonus position). */
+STG_API int stg_spec_verify(StgHandle handle, const StgSpecBatch *batch, void *stream);
+
+/* MTP verification rule for `rows` rows: accept iff draft == argmax(row) or (p_min < 1 and
+ * softmax(row)[draft] >= p_min), the softmax accumulated in double: MtpDecoder.AcceptDraft +
+ * SoftmaxProbAt, src/OpenTail.Stingray.Engine/MtpDecoder.cs:562-596.  Device arrays; accept is
+ * int32 [rows], argmax int32 [rows] or NULL, draft_prob float [rows] or NULL. */
+STG_API int stg_mtp_accept(StgHandle handle, const void *logits, int32_t logits_dtype, int32_t rows,
+                           int32_t vocab, int64_t row_stride, const int32_t *draft_tokens,
+                           float p_min, int32_t *accept, int32_t *argmax, float *draft_prob,
+                           void *stream);
+
+/* ---- vocabulary-sharded mode (no counterpart in the reference, which is single-device:
+ *      src/OpenTail.Stingray.Cli/RunCommand.cs:100) ------------------------------------------------
+ * Each rank holds the column slice [vocab_offset, vocab_offset + batch->vocab) of every row, the
+ * layout a tensor-parallel lm-head leaves behind.  stg_shard_select picks, per row, the local
+ * candidates of the top-k path (batch->vocab is the slice width, history ids are global token
+ * ids) into the handle's exchange buffer; stg_shard_allgather exchanges them between ranks with
+ * one ncclAllGather; stg_shard_finish merges the gathered candidates and finishes the sampling
+ * chain.  Only rows on the top-k path or greedy rows without penalties are supported; other rows
+ * return STG_ERR_UNSUPPORTED (use row sharding for those). */
+STG_API int stg_comm_unique_id(void *out_id128); /* 128 bytes; call on rank 0, then broadcast */
+STG_API int stg_comm_init(StgHandle handle, const void *id128, int32_t rank, int32_t n_ranks);
+STG_API int stg_comm_destroy(StgHandle handle);
+STG_API int stg_shard_select(StgHandle handle, const StgSampleBatch *batch, int32_t vocab_offset,
+                             int32_t global_vocab, void *stream);
+STG_API int stg_shard_allgather(StgHandle handle, void *stream);
+STG_API int stg_shard_finish(StgHandle handle, const StgSampleBatch *batch, int32_t global_vocab,
+                             void *stream);
+/* Single-process variant of the exchange for tests: copies `n_ranks` handles' local candidate
+ * buffers (all on the same device) into `handle`'s gather buffer as the all-gather would. */
+STG_API int stg_shard_gather_local(StgHandle handle, const StgHandle *peers, int32_t n_ranks,
+                                   void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* STINGRAY_SAMPLER_H */

@@ -1,0 +1,527 @@
+// C ABI of the sampling library: argument checks, the per-step host planner, staging of host
+// arrays, and the launches.  Everything behind this file is CUDA; there is no CPU code path.
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+#include <string.h>
+
+#include <algorithm>
+#include <string>
+#include <vector>
+
+#include "stg_handle.h"
+#include "stg_launch.h"
+#include "stg_types.h"
+
+using namespace stg;
+
+namespace stg {
+
+static std::string g_create_error;
+
+int fail(StgHandle h, int code, const std::string &msg)
+{
+    if (h) h->err = msg; else g_create_error = msg;
+    return code;
+}
+
+int cuda_fail(StgHandle h, cudaError_t e, const char *what)
+{
+    return fail(h, STG_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+int dev_alloc(StgHandle h, DevBuf &b, size_t bytes)
+{
+    bytes = std::max<size_t>(bytes, 256);
+    cudaError_t e = cudaMalloc(&b.p, bytes);
+    if (e != cudaSuccess) return cuda_fail(h, e, "cudaMalloc");
+    b.bytes = bytes;
+    return STG_OK;
+}
+
+void dev_free(DevBuf &b)
+{
+    if (b.p) cudaFree(b.p);
+    b.p = nullptr;
+    b.bytes = 0;
+}
+
+}  // namespace stg
+
+namespace {
+
+// RepeatWindowStart, src/OpenTail.Stingray.Engine/Sampler.cs:364-365
+int repeat_window_start(int count, int last_n) { return (last_n <= 0 || last_n >= count) ? 0 : count - last_n; }
+
+struct Plan {
+    std::vector<RowPlan> rows;
+    std::vector<WorkItem> items;
+    std::vector<float> pow_tab;
+    int chunk_len = 0;
+    int cap = kSubTile + 1;
+    bool any_row_item = false;
+    size_t smem = 0;
+    uint64_t n_greedy = 0, n_topk = 0, n_full = 0;
+};
+
+// Resolves every row's path exactly as Sampler.Sample dispatches (Sampler.cs:19-39) and lays out
+// the work items: whole-row items first (they run longest), then the chunk items row by row.
+int make_plan(StgHandle h, const StgSampleBatch *b, int mode, bool shard, Plan &pl)
+{
+    const int rows = b->rows, V = b->vocab;
+    pl.rows.resize(rows);
+    std::vector<std::pair<uint32_t, int>> reps;  // distinct repetition penalties -> table offset
+    int n_chunk_rows = 0, max_sel = 1;
+    for (int r = 0; r < rows; r++) {
+        const StgRowParams &p = b->params[r];
+        RowPlan &rp = pl.rows[r];
+        memset(&rp, 0, sizeof(rp));
+        rp.temperature = p.temperature; rp.top_p = p.top_p; rp.min_p = p.min_p;
+        rp.rep = p.repetition_penalty; rp.pres = p.presence_penalty; rp.freq = p.frequency_penalty;
+        rp.top_k = p.top_k;
+        int hoff = 0, hlen = 0, boff = 0, blen = 0;
+        if (b->history_offsets && b->history_ids) {
+            hoff = b->history_offsets[r];
+            hlen = b->history_offsets[r + 1] - hoff;
+        }
+        if (b->bias_offsets && b->bias_ids && b->bias_values) {
+            boff = b->bias_offsets[r];
+            blen = b->bias_offsets[r + 1] - boff;
+        }
+        if (hlen < 0 || blen < 0) return fail(h, STG_ERR_INVALID_ARGUMENT, "CSR offsets must be non-decreasing");
+        if (hlen > h->cfg.max_history) return fail(h, STG_ERR_CAPACITY, "history longer than max_history");
+        if (blen > h->cfg.max_bias) return fail(h, STG_ERR_CAPACITY, "more bias entries than max_bias");
+        rp.hist_off = hoff; rp.hist_len = hlen; rp.bias_off = boff; rp.bias_len = blen;
+        rp.window_start = repeat_window_start(hlen, p.repeat_last_n);
+        rp.use_mask = b->mask != nullptr && (b->row_uses_mask == nullptr || b->row_uses_mask[r] != 0);
+        rp.pow_off = -1;
+        const bool pen_set = p.repetition_penalty != 1.0f || p.presence_penalty != 0.f || p.frequency_penalty != 0.f;
+        rp.has_penalty = pen_set && hlen > 0;
+        rp.sel = 1;
+        if (mode == 1) {
+            rp.path = p.temperature <= 0.f ? (rp.has_penalty ? kPathGreedyPen : kPathGreedy) : kPathFull;
+            rp.n_chunks = 0;
+        } else if (p.temperature <= 0.f) {
+            rp.path = rp.has_penalty ? kPathGreedyPen : kPathGreedy;
+        } else if (p.top_k > 0 && p.top_k < V && blen == 0) {
+            rp.path = kPathTopK;
+            int64_t want = (int64_t)p.top_k + (rp.has_penalty ? hlen : 0);
+            rp.sel = (int)std::min<int64_t>(want, V);
+            if (p.top_k > h->cfg.max_top_k) return fail(h, STG_ERR_CAPACITY, "top_k larger than max_top_k");
+            if (rp.sel > kMaxSel) return fail(h, STG_ERR_CAPACITY, "top_k + history length exceeds 8192");
+            if (rp.has_penalty && p.repetition_penalty != 1.0f) {
+                uint32_t bits;
+                memcpy(&bits, &p.repetition_penalty, 4);
+                int off = -1;
+                for (auto &e : reps) if (e.first == bits) off = e.second;
+                if (off < 0) {
+                    off = (int)pl.pow_tab.size();
+                    reps.push_back({bits, off});
+                    // MathF.Pow(RepetitionPenalty, occWindow), Sampler.cs:283, through the host's libm
+                    for (int o = 1; o <= kPowTab; o++) pl.pow_tab.push_back(powf(p.repetition_penalty, (float)o));
+                }
+                rp.pow_off = off;
+            }
+        } else {
+            rp.path = kPathFull;
+        }
+        if (rp.path == kPathFull) {
+            if (p.top_k > 4096 && p.top_k < V)
+                return fail(h, STG_ERR_UNSUPPORTED, "top_k above 4096 on the full-vocabulary path");
+            if (hlen + blen > kMaxOverride) return fail(h, STG_ERR_CAPACITY, "history + bias entries exceed 16384");
+        }
+        if (shard && !(rp.path == kPathTopK || rp.path == kPathGreedy))
+            return fail(h, STG_ERR_UNSUPPORTED, "vocabulary-sharded mode supports top-k and plain greedy rows only");
+        const bool chunked = mode != 1 && (rp.path == kPathGreedy || rp.path == kPathTopK);
+        if (chunked) { n_chunk_rows++; max_sel = std::max(max_sel, rp.sel); }
+        else pl.any_row_item = true;
+        if (rp.path == kPathTopK) pl.n_topk++; else if (rp.path == kPathFull) pl.n_full++; else pl.n_greedy++;
+    }
+    // chunking: enough chunk items to balance the SMs, whole 4096-element sub-tiles per chunk
+    int S = 1;
+    if (n_chunk_rows > 0) {
+        int want = (4 * h->sm_count + n_chunk_rows - 1) / n_chunk_rows;
+        int max_s = std::max(1, (V + 16383) / 16384);
+        S = std::max(1, std::min({want, max_s, 64}));
+        if (shard) S = std::min(S, 16);
+    }
+    for (;;) {
+        pl.chunk_len = (int)round_up((size_t)((V + S - 1) / S), kSubTile);
+        int n_chunks = (V + pl.chunk_len - 1) / pl.chunk_len;
+        size_t need = 0;
+        for (auto &rp : pl.rows)
+            if (rp.path == kPathGreedy || rp.path == kPathTopK) need += (size_t)n_chunks * (size_t)rp.sel;
+        if (n_chunks == 1 || need <= h->cand_entries) { S = n_chunks; break; }
+        S = std::max(1, S / 2);
+    }
+    int cand_off = 0, slot = 0;
+    for (int r = 0; r < rows; r++) {
+        RowPlan &rp = pl.rows[r];
+        if (mode != 1 && (rp.path == kPathGreedy || rp.path == kPathTopK)) {
+            rp.n_chunks = S;
+            rp.cand_off = cand_off;
+            rp.slot = slot;
+            cand_off += S * rp.sel;
+            slot += S;
+        }
+    }
+    for (int r = 0; r < rows; r++)
+        if (pl.rows[r].n_chunks == 0) pl.items.push_back({r, -1});
+    for (int r = 0; r < rows; r++)
+        for (int c = 0; c < pl.rows[r].n_chunks; c++) pl.items.push_back({r, c});
+    pl.cap = max_sel + kSubTile;
+    pl.smem = (size_t)pl.cap * 16;
+    if (pl.any_row_item) pl.smem = std::max(pl.smem, kRowArenaBytes);
+    pl.smem = std::max<size_t>(pl.smem, 1024);
+    return STG_OK;
+}
+
+// Uploads the plan unless it is byte-identical to the one already resident on the device.
+int upload_plan(StgHandle h, const Plan &pl, cudaStream_t stream, const RowPlan **d_rows,
+                const WorkItem **d_items, const float **d_pow)
+{
+    const size_t b_rows = round_up(pl.rows.size() * sizeof(RowPlan), 256);
+    const size_t b_items = round_up(pl.items.size() * sizeof(WorkItem), 256);
+    const size_t b_pow = round_up(pl.pow_tab.size() * sizeof(float), 256);
+    const size_t total = b_rows + b_items + b_pow;
+    if (total > h->plan_bytes_cap) return fail(h, STG_ERR_CAPACITY, "plan exceeds the workspace");
+    std::vector<unsigned char> bytes(total, 0);
+    memcpy(bytes.data(), pl.rows.data(), pl.rows.size() * sizeof(RowPlan));
+    memcpy(bytes.data() + b_rows, pl.items.data(), pl.items.size() * sizeof(WorkItem));
+    if (!pl.pow_tab.empty()) memcpy(bytes.data() + b_rows + b_items, pl.pow_tab.data(), pl.pow_tab.size() * sizeof(float));
+    unsigned char *dev = (unsigned char *)h->plan_dev.p;
+    *d_rows = (const RowPlan *)dev;
+    *d_items = (const WorkItem *)(dev + b_rows);
+    *d_pow = pl.pow_tab.empty() ? nullptr : (const float *)(dev + b_rows + b_items);
+    if (bytes == h->plan_cache) return STG_OK;
+    const int slot = h->plan_slot;
+    h->plan_slot = (slot + 1) & 3;
+    CK(cudaEventSynchronize(h->plan_ev[slot]));
+    unsigned char *pin = h->plan_host + (size_t)slot * h->plan_bytes_cap;
+    memcpy(pin, bytes.data(), total);
+    CK(cudaMemcpyAsync(dev, pin, total, cudaMemcpyHostToDevice, stream));
+    CK(cudaEventRecord(h->plan_ev[slot], stream));
+    h->plan_cache.swap(bytes);
+    h->stats.plan_uploads++;
+    return STG_OK;
+}
+
+}  // namespace
+
+namespace stg {
+// Returns the device address of a caller array, copying it into `stage` first when it is host memory.
+int stage_in(StgHandle h, const void *src, size_t bytes, bool on_host, DevBuf &stage, cudaStream_t stream,
+             const void **out)
+{
+    if (src == nullptr || bytes == 0) { *out = src; return STG_OK; }
+    if (!on_host) { *out = src; return STG_OK; }
+    if (bytes > stage.bytes) {
+        // staging for host arrays is sized at creation from the handle's capacities; only the
+        // logits staging (the one large array) is grown on first use
+        if (&stage != &h->st_logits && &stage != &h->st_mask)
+            return fail(h, STG_ERR_CAPACITY, "host array larger than the staging buffer");
+        CK(cudaStreamSynchronize(stream));
+        dev_free(stage);
+        int rc = dev_alloc(h, stage, bytes);
+        if (rc) return rc;
+    }
+    CK(cudaMemcpyAsync(stage.p, src, bytes, cudaMemcpyHostToDevice, stream));
+    *out = stage.p;
+    return STG_OK;
+}
+
+}  // namespace stg
+
+namespace {
+
+int check_batch(StgHandle h, const StgSampleBatch *b)
+{
+    if (!h) return STG_ERR_INVALID_ARGUMENT;
+    if (!b || b->struct_size != (int32_t)sizeof(StgSampleBatch)) return fail(h, STG_ERR_INVALID_ARGUMENT, "bad StgSampleBatch");
+    if (b->rows < 0 || b->vocab <= 0) return fail(h, STG_ERR_INVALID_ARGUMENT, "rows must be >= 0 and vocab > 0");
+    if (b->rows > h->cfg.max_rows) return fail(h, STG_ERR_CAPACITY, "rows exceed max_rows");
+    if (b->vocab > h->cfg.max_vocab) return fail(h, STG_ERR_CAPACITY, "vocab exceeds max_vocab");
+    if (b->rows > 0 && (!b->logits || !b->params)) return fail(h, STG_ERR_INVALID_ARGUMENT, "logits and params are required");
+    if (b->row_stride < b->vocab) return fail(h, STG_ERR_INVALID_ARGUMENT, "row_stride smaller than vocab");
+    if (b->logits_dtype != STG_DTYPE_F32 && b->logits_dtype != STG_DTYPE_BF16) return fail(h, STG_ERR_INVALID_ARGUMENT, "unknown logits_dtype");
+    if (b->mask && b->mask_row_stride < (b->vocab + 31) / 32) return fail(h, STG_ERR_INVALID_ARGUMENT, "mask_row_stride too small");
+    return STG_OK;
+}
+
+bool rows_aligned(const void *p, int64_t row_stride, int dtype)
+{
+    const size_t esz = dtype == STG_DTYPE_BF16 ? 2 : 4;
+    const size_t need = dtype == STG_DTYPE_BF16 ? 8 : 16;
+    return ((uintptr_t)p % need) == 0 && ((size_t)row_stride * esz) % need == 0;
+}
+
+int run_batch(StgHandle h, const StgSampleBatch *b, int mode, float *dist_out, void *pairs_out, void *stream_)
+{
+    cudaStream_t stream = (cudaStream_t)stream_;
+    int rc = check_batch(h, b);
+    if (rc) return rc;
+    if (b->rows == 0) return STG_OK;
+    CK(cudaSetDevice(h->cfg.device));
+    const uint32_t mf = b->mem_flags;
+    const int rows = b->rows, V = b->vocab;
+    if (mode == 0 && !pairs_out && !b->tokens) return fail(h, STG_ERR_INVALID_ARGUMENT, "tokens is required");
+
+    Plan pl;
+    rc = make_plan(h, b, mode, false, pl);
+    if (rc) return rc;
+    if (pl.smem > h->smem_optin) return fail(h, STG_ERR_CAPACITY, "shared memory needed exceeds the device limit");
+    const RowPlan *d_rows; const WorkItem *d_items; const float *d_pow;
+    rc = upload_plan(h, pl, stream, &d_rows, &d_items, &d_pow);
+    if (rc) return rc;
+
+    SampleArgs a;
+    memset(&a, 0, sizeof(a));
+    const size_t esz = b->logits_dtype == STG_DTYPE_BF16 ? 2 : 4;
+    const void *p;
+    rc = stage_in(h, b->logits, ((size_t)(rows - 1) * b->row_stride + V) * esz, mf & STG_MEM_HOST_LOGITS, h->st_logits, stream, &p);
+    if (rc) return rc;
+    a.logits = p;
+    const int hist_total = (b->history_offsets && b->history_ids) ? b->history_offsets[rows] : 0;
+    rc = stage_in(h, b->history_ids, (size_t)hist_total * 4, mf & STG_MEM_HOST_HISTORY, h->st_hist, stream, &p);
+    if (rc) return rc;
+    a.hist_ids = (const int32_t *)p;
+    const int bias_total = (b->bias_offsets && b->bias_ids) ? b->bias_offsets[rows] : 0;
+    rc = stage_in(h, b->bias_ids, (size_t)bias_total * 4, mf & STG_MEM_HOST_BIAS, h->st_bias_ids, stream, &p);
+    if (rc) return rc;
+    a.bias_ids = (const int32_t *)p;
+    rc = stage_in(h, b->bias_values, (size_t)bias_total * 4, mf & STG_MEM_HOST_BIAS, h->st_bias_vals, stream, &p);
+    if (rc) return rc;
+    a.bias_vals = (const float *)p;
+    rc = stage_in(h, b->mask, b->mask ? ((size_t)(rows - 1) * b->mask_row_stride + (V + 31) / 32) * 4 : 0, mf & STG_MEM_HOST_MASK, h->st_mask, stream, &p);
+    if (rc) return rc;
+    a.mask = (const uint32_t *)p;
+    rc = stage_in(h, b->uniforms, (size_t)rows * 4, mf & STG_MEM_HOST_UNIFORMS, h->st_uniforms, stream, &p);
+    if (rc) return rc;
+    a.uniforms = (const float *)p;
+
+    const bool host_out = mf & STG_MEM_HOST_OUTPUTS;
+    const int ts = b->topk_stride;
+    if ((b->topk_ids || b->topk_logits || b->topk_probs) && ts < 1) return fail(h, STG_ERR_INVALID_ARGUMENT, "topk_stride must be positive");
+    if (host_out && (b->topk_ids || b->topk_logits || b->topk_probs) && (size_t)rows * ts * 4 > h->o_topk_ids.bytes)
+        return fail(h, STG_ERR_CAPACITY, "topk outputs exceed max_rows * max_top_k");
+    a.tokens = host_out ? (int32_t *)h->o_tokens.p : b->tokens;
+    a.token_probs = b->token_probs ? (host_out ? (float *)h->o_probs.p : b->token_probs) : nullptr;
+    a.row_flags = b->row_flags ? (host_out ? (uint32_t *)h->o_flags.p : b->row_flags) : nullptr;
+    a.topk_ids = b->topk_ids ? (host_out ? (int32_t *)h->o_topk_ids.p : b->topk_ids) : nullptr;
+    a.topk_logits = b->topk_logits ? (host_out ? (float *)h->o_topk_vals.p : b->topk_logits) : nullptr;
+    a.topk_probs = b->topk_probs ? (host_out ? (float *)h->o_topk_probs.p : b->topk_probs) : nullptr;
+    a.topk_stride = ts;
+    a.pairs_out = pairs_out;
+    if (mode == 1) {
+        if (!dist_out) return fail(h, STG_ERR_INVALID_ARGUMENT, "probs is required");
+        if (host_out) {
+            const size_t bytes = (size_t)rows * V * 4;
+            if (bytes > h->st_logits.bytes) {
+                // distribution rows staged in a device buffer when the caller wants them on the host
+                if (a.logits == h->st_logits.p) return fail(h, STG_ERR_UNSUPPORTED, "host logits and host probs together");
+                CK(cudaStreamSynchronize(stream));
+                dev_free(h->st_logits);
+                rc = dev_alloc(h, h->st_logits, bytes);
+                if (rc) return rc;
+            } else if (a.logits == h->st_logits.p) {
+                return fail(h, STG_ERR_UNSUPPORTED, "host logits and host probs together");
+            }
+            a.dist_out = (float *)h->st_logits.p;
+        } else {
+            a.dist_out = dist_out;
+        }
+        if (a.tokens == nullptr) a.tokens = (int32_t *)h->o_tokens.p;
+    }
+    a.plans = d_rows; a.items = d_items; a.pow_tab = d_pow;
+    a.cand = (unsigned long long *)h->cand.p;
+    a.cand_count = (int32_t *)h->cand_count.p;
+    a.tickets = (uint32_t *)h->tickets.p;
+    a.work_counter = (uint32_t *)h->work_counter.p;
+    a.escratch = (float *)h->escratch.p;
+    a.keyscratch = (unsigned long long *)h->keyscratch.p;
+    a.dists = nullptr;
+    a.row_stride = b->row_stride;
+    a.mask_stride = b->mask_row_stride;
+    a.escratch_stride = h->escratch_stride;
+    a.key_stride = h->key_stride;
+    a.work_base = h->work_base;
+    a.n_items = (int)pl.items.size();
+    a.rows = rows; a.vocab = V; a.dtype = b->logits_dtype;
+    a.chunk_len = pl.chunk_len;
+    a.cap = pl.cap;
+    a.vec = rows_aligned(a.logits, b->row_stride, b->logits_dtype) ? 4 : 1;
+    a.mode = mode;
+    a.vocab_offset = 0; a.shard_mode = 0; a.n_ranks = 1;
+
+    const int grid = std::min(a.n_items, h->sm_count);
+    cudaError_t e = launch_sample(a, grid, pl.smem, stream);
+    if (e != cudaSuccess) {
+        cudaMemsetAsync(h->work_counter.p, 0, 4, stream);
+        cudaMemsetAsync(h->tickets.p, 0, h->tickets.bytes, stream);
+        h->work_base = 0;
+        return cuda_fail(h, e, "k_sample launch");
+    }
+    h->work_base += (uint32_t)a.n_items + (uint32_t)grid;
+    h->stats.calls++;
+    h->stats.kernel_launches++;
+    h->stats.rows_sampled += rows;
+    h->stats.rows_greedy += pl.n_greedy; h->stats.rows_topk_path += pl.n_topk; h->stats.rows_full_path += pl.n_full;
+
+    if (host_out) {
+        if (mode == 0 && b->tokens) CK(cudaMemcpyAsync(b->tokens, a.tokens, (size_t)rows * 4, cudaMemcpyDeviceToHost, stream));
+        if (b->token_probs) CK(cudaMemcpyAsync(b->token_probs, a.token_probs, (size_t)rows * 4, cudaMemcpyDeviceToHost, stream));
+        if (b->row_flags) CK(cudaMemcpyAsync(b->row_flags, a.row_flags, (size_t)rows * 4, cudaMemcpyDeviceToHost, stream));
+        if (b->topk_ids) CK(cudaMemcpyAsync(b->topk_ids, a.topk_ids, (size_t)rows * ts * 4, cudaMemcpyDeviceToHost, stream));
+        if (b->topk_logits) CK(cudaMemcpyAsync(b->topk_logits, a.topk_logits, (size_t)rows * ts * 4, cudaMemcpyDeviceToHost, stream));
+        if (b->topk_probs) CK(cudaMemcpyAsync(b->topk_probs, a.topk_probs, (size_t)rows * ts * 4, cudaMemcpyDeviceToHost, stream));
+        if (mode == 1) CK(cudaMemcpyAsync(dist_out, a.dist_out, (size_t)rows * V * 4, cudaMemcpyDeviceToHost, stream));
+        CK(cudaStreamSynchronize(stream));
+    }
+    return STG_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int stg_abi_version(void) { return STG_ABI_VERSION; }
+
+int stg_create(const StgConfig *cfg, StgHandle *out)
+{
+    StgHandle h = nullptr;
+    if (!cfg || !out || cfg->struct_size != (int32_t)sizeof(StgConfig))
+        return fail(nullptr, STG_ERR_INVALID_ARGUMENT, "bad StgConfig");
+    *out = nullptr;
+    if (cfg->max_rows <= 0 || cfg->max_vocab <= 0 || cfg->max_history < 0 || cfg->max_top_k < 0 || cfg->max_bias < 0)
+        return fail(nullptr, STG_ERR_INVALID_ARGUMENT, "capacities must be positive");
+    if ((int64_t)cfg->max_top_k + cfg->max_history > kMaxSel)
+        return fail(nullptr, STG_ERR_CAPACITY, "max_top_k + max_history must not exceed 8192");
+    int n_dev = 0;
+    cudaError_t e = cudaGetDeviceCount(&n_dev);
+    if (e != cudaSuccess || n_dev <= 0 || cfg->device < 0 || cfg->device >= n_dev)
+        return fail(nullptr, STG_ERR_NO_DEVICE, std::string("no usable CUDA device (there is no CPU fallback): ") + cudaGetErrorString(e));
+    e = cudaSetDevice(cfg->device);
+    if (e != cudaSuccess) return fail(nullptr, STG_ERR_NO_DEVICE, cudaGetErrorString(e));
+    cudaDeviceProp prop;
+    e = cudaGetDeviceProperties(&prop, cfg->device);
+    if (e != cudaSuccess) return fail(nullptr, STG_ERR_CUDA, cudaGetErrorString(e));
+    if (prop.major < 10) return fail(nullptr, STG_ERR_NO_DEVICE, "this library is built for sm_100a (B200) only");
+
+    h = new StgSampler_();
+    h->cfg = *cfg;
+    h->sm_count = prop.multiProcessorCount;
+    h->smem_optin = prop.sharedMemPerBlockOptin > 4096 ? prop.sharedMemPerBlockOptin - 4096 : 0;
+    const size_t R = (size_t)cfg->max_rows, V = (size_t)cfg->max_vocab;
+    const size_t sel_max = std::max<size_t>(1, (size_t)cfg->max_top_k + cfg->max_history);
+    h->cand_entries = R * std::max<size_t>(4 * sel_max, 64);
+    h->escratch_stride = (int64_t)round_up(V + 8, 64);
+    h->key_stride = (int64_t)round_up(V + 8, 64);
+    h->plan_bytes_cap = round_up(R * sizeof(RowPlan), 256) + round_up((R * 65) * sizeof(WorkItem), 256) +
+                        round_up(R * kPowTab * sizeof(float), 256) + 1024;
+    int rc = STG_OK;
+    auto A = [&](DevBuf &b, size_t bytes) { if (rc == STG_OK) rc = dev_alloc(h, b, bytes); };
+    A(h->plan_dev, h->plan_bytes_cap);
+    A(h->cand, h->cand_entries * 8);
+    A(h->cand_count, R * 64 * 4);
+    A(h->tickets, R * 4);
+    A(h->work_counter, 256);
+    A(h->escratch, (size_t)h->sm_count * h->escratch_stride * 4);
+    A(h->keyscratch, (size_t)h->sm_count * h->key_stride * 8);
+    A(h->st_hist, R * std::max<size_t>(cfg->max_history, 1) * 4);
+    A(h->st_bias_ids, R * std::max<size_t>(cfg->max_bias, 1) * 4);
+    A(h->st_bias_vals, R * std::max<size_t>(cfg->max_bias, 1) * 4);
+    A(h->st_uniforms, R * 4);
+    A(h->st_mask, 256);
+    A(h->st_logits, 256);
+    A(h->o_tokens, R * 4); A(h->o_probs, R * 4); A(h->o_flags, R * 4);
+    const size_t tk = R * std::max<size_t>(cfg->max_top_k, 1) * 4;
+    A(h->o_topk_ids, tk); A(h->o_topk_vals, tk); A(h->o_topk_probs, tk);
+    if (cfg->max_spec_draft > 0) {
+        const size_t L = (size_t)cfg->max_spec_draft;
+        A(h->sp_draft, R * L * 4); A(h->sp_uniforms, R * (L + 2) * 8);
+        A(h->sp_accepted, R * 4); A(h->sp_correction, R * 4); A(h->sp_aprobs, R * L * 4); A(h->sp_flags, R * 4);
+        A(h->dists, R * (2 * L + 1) * sizeof(RowDist));
+    }
+    if (rc == STG_OK) {
+        e = cudaHostAlloc((void **)&h->plan_host, h->plan_bytes_cap * 4, cudaHostAllocDefault);
+        if (e != cudaSuccess) rc = cuda_fail(nullptr, e, "cudaHostAlloc");
+    }
+    for (int i = 0; i < 4 && rc == STG_OK; i++) {
+        e = cudaEventCreateWithFlags(&h->plan_ev[i], cudaEventDisableTiming);
+        if (e != cudaSuccess) rc = cuda_fail(nullptr, e, "cudaEventCreate");
+    }
+    if (rc == STG_OK) {
+        e = cudaMemset(h->work_counter.p, 0, 256);
+        if (e == cudaSuccess) e = cudaMemset(h->tickets.p, 0, h->tickets.bytes);
+        if (e != cudaSuccess) rc = cuda_fail(nullptr, e, "cudaMemset");
+    }
+    if (rc != STG_OK) {
+        stg::g_create_error = h->err.empty() ? stg::g_create_error : h->err;
+        stg_destroy(h);
+        return rc;
+    }
+    *out = h;
+    return STG_OK;
+}
+
+int stg_destroy(StgHandle h)
+{
+    if (!h) return STG_OK;
+    cudaSetDevice(h->cfg.device);
+    cudaDeviceSynchronize();
+    stg_comm_destroy(h);
+    DevBuf *all[] = {&h->plan_dev, &h->cand, &h->cand_count, &h->tickets, &h->work_counter, &h->escratch, &h->keyscratch,
+                     &h->dists, &h->st_hist, &h->st_bias_ids, &h->st_bias_vals, &h->st_uniforms, &h->st_mask, &h->st_logits,
+                     &h->o_tokens, &h->o_probs, &h->o_flags, &h->o_topk_ids, &h->o_topk_vals, &h->o_topk_probs, &h->o_pairs,
+                     &h->sp_draft, &h->sp_uniforms, &h->sp_accepted, &h->sp_correction, &h->sp_aprobs, &h->sp_flags,
+                     &h->sp_rowstats, &h->xchg_local, &h->xchg_gather, &h->xchg_count_local, &h->xchg_count_gather};
+    for (DevBuf *b : all) dev_free(*b);
+    if (h->plan_host) cudaFreeHost(h->plan_host);
+    for (auto &ev : h->plan_ev) if (ev) cudaEventDestroy(ev);
+    delete h;
+    return STG_OK;
+}
+
+size_t stg_last_error(StgHandle h, char *buf, size_t len)
+{
+    const std::string &s = h ? h->err : stg::g_create_error;
+    if (buf && len) {
+        size_t n = std::min(len - 1, s.size());
+        memcpy(buf, s.data(), n);
+        buf[n] = 0;
+    }
+    return s.size() + 1;
+}
+
+int stg_get_stats(StgHandle h, StgStats *out)
+{
+    if (!h || !out) return STG_ERR_INVALID_ARGUMENT;
+    *out = h->stats;
+    return STG_OK;
+}
+
+int stg_sample_rows(StgHandle h, const StgSampleBatch *b, void *stream) { return run_batch(h, b, 0, nullptr, nullptr, stream); }
+
+int stg_build_distribution(StgHandle h, const StgSampleBatch *b, float *probs, void *stream)
+{
+    return run_batch(h, b, 1, probs, nullptr, stream);
+}
+
+int stg_argmax_rows(StgHandle h, const void *logits, int32_t dtype, int32_t rows, int32_t vocab, int64_t row_stride,
+                    void *out_pairs, void *stream)
+{
+    if (!h) return STG_ERR_INVALID_ARGUMENT;
+    if (!out_pairs) return fail(h, STG_ERR_INVALID_ARGUMENT, "out_pairs is required");
+    if (rows < 0 || rows > h->cfg.max_rows) return fail(h, STG_ERR_CAPACITY, "rows exceed max_rows");
+    std::vector<StgRowParams> params((size_t)std::max(rows, 1));
+    for (auto &p : params) { memset(&p, 0, sizeof(p)); p.temperature = 0.f; p.top_p = 1.f; p.repetition_penalty = 1.f; }
+    StgSampleBatch b;
+    memset(&b, 0, sizeof(b));
+    b.struct_size = sizeof(b);
+    b.rows = rows; b.vocab = vocab; b.logits_dtype = dtype; b.logits = logits; b.row_stride = row_stride;
+    b.params = params.data();
+    b.tokens = (int32_t *)h->o_tokens.p;
+    return run_batch(h, &b, 0, nullptr, out_pairs, stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,67 @@
+// Internal: the handle behind StgHandle and helpers shared by the C-ABI translation units.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <algorithm>
+#include <string>
+#include <vector>
+
+#include "../../../include/stingray_sampler.h"
+#include "stg_types.h"
+
+namespace stg {
+
+struct DevBuf {
+    void *p = nullptr;
+    size_t bytes = 0;
+};
+
+}  // namespace stg
+
+struct StgSampler_ {
+    StgConfig cfg{};
+    int sm_count = 0;
+    size_t smem_optin = 0;
+    std::string err;
+    StgStats stats{};
+
+    // workspace (allocated once at creation)
+    stg::DevBuf plan_dev;                // RowPlan[], WorkItem[], pow table
+    unsigned char *plan_host = nullptr;  // pinned mirror ring
+    cudaEvent_t plan_ev[4]{};
+    int plan_slot = 0;
+    std::vector<unsigned char> plan_cache;  // bytes of the plan last uploaded
+    stg::DevBuf cand, cand_count, tickets, work_counter, escratch, keyscratch, dists;
+    stg::DevBuf st_hist, st_bias_ids, st_bias_vals, st_uniforms, st_mask, st_logits;
+    stg::DevBuf o_tokens, o_probs, o_flags, o_topk_ids, o_topk_vals, o_topk_probs, o_pairs;
+    stg::DevBuf sp_draft, sp_uniforms, sp_accepted, sp_correction, sp_aprobs, sp_flags, sp_rowstats;
+    int64_t escratch_stride = 0, key_stride = 0;
+    size_t cand_entries = 0;
+    uint32_t work_base = 0;
+    size_t plan_bytes_cap = 0;
+    // exchange buffers of the vocabulary-sharded mode
+    stg::DevBuf xchg_local, xchg_gather, xchg_count_local, xchg_count_gather;
+    void *nccl_lib = nullptr;
+    void *nccl_comm = nullptr;
+    int rank = 0, n_ranks = 1;
+    int shard_sel = 0, shard_rows = 0;
+};
+
+namespace stg {
+
+int fail(StgHandle h, int code, const std::string &msg);
+int cuda_fail(StgHandle h, cudaError_t e, const char *what);
+int dev_alloc(StgHandle h, DevBuf &b, size_t bytes);
+void dev_free(DevBuf &b);
+inline size_t round_up(size_t v, size_t m) { return (v + m - 1) / m * m; }
+int stage_in(StgHandle h, const void *src, size_t bytes, bool on_host, DevBuf &stage, cudaStream_t stream,
+             const void **out);
+
+#define CK(call)                                                        \
+    do {                                                                \
+        cudaError_t e_ = (call);                                        \
+        if (e_ != cudaSuccess) return stg::cuda_fail(h, e_, #call);     \
+    } while (0)
+
+}  // namespace stg

@@ -1,0 +1,522 @@
+// Streaming exact top-N selection over a row (or a chunk of one), the block-wide sort that orders
+// the survivors, and the sequential finish of the top-k sampling path.
+//
+// Selection semantics follow SampleTopK's insertion select
+// (src/OpenTail.Stingray.Engine/Sampler.cs:240-249): the N largest raw logits, descending, equal
+// values in ascending token order, the earlier token kept on a tie at the boundary, -infinity never
+// selected.  A candidate is the 64-bit key (order-preserving float bits << 32) | ~token, so
+// "larger key" is exactly that order and keys are distinct.
+#pragma once
+#include <cuda_runtime.h>
+#include <math_constants.h>
+#include <stdint.h>
+
+#include "stg_types.h"
+
+namespace stg {
+
+typedef unsigned long long u64;
+
+__device__ __forceinline__ uint32_t ord32(float v)
+{
+    v = v + 0.0f;  // -0 -> +0: the reference compares floats, for which the two are equal
+    uint32_t b = __float_as_uint(v);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__device__ __forceinline__ float unord32(uint32_t k)
+{
+    return __uint_as_float((k & 0x80000000u) ? (k & 0x7FFFFFFFu) : ~k);
+}
+__device__ __forceinline__ u64 make_key(float v, int idx)
+{
+    return ((u64)ord32(v) << 32) | (u64)(0xFFFFFFFFu - (uint32_t)idx);
+}
+__device__ __forceinline__ float key_val(u64 k) { return unord32((uint32_t)(k >> 32)); }
+__device__ __forceinline__ int key_idx(u64 k) { return (int)(0xFFFFFFFFu - (uint32_t)k); }
+
+// ---- element access --------------------------------------------------------------------------
+__device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
+
+template <bool BF16, bool STREAM>
+__device__ __forceinline__ void load_vec4(const void *rowp, int i, float v[4])
+{
+    if (BF16) {
+        const uint2 *p = (const uint2 *)((const uint16_t *)rowp + i);
+        uint2 t = STREAM ? __ldcs(p) : __ldg(p);
+        v[0] = bf16_lo(t.x); v[1] = bf16_hi(t.x); v[2] = bf16_lo(t.y); v[3] = bf16_hi(t.y);
+    } else {
+        const float4 *p = (const float4 *)((const float *)rowp + i);
+        float4 t = STREAM ? __ldcs(p) : __ldg(p);
+        v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+    }
+}
+template <bool BF16>
+__device__ __forceinline__ float load_one(const void *rowp, int i)
+{
+    if (BF16) return __uint_as_float((uint32_t)__ldg((const uint16_t *)rowp + i) << 16);
+    return __ldg((const float *)rowp + i);
+}
+__device__ __forceinline__ float load_one_dyn(const void *rowp, int dtype, int i)
+{
+    return dtype ? load_one<true>(rowp, i) : load_one<false>(rowp, i);
+}
+__device__ __forceinline__ bool mask_bit(const uint32_t *mrow, int i)
+{
+    return (__ldg(mrow + (i >> 5)) >> (i & 31)) & 1u;
+}
+
+// Loads the 4 elements a thread owns in sub-step `u` of a 16384-element iteration starting at
+// `base`, applying the allowed-token mask; out-of-range elements read as -infinity.
+// VEC == 4: elements base + (u*1024 + tid)*4 + e (one 128-bit / 64-bit load);
+// VEC == 1: elements base + (u*4 + e)*1024 + tid (scalar loads, any alignment).
+template <int VEC, bool BF16, bool STREAM>
+__device__ __forceinline__ void load_items(const void *rowp, const uint32_t *mrow, int base, int u,
+                                           int end, float v[4], int idx[4])
+{
+    const int tid = threadIdx.x;
+    if (VEC == 4) {
+        int i = base + (u * kThreads + tid) * 4;
+#pragma unroll
+        for (int e = 0; e < 4; e++) idx[e] = i + e;
+        if (i + 3 < end) {
+            load_vec4<BF16, STREAM>(rowp, i, v);
+        } else {
+#pragma unroll
+            for (int e = 0; e < 4; e++) v[e] = (i + e < end) ? load_one<BF16>(rowp, i + e) : -CUDART_INF_F;
+        }
+        if (mrow != nullptr && i < end) {
+            uint32_t bits = __ldg(mrow + (i >> 5)) >> (i & 31);
+#pragma unroll
+            for (int e = 0; e < 4; e++)
+                if (!((bits >> e) & 1u)) v[e] = -CUDART_INF_F;
+        }
+    } else {
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            int i = base + (u * 4 + e) * kThreads + tid;
+            idx[e] = i;
+            float x = -CUDART_INF_F;
+            if (i < end) {
+                x = load_one<BF16>(rowp, i);
+                if (mrow != nullptr && !mask_bit(mrow, i)) x = -CUDART_INF_F;
+            }
+            v[e] = x;
+        }
+    }
+}
+
+// ---- block utilities ---------------------------------------------------------------------------
+__device__ __forceinline__ int warp_sum(int v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+    return v;
+}
+
+// Control block of one selection, in shared memory.
+struct SelCtl {
+    int cnt;          // entries in the active buffer
+    int cnt2;         // entries written to the other buffer during a compaction
+    int overflow;     // an optimistic append ran out of room
+    int cur;          // active buffer (0/1)
+    int tmp;          // block-wide counter scratch
+    float tau;        // a later element can only be selected if it is > tau
+    int want;
+    int stop;
+    u64 prefix;
+    u64 thr;
+    u64 minkey;
+    unsigned hist[256];
+};
+
+struct Sel {
+    SelCtl *c;
+    u64 *buf[2];
+    int cap;
+    int n;        // selection count N
+    int idx_off;  // added to a column index to form the token id stored in a key
+};
+
+__device__ __forceinline__ void sel_reset(Sel &s)
+{
+    if (threadIdx.x == 0) {
+        s.c->cnt = 0; s.c->cnt2 = 0; s.c->overflow = 0; s.c->cur = 0; s.c->tmp = 0;
+        s.c->tau = -CUDART_INF_F;
+    }
+    __syncthreads();
+}
+
+// Keeps the N largest keys of the active buffer (block-wide radix select on the 64-bit keys, most
+// significant byte first), moves them to the other buffer and raises tau to the N-th value.
+// Requires cnt > N.  All threads call it.
+__device__ void sel_compact(Sel &s)
+{
+    SelCtl *c = s.c;
+    const int tid = threadIdx.x;
+    const int cnt = c->cnt;
+    const u64 *src = s.buf[c->cur];
+    u64 *dst = s.buf[c->cur ^ 1];
+    __syncthreads();
+    if (tid == 0) { c->want = s.n; c->prefix = 0; c->stop = 0; c->cnt2 = 0; c->minkey = ~0ull; }
+    for (int pass = 7; pass >= 0; --pass) {
+        if (tid < 256) c->hist[tid] = 0;
+        __syncthreads();
+        const u64 prefix = c->prefix;
+        const int sh = 8 * pass;
+        for (int e = tid; e < cnt; e += kThreads) {
+            u64 k = src[e];
+            if (pass == 7 || (k >> (sh + 8)) == prefix) atomicAdd(&c->hist[(unsigned)(k >> sh) & 255u], 1u);
+        }
+        __syncthreads();
+        if (tid < 32) {
+            // lane l owns bins 8l..8l+7; suffix sums locate the bin holding the want-th largest key
+            unsigned h[8];
+            unsigned local = 0;
+#pragma unroll
+            for (int j = 0; j < 8; j++) { h[j] = c->hist[tid * 8 + j]; local += h[j]; }
+            const unsigned want = (unsigned)c->want;  // read before the shuffles order the lanes
+            unsigned above = 0;  // keys in bins of higher lanes
+            unsigned run = local;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                unsigned t = __shfl_down_sync(0xFFFFFFFFu, run, o);
+                if (tid + o < 32) run += t;
+            }
+            above = run - local;
+            bool mine = above < want && want <= above + local;
+            if (mine) {
+                unsigned acc = above;
+                for (int j = 7; j >= 0; --j) {
+                    if (want <= acc + h[j]) {
+                        c->prefix = (prefix << 8) | (u64)(tid * 8 + j);
+                        c->want = (int)(want - acc);
+                        if (h[j] == want - acc || pass == 0) {
+                            c->stop = 1;
+                            c->thr = ((prefix << 8) | (u64)(tid * 8 + j)) << sh;
+                        }
+                        break;
+                    }
+                    acc += h[j];
+                }
+            }
+        }
+        __syncthreads();
+        if (c->stop) break;
+    }
+    const u64 thr = c->thr;
+    u64 mymin = ~0ull;
+    for (int e = tid; e < cnt; e += kThreads) {
+        u64 k = src[e];
+        if (k >= thr) {
+            int slot = atomicAdd(&c->cnt2, 1);
+            dst[slot] = k;
+            if (k < mymin) mymin = k;
+        }
+    }
+    if (mymin != ~0ull) atomicMin(&c->minkey, mymin);
+    __syncthreads();
+    if (tid == 0) {
+        c->cnt = c->cnt2;
+        c->cur ^= 1;
+        c->tau = key_val(c->minkey);
+    }
+    __syncthreads();
+}
+
+// Appends the caller's up-to-4 passing elements; exact (counted) form used when room is short.
+__device__ __forceinline__ void sel_append_exact(Sel &s, const float v[4], const int idx[4], int end)
+{
+    SelCtl *c = s.c;
+    for (;;) {
+        const float tau = c->tau;
+        int n = 0;
+#pragma unroll
+        for (int e = 0; e < 4; e++) n += (idx[e] < end && v[e] > tau) ? 1 : 0;
+        int w = warp_sum(n);
+        if ((threadIdx.x & 31) == 0 && w) atomicAdd(&c->tmp, w);
+        __syncthreads();
+        const int total = c->tmp;
+        const int cnt = c->cnt;
+        __syncthreads();
+        if (threadIdx.x == 0) c->tmp = 0;
+        if (cnt + total > s.cap) {
+            sel_compact(s);  // cnt > N here because cap >= N + kSubTile >= N + total
+            continue;
+        }
+        if (n) {
+            int slot = atomicAdd(&c->cnt, n);
+            u64 *b = s.buf[c->cur];
+#pragma unroll
+            for (int e = 0; e < 4; e++)
+                if (idx[e] < end && v[e] > tau) b[slot++] = make_key(v[e], idx[e] + s.idx_off);
+        }
+        __syncthreads();
+        return;
+    }
+}
+
+// Streams elements [begin, end) of one row through the selection.  Elements are visited in
+// ascending token order per 16384-element iteration, which is what makes the strict `> tau` test
+// exact: an element equal to the N-th best value arrives after N better-or-earlier ones.
+template <int VEC, bool BF16>
+__device__ void sel_stream(Sel &s, const void *rowp, const uint32_t *mrow, int begin, int end)
+{
+    SelCtl *c = s.c;
+    constexpr int U = 4;
+    int cnt0 = c->cnt;
+    for (int base = begin; base < end; base += kThreads * 4 * U) {
+        float v[U][4];
+        int idx[U][4];
+#pragma unroll
+        for (int u = 0; u < U; u++) load_items<VEC, BF16, true>(rowp, mrow, base, u, end, v[u], idx[u]);
+        const float tau = c->tau;
+        int n = 0;
+#pragma unroll
+        for (int u = 0; u < U; u++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) n += (v[u][e] > tau) ? 1 : 0;  // out of range reads -inf
+        if (n) {
+            int slot = atomicAdd(&c->cnt, n);
+            if (slot + n > s.cap) {
+                c->overflow = 1;
+            } else {
+                u64 *b = s.buf[c->cur];
+#pragma unroll
+                for (int u = 0; u < U; u++)
+#pragma unroll
+                    for (int e = 0; e < 4; e++)
+                        if (v[u][e] > tau) b[slot++] = make_key(v[u][e], idx[u][e] + s.idx_off);
+            }
+        }
+        __syncthreads();
+        if (c->overflow) {
+            __syncthreads();
+            if (threadIdx.x == 0) { c->cnt = cnt0; c->overflow = 0; }
+            __syncthreads();
+            if (c->cnt > s.n) sel_compact(s);
+#pragma unroll
+            for (int u = 0; u < U; u++) sel_append_exact(s, v[u], idx[u], end);
+        }
+        cnt0 = c->cnt;
+        __syncthreads();
+    }
+    if (c->cnt > s.n) sel_compact(s);
+}
+
+// Appends `count` keys from global memory (another chunk's survivors).
+__device__ void sel_append_keys(Sel &s, const u64 *keys, int count)
+{
+    SelCtl *c = s.c;
+    for (int base = 0; base < count; base += kSubTile) {
+        int m = min(kSubTile, count - base);
+        __syncthreads();
+        if (c->cnt + m > s.cap) sel_compact(s);
+        u64 *b = s.buf[c->cur];
+        const int cnt = c->cnt;
+        __syncthreads();
+        for (int e = threadIdx.x; e < m; e += kThreads) b[cnt + e] = __ldcg(keys + base + e);
+        __syncthreads();
+        if (threadIdx.x == 0) c->cnt = cnt + m;
+        __syncthreads();
+    }
+    if (c->cnt > s.n) sel_compact(s);
+}
+
+// ---- block-wide bitonic sort, descending, of `p2` (power of two) 64-bit keys in shared memory --
+__device__ void bitonic_sort_desc(u64 *a, int p2)
+{
+    for (int k = 2; k <= p2; k <<= 1) {
+        for (int j = k >> 1; j > 0; j >>= 1) {
+            for (int t = threadIdx.x; t < (p2 >> 1); t += kThreads) {
+                int i = ((t & ~(j - 1)) << 1) | (t & (j - 1));
+                int l = i | j;
+                bool desc = ((i & k) == 0);
+                u64 x = a[i], y = a[l];
+                if ((x < y) == desc) { a[i] = y; a[l] = x; }
+            }
+            __syncthreads();
+        }
+    }
+}
+
+__device__ __forceinline__ int pow2_ceil(int n)
+{
+    int p = 1;
+    while (p < n) p <<= 1;
+    return p;
+}
+
+// ---- history lookups of the top-k path ---------------------------------------------------------
+// occurrences of `id` in the whole history and inside the repetition window
+// (Sampler.cs:271-279).  All threads scan the same addresses, so the loads broadcast.
+__device__ __forceinline__ void count_occurrences(const int32_t *hist, int hlen, int wstart, int id,
+                                                  int &occ_all, int &occ_w)
+{
+    int a = 0, w = 0;
+    for (int h = 0; h < hlen; h++) {
+        int x = __ldg(hist + h);
+        if (x == id) { a++; w += (h >= wstart) ? 1 : 0; }
+    }
+    occ_all = a;
+    occ_w = w;
+}
+
+// powf(rep, occ) as the host's libm gives it (table built by the planner), falling back to a
+// correctly rounded double evaluation beyond the table.
+__device__ __forceinline__ float pow_rep(const float *tab, float rep, int occ)
+{
+    if (tab != nullptr && occ <= kPowTab) return __ldg(tab + occ - 1);
+    return (float)pow((double)rep, (double)occ);
+}
+
+struct FinishOut {
+    int token;
+    float prob;
+    uint32_t flags;
+};
+
+// Finishes the top-k path for one row whose exact top-`sel` raw candidates sit (unsorted) in the
+// active buffer: sort, penalise, stable re-sort, softmax over the first k, min-p, top-p, draw.
+// Every fp32 operation is issued separately (no fused multiply-add), in the order of
+// Sampler.cs:257-349.  `vals`/`ids`/`probs` views alias the inactive buffer.
+__device__ void finish_topk(Sel &s, const RowPlan &rp, const int32_t *hist, const float *pow_tab,
+                            float uniform, FinishOut *out_sh, int32_t *o_ids, float *o_vals,
+                            float *o_probs)
+{
+    SelCtl *c = s.c;
+    const int tid = threadIdx.x;
+    const int cnt = c->cnt;
+    u64 *a = s.buf[c->cur];
+    u64 *b = s.buf[c->cur ^ 1];
+    const int k = rp.top_k;
+    const int sel = rp.sel;
+    if (cnt == 0) {  // Sampler.cs:254-255: no finite logit -> Greedy(raw) == token 0
+        if (tid == 0) { out_sh->token = 0; out_sh->prob = 0.f; out_sh->flags = kPathTopKNoFinite | (1u << 6); }
+        for (int t = tid; t < k; t += kThreads) {
+            if (o_ids) o_ids[t] = -1;
+            if (o_vals) o_vals[t] = -CUDART_INF_F;
+            if (o_probs) o_probs[t] = 0.f;
+        }
+        __syncthreads();
+        return;
+    }
+    const int p2 = pow2_ceil(max(cnt, 2));
+    for (int t = cnt + tid; t < p2; t += kThreads) a[t] = 0ull;
+    __syncthreads();
+    bitonic_sort_desc(a, p2);
+
+    if (rp.has_penalty) {
+        // penalise each candidate (Sampler.cs:263-287), then stable re-sort by penalised value
+        // (Sampler.cs:289-294): key = (penalised value, raw rank)
+        for (int t = tid; t < p2; t += kThreads) {
+            u64 key2 = 0ull;
+            if (t < cnt) {
+                float v = key_val(a[t]);
+                int id = key_idx(a[t]);
+                int occ_all, occ_w;
+                count_occurrences(hist, rp.hist_len, rp.window_start, id, occ_all, occ_w);
+                if (occ_all > 0) {
+                    if (rp.rep != 1.0f && occ_w > 0) {
+                        float pen = pow_rep(pow_tab, rp.rep, occ_w);
+                        v = v > 0.f ? __fdiv_rn(v, pen) : __fmul_rn(v, pen);
+                    }
+                    float add = __fadd_rn(rp.pres, __fmul_rn(rp.freq, (float)occ_all));
+                    v = __fsub_rn(v, add);
+                }
+                key2 = ((u64)ord32(v) << 32) | (u64)(0xFFFFFFFFu - (uint32_t)t);
+            }
+            b[t] = key2;
+        }
+        __syncthreads();
+        bitonic_sort_desc(b, p2);
+    }
+
+    // first k candidates -> registers -> compact arrays over the buffer that is no longer needed
+    constexpr int R = kMaxSel / kThreads;
+    float rv[R];
+    int ri[R];
+#pragma unroll
+    for (int j = 0; j < R; j++) {
+        int t = tid + j * kThreads;
+        rv[j] = -CUDART_INF_F;
+        ri[j] = -1;
+        if (t < k && t < cnt) {
+            if (rp.has_penalty) {
+                u64 k2 = b[t];
+                int raw_rank = (int)(0xFFFFFFFFu - (uint32_t)k2);
+                rv[j] = unord32((uint32_t)(k2 >> 32));
+                ri[j] = key_idx(a[raw_rank]);
+            } else {
+                rv[j] = key_val(a[t]);
+                ri[j] = key_idx(a[t]);
+            }
+        }
+    }
+    __syncthreads();
+    float *vals = (float *)b;
+    int *ids = (int *)(vals + k);
+    float *probs = (float *)(ids + k);
+    const float inv_t = rp.temperature == 1.0f ? 1.0f : __fdiv_rn(1.0f, rp.temperature);
+#pragma unroll
+    for (int j = 0; j < R; j++) {
+        int t = tid + j * kThreads;
+        if (t < k) { vals[t] = rv[j]; ids[t] = ri[j]; }
+    }
+    __syncthreads();
+    const float mx = __fmul_rn(vals[0], inv_t);
+    for (int t = tid; t < k; t += kThreads) {
+        float v = vals[t];
+        float e = 0.f;
+        if (!(isinf(v) && v < 0.f)) e = (float)exp((double)__fsub_rn(__fmul_rn(v, inv_t), mx));
+        probs[t] = e;
+    }
+    __syncthreads();
+    __shared__ float sh_inv_sum;
+    if (tid == 0) {
+        float sum = 0.f;
+        for (int t = 0; t < k; t++) sum = __fadd_rn(sum, probs[t]);
+        sh_inv_sum = sum > 0.f ? __fdiv_rn(1.0f, sum) : 0.f;
+    }
+    __syncthreads();
+    const float inv_sum = sh_inv_sum;
+    for (int t = tid; t < k; t += kThreads) probs[t] = __fmul_rn(probs[t], inv_sum);
+    __syncthreads();
+    if (tid == 0) {
+        int count = k;
+        if (rp.min_p > 0.f) {
+            float thr = __fmul_rn(rp.min_p, probs[0]);
+            for (int t = 0; t < count; t++)
+                if (probs[t] < thr) { count = t; break; }
+        }
+        if (rp.top_p < 1.0f && rp.top_p > 0.f) {
+            float cum = 0.f;
+            for (int t = 0; t < count; t++) {
+                cum = __fadd_rn(cum, probs[t]);
+                if (cum >= rp.top_p) { count = t + 1; break; }
+            }
+        }
+        float kept = 0.f;
+        for (int t = 0; t < count; t++) kept = __fadd_rn(kept, probs[t]);
+        float r = __fmul_rn(uniform, kept);
+        float cacc = 0.f;
+        int tok = ids[0];
+        float pr = probs[0];
+        uint32_t fl = kPathTopK | (1u << 5);
+        for (int t = 0; t < count; t++) {
+            cacc = __fadd_rn(cacc, probs[t]);
+            if (r <= cacc && ids[t] >= 0) { tok = ids[t]; pr = probs[t]; fl = kPathTopK; break; }
+        }
+        out_sh->token = tok;
+        out_sh->prob = kept > 0.f ? pr / kept : 0.f;
+        out_sh->flags = fl;
+    }
+    for (int t = tid; t < k; t += kThreads) {
+        if (o_ids) o_ids[t] = ids[t];
+        if (o_vals) o_vals[t] = vals[t];
+        if (o_probs) o_probs[t] = probs[t];
+    }
+    __syncthreads();
+}
+
+}  // namespace stg

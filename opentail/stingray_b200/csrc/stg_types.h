@@ -1,0 +1,104 @@
+// Plain structs shared by the host planner and the kernels.
+#pragma once
+#include <stdint.h>
+
+namespace stg {
+
+constexpr int kThreads = 1024;          // threads per CTA of every kernel in this library
+constexpr int kSubTile = 4096;          // elements one CTA filters per exact-append step
+constexpr int kMaxSel = 8192;           // largest selection count (top_k + history length)
+constexpr int kPowTab = 32;             // host-computed powf(rep, occ) entries per distinct rep
+constexpr int kEmulItems = 8;           // consecutive elements per thread in the sequential-sum scan
+constexpr int kEmulTile = kThreads * kEmulItems;
+constexpr int kSortCap = 32768;         // top-p candidate keys sorted in shared memory
+constexpr int kHistBins = 4096;         // probability histogram bins (exponent + 4 mantissa bits)
+constexpr int kMaxOverride = 16384;     // history + bias entries per row on the full-vocabulary path
+
+enum Path : int32_t {
+    kPathGreedy = 0,        // Sampler.Greedy
+    kPathGreedyPen = 1,     // GreedyWithHistoryPenalties
+    kPathTopK = 2,          // SampleTopK
+    kPathFull = 3,          // full-vocabulary pipeline
+    kPathTopKNoFinite = 4,  // SampleTopK fell back to Greedy
+};
+
+// One row of a sampling step, resolved by the host planner from StgRowParams and the CSR arrays.
+struct RowPlan {
+    float temperature, top_p, min_p, rep, pres, freq;
+    int32_t top_k, window_start;
+    int32_t hist_off, hist_len, bias_off, bias_len;
+    int32_t path;       // Path
+    int32_t sel;        // selection count of the streaming select (1 for plain greedy)
+    int32_t n_chunks;   // chunk work items of this row (0 for row-type rows)
+    int32_t cand_off;   // first entry of this row's candidate scratch (entries of 8 bytes)
+    int32_t use_mask, has_penalty, pow_off, slot;
+};
+
+struct WorkItem {
+    int32_t row;
+    int32_t chunk;  // -1: the whole row is one work item
+};
+
+// Distribution descriptor of one row on the full-vocabulary pipeline: everything needed to
+// evaluate p[i] from the row's logit i without any per-row scratch.
+struct RowDist {
+    float max_x;      // maximum of the adjusted, temperature-scaled logits
+    float inv_t;      // 1/T (1 when T == 1)
+    float inv1;       // softmax: 1/sum (multiplied in when scale1)
+    float kth;        // top-k: smallest surviving probability (before its normalise)
+    float inv2;       // top-k normalise
+    float minp_thr;   // min-p threshold
+    float tstar;      // top-p: smallest surviving probability
+    float inv3;       // final normalise
+    int32_t tie_idx_max;  // top-p: ties at tstar survive up to this token id
+    uint32_t flags;       // kDist*
+    float uniform_p;      // probability of every token when no logit is finite
+    float sum_end;        // last value of the sequential CDF (diagnostic)
+};
+enum : uint32_t {
+    kDistScale1 = 1u, kDistTopK = 2u, kDistScale2 = 4u, kDistMinP = 8u, kDistTopP = 16u,
+    kDistScale3 = 32u, kDistUniform = 64u, kDistOneHot = 128u,
+};
+
+struct SampleArgs {
+    const void *logits;
+    const RowPlan *plans;
+    const WorkItem *items;
+    const int32_t *hist_ids;
+    const int32_t *bias_ids;
+    const float *bias_vals;
+    const uint32_t *mask;
+    const float *uniforms;
+    const float *pow_tab;
+    int32_t *tokens;
+    float *token_probs;
+    uint32_t *row_flags;
+    int32_t *topk_ids;
+    float *topk_logits;
+    float *topk_probs;
+    float *dist_out;                 // build_distribution: [rows, vocab] probabilities or null
+    void *pairs_out;                 // argmax_rows: rows x {int32 index, float value} or null
+    unsigned long long *cand;        // candidate scratch
+    int32_t *cand_count;             // per (row, chunk) entry counts
+    uint32_t *tickets;               // per-row arrival counters (self-resetting)
+    uint32_t *work_counter;
+    float *escratch;                 // per-CTA exp scratch rows [grid, escratch_stride]
+    unsigned long long *keyscratch;  // per-CTA wide-nucleus key scratch [grid, key_stride]
+    RowDist *dists;                  // per-row distribution descriptors (optional output)
+    int64_t row_stride;
+    int64_t mask_stride;
+    int64_t escratch_stride;
+    int64_t key_stride;
+    uint32_t work_base;
+    int32_t n_items;
+    int32_t rows, vocab, dtype, topk_stride;
+    int32_t chunk_len;               // elements per chunk work item (multiple of kSubTile)
+    int32_t cap;                     // entries per candidate buffer in shared memory
+    int32_t vec;                     // 4: rows are 16-byte (fp32) / 8-byte (bf16) aligned
+    int32_t mode;                    // 0 sample, 1 build distribution only
+    int32_t vocab_offset;            // vocabulary-sharded mode: global id of local column 0
+    int32_t shard_mode;              // 0 off, 1 select only (write candidates), 2 finish from gather
+    int32_t n_ranks;
+};
+
+}  // namespace stg

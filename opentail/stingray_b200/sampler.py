@@ -1,0 +1,397 @@
+"""Host-side mirror of the reference's sampler API over the C-ABI CUDA library.
+
+Names, argument meaning and error behaviour follow the reference's managed API
+(``src/OpenTail.Stingray.Engine/Sampler.cs``): ``SamplingParams`` keeps the reference's property
+names, ``Sampler.Sample / Greedy / BuildFilteredDistribution / SampleWithDistribution`` keep their
+signatures, and a ``Random`` is consumed exactly as there (one ``NextDouble()`` per non-greedy
+sample, none when greedy).  ``BatchSampler`` is the batched form the reference does not have: one
+call per decode step over device-resident ``[rows, vocab]`` logits, replacing the serial per-row
+loop of ``ContinuousBatchingEngine.cs:609-644``.
+
+Nothing here computes on the CPU: every method forwards to ``libstingray_sampler.so`` and raises
+``StingrayError`` (the counterpart of the reference's ``InvalidOperationException`` on a non-zero
+native status, ``CudaBackend.cs:4110-4111``) when the library reports a failure.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+
+from . import _native as N
+
+PARAMS_DTYPE = np.dtype([
+    ("temperature", "<f4"), ("top_p", "<f4"), ("min_p", "<f4"), ("repetition_penalty", "<f4"),
+    ("presence_penalty", "<f4"), ("frequency_penalty", "<f4"), ("top_k", "<i4"),
+    ("repeat_last_n", "<i4"),
+])
+
+
+class StingrayError(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(f"{N.ERR_NAMES.get(code, code)}: {message}")
+        self.code = code
+
+
+@dataclass
+class SamplingParams:
+    """The sampler-relevant fields of the reference's ``SamplingParams`` record
+    (``Sampler.cs:648-686, 795``), same names and defaults."""
+
+    Temperature: float = 1.0
+    TopK: int = 0
+    TopP: float = 1.0
+    MinP: float = 0.0
+    RepetitionPenalty: float = 1.0
+    RepeatLastN: int = 64
+    PresencePenalty: float = 0.0
+    FrequencyPenalty: float = 0.0
+    LogitBias: Optional[Dict[int, float]] = None
+    PreviousTokens: Optional[Sequence[int]] = None
+    SpecDraftPMin: float = 1.0
+
+    @property
+    def HasHistoryPenalty(self) -> bool:  # Sampler.cs:686
+        return (np.float32(self.RepetitionPenalty) != 1.0 or np.float32(self.PresencePenalty) != 0.0
+                or np.float32(self.FrequencyPenalty) != 0.0)
+
+    def row(self):
+        return (self.Temperature, self.TopP, self.MinP, self.RepetitionPenalty, self.PresencePenalty,
+                self.FrequencyPenalty, self.TopK, self.RepeatLastN)
+
+
+class Random:
+    """Stand-in for ``System.Random``: only ``NextDouble()`` is used by the sampler.  The stream is
+    NumPy's PCG64, not .NET's generator; what matters for parity is how many draws are consumed."""
+
+    def __init__(self, seed: Optional[int] = None):
+        self._g = np.random.default_rng(seed)
+        self.draws = 0
+
+    def NextDouble(self) -> float:
+        self.draws += 1
+        return float(self._g.random())
+
+
+def _is_torch(x) -> bool:
+    return hasattr(x, "data_ptr")
+
+
+def _ptr(x) -> Optional[int]:
+    if x is None:
+        return None
+    if _is_torch(x):
+        return x.data_ptr()
+    return x.ctypes.data
+
+
+def params_array(params) -> np.ndarray:
+    if isinstance(params, np.ndarray) and params.dtype == PARAMS_DTYPE:
+        return np.ascontiguousarray(params)
+    return np.array([p.row() for p in params], dtype=PARAMS_DTYPE)
+
+
+class BatchSampler:
+    """A library handle plus its workspace (``stg_create``).  One instance per device and calling
+    thread, like the reference's backend (``IThreadAffineBackend.cs:11-21``)."""
+
+    def __init__(self, max_rows: int, max_vocab: int, max_history: int = 512, max_top_k: int = 256,
+                 max_bias: int = 64, max_spec_draft: int = 0, device: int = 0):
+        self._lib = N.load()
+        cfg = N.StgConfig(C.sizeof(N.StgConfig), device, max_rows, max_vocab, max_history, max_top_k,
+                          max_bias, max_spec_draft, 0)
+        h = C.c_void_p()
+        rc = self._lib.stg_create(C.byref(cfg), C.byref(h))
+        if rc != N.STG_OK:
+            raise StingrayError(rc, self._error(None))
+        self._h = h
+        self.device = device
+        self.max_rows, self.max_vocab, self.max_top_k = max_rows, max_vocab, max_top_k
+
+    # -- plumbing -------------------------------------------------------------------------------
+    def _error(self, h) -> str:
+        buf = C.create_string_buffer(512)
+        self._lib.stg_last_error(h, buf, 512)
+        return buf.value.decode("utf-8", "replace")
+
+    def _check(self, rc: int):
+        if rc != N.STG_OK:
+            raise StingrayError(rc, self._error(self._h))
+
+    def close(self):
+        if getattr(self, "_h", None):
+            self._lib.stg_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def stats(self) -> dict:
+        s = N.StgStats()
+        self._check(self._lib.stg_get_stats(self._h, C.byref(s)))
+        return {n: getattr(s, n) for n, _ in s._fields_}
+
+    @staticmethod
+    def _stream(stream) -> Optional[int]:
+        if stream is not None:
+            return stream
+        import torch
+
+        return torch.cuda.current_stream().cuda_stream
+
+    def _alloc(self, shape, dtype, host: bool):
+        if host:
+            return np.empty(shape, dtype)
+        import torch
+
+        td = {np.int32: torch.int32, np.float32: torch.float32, np.uint32: torch.int32}[dtype]
+        return torch.empty(shape, dtype=td, device=f"cuda:{self.device}")
+
+    def _batch(self, logits, params, history_ids, history_offsets, mask, row_uses_mask, bias,
+               uniforms):
+        """Builds the StgSampleBatch; returns it with the objects that must stay alive."""
+        keep = []
+        rows, vocab = logits.shape
+        if _is_torch(logits):
+            import torch
+
+            assert logits.is_cuda and logits.stride(1) == 1
+            dtype = {torch.float32: N.DTYPE_F32, torch.bfloat16: N.DTYPE_BF16}[logits.dtype]
+            stride = logits.stride(0) if rows > 1 else vocab
+            flags = 0
+        else:
+            logits = np.ascontiguousarray(logits)
+            dtype = N.DTYPE_BF16 if logits.dtype == np.uint16 else N.DTYPE_F32
+            assert logits.dtype in (np.float32, np.uint16)
+            stride = vocab
+            flags = N.MEM_HOST_LOGITS
+        keep.append(logits)
+        pa = params_array(params)
+        assert pa.shape[0] == rows
+        keep.append(pa)
+        b = N.StgSampleBatch()
+        b.struct_size = C.sizeof(N.StgSampleBatch)
+        b.rows, b.vocab, b.logits_dtype = rows, vocab, dtype
+        b.logits, b.row_stride, b.params = _ptr(logits), stride, pa.ctypes.data
+        if history_ids is not None:
+            ho = np.ascontiguousarray(history_offsets, dtype=np.int32)
+            if not _is_torch(history_ids):
+                history_ids = np.ascontiguousarray(history_ids, dtype=np.int32)
+                flags |= N.MEM_HOST_HISTORY
+            keep += [ho, history_ids]
+            b.history_ids, b.history_offsets = _ptr(history_ids), ho.ctypes.data
+        if mask is not None:
+            if not _is_torch(mask):
+                mask = np.ascontiguousarray(mask, dtype=np.uint32)
+                flags |= N.MEM_HOST_MASK
+                mstride = mask.shape[1]
+            else:
+                mstride = mask.stride(0) if rows > 1 else mask.shape[1]
+            keep.append(mask)
+            b.mask, b.mask_row_stride = _ptr(mask), mstride
+            if row_uses_mask is not None:
+                rum = np.ascontiguousarray(row_uses_mask, dtype=np.uint8)
+                keep.append(rum)
+                b.row_uses_mask = rum.ctypes.data
+        if bias is not None:
+            bi, bv, bo = bias
+            bo = np.ascontiguousarray(bo, dtype=np.int32)
+            if not _is_torch(bi):
+                bi = np.ascontiguousarray(bi, dtype=np.int32)
+                bv = np.ascontiguousarray(bv, dtype=np.float32)
+                flags |= N.MEM_HOST_BIAS
+            keep += [bi, bv, bo]
+            b.bias_ids, b.bias_values, b.bias_offsets = _ptr(bi), _ptr(bv), bo.ctypes.data
+        if uniforms is not None:
+            if not _is_torch(uniforms):
+                uniforms = np.ascontiguousarray(uniforms, dtype=np.float32)
+                flags |= N.MEM_HOST_UNIFORMS
+            keep.append(uniforms)
+            b.uniforms = _ptr(uniforms)
+        b.mem_flags = flags
+        return b, keep
+
+    # -- entry points ------------------------------------------------------------------------------
+    def argmax_rows(self, logits, valid_len: Optional[int] = None, stream=None):
+        """``CudaBackend.ArgmaxRowsToDevice`` (``CudaBackend.cs:4176-4190``): returns device
+        tensors (index, value) of the per-row argmax over ``[0, valid_len)``."""
+        import torch
+
+        rows, width = logits.shape
+        vocab = width if valid_len is None else valid_len
+        dtype = {torch.float32: N.DTYPE_F32, torch.bfloat16: N.DTYPE_BF16}[logits.dtype]
+        out = torch.empty((rows, 2), dtype=torch.int32, device=logits.device)
+        self._check(self._lib.stg_argmax_rows(self._h, logits.data_ptr(), dtype, rows, vocab,
+                                              logits.stride(0) if rows > 1 else width,
+                                              out.data_ptr(), self._stream(stream)))
+        return out[:, 0], out[:, 1].view(torch.float32)
+
+    def sample_rows(self, logits, params, *, history_ids=None, history_offsets=None, mask=None,
+                    row_uses_mask=None, bias=None, uniforms=None, want_probs=False,
+                    want_flags=False, want_topk=0, host_outputs: Optional[bool] = None, stream=None):
+        """One sampling step (``stg_sample_rows``).  ``logits`` is a CUDA tensor (fp32/bf16) or a
+        NumPy array (float32, or uint16 bf16 bit patterns); ``params`` a list of SamplingParams or
+        a PARAMS_DTYPE array; histories/bias are CSR; ``uniforms`` one float per row.  Returns a
+        dict with ``tokens`` and the optional outputs, on the device unless ``host_outputs``."""
+        b, keep = self._batch(logits, params, history_ids, history_offsets, mask, row_uses_mask,
+                              bias, uniforms)
+        host = (not _is_torch(logits)) if host_outputs is None else host_outputs
+        rows = b.rows
+        out = {"tokens": self._alloc((rows,), np.int32, host)}
+        b.tokens = _ptr(out["tokens"])
+        if want_probs:
+            out["probs"] = self._alloc((rows,), np.float32, host)
+            b.token_probs = _ptr(out["probs"])
+        if want_flags:
+            out["flags"] = self._alloc((rows,), np.uint32, host)
+            b.row_flags = _ptr(out["flags"])
+        if want_topk:
+            out["topk_ids"] = self._alloc((rows, want_topk), np.int32, host)
+            out["topk_logits"] = self._alloc((rows, want_topk), np.float32, host)
+            out["topk_probs"] = self._alloc((rows, want_topk), np.float32, host)
+            b.topk_ids, b.topk_logits = _ptr(out["topk_ids"]), _ptr(out["topk_logits"])
+            b.topk_probs, b.topk_stride = _ptr(out["topk_probs"]), want_topk
+        if host:
+            b.mem_flags |= N.MEM_HOST_OUTPUTS
+        self._check(self._lib.stg_sample_rows(self._h, C.byref(b), self._stream(stream)))
+        return out
+
+    def build_distribution(self, logits, params, *, history_ids=None, history_offsets=None,
+                           mask=None, bias=None, host_outputs: Optional[bool] = None, stream=None):
+        """``Sampler.BuildFilteredDistribution`` for every row: returns ``[rows, vocab]`` float32."""
+        b, keep = self._batch(logits, params, history_ids, history_offsets, mask, None, bias, None)
+        host = (not _is_torch(logits)) if host_outputs is None else host_outputs
+        probs = self._alloc((b.rows, b.vocab), np.float32, host)
+        if host:
+            b.mem_flags |= N.MEM_HOST_OUTPUTS
+        self._check(self._lib.stg_build_distribution(self._h, C.byref(b), _ptr(probs),
+                                                     self._stream(stream)))
+        return probs
+
+    def spec_verify(self, target_logits, draft_logits, draft_tokens, params, uniforms, *, mode=0,
+                    p_min=1.0, want_probs=False, stream=None):
+        """``SpeculativeDecoder.StepSampled``'s accept loop for ``n_seq`` sequences
+        (``stg_spec_verify``).  target ``[n_seq, L + 1, V]``, draft ``[n_seq, L, V]`` CUDA tensors,
+        draft_tokens ``[n_seq, L]`` int32, uniforms ``[n_seq, L + 2]`` float64 (host or device)."""
+        import torch
+
+        n_seq, lp1, vocab = target_logits.shape
+        L = lp1 - 1
+        pa = params_array(params)
+        dtype = {torch.float32: N.DTYPE_F32, torch.bfloat16: N.DTYPE_BF16}[target_logits.dtype]
+        flags = 0
+        if not _is_torch(draft_tokens):
+            draft_tokens = np.ascontiguousarray(draft_tokens, dtype=np.int32)
+            flags |= N.MEM_HOST_DRAFT
+        if not _is_torch(uniforms):
+            uniforms = np.ascontiguousarray(uniforms, dtype=np.float64)
+            flags |= N.MEM_HOST_UNIFORMS
+        dev = target_logits.device
+        accepted = torch.empty(n_seq, dtype=torch.int32, device=dev)
+        correction = torch.empty(n_seq, dtype=torch.int32, device=dev)
+        aprobs = torch.empty((n_seq, max(L, 1)), dtype=torch.float32, device=dev)
+        sflags = torch.empty(n_seq, dtype=torch.int32, device=dev)
+        b = N.StgSpecBatch()
+        b.struct_size = C.sizeof(N.StgSpecBatch)
+        b.n_seq, b.n_draft, b.vocab, b.logits_dtype, b.mode = n_seq, L, vocab, dtype, mode
+        assert target_logits.is_contiguous() and (draft_logits is None or draft_logits.is_contiguous())
+        b.target_logits = target_logits.data_ptr()
+        b.draft_logits = draft_logits.data_ptr() if draft_logits is not None else None
+        b.draft_tokens, b.params, b.uniforms = _ptr(draft_tokens), pa.ctypes.data, _ptr(uniforms)
+        b.p_min = p_min
+        b.accepted, b.correction = accepted.data_ptr(), correction.data_ptr()
+        b.accept_probs, b.seq_flags, b.mem_flags = aprobs.data_ptr(), sflags.data_ptr(), flags
+        self._check(self._lib.stg_spec_verify(self._h, C.byref(b), self._stream(stream)))
+        out = {"accepted": accepted, "correction": correction, "flags": sflags}
+        if want_probs:
+            out["accept_probs"] = aprobs
+        return out
+
+    def mtp_accept(self, logits, draft_tokens, p_min: float, stream=None):
+        """``MtpDecoder.AcceptDraft`` per row (``stg_mtp_accept``): returns (accept, argmax, prob)."""
+        import torch
+
+        rows, vocab = logits.shape
+        dtype = {torch.float32: N.DTYPE_F32, torch.bfloat16: N.DTYPE_BF16}[logits.dtype]
+        acc = torch.empty(rows, dtype=torch.int32, device=logits.device)
+        am = torch.empty(rows, dtype=torch.int32, device=logits.device)
+        pr = torch.empty(rows, dtype=torch.float32, device=logits.device)
+        self._check(self._lib.stg_mtp_accept(self._h, logits.data_ptr(), dtype, rows, vocab,
+                                             logits.stride(0) if rows > 1 else vocab,
+                                             draft_tokens.data_ptr(), p_min, acc.data_ptr(),
+                                             am.data_ptr(), pr.data_ptr(), self._stream(stream)))
+        return acc, am, pr
+
+
+_shared: Dict[int, BatchSampler] = {}
+
+
+def _single(vocab: int) -> BatchSampler:
+    """Handle used by the static single-row API, grown when a larger vocabulary shows up."""
+    s = _shared.get(0)
+    if s is None or s.max_vocab < vocab:
+        if s is not None:
+            s.close()
+        s = BatchSampler(max_rows=8, max_vocab=max(vocab, 4096), max_history=4096, max_top_k=1024,
+                         max_bias=256)
+        _shared[0] = s
+    return s
+
+
+def _csr(seq):
+    ids = np.asarray(list(seq) if seq is not None else [], dtype=np.int32)
+    return ids, np.array([0, ids.size], dtype=np.int32)
+
+
+class Sampler:
+    """Static single-row API with the reference's signatures (``Sampler.cs:12-646``)."""
+
+    @staticmethod
+    def Greedy(logits) -> int:
+        """``Sampler.Greedy`` (``Sampler.cs:442-446``): highest logit, lowest index on ties;
+        an empty span returns 0."""
+        a = np.ascontiguousarray(logits, dtype=np.float32).reshape(1, -1)
+        if a.shape[1] == 0:
+            return 0
+        p = SamplingParams(Temperature=0.0)
+        return int(_single(a.shape[1]).sample_rows(a, [p])["tokens"][0])
+
+    @staticmethod
+    def Sample(logits, p: SamplingParams, rng: Optional[Random] = None) -> int:
+        """``Sampler.Sample`` (``Sampler.cs:17-102``)."""
+        a = np.ascontiguousarray(logits, dtype=np.float32).reshape(1, -1)
+        kw = {}
+        if p.PreviousTokens is not None and len(p.PreviousTokens) > 0:
+            kw["history_ids"], kw["history_offsets"] = _csr(p.PreviousTokens)
+        if p.Temperature > 0:
+            rng = rng or _default_rng
+            kw["uniforms"] = np.array([np.float32(rng.NextDouble())], dtype=np.float32)
+            if p.LogitBias:
+                ids = np.array(list(p.LogitBias.keys()), dtype=np.int32)
+                vals = np.array(list(p.LogitBias.values()), dtype=np.float32)
+                kw["bias"] = (ids, vals, np.array([0, ids.size], dtype=np.int32))
+        return int(_single(a.shape[1]).sample_rows(a, [p], **kw)["tokens"][0])
+
+    @staticmethod
+    def BuildFilteredDistribution(logits, p: SamplingParams, probs: np.ndarray) -> None:
+        """``Sampler.BuildFilteredDistribution`` (``Sampler.cs:118-163``): fills ``probs``."""
+        a = np.ascontiguousarray(logits, dtype=np.float32).reshape(1, -1)
+        if probs.shape[-1] != a.shape[1]:
+            raise ValueError(
+                f"probs length ({probs.shape[-1]}) must equal logits length ({a.shape[1]}).")
+        kw = {}
+        if p.PreviousTokens is not None and len(p.PreviousTokens) > 0:
+            kw["history_ids"], kw["history_offsets"] = _csr(p.PreviousTokens)
+        if p.LogitBias and p.Temperature > 0:
+            ids = np.array(list(p.LogitBias.keys()), dtype=np.int32)
+            vals = np.array(list(p.LogitBias.values()), dtype=np.float32)
+            kw["bias"] = (ids, vals, np.array([0, ids.size], dtype=np.int32))
+        probs[...] = _single(a.shape[1]).build_distribution(a, [p], **kw)[0]
+
+
+_default_rng = Random()
