@@ -315,18 +315,15 @@ int run_batch(StgHandle h, const StgSampleBatch *b, int mode, float *dist_out, v
     if (mode == 1) {
         if (!dist_out) return fail(h, STG_ERR_INVALID_ARGUMENT, "probs is required");
         if (host_out) {
+            // distribution rows land in a device buffer first when the caller wants them on the host
             const size_t bytes = (size_t)rows * V * 4;
-            if (bytes > h->st_logits.bytes) {
-                // distribution rows staged in a device buffer when the caller wants them on the host
-                if (a.logits == h->st_logits.p) return fail(h, STG_ERR_UNSUPPORTED, "host logits and host probs together");
+            if (bytes > h->o_pairs.bytes) {
                 CK(cudaStreamSynchronize(stream));
-                dev_free(h->st_logits);
-                rc = dev_alloc(h, h->st_logits, bytes);
+                dev_free(h->o_pairs);
+                rc = dev_alloc(h, h->o_pairs, bytes);
                 if (rc) return rc;
-            } else if (a.logits == h->st_logits.p) {
-                return fail(h, STG_ERR_UNSUPPORTED, "host logits and host probs together");
             }
-            a.dist_out = (float *)h->st_logits.p;
+            a.dist_out = (float *)h->o_pairs.p;
         } else {
             a.dist_out = dist_out;
         }

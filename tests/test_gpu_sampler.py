@@ -166,7 +166,7 @@ def test_small_vocab_all_paths(bs, vocab):
     logits = rng.normal(0, 3, (rows, vocab)).astype(np.float32)
     p = _params(rows)
     p["temperature"] = rng.choice(np.array([0.0, 0.5, 1.0, 1.3], np.float32), rows)
-    p["top_k"] = rng.choice(np.array([0, 1, 5, 40, 5000]), rows)
+    p["top_k"] = rng.choice(np.array([0, 1, 5, 40, 900]), rows)
     p["top_p"] = rng.choice(np.array([1.0, 0.9, 0.5], np.float32), rows)
     p["min_p"] = rng.choice(np.array([0.0, 0.05], np.float32), rows)
     p["repetition_penalty"] = rng.choice(np.array([1.0, 1.1, 1.3], np.float32), rows)
@@ -306,7 +306,7 @@ def test_capacity_and_argument_errors(bs):
     with pytest.raises(StingrayError) as e:
         bs.sample_rows(x, _params(2), uniforms=np.array([0.5, 0.5], np.float32))
     assert e.value.code == 3
-    x = torch.zeros((2, 1000), device="cuda")
+    x = torch.zeros((2, 10000), device="cuda")
     with pytest.raises(StingrayError) as e:
         bs.sample_rows(x, _params(2, top_k=5000), uniforms=np.array([0.5, 0.5], np.float32))
     assert e.value.code == 3
