@@ -207,6 +207,19 @@ STG_API int stg_argmax_rows(StgHandle handle, const void *logits, int32_t logits
                             int32_t rows, int32_t vocab, int64_t row_stride, void *out_pairs,
                             void *stream);
 
+/* The same arg-max for callers that cannot allocate device memory where they need it (inside
+ * another component's stream capture, behind a plug-in interface that hands over a stream but no
+ * allocator, under a memory budget fixed at start-up).  It has no counterpart in the reference.
+ * It takes no handle and allocates nothing: its scratch is a fixed array inside the library's
+ * device image (about 1 MiB per GPU that loads the library, held until exit), so at most
+ * STG_STATIC_MAX_ROWS rows per call are accepted (STG_ERR_CAPACITY beyond).  The first call on a
+ * device looks up that array's device address, so make one call before any stream capture starts.
+ * All calls on a device share the scratch: calls whose kernels could overlap on the GPU must be
+ * ordered (same stream, or events).  Uses the current device; arrays are device pointers. */
+#define STG_STATIC_MAX_ROWS 4096
+STG_API int stg_argmax_rows_static(const void *logits, int32_t logits_dtype, int32_t rows,
+                                   int32_t vocab, int64_t row_stride, void *out_pairs, void *stream);
+
 /* One sampling step for every row of the batch: mask, logit bias, history penalties, temperature,
  * top-k, min-p, top-p and the inverse-CDF draw.  Replaces the serial loop
  *   ctr.Filter(row) -> Sampler.Greedy(row) | Sampler.Sample(row, spWithHistory, seq.Rng)

@@ -30,21 +30,21 @@ struct EmulCtl {
     int wa0[32], wa1[32];
 };
 
-__device__ __forceinline__ int sat_add(int a, int b)
+static __device__ __forceinline__ int sat_add(int a, int b)
 {
     int s = a + b;
     return s > (1 << 28) ? (1 << 28) : s;
 }
 
 // (a0, a1) then (b0, b1): offset for an even / odd starting sum
-__device__ __forceinline__ void comp(int a0, int a1, int b0, int b1, int &r0, int &r1)
+static __device__ __forceinline__ void comp(int a0, int a1, int b0, int b1, int &r0, int &r1)
 {
     r0 = sat_add(a0, (a0 & 1) ? b1 : b0);
     r1 = sat_add(a1, ((1 + a1) & 1) ? b1 : b0);
 }
 
 // increments of x >= 0 in units of 2^(eb-150), eb the biased exponent of the running sum (>= 1)
-__device__ __forceinline__ void unit_incr(float x, int eb, int &d0, int &d1)
+static __device__ __forceinline__ void unit_incr(float x, int eb, int &d0, int &d1)
 {
     uint32_t xb = __float_as_uint(x);
     if (!(x > 0.f)) { d0 = d1 = 0; return; }  // zero, negative or NaN terms add nothing here
@@ -68,7 +68,7 @@ __device__ __forceinline__ void unit_incr(float x, int eb, int &d0, int &d1)
 // the hit, or the final sum.  POS_ONLY: only elements > 0 are added and tested (ResampleResidual).
 // Prov::load(int base, int n, float x[kEmulItems]) yields elements base..base+7 (0 beyond n).
 template <class Prov, bool POS_ONLY>
-__device__ int emul_scan(EmulCtl *c, const Prov &pv, int n, float target, bool has_target,
+static __device__ int emul_scan(EmulCtl *c, const Prov &pv, int n, float target, bool has_target,
                          float *sum_out)
 {
     const int tid = threadIdx.x;
@@ -187,7 +187,7 @@ __device__ int emul_scan(EmulCtl *c, const Prov &pv, int n, float target, bool h
 }
 
 // ---- deterministic block sums ----------------------------------------------------------------
-__device__ __forceinline__ double block_sum_double(double v, double *scratch /* 32 */)
+static __device__ __forceinline__ double block_sum_double(double v, double *scratch /* 32 */)
 {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
@@ -206,7 +206,7 @@ __device__ __forceinline__ double block_sum_double(double v, double *scratch /* 
     return v;
 }
 
-__device__ __forceinline__ int block_sum_int(int v, int *scratch /* 32 */)
+static __device__ __forceinline__ int block_sum_int(int v, int *scratch /* 32 */)
 {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);

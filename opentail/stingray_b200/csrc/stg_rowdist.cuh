@@ -99,7 +99,7 @@ struct SrcScratch {
 };
 
 // ---- probability of an element from its exp value -----------------------------------------------
-__device__ __forceinline__ float eval_p2(float e, const RowDist &d)  // after softmax and min-p
+static __device__ __forceinline__ float eval_p2(float e, const RowDist &d)  // after softmax and min-p
 {
     float p = (d.flags & kDistScale1) ? __fmul_rn(e, d.inv1) : e;
     if (d.flags & kDistTopK) {
@@ -109,7 +109,7 @@ __device__ __forceinline__ float eval_p2(float e, const RowDist &d)  // after so
     if ((d.flags & kDistMinP) && p < d.minp_thr) p = 0.f;
     return p;
 }
-__device__ __forceinline__ float eval_p3(float e, int i, const RowDist &d)  // final probability
+static __device__ __forceinline__ float eval_p3(float e, int i, const RowDist &d)  // final probability
 {
     float p = eval_p2(e, d);
     if (d.flags & kDistTopP) {
@@ -203,7 +203,7 @@ struct ProvKeys {  // descending sorted probability bit patterns
 
 // ---- block-wide helpers ----------------------------------------------------------------------------
 template <class T>
-__device__ void bitonic_sort_desc_t(T *a, int p2)
+static __device__ void bitonic_sort_desc_t(T *a, int p2)
 {
     for (int k = 2; k <= p2; k <<= 1) {
         for (int j = k >> 1; j > 0; j >>= 1) {
@@ -219,7 +219,7 @@ __device__ void bitonic_sort_desc_t(T *a, int p2)
     }
 }
 
-__device__ __forceinline__ u64 block_max_key_r(u64 k, u64 *scratch)
+static __device__ __forceinline__ u64 block_max_key_r(u64 k, u64 *scratch)
 {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -246,7 +246,7 @@ __device__ __forceinline__ u64 block_max_key_r(u64 k, u64 *scratch)
 
 // (max value, lowest index of it) of the source as a key; 0 when nothing is > -infinity
 template <class Src>
-__device__ u64 pass_max(const Src &src, int n, u64 *red)
+static __device__ u64 pass_max(const Src &src, int n, u64 *red)
 {
     float best = -CUDART_INF_F;
     int best_i = -1;
@@ -264,7 +264,7 @@ __device__ u64 pass_max(const Src &src, int n, u64 *red)
 }
 
 // index of the `kth` (1-based) element, in token order, whose post-min-p probability equals tstar
-__device__ int find_kth_match(RowCtl *rc, const float *scratch, int n, const RowDist &d, float tstar,
+static __device__ int find_kth_match(RowCtl *rc, const float *scratch, int n, const RowDist &d, float tstar,
                               int kth)
 {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -324,7 +324,7 @@ __device__ int find_kth_match(RowCtl *rc, const float *scratch, int n, const Row
 // sorted by token so that one thread owns each distinct token and applies, in the reference's
 // order, the bias additions, the per-occurrence repetition penalty inside the window, and the
 // presence/frequency penalty over the whole history.
-__device__ void apply_overrides(const SampleArgs &a, const RowPlan &rp, float *scratch, int n,
+static __device__ void apply_overrides(const SampleArgs &a, const RowPlan &rp, float *scratch, int n,
                                 bool with_bias, u64 *keys /* arena */)
 {
     const int tid = threadIdx.x;
@@ -386,7 +386,7 @@ __device__ void apply_overrides(const SampleArgs &a, const RowPlan &rp, float *s
 // Leaves the exp values in `scratch` and the descriptor in rc->dist.  `src` yields the adjusted,
 // temperature-scaled logits.
 template <class Src>
-__device__ void build_dist(RowCtl *rc, SelCtl *sctl, const Src &src, const RowPlan &rp, int n,
+static __device__ void build_dist(RowCtl *rc, SelCtl *sctl, const Src &src, const RowPlan &rp, int n,
                            float *scratch, unsigned char *arena, uint32_t *gkeys, int gkeys_cap,
                            uint32_t *flags_out)
 {
@@ -580,7 +580,7 @@ __device__ void build_dist(RowCtl *rc, SelCtl *sctl, const Src &src, const RowPl
 }
 
 template <bool BF16>
-__device__ void run_row(const SampleArgs &a, int row, SelCtl *sctl, unsigned char *arena)
+static __device__ void run_row(const SampleArgs &a, int row, SelCtl *sctl, unsigned char *arena)
 {
     __shared__ RowCtl rc;
     const int tid = threadIdx.x;

@@ -17,29 +17,29 @@ namespace stg {
 
 typedef unsigned long long u64;
 
-__device__ __forceinline__ uint32_t ord32(float v)
+static __device__ __forceinline__ uint32_t ord32(float v)
 {
     v = v + 0.0f;  // -0 -> +0: the reference compares floats, for which the two are equal
     uint32_t b = __float_as_uint(v);
     return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
 }
-__device__ __forceinline__ float unord32(uint32_t k)
+static __device__ __forceinline__ float unord32(uint32_t k)
 {
     return __uint_as_float((k & 0x80000000u) ? (k & 0x7FFFFFFFu) : ~k);
 }
-__device__ __forceinline__ u64 make_key(float v, int idx)
+static __device__ __forceinline__ u64 make_key(float v, int idx)
 {
     return ((u64)ord32(v) << 32) | (u64)(0xFFFFFFFFu - (uint32_t)idx);
 }
-__device__ __forceinline__ float key_val(u64 k) { return unord32((uint32_t)(k >> 32)); }
-__device__ __forceinline__ int key_idx(u64 k) { return (int)(0xFFFFFFFFu - (uint32_t)k); }
+static __device__ __forceinline__ float key_val(u64 k) { return unord32((uint32_t)(k >> 32)); }
+static __device__ __forceinline__ int key_idx(u64 k) { return (int)(0xFFFFFFFFu - (uint32_t)k); }
 
 // ---- element access --------------------------------------------------------------------------
-__device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
-__device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
+static __device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
+static __device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
 
 template <bool BF16, bool STREAM>
-__device__ __forceinline__ void load_vec4(const void *rowp, int i, float v[4])
+static __device__ __forceinline__ void load_vec4(const void *rowp, int i, float v[4])
 {
     if (BF16) {
         const uint2 *p = (const uint2 *)((const uint16_t *)rowp + i);
@@ -52,16 +52,16 @@ __device__ __forceinline__ void load_vec4(const void *rowp, int i, float v[4])
     }
 }
 template <bool BF16>
-__device__ __forceinline__ float load_one(const void *rowp, int i)
+static __device__ __forceinline__ float load_one(const void *rowp, int i)
 {
     if (BF16) return __uint_as_float((uint32_t)__ldg((const uint16_t *)rowp + i) << 16);
     return __ldg((const float *)rowp + i);
 }
-__device__ __forceinline__ float load_one_dyn(const void *rowp, int dtype, int i)
+static __device__ __forceinline__ float load_one_dyn(const void *rowp, int dtype, int i)
 {
     return dtype ? load_one<true>(rowp, i) : load_one<false>(rowp, i);
 }
-__device__ __forceinline__ bool mask_bit(const uint32_t *mrow, int i)
+static __device__ __forceinline__ bool mask_bit(const uint32_t *mrow, int i)
 {
     return (__ldg(mrow + (i >> 5)) >> (i & 31)) & 1u;
 }
@@ -71,7 +71,7 @@ __device__ __forceinline__ bool mask_bit(const uint32_t *mrow, int i)
 // VEC == 4: elements base + (u*1024 + tid)*4 + e (one 128-bit / 64-bit load);
 // VEC == 1: elements base + (u*4 + e)*1024 + tid (scalar loads, any alignment).
 template <int VEC, bool BF16, bool STREAM>
-__device__ __forceinline__ void load_items(const void *rowp, const uint32_t *mrow, int base, int u,
+static __device__ __forceinline__ void load_items(const void *rowp, const uint32_t *mrow, int base, int u,
                                            int end, float v[4], int idx[4])
 {
     const int tid = threadIdx.x;
@@ -107,7 +107,7 @@ __device__ __forceinline__ void load_items(const void *rowp, const uint32_t *mro
 }
 
 // ---- block utilities ---------------------------------------------------------------------------
-__device__ __forceinline__ int warp_sum(int v)
+static __device__ __forceinline__ int warp_sum(int v)
 {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
@@ -138,7 +138,7 @@ struct Sel {
     int idx_off;  // added to a column index to form the token id stored in a key
 };
 
-__device__ __forceinline__ void sel_reset(Sel &s)
+static __device__ __forceinline__ void sel_reset(Sel &s)
 {
     if (threadIdx.x == 0) {
         s.c->cnt = 0; s.c->cnt2 = 0; s.c->overflow = 0; s.c->cur = 0; s.c->tmp = 0;
@@ -150,7 +150,7 @@ __device__ __forceinline__ void sel_reset(Sel &s)
 // Keeps the N largest keys of the active buffer (block-wide radix select on the 64-bit keys, most
 // significant byte first), moves them to the other buffer and raises tau to the N-th value.
 // Requires cnt > N.  All threads call it.
-__device__ void sel_compact(Sel &s)
+static __device__ void sel_compact(Sel &s)
 {
     SelCtl *c = s.c;
     const int tid = threadIdx.x;
@@ -225,7 +225,7 @@ __device__ void sel_compact(Sel &s)
 }
 
 // Appends the caller's up-to-4 passing elements; exact (counted) form used when room is short.
-__device__ __forceinline__ void sel_append_exact(Sel &s, const float v[4], const int idx[4], int end)
+static __device__ __forceinline__ void sel_append_exact(Sel &s, const float v[4], const int idx[4], int end)
 {
     SelCtl *c = s.c;
     for (;;) {
@@ -260,7 +260,7 @@ __device__ __forceinline__ void sel_append_exact(Sel &s, const float v[4], const
 // ascending token order per 16384-element iteration, which is what makes the strict `> tau` test
 // exact: an element equal to the N-th best value arrives after N better-or-earlier ones.
 template <int VEC, bool BF16>
-__device__ void sel_stream(Sel &s, const void *rowp, const uint32_t *mrow, int begin, int end)
+static __device__ void sel_stream(Sel &s, const void *rowp, const uint32_t *mrow, int begin, int end)
 {
     SelCtl *c = s.c;
     constexpr int U = 4;
@@ -305,7 +305,7 @@ __device__ void sel_stream(Sel &s, const void *rowp, const uint32_t *mrow, int b
 }
 
 // Appends `count` keys from global memory (another chunk's survivors).
-__device__ void sel_append_keys(Sel &s, const u64 *keys, int count)
+static __device__ void sel_append_keys(Sel &s, const u64 *keys, int count)
 {
     SelCtl *c = s.c;
     for (int base = 0; base < count; base += kSubTile) {
@@ -324,7 +324,7 @@ __device__ void sel_append_keys(Sel &s, const u64 *keys, int count)
 }
 
 // ---- block-wide bitonic sort, descending, of `p2` (power of two) 64-bit keys in shared memory --
-__device__ void bitonic_sort_desc(u64 *a, int p2)
+static __device__ void bitonic_sort_desc(u64 *a, int p2)
 {
     for (int k = 2; k <= p2; k <<= 1) {
         for (int j = k >> 1; j > 0; j >>= 1) {
@@ -340,7 +340,7 @@ __device__ void bitonic_sort_desc(u64 *a, int p2)
     }
 }
 
-__device__ __forceinline__ int pow2_ceil(int n)
+static __device__ __forceinline__ int pow2_ceil(int n)
 {
     int p = 1;
     while (p < n) p <<= 1;
@@ -350,7 +350,7 @@ __device__ __forceinline__ int pow2_ceil(int n)
 // ---- history lookups of the top-k path ---------------------------------------------------------
 // occurrences of `id` in the whole history and inside the repetition window
 // (Sampler.cs:271-279).  All threads scan the same addresses, so the loads broadcast.
-__device__ __forceinline__ void count_occurrences(const int32_t *hist, int hlen, int wstart, int id,
+static __device__ __forceinline__ void count_occurrences(const int32_t *hist, int hlen, int wstart, int id,
                                                   int &occ_all, int &occ_w)
 {
     int a = 0, w = 0;
@@ -364,7 +364,7 @@ __device__ __forceinline__ void count_occurrences(const int32_t *hist, int hlen,
 
 // powf(rep, occ) as the host's libm gives it (table built by the planner), falling back to a
 // correctly rounded double evaluation beyond the table.
-__device__ __forceinline__ float pow_rep(const float *tab, float rep, int occ)
+static __device__ __forceinline__ float pow_rep(const float *tab, float rep, int occ)
 {
     if (tab != nullptr && occ <= kPowTab) return __ldg(tab + occ - 1);
     return (float)pow((double)rep, (double)occ);
@@ -380,7 +380,7 @@ struct FinishOut {
 // active buffer: sort, penalise, stable re-sort, softmax over the first k, min-p, top-p, draw.
 // Every fp32 operation is issued separately (no fused multiply-add), in the order of
 // Sampler.cs:257-349.  `vals`/`ids`/`probs` views alias the inactive buffer.
-__device__ void finish_topk(Sel &s, const RowPlan &rp, const int32_t *hist, const float *pow_tab,
+static __device__ void finish_topk(Sel &s, const RowPlan &rp, const int32_t *hist, const float *pow_tab,
                             float uniform, FinishOut *out_sh, int32_t *o_ids, float *o_vals,
                             float *o_probs)
 {
