@@ -66,9 +66,10 @@ struct Plan {
 
 // Resolves every row's path exactly as Sampler.Sample dispatches (Sampler.cs:19-39) and lays out
 // the work items: whole-row items first (they run longest), then the chunk items row by row.
-int make_plan(StgHandle h, const StgSampleBatch *b, int mode, bool shard, Plan &pl)
+int make_plan(StgHandle h, const StgSampleBatch *b, int mode, bool shard, int global_vocab, Plan &pl)
 {
     const int rows = b->rows, V = b->vocab;
+    const int GV = global_vocab > 0 ? global_vocab : V;  // the vocabulary the reference's rules see
     pl.rows.resize(rows);
     std::vector<std::pair<uint32_t, int>> reps;  // distinct repetition penalties -> table offset
     int n_chunk_rows = 0, max_sel = 1;
@@ -98,15 +99,15 @@ int make_plan(StgHandle h, const StgSampleBatch *b, int mode, bool shard, Plan &
         const bool pen_set = p.repetition_penalty != 1.0f || p.presence_penalty != 0.f || p.frequency_penalty != 0.f;
         rp.has_penalty = pen_set && hlen > 0;
         rp.sel = 1;
-        if (mode == 1) {
+        if (mode != 0) {
             rp.path = p.temperature <= 0.f ? (rp.has_penalty ? kPathGreedyPen : kPathGreedy) : kPathFull;
             rp.n_chunks = 0;
         } else if (p.temperature <= 0.f) {
             rp.path = rp.has_penalty ? kPathGreedyPen : kPathGreedy;
-        } else if (p.top_k > 0 && p.top_k < V && blen == 0) {
+        } else if (p.top_k > 0 && p.top_k < GV && blen == 0) {
             rp.path = kPathTopK;
             int64_t want = (int64_t)p.top_k + (rp.has_penalty ? hlen : 0);
-            rp.sel = (int)std::min<int64_t>(want, V);
+            rp.sel = (int)std::min<int64_t>(want, GV);
             if (p.top_k > h->cfg.max_top_k) return fail(h, STG_ERR_CAPACITY, "top_k larger than max_top_k");
             if (rp.sel > kMaxSel) return fail(h, STG_ERR_CAPACITY, "top_k + history length exceeds 8192");
             if (rp.has_penalty && p.repetition_penalty != 1.0f) {
@@ -126,13 +127,13 @@ int make_plan(StgHandle h, const StgSampleBatch *b, int mode, bool shard, Plan &
             rp.path = kPathFull;
         }
         if (rp.path == kPathFull) {
-            if (p.top_k > 4096 && p.top_k < V)
+            if (p.top_k > 4096 && p.top_k < GV)
                 return fail(h, STG_ERR_UNSUPPORTED, "top_k above 4096 on the full-vocabulary path");
             if (hlen + blen > kMaxOverride) return fail(h, STG_ERR_CAPACITY, "history + bias entries exceed 16384");
         }
         if (shard && !(rp.path == kPathTopK || rp.path == kPathGreedy))
             return fail(h, STG_ERR_UNSUPPORTED, "vocabulary-sharded mode supports top-k and plain greedy rows only");
-        const bool chunked = mode != 1 && (rp.path == kPathGreedy || rp.path == kPathTopK);
+        const bool chunked = mode == 0 && (rp.path == kPathGreedy || rp.path == kPathTopK);
         if (chunked) { n_chunk_rows++; max_sel = std::max(max_sel, rp.sel); }
         else pl.any_row_item = true;
         if (rp.path == kPathTopK) pl.n_topk++; else if (rp.path == kPathFull) pl.n_full++; else pl.n_greedy++;
@@ -150,14 +151,14 @@ int make_plan(StgHandle h, const StgSampleBatch *b, int mode, bool shard, Plan &
         int n_chunks = (V + pl.chunk_len - 1) / pl.chunk_len;
         size_t need = 0;
         for (auto &rp : pl.rows)
-            if (rp.path == kPathGreedy || rp.path == kPathTopK) need += (size_t)n_chunks * (size_t)rp.sel;
+            if (mode == 0 && (rp.path == kPathGreedy || rp.path == kPathTopK)) need += (size_t)n_chunks * (size_t)rp.sel;
         if (n_chunks == 1 || need <= h->cand_entries) { S = n_chunks; break; }
         S = std::max(1, S / 2);
     }
     int cand_off = 0, slot = 0;
     for (int r = 0; r < rows; r++) {
         RowPlan &rp = pl.rows[r];
-        if (mode != 1 && (rp.path == kPathGreedy || rp.path == kPathTopK)) {
+        if (mode == 0 && (rp.path == kPathGreedy || rp.path == kPathTopK)) {
             rp.n_chunks = S;
             rp.cand_off = cand_off;
             rp.slot = slot;
@@ -234,14 +235,14 @@ int stage_in(StgHandle h, const void *src, size_t bytes, bool on_host, DevBuf &s
 
 namespace {
 
-int check_batch(StgHandle h, const StgSampleBatch *b)
+int check_batch(StgHandle h, const StgSampleBatch *b, bool no_logits)
 {
     if (!h) return STG_ERR_INVALID_ARGUMENT;
     if (!b || b->struct_size != (int32_t)sizeof(StgSampleBatch)) return fail(h, STG_ERR_INVALID_ARGUMENT, "bad StgSampleBatch");
     if (b->rows < 0 || b->vocab <= 0) return fail(h, STG_ERR_INVALID_ARGUMENT, "rows must be >= 0 and vocab > 0");
     if (b->rows > h->cfg.max_rows) return fail(h, STG_ERR_CAPACITY, "rows exceed max_rows");
     if (b->vocab > h->cfg.max_vocab) return fail(h, STG_ERR_CAPACITY, "vocab exceeds max_vocab");
-    if (b->rows > 0 && (!b->logits || !b->params)) return fail(h, STG_ERR_INVALID_ARGUMENT, "logits and params are required");
+    if (b->rows > 0 && ((!b->logits && !no_logits) || !b->params)) return fail(h, STG_ERR_INVALID_ARGUMENT, "logits and params are required");
     if (b->row_stride < b->vocab) return fail(h, STG_ERR_INVALID_ARGUMENT, "row_stride smaller than vocab");
     if (b->logits_dtype != STG_DTYPE_F32 && b->logits_dtype != STG_DTYPE_BF16) return fail(h, STG_ERR_INVALID_ARGUMENT, "unknown logits_dtype");
     if (b->mask && b->mask_row_stride < (b->vocab + 31) / 32) return fail(h, STG_ERR_INVALID_ARGUMENT, "mask_row_stride too small");
@@ -255,19 +256,27 @@ bool rows_aligned(const void *p, int64_t row_stride, int dtype)
     return ((uintptr_t)p % need) == 0 && ((size_t)row_stride * esz) % need == 0;
 }
 
-int run_batch(StgHandle h, const StgSampleBatch *b, int mode, float *dist_out, void *pairs_out, void *stream_)
+}  // namespace
+
+namespace stg {
+
+int run_batch(StgHandle h, const StgSampleBatch *b, const BatchExtra &x, void *stream_)
 {
+    const int mode = x.mode;
+    float *dist_out = x.dist_out;
+    void *pairs_out = x.pairs_out;
     cudaStream_t stream = (cudaStream_t)stream_;
-    int rc = check_batch(h, b);
+    int rc = check_batch(h, b, x.shard_mode == 2);
     if (rc) return rc;
     if (b->rows == 0) return STG_OK;
     CK(cudaSetDevice(h->cfg.device));
     const uint32_t mf = b->mem_flags;
     const int rows = b->rows, V = b->vocab;
-    if (mode == 0 && !pairs_out && !b->tokens) return fail(h, STG_ERR_INVALID_ARGUMENT, "tokens is required");
+    if (mode == 0 && !pairs_out && !b->tokens && !x.shard_mode) return fail(h, STG_ERR_INVALID_ARGUMENT, "tokens is required");
+    if (x.shard_mode && (!h->xchg_local.p || b->rows > h->shard_rows)) return fail(h, STG_ERR_CAPACITY, "exchange buffers are missing or too small");
 
     Plan pl;
-    rc = make_plan(h, b, mode, false, pl);
+    rc = make_plan(h, b, mode, x.shard_mode != 0, x.global_vocab, pl);
     if (rc) return rc;
     if (pl.smem > h->smem_optin) return fail(h, STG_ERR_CAPACITY, "shared memory needed exceeds the device limit");
     const RowPlan *d_rows; const WorkItem *d_items; const float *d_pow;
@@ -278,8 +287,11 @@ int run_batch(StgHandle h, const StgSampleBatch *b, int mode, float *dist_out, v
     memset(&a, 0, sizeof(a));
     const size_t esz = b->logits_dtype == STG_DTYPE_BF16 ? 2 : 4;
     const void *p;
-    rc = stage_in(h, b->logits, ((size_t)(rows - 1) * b->row_stride + V) * esz, mf & STG_MEM_HOST_LOGITS, h->st_logits, stream, &p);
-    if (rc) return rc;
+    p = nullptr;
+    if (x.shard_mode != 2) {
+        rc = stage_in(h, b->logits, ((size_t)(rows - 1) * b->row_stride + V) * esz, mf & STG_MEM_HOST_LOGITS, h->st_logits, stream, &p);
+        if (rc) return rc;
+    }
     a.logits = p;
     const int hist_total = (b->history_offsets && b->history_ids) ? b->history_offsets[rows] : 0;
     rc = stage_in(h, b->history_ids, (size_t)hist_total * 4, mf & STG_MEM_HOST_HISTORY, h->st_hist, stream, &p);
@@ -336,7 +348,10 @@ int run_batch(StgHandle h, const StgSampleBatch *b, int mode, float *dist_out, v
     a.work_counter = (uint32_t *)h->work_counter.p;
     a.escratch = (float *)h->escratch.p;
     a.keyscratch = (unsigned long long *)h->keyscratch.p;
-    a.dists = nullptr;
+    a.dists = x.dists_out;
+    a.xchg_local = (unsigned long long *)h->xchg_local.p;
+    a.xchg_count = (int32_t *)h->xchg_count_local.p;
+    a.xchg_stride = h->shard_sel;
     a.row_stride = b->row_stride;
     a.mask_stride = b->mask_row_stride;
     a.escratch_stride = h->escratch_stride;
@@ -348,8 +363,22 @@ int run_batch(StgHandle h, const StgSampleBatch *b, int mode, float *dist_out, v
     a.cap = pl.cap;
     a.vec = rows_aligned(a.logits, b->row_stride, b->logits_dtype) ? 4 : 1;
     a.mode = mode;
-    a.vocab_offset = 0; a.shard_mode = 0; a.n_ranks = 1;
+    a.vocab_offset = x.vocab_offset; a.shard_mode = x.shard_mode; a.n_ranks = h->n_ranks;
 
+    if (x.shard_mode == 1) h->shard_rows_used = rows;
+    if (x.shard_mode == 2) {
+        if (rows != h->shard_rows_used) return fail(h, STG_ERR_INVALID_ARGUMENT, "batch differs from the one selected");
+        cudaError_t e2 = launch_shard_finish(a, h->xchg_gather.p, (const int32_t *)h->xchg_count_gather.p, (size_t)pl.cap * 16, stream);
+        if (e2 != cudaSuccess) return cuda_fail(h, e2, "k_shard_finish launch");
+        h->stats.kernel_launches++;
+        if (host_out) {
+            if (b->tokens) CK(cudaMemcpyAsync(b->tokens, a.tokens, (size_t)rows * 4, cudaMemcpyDeviceToHost, stream));
+            if (b->token_probs) CK(cudaMemcpyAsync(b->token_probs, a.token_probs, (size_t)rows * 4, cudaMemcpyDeviceToHost, stream));
+            if (b->row_flags) CK(cudaMemcpyAsync(b->row_flags, a.row_flags, (size_t)rows * 4, cudaMemcpyDeviceToHost, stream));
+            CK(cudaStreamSynchronize(stream));
+        }
+        return STG_OK;
+    }
     const int grid = std::min(a.n_items, h->sm_count);
     cudaError_t e = launch_sample(a, grid, pl.smem, stream);
     if (e != cudaSuccess) {
@@ -377,7 +406,7 @@ int run_batch(StgHandle h, const StgSampleBatch *b, int mode, float *dist_out, v
     return STG_OK;
 }
 
-}  // namespace
+}  // namespace stg
 
 extern "C" {
 
@@ -497,11 +526,18 @@ int stg_get_stats(StgHandle h, StgStats *out)
     return STG_OK;
 }
 
-int stg_sample_rows(StgHandle h, const StgSampleBatch *b, void *stream) { return run_batch(h, b, 0, nullptr, nullptr, stream); }
+int stg_sample_rows(StgHandle h, const StgSampleBatch *b, void *stream)
+{
+    BatchExtra x;
+    return run_batch(h, b, x, stream);
+}
 
 int stg_build_distribution(StgHandle h, const StgSampleBatch *b, float *probs, void *stream)
 {
-    return run_batch(h, b, 1, probs, nullptr, stream);
+    BatchExtra x;
+    x.mode = 1;
+    x.dist_out = probs;
+    return run_batch(h, b, x, stream);
 }
 
 int stg_argmax_rows(StgHandle h, const void *logits, int32_t dtype, int32_t rows, int32_t vocab, int64_t row_stride,
@@ -518,7 +554,9 @@ int stg_argmax_rows(StgHandle h, const void *logits, int32_t dtype, int32_t rows
     b.rows = rows; b.vocab = vocab; b.logits_dtype = dtype; b.logits = logits; b.row_stride = row_stride;
     b.params = params.data();
     b.tokens = (int32_t *)h->o_tokens.p;
-    return run_batch(h, &b, 0, nullptr, out_pairs, stream);
+    BatchExtra x;
+    x.pairs_out = out_pairs;
+    return run_batch(h, &b, x, stream);
 }
 
 }  // extern "C"

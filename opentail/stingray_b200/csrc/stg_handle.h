@@ -45,7 +45,7 @@ struct StgSampler_ {
     void *nccl_lib = nullptr;
     void *nccl_comm = nullptr;
     int rank = 0, n_ranks = 1;
-    int shard_sel = 0, shard_rows = 0;
+    int shard_sel = 0, shard_rows = 0, shard_rows_used = 0;
 };
 
 namespace stg {
@@ -55,6 +55,17 @@ int cuda_fail(StgHandle h, cudaError_t e, const char *what);
 int dev_alloc(StgHandle h, DevBuf &b, size_t bytes);
 void dev_free(DevBuf &b);
 inline size_t round_up(size_t v, size_t m) { return (v + m - 1) / m * m; }
+// What distinguishes the callers of the shared batch runner.
+struct BatchExtra {
+    int mode = 0;                 // 0 sample, 1 materialise distributions, 2 descriptors only
+    float *dist_out = nullptr;    // mode 1
+    void *pairs_out = nullptr;    // stg_argmax_rows
+    RowDist *dists_out = nullptr; // mode 2
+    int shard_mode = 0;           // 1: export each row's local candidates to the exchange buffer
+    int vocab_offset = 0;
+    int global_vocab = 0;         // 0: same as the batch's vocab
+};
+int run_batch(StgHandle h, const StgSampleBatch *b, const BatchExtra &x, void *stream);
 int stage_in(StgHandle h, const void *src, size_t bytes, bool on_host, DevBuf &stage, cudaStream_t stream,
              const void **out);
 

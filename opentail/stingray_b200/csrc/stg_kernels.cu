@@ -129,6 +129,13 @@ __device__ void run_chunk(const SampleArgs &a, int row, int chunk, SelCtl *ctl, 
             if (!ish->last) return;
             k = ish->best;
         }
+        if (a.shard_mode == 1) {
+            if (threadIdx.x == 0) {
+                a.xchg_local[(int64_t)row * a.xchg_stride] = k;
+                a.xchg_count[row] = k ? 1 : 0;
+            }
+            return;
+        }
         write_greedy(a, row, k, rowp);
         return;
     }
@@ -166,6 +173,16 @@ __device__ void run_chunk(const SampleArgs &a, int row, int chunk, SelCtl *ctl, 
             sel_append_keys(s, a.cand + rp.cand_off + (int64_t)c * rp.sel, m);
         }
     }
+    if (a.shard_mode == 1) {
+        // vocabulary-sharded mode: hand this rank's survivors to the exchange buffer
+        const int cnt = ctl->cnt;
+        const u64 *src = s.buf[ctl->cur];
+        u64 *dst = a.xchg_local + (int64_t)row * a.xchg_stride;
+        for (int e = threadIdx.x; e < cnt; e += kThreads) dst[e] = src[e];
+        if (threadIdx.x == 0) a.xchg_count[row] = cnt;
+        __syncthreads();
+        return;
+    }
     const int32_t *hist = a.hist_ids ? a.hist_ids + rp.hist_off : nullptr;
     const float *ptab = (a.pow_tab && rp.pow_off >= 0) ? a.pow_tab + rp.pow_off : nullptr;
     float u = a.uniforms ? __ldg(a.uniforms + row) : 0.5f;
@@ -199,6 +216,65 @@ __global__ void __launch_bounds__(kThreads, 1) k_sample(const __grid_constant__ 
             run_row<BF16>(a, w.row, &ctl, arena);
         __syncthreads();
     }
+}
+
+// Vocabulary-sharded mode, after the exchange: one CTA per row merges the ranks' candidate lists
+// (gather layout [rank][row][stride]) and finishes the row.
+__global__ void __launch_bounds__(kThreads, 1) k_shard_finish(const __grid_constant__ SampleArgs a,
+                                                              const u64 *gather, const int32_t *gcount)
+{
+    extern __shared__ __align__(16) unsigned char arena[];
+    __shared__ SelCtl ctl;
+    __shared__ ItemShared ish;
+    const int row = blockIdx.x;
+    const RowPlan rp = a.plans[row];
+    if (rp.path == kPathGreedy) {
+        if (threadIdx.x == 0) {
+            u64 best = 0ull;
+            for (int r = 0; r < a.n_ranks; r++) {
+                if (gcount[(int64_t)r * a.rows + row] > 0) {
+                    u64 t = gather[((int64_t)r * a.rows + row) * a.xchg_stride];
+                    best = t > best ? t : best;
+                }
+            }
+            a.tokens[row] = best ? key_idx(best) : 0;
+            if (a.token_probs) a.token_probs[row] = 1.f;
+            if (a.row_flags) a.row_flags[row] = kPathGreedy | (best ? 0u : (1u << 6));
+        }
+        return;
+    }
+    Sel s;
+    s.c = &ctl;
+    s.buf[0] = (u64 *)arena;
+    s.buf[1] = s.buf[0] + a.cap;
+    s.cap = a.cap;
+    s.n = rp.sel;
+    s.idx_off = 0;
+    sel_reset(s);
+    for (int r = 0; r < a.n_ranks; r++) {
+        int m = gcount[(int64_t)r * a.rows + row];
+        sel_append_keys(s, gather + ((int64_t)r * a.rows + row) * a.xchg_stride, m);
+    }
+    const int32_t *hist = a.hist_ids ? a.hist_ids + rp.hist_off : nullptr;
+    const float *ptab = (a.pow_tab && rp.pow_off >= 0) ? a.pow_tab + rp.pow_off : nullptr;
+    float u = a.uniforms ? __ldg(a.uniforms + row) : 0.5f;
+    int64_t o = (int64_t)row * a.topk_stride;
+    finish_topk(s, rp, hist, ptab, u, &ish.fout, a.topk_ids ? a.topk_ids + o : nullptr,
+                a.topk_logits ? a.topk_logits + o : nullptr, a.topk_probs ? a.topk_probs + o : nullptr);
+    if (threadIdx.x == 0) {
+        a.tokens[row] = ish.fout.token;
+        if (a.token_probs) a.token_probs[row] = ish.fout.prob;
+        if (a.row_flags) a.row_flags[row] = ish.fout.flags;
+    }
+}
+
+cudaError_t launch_shard_finish(const SampleArgs &a, const void *gather, const int32_t *gcount, size_t smem,
+                                cudaStream_t stream)
+{
+    cudaError_t e = cudaFuncSetAttribute(k_shard_finish, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    k_shard_finish<<<a.rows, kThreads, smem, stream>>>(a, (const u64 *)gather, gcount);
+    return cudaGetLastError();
 }
 
 cudaError_t launch_sample(const SampleArgs &a, int grid, size_t smem, cudaStream_t stream)

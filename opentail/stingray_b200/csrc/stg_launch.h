@@ -10,5 +10,27 @@ namespace stg {
 constexpr size_t kRowArenaBytes = (size_t)kSortCap * 4 + 2048 * 4 + 2048 * 8;
 
 cudaError_t launch_sample(const SampleArgs &a, int grid, size_t smem, cudaStream_t stream);
+cudaError_t launch_shard_finish(const SampleArgs &a, const void *gather, const int32_t *gcount, size_t smem,
+                                cudaStream_t stream);
+
+// speculative verification, second phase (stg_spec.cu)
+struct SpecArgs {
+    const void *target;
+    const void *draft;
+    const int32_t *draft_tokens;
+    const double *uniforms;
+    const RowDist *tdist;
+    const RowDist *ddist;
+    int32_t *accepted;
+    int32_t *correction;
+    float *accept_probs;
+    uint32_t *seq_flags;
+    float p_min;
+    int32_t n_seq, n_draft, vocab, dtype, mode, vec;
+};
+cudaError_t launch_spec_finish(const SpecArgs &a, cudaStream_t stream);
+cudaError_t launch_mtp_accept(const void *logits, int dtype, int rows, int vocab, int64_t row_stride, int vec,
+                              const int32_t *draft, float p_min, int32_t *accept, int32_t *argmax, float *prob,
+                              cudaStream_t stream);
 
 }  // namespace stg

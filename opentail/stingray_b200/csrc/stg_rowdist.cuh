@@ -404,7 +404,7 @@ static __device__ void build_dist(RowCtl *rc, SelCtl *sctl, const Src &src, cons
     d.inv_t = src.inv_t;
     d.tie_idx_max = INT_MAX;
     d.kth = 0.f; d.inv2 = 1.f; d.minp_thr = 0.f; d.tstar = 0.f; d.inv3 = 1.f; d.inv1 = 1.f;
-    d.uniform_p = 0.f; d.sum_end = 0.f;
+    d.uniform_p = 0.f; d.sum_end = 0.f; d.argmax = 0;
     if (want_topp) {
         for (int t = tid; t < kBins; t += kThreads) { hcount[t] = 0u; hmass[t] = 0ull; }
     }
@@ -627,6 +627,19 @@ static __device__ void run_row(const SampleArgs &a, int row, SelCtl *sctl, unsig
         if (overrides) { SrcScratch s{scratch, 1.f, false}; mk = pass_max(s, n, rc.red_k); }
         else { SrcLogits<BF16> s{rowp, mrow, a.vec == 4, 1.f, false}; mk = pass_max(s, n, rc.red_k); }
         int tok = mk ? key_idx(mk) : 0;
+        if (a.mode == 2) {
+            if (tid == 0) {
+                RowDist d;
+                memset(&d, 0, sizeof(d));
+                d.flags = kDistOneHot;
+                d.tie_idx_max = tok;
+                d.argmax = tok;
+                d.inv_t = 1.f; d.inv1 = 1.f; d.inv2 = 1.f; d.inv3 = 1.f;
+                a.dists[row] = d;
+            }
+            __syncthreads();
+            return;
+        }
         if (a.mode == 1 && a.dist_out) {
             float *o = a.dist_out + (int64_t)row * n;
             for (int i = tid; i < n; i += kThreads) o[i] = (i == tok) ? 1.f : 0.f;
@@ -649,7 +662,17 @@ static __device__ void run_row(const SampleArgs &a, int row, SelCtl *sctl, unsig
         SrcLogits<BF16> s{rowp, mrow, a.vec == 4, inv_t, scale};
         build_dist(&rc, sctl, s, rp, n, scratch, arena, gkeys, gkeys_cap, &sh_flags);
     }
-    if (a.dists && tid == 0) a.dists[row] = rc.dist;
+    if (a.mode == 2) {
+        // descriptor only; the raw arg-max goes with it (the looser accept rule compares against it)
+        SrcLogits<BF16> raw{rowp, mrow, a.vec == 4, 1.f, false};
+        u64 mk = pass_max(raw, n, rc.red_k);
+        if (tid == 0) {
+            rc.dist.argmax = mk ? key_idx(mk) : 0;
+            a.dists[row] = rc.dist;
+        }
+        __syncthreads();
+        return;
+    }
 
     // draw: SampleFromDistribution (Sampler.cs:564-576)
     float *dout = (a.mode == 1 && a.dist_out) ? a.dist_out + (int64_t)row * n : nullptr;

@@ -1,19 +1,287 @@
-// Speculative verification and vocabulary-sharded entry points (being filled in).
+// C ABI, second part: speculative verification, the MTP accept rule, and the vocabulary-sharded
+// mode with its NCCL exchange.
+#include <dlfcn.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <vector>
+
 #include "stg_handle.h"
+#include "stg_launch.h"
 
 using namespace stg;
 
+namespace {
+
+bool rows_aligned2(const void *p, int64_t row_stride, int dtype)
+{
+    const size_t esz = dtype == STG_DTYPE_BF16 ? 2 : 4;
+    const size_t need = dtype == STG_DTYPE_BF16 ? 8 : 16;
+    return ((uintptr_t)p % need) == 0 && ((size_t)row_stride * esz) % need == 0;
+}
+
+// ---- NCCL through dlopen: the library has no link-time dependency on it ------------------------
+struct NcclId { char internal[128]; };
+typedef int (*fn_get_unique_id)(NcclId *);
+typedef int (*fn_comm_init_rank)(void **, int, NcclId, int);
+typedef int (*fn_comm_destroy)(void *);
+typedef int (*fn_all_gather)(const void *, void *, size_t, int, void *, cudaStream_t);
+typedef const char *(*fn_error_string)(int);
+
+struct NcclApi {
+    void *lib = nullptr;
+    fn_get_unique_id get_unique_id = nullptr;
+    fn_comm_init_rank comm_init_rank = nullptr;
+    fn_comm_destroy comm_destroy = nullptr;
+    fn_all_gather all_gather = nullptr;
+    fn_error_string error_string = nullptr;
+};
+NcclApi g_nccl;
+
+bool load_nccl(std::string &why)
+{
+    if (g_nccl.lib) return true;
+    const char *env = getenv("STG_NCCL_LIB");
+    const char *names[] = {env, "libnccl.so.2", "libnccl.so"};
+    for (const char *n : names) {
+        if (!n || !*n) continue;
+        g_nccl.lib = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
+        if (g_nccl.lib) break;
+    }
+    if (!g_nccl.lib) { why = std::string("cannot load libnccl: ") + dlerror(); return false; }
+    g_nccl.get_unique_id = (fn_get_unique_id)dlsym(g_nccl.lib, "ncclGetUniqueId");
+    g_nccl.comm_init_rank = (fn_comm_init_rank)dlsym(g_nccl.lib, "ncclCommInitRank");
+    g_nccl.comm_destroy = (fn_comm_destroy)dlsym(g_nccl.lib, "ncclCommDestroy");
+    g_nccl.all_gather = (fn_all_gather)dlsym(g_nccl.lib, "ncclAllGather");
+    g_nccl.error_string = (fn_error_string)dlsym(g_nccl.lib, "ncclGetErrorString");
+    if (!g_nccl.get_unique_id || !g_nccl.comm_init_rank || !g_nccl.comm_destroy || !g_nccl.all_gather) {
+        why = "libnccl lacks a required symbol";
+        return false;
+    }
+    return true;
+}
+
+int nccl_fail(StgHandle h, int code, const char *what)
+{
+    std::string msg = std::string(what) + ": ";
+    msg += g_nccl.error_string ? g_nccl.error_string(code) : "NCCL error";
+    return fail(h, STG_ERR_NCCL, msg);
+}
+
+int ensure_exchange(StgHandle h, int n_ranks)
+{
+    const size_t R = (size_t)h->cfg.max_rows;
+    const size_t sel = std::max<size_t>(1, (size_t)h->cfg.max_top_k + h->cfg.max_history);
+    const size_t local = R * sel * 8, gather = local * (size_t)n_ranks;
+    int rc = STG_OK;
+    if (h->xchg_local.bytes < local) {
+        dev_free(h->xchg_local); dev_free(h->xchg_count_local);
+        rc = dev_alloc(h, h->xchg_local, local);
+        if (!rc) rc = dev_alloc(h, h->xchg_count_local, R * 4);
+    }
+    if (!rc && h->xchg_gather.bytes < gather) {
+        // only the receive side grows with the number of ranks; this rank's own candidates stay
+        dev_free(h->xchg_gather); dev_free(h->xchg_count_gather);
+        rc = dev_alloc(h, h->xchg_gather, gather);
+        if (!rc) rc = dev_alloc(h, h->xchg_count_gather, R * 4 * (size_t)n_ranks);
+    }
+    if (rc) return rc;
+    h->shard_sel = (int)sel;
+    h->shard_rows = (int)R;
+    return STG_OK;
+}
+
+}  // namespace
+
 extern "C" {
 
-int stg_spec_verify(StgHandle h, const StgSpecBatch *, void *) { return fail(h, STG_ERR_UNSUPPORTED, "not built yet"); }
-int stg_mtp_accept(StgHandle h, const void *, int32_t, int32_t, int32_t, int64_t, const int32_t *, float, int32_t *,
-                   int32_t *, float *, void *) { return fail(h, STG_ERR_UNSUPPORTED, "not built yet"); }
-int stg_comm_unique_id(void *) { return STG_ERR_UNSUPPORTED; }
-int stg_comm_init(StgHandle h, const void *, int32_t, int32_t) { return fail(h, STG_ERR_UNSUPPORTED, "not built yet"); }
-int stg_comm_destroy(StgHandle) { return STG_OK; }
-int stg_shard_select(StgHandle h, const StgSampleBatch *, int32_t, int32_t, void *) { return fail(h, STG_ERR_UNSUPPORTED, "not built yet"); }
-int stg_shard_allgather(StgHandle h, void *) { return fail(h, STG_ERR_UNSUPPORTED, "not built yet"); }
-int stg_shard_finish(StgHandle h, const StgSampleBatch *, int32_t, void *) { return fail(h, STG_ERR_UNSUPPORTED, "not built yet"); }
-int stg_shard_gather_local(StgHandle h, const StgHandle *, int32_t, void *) { return fail(h, STG_ERR_UNSUPPORTED, "not built yet"); }
+int stg_spec_verify(StgHandle h, const StgSpecBatch *b, void *stream_)
+{
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (!h) return STG_ERR_INVALID_ARGUMENT;
+    if (!b || b->struct_size != (int32_t)sizeof(StgSpecBatch)) return fail(h, STG_ERR_INVALID_ARGUMENT, "bad StgSpecBatch");
+    const int S = b->n_seq, L = b->n_draft, V = b->vocab;
+    if (S < 0 || L < 0 || V <= 0) return fail(h, STG_ERR_INVALID_ARGUMENT, "n_seq, n_draft >= 0 and vocab > 0 are required");
+    if (S == 0) return STG_OK;
+    if (L > h->cfg.max_spec_draft) return fail(h, STG_ERR_CAPACITY, "n_draft exceeds max_spec_draft");
+    if ((int64_t)S * (L + 1) > h->cfg.max_rows) return fail(h, STG_ERR_CAPACITY, "n_seq * (n_draft + 1) exceeds max_rows");
+    if (V > h->cfg.max_vocab) return fail(h, STG_ERR_CAPACITY, "vocab exceeds max_vocab");
+    if (!b->target_logits || !b->params || !b->uniforms || !b->accepted || !b->correction || (L > 0 && !b->draft_tokens))
+        return fail(h, STG_ERR_INVALID_ARGUMENT, "a required array is null");
+    if (b->mode != 0 && b->mode != 1) return fail(h, STG_ERR_INVALID_ARGUMENT, "mode must be 0 or 1");
+    bool any_sampled = false;
+    for (int s = 0; s < S; s++) any_sampled |= b->params[s].temperature > 0.f;
+    if (b->mode == 0 && L > 0 && any_sampled && !b->draft_logits)
+        return fail(h, STG_ERR_INVALID_ARGUMENT, "draft_logits are required for the p/q accept rule");
+    if (b->mem_flags & STG_MEM_HOST_LOGITS) return fail(h, STG_ERR_UNSUPPORTED, "stg_spec_verify takes device logits");
+    CK(cudaSetDevice(h->cfg.device));
 
+    RowDist *tdist = (RowDist *)h->dists.p;
+    RowDist *ddist = tdist + (size_t)S * (L + 1);
+    // phase one: a distribution descriptor per target row, then per draft row
+    for (int which = 0; which < 2; which++) {
+        const int per = which == 0 ? L + 1 : L;
+        const void *logits = which == 0 ? b->target_logits : b->draft_logits;
+        if (per == 0 || logits == nullptr || (which == 1 && b->mode == 1)) continue;
+        std::vector<StgRowParams> params((size_t)S * per);
+        for (int s = 0; s < S; s++)
+            for (int i = 0; i < per; i++) params[(size_t)s * per + i] = b->params[s];
+        StgSampleBatch sb;
+        memset(&sb, 0, sizeof(sb));
+        sb.struct_size = sizeof(sb);
+        sb.rows = S * per; sb.vocab = V; sb.logits_dtype = b->logits_dtype; sb.logits = logits; sb.row_stride = V;
+        sb.params = params.data();
+        BatchExtra x;
+        x.mode = 2;
+        x.dists_out = which == 0 ? tdist : ddist;
+        int rc = run_batch(h, &sb, x, stream);
+        if (rc) return rc;
+    }
+    const void *p;
+    int rc = stage_in(h, b->draft_tokens, (size_t)S * L * 4, b->mem_flags & STG_MEM_HOST_DRAFT, h->sp_draft, stream, &p);
+    if (rc) return rc;
+    SpecArgs a;
+    memset(&a, 0, sizeof(a));
+    a.draft_tokens = (const int32_t *)p;
+    rc = stage_in(h, b->uniforms, (size_t)S * (L + 2) * 8, b->mem_flags & STG_MEM_HOST_UNIFORMS, h->sp_uniforms, stream, &p);
+    if (rc) return rc;
+    a.uniforms = (const double *)p;
+    const bool host_out = b->mem_flags & STG_MEM_HOST_OUTPUTS;
+    a.target = b->target_logits; a.draft = b->mode == 0 ? b->draft_logits : nullptr;
+    a.tdist = tdist; a.ddist = b->mode == 0 ? ddist : nullptr;
+    a.accepted = host_out ? (int32_t *)h->sp_accepted.p : b->accepted;
+    a.correction = host_out ? (int32_t *)h->sp_correction.p : b->correction;
+    a.accept_probs = b->accept_probs ? (host_out ? (float *)h->sp_aprobs.p : b->accept_probs) : nullptr;
+    a.seq_flags = b->seq_flags ? (host_out ? (uint32_t *)h->sp_flags.p : b->seq_flags) : nullptr;
+    a.p_min = b->p_min;
+    a.n_seq = S; a.n_draft = L; a.vocab = V; a.dtype = b->logits_dtype; a.mode = b->mode;
+    a.vec = rows_aligned2(b->target_logits, V, b->logits_dtype) &&
+            (!b->draft_logits || rows_aligned2(b->draft_logits, V, b->logits_dtype)) ? 4 : 1;
+    cudaError_t e = launch_spec_finish(a, stream);
+    if (e != cudaSuccess) return cuda_fail(h, e, "k_spec_finish launch");
+    h->stats.kernel_launches++;
+    h->stats.sequences_verified += S;
+    if (host_out) {
+        CK(cudaMemcpyAsync(b->accepted, a.accepted, (size_t)S * 4, cudaMemcpyDeviceToHost, stream));
+        CK(cudaMemcpyAsync(b->correction, a.correction, (size_t)S * 4, cudaMemcpyDeviceToHost, stream));
+        if (b->accept_probs) CK(cudaMemcpyAsync(b->accept_probs, a.accept_probs, (size_t)S * L * 4, cudaMemcpyDeviceToHost, stream));
+        if (b->seq_flags) CK(cudaMemcpyAsync(b->seq_flags, a.seq_flags, (size_t)S * 4, cudaMemcpyDeviceToHost, stream));
+        CK(cudaStreamSynchronize(stream));
+    }
+    return STG_OK;
 }
+
+int stg_mtp_accept(StgHandle h, const void *logits, int32_t dtype, int32_t rows, int32_t vocab, int64_t row_stride,
+                   const int32_t *draft, float p_min, int32_t *accept, int32_t *argmax, float *prob, void *stream)
+{
+    if (!h) return STG_ERR_INVALID_ARGUMENT;
+    if (!logits || !draft || !accept || rows < 0 || vocab <= 0 || row_stride < vocab)
+        return fail(h, STG_ERR_INVALID_ARGUMENT, "bad arguments to stg_mtp_accept");
+    if (dtype != STG_DTYPE_F32 && dtype != STG_DTYPE_BF16) return fail(h, STG_ERR_INVALID_ARGUMENT, "unknown logits_dtype");
+    if (rows == 0) return STG_OK;
+    CK(cudaSetDevice(h->cfg.device));
+    cudaError_t e = launch_mtp_accept(logits, dtype, rows, vocab, row_stride, rows_aligned2(logits, row_stride, dtype) ? 4 : 1,
+                                      draft, p_min, accept, argmax, prob, (cudaStream_t)stream);
+    if (e != cudaSuccess) return cuda_fail(h, e, "k_mtp_accept launch");
+    h->stats.kernel_launches++;
+    return STG_OK;
+}
+
+// ---- vocabulary-sharded mode ---------------------------------------------------------------------
+
+int stg_comm_unique_id(void *out_id128)
+{
+    std::string why;
+    if (!out_id128) return STG_ERR_INVALID_ARGUMENT;
+    if (!load_nccl(why)) return fail(nullptr, STG_ERR_NCCL, why);
+    NcclId id;
+    int rc = g_nccl.get_unique_id(&id);
+    if (rc != 0) return nccl_fail(nullptr, rc, "ncclGetUniqueId");
+    memcpy(out_id128, &id, sizeof(id));
+    return STG_OK;
+}
+
+int stg_comm_init(StgHandle h, const void *id128, int32_t rank, int32_t n_ranks)
+{
+    if (!h || !id128 || n_ranks < 1 || rank < 0 || rank >= n_ranks) return fail(h, STG_ERR_INVALID_ARGUMENT, "bad communicator arguments");
+    std::string why;
+    if (!load_nccl(why)) return fail(h, STG_ERR_NCCL, why);
+    CK(cudaSetDevice(h->cfg.device));
+    NcclId id;
+    memcpy(&id, id128, sizeof(id));
+    void *comm = nullptr;
+    int rc = g_nccl.comm_init_rank(&comm, n_ranks, id, rank);
+    if (rc != 0) return nccl_fail(h, rc, "ncclCommInitRank");
+    h->nccl_comm = comm;
+    h->rank = rank;
+    h->n_ranks = n_ranks;
+    return ensure_exchange(h, n_ranks);
+}
+
+int stg_comm_destroy(StgHandle h)
+{
+    if (h && h->nccl_comm && g_nccl.comm_destroy) {
+        g_nccl.comm_destroy(h->nccl_comm);
+        h->nccl_comm = nullptr;
+    }
+    return STG_OK;
+}
+
+int stg_shard_select(StgHandle h, const StgSampleBatch *b, int32_t vocab_offset, int32_t global_vocab, void *stream)
+{
+    if (!h) return STG_ERR_INVALID_ARGUMENT;
+    int rc = ensure_exchange(h, h->n_ranks);
+    if (rc) return rc;
+    BatchExtra x;
+    x.shard_mode = 1;
+    x.vocab_offset = vocab_offset;
+    x.global_vocab = global_vocab;
+    return run_batch(h, b, x, stream);
+}
+
+int stg_shard_allgather(StgHandle h, void *stream)
+{
+    if (!h) return STG_ERR_INVALID_ARGUMENT;
+    if (!h->nccl_comm) return fail(h, STG_ERR_NCCL, "stg_comm_init has not been called");
+    int rc = g_nccl.all_gather(h->xchg_local.p, h->xchg_gather.p, (size_t)h->shard_rows_used * h->shard_sel * 8, 1 /* ncclUint8 */,
+                               h->nccl_comm, (cudaStream_t)stream);
+    if (rc != 0) return nccl_fail(h, rc, "ncclAllGather(candidates)");
+    rc = g_nccl.all_gather(h->xchg_count_local.p, h->xchg_count_gather.p, (size_t)h->shard_rows_used * 4, 1, h->nccl_comm,
+                           (cudaStream_t)stream);
+    if (rc != 0) return nccl_fail(h, rc, "ncclAllGather(counts)");
+    return STG_OK;
+}
+
+int stg_shard_gather_local(StgHandle h, const StgHandle *peers, int32_t n_ranks, void *stream_)
+{
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (!h || !peers || n_ranks < 1) return STG_ERR_INVALID_ARGUMENT;
+    h->n_ranks = n_ranks;
+    int rc = ensure_exchange(h, n_ranks);
+    if (rc) return rc;
+    h->shard_rows_used = peers[0] ? peers[0]->shard_rows_used : 0;
+    const size_t lb = (size_t)h->shard_rows_used * h->shard_sel * 8, cb = (size_t)h->shard_rows_used * 4;
+    for (int r = 0; r < n_ranks; r++) {
+        StgHandle p = peers[r];
+        if (!p || p->shard_sel != h->shard_sel || p->shard_rows_used != h->shard_rows_used || !p->xchg_local.p)
+            return fail(h, STG_ERR_INVALID_ARGUMENT, "peer handles must share the capacities of this one");
+        CK(cudaMemcpyAsync((char *)h->xchg_gather.p + lb * r, p->xchg_local.p, lb, cudaMemcpyDeviceToDevice, stream));
+        CK(cudaMemcpyAsync((char *)h->xchg_count_gather.p + cb * r, p->xchg_count_local.p, cb, cudaMemcpyDeviceToDevice, stream));
+    }
+    return STG_OK;
+}
+
+int stg_shard_finish(StgHandle h, const StgSampleBatch *b, int32_t global_vocab, void *stream_)
+{
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (!h || !b) return STG_ERR_INVALID_ARGUMENT;
+    if (!h->xchg_gather.p) return fail(h, STG_ERR_INVALID_ARGUMENT, "nothing has been gathered");
+    // Re-plan with the same inputs as stg_shard_select (row paths, selection counts, pow table);
+    // only the arrays the finish reads are staged.
+    BatchExtra x;
+    x.shard_mode = 2;
+    x.global_vocab = global_vocab;
+    return run_batch(h, b, x, stream);
+}
+
+}  // extern "C"

@@ -53,6 +53,7 @@ struct RowDist {
     int32_t tie_idx_max;  // top-p: ties at tstar survive up to this token id
     uint32_t flags;       // kDist*
     float uniform_p;      // probability of every token when no logit is finite
+    int32_t argmax;       // arg-max of the raw row (distribution-only mode)
     float sum_end;        // last value of the sequential CDF (diagnostic)
 };
 enum : uint32_t {
@@ -85,6 +86,9 @@ struct SampleArgs {
     float *escratch;                 // per-CTA exp scratch rows [grid, escratch_stride]
     unsigned long long *keyscratch;  // per-CTA wide-nucleus key scratch [grid, key_stride]
     RowDist *dists;                  // per-row distribution descriptors (optional output)
+    unsigned long long *xchg_local;  // vocabulary-sharded mode: this rank's candidates [rows, xchg_stride]
+    int32_t *xchg_count;             // ... and how many each row has
+    int32_t xchg_stride;
     int64_t row_stride;
     int64_t mask_stride;
     int64_t escratch_stride;
@@ -95,7 +99,7 @@ struct SampleArgs {
     int32_t chunk_len;               // elements per chunk work item (multiple of kSubTile)
     int32_t cap;                     // entries per candidate buffer in shared memory
     int32_t vec;                     // 4: rows are 16-byte (fp32) / 8-byte (bf16) aligned
-    int32_t mode;                    // 0 sample, 1 build distribution only
+    int32_t mode;                    // 0 sample, 1 materialise distributions, 2 distribution descriptors only
     int32_t vocab_offset;            // vocabulary-sharded mode: global id of local column 0
     int32_t shard_mode;              // 0 off, 1 select only (write candidates), 2 finish from gather
     int32_t n_ranks;

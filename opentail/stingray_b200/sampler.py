@@ -328,6 +328,78 @@ class BatchSampler:
         return acc, am, pr
 
 
+    # -- vocabulary-sharded mode ---------------------------------------------------------------------
+    @staticmethod
+    def comm_unique_id() -> bytes:
+        """128 bytes identifying a new communicator; create on rank 0 and broadcast."""
+        buf = C.create_string_buffer(128)
+        rc = N.load().stg_comm_unique_id(buf)
+        if rc != N.STG_OK:
+            raise StingrayError(rc, "stg_comm_unique_id failed")
+        return buf.raw
+
+    def comm_init(self, unique_id: bytes, rank: int, n_ranks: int):
+        self._check(self._lib.stg_comm_init(self._h, unique_id, rank, n_ranks))
+
+    def shard_select(self, logits, params, vocab_offset: int, global_vocab: int, *, history_ids=None,
+                     history_offsets=None, mask=None, uniforms=None, stream=None):
+        """Selects this rank's candidates over its vocabulary slice (``stg_shard_select``)."""
+        b, keep = self._batch(logits, params, history_ids, history_offsets, mask, None, None, uniforms)
+        self._check(self._lib.stg_shard_select(self._h, C.byref(b), vocab_offset, global_vocab,
+                                               self._stream(stream)))
+
+    def shard_allgather(self, stream=None):
+        self._check(self._lib.stg_shard_allgather(self._h, self._stream(stream)))
+
+    def shard_gather_local(self, peers: "Sequence[BatchSampler]", stream=None):
+        arr = (C.c_void_p * len(peers))(*[p._h for p in peers])
+        self._check(self._lib.stg_shard_gather_local(self._h, arr, len(peers), self._stream(stream)))
+
+    def shard_finish(self, rows: int, local_vocab: int, params, global_vocab: int, *, history_ids=None,
+                     history_offsets=None, uniforms=None, want_probs=False, want_flags=False,
+                     want_topk=0, stream=None):
+        """Merges the gathered candidates and finishes every row (``stg_shard_finish``)."""
+        import torch
+
+        pa = params_array(params)
+        b = N.StgSampleBatch()
+        b.struct_size = C.sizeof(N.StgSampleBatch)
+        b.rows, b.vocab, b.logits_dtype, b.row_stride = rows, local_vocab, N.DTYPE_F32, local_vocab
+        b.params = pa.ctypes.data
+        keep = [pa]
+        flags = 0
+        if history_ids is not None:
+            ho = np.ascontiguousarray(history_offsets, dtype=np.int32)
+            if not _is_torch(history_ids):
+                history_ids = np.ascontiguousarray(history_ids, dtype=np.int32)
+                flags |= N.MEM_HOST_HISTORY
+            keep += [ho, history_ids]
+            b.history_ids, b.history_offsets = _ptr(history_ids), ho.ctypes.data
+        if uniforms is not None:
+            if not _is_torch(uniforms):
+                uniforms = np.ascontiguousarray(uniforms, dtype=np.float32)
+                flags |= N.MEM_HOST_UNIFORMS
+            keep.append(uniforms)
+            b.uniforms = _ptr(uniforms)
+        b.mem_flags = flags
+        out = {"tokens": self._alloc((rows,), np.int32, False)}
+        b.tokens = _ptr(out["tokens"])
+        if want_probs:
+            out["probs"] = self._alloc((rows,), np.float32, False)
+            b.token_probs = _ptr(out["probs"])
+        if want_flags:
+            out["flags"] = self._alloc((rows,), np.uint32, False)
+            b.row_flags = _ptr(out["flags"])
+        if want_topk:
+            out["topk_ids"] = self._alloc((rows, want_topk), np.int32, False)
+            out["topk_logits"] = self._alloc((rows, want_topk), np.float32, False)
+            out["topk_probs"] = self._alloc((rows, want_topk), np.float32, False)
+            b.topk_ids, b.topk_logits = _ptr(out["topk_ids"]), _ptr(out["topk_logits"])
+            b.topk_probs, b.topk_stride = _ptr(out["topk_probs"]), want_topk
+        self._check(self._lib.stg_shard_finish(self._h, C.byref(b), global_vocab, self._stream(stream)))
+        return out
+
+
 _shared: Dict[int, BatchSampler] = {}
 
 
