@@ -195,6 +195,11 @@ STG_API int stg_abi_version(void);
  * nvrtcGetProgramLogSize + nvrtcGetProgramLog (NvrtcInterop.cs:268-272). */
 STG_API size_t stg_last_error(StgHandle handle, char *buf, size_t buf_len);
 STG_API int stg_get_stats(StgHandle handle, StgStats *out);
+/* Diagnostic: per work item of the last sampling step, 32 device time stamps (nanoseconds) taken at
+ * the boundaries of its phases.  Only recorded when the handle was created with STG_PHASE_TICKS=1
+ * in the environment; blocks.  The reference's counterpart is its env-gated Stopwatch buckets
+ * (src/OpenTail.Stingray.Engine/DecodeProfileTimers.cs:17-67). */
+STG_API int stg_debug_phase_ticks(StgHandle handle, uint64_t *out, int32_t max_items, int32_t *n_items);
 
 /* ---- the hot path ------------------------------------------------------------------------------- */
 

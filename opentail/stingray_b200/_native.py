@@ -17,7 +17,7 @@ MEM_HOST_LOGITS, MEM_HOST_HISTORY, MEM_HOST_MASK, MEM_HOST_BIAS = 1, 2, 4, 8
 MEM_HOST_UNIFORMS, MEM_HOST_OUTPUTS, MEM_HOST_DRAFT = 16, 32, 64
 
 EXPORTS = [
-    "stg_abi_version", "stg_create", "stg_destroy", "stg_last_error", "stg_get_stats",
+    "stg_abi_version", "stg_create", "stg_destroy", "stg_last_error", "stg_get_stats", "stg_debug_phase_ticks",
     "stg_argmax_rows", "stg_argmax_rows_static", "stg_sample_rows", "stg_build_distribution", "stg_spec_verify",
     "stg_mtp_accept", "stg_comm_unique_id", "stg_comm_init", "stg_comm_destroy",
     "stg_shard_select", "stg_shard_allgather", "stg_shard_finish", "stg_shard_gather_local",
@@ -90,6 +90,7 @@ def load() -> C.CDLL:
     lib.stg_last_error.restype = C.c_size_t
     lib.stg_last_error.argtypes = [vp, C.c_char_p, C.c_size_t]
     lib.stg_get_stats.argtypes = [vp, C.POINTER(StgStats)]
+    lib.stg_debug_phase_ticks.argtypes = [vp, vp, i32, C.POINTER(C.c_int32)]
     lib.stg_argmax_rows.argtypes = [vp, vp, i32, i32, i32, i64, vp, vp]
     lib.stg_argmax_rows_static.argtypes = [vp, i32, i32, i32, i64, vp, vp]
     lib.stg_sample_rows.argtypes = [vp, C.POINTER(StgSampleBatch), vp]

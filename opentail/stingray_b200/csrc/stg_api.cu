@@ -3,6 +3,7 @@
 #include <cuda_runtime.h>
 #include <math.h>
 #include <stdint.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <algorithm>
@@ -60,6 +61,7 @@ struct Plan {
     int chunk_len = 0;
     int cap = kSubTile + 1;
     bool any_row_item = false;
+    int n_row_items = 0;
     size_t smem = 0;
     uint64_t n_greedy = 0, n_topk = 0, n_full = 0;
 };
@@ -126,10 +128,10 @@ int make_plan(StgHandle h, const StgSampleBatch *b, int mode, bool shard, int gl
         } else {
             rp.path = kPathFull;
         }
-        if (rp.path == kPathFull) {
+        if (rp.path == kPathFull || rp.path == kPathGreedyPen) {
             if (p.top_k > 4096 && p.top_k < GV)
                 return fail(h, STG_ERR_UNSUPPORTED, "top_k above 4096 on the full-vocabulary path");
-            if (hlen + blen > kMaxOverride) return fail(h, STG_ERR_CAPACITY, "history + bias entries exceed 16384");
+            if (hlen + blen > kMaxOverride) return fail(h, STG_ERR_CAPACITY, "history + bias entries exceed 2048 on the full-vocabulary path");
         }
         if (shard && !(rp.path == kPathTopK || rp.path == kPathGreedy))
             return fail(h, STG_ERR_UNSUPPORTED, "vocabulary-sharded mode supports top-k and plain greedy rows only");
@@ -141,7 +143,7 @@ int make_plan(StgHandle h, const StgSampleBatch *b, int mode, bool shard, int gl
     // chunking: enough chunk items to balance the SMs, whole 4096-element sub-tiles per chunk
     int S = 1;
     if (n_chunk_rows > 0) {
-        int want = (4 * h->sm_count + n_chunk_rows - 1) / n_chunk_rows;
+        int want = (2 * h->sm_count + n_chunk_rows - 1) / n_chunk_rows;  // about two items per SM
         int max_s = std::max(1, (V + 16383) / 16384);
         S = std::max(1, std::min({want, max_s, 64}));
         if (shard) S = std::min(S, 16);
@@ -151,7 +153,7 @@ int make_plan(StgHandle h, const StgSampleBatch *b, int mode, bool shard, int gl
         int n_chunks = (V + pl.chunk_len - 1) / pl.chunk_len;
         size_t need = 0;
         for (auto &rp : pl.rows)
-            if (mode == 0 && (rp.path == kPathGreedy || rp.path == kPathTopK)) need += (size_t)n_chunks * (size_t)rp.sel;
+            if (mode == 0 && (rp.path == kPathGreedy || rp.path == kPathTopK)) need += (size_t)n_chunks * 2 * (size_t)rp.sel;
         if (n_chunks == 1 || need <= h->cand_entries) { S = n_chunks; break; }
         S = std::max(1, S / 2);
     }
@@ -162,18 +164,19 @@ int make_plan(StgHandle h, const StgSampleBatch *b, int mode, bool shard, int gl
             rp.n_chunks = S;
             rp.cand_off = cand_off;
             rp.slot = slot;
-            cand_off += S * rp.sel;
+            cand_off += S * 2 * rp.sel;
             slot += S;
         }
     }
     for (int r = 0; r < rows; r++)
         if (pl.rows[r].n_chunks == 0) pl.items.push_back({r, -1});
+    pl.n_row_items = (int)pl.items.size();
     for (int r = 0; r < rows; r++)
         for (int c = 0; c < pl.rows[r].n_chunks; c++) pl.items.push_back({r, c});
-    pl.cap = max_sel + kSubTile;
-    pl.smem = (size_t)pl.cap * 16;
-    if (pl.any_row_item) pl.smem = std::max(pl.smem, kRowArenaBytes);
-    pl.smem = std::max<size_t>(pl.smem, 1024);
+    // room for two 4096-element sub-tiles beyond the selection when shared memory allows it: fewer compactions
+    pl.cap = max_sel + 2 * kSubTile;
+    if ((size_t)pl.cap * 16 > h->smem_optin) pl.cap = max_sel + kSubTile;
+    pl.smem = std::max<size_t>((size_t)pl.cap * 16, 1024);  // chunk kernel; the row kernel has a fixed arena
     return STG_OK;
 }
 
@@ -278,7 +281,7 @@ int run_batch(StgHandle h, const StgSampleBatch *b, const BatchExtra &x, void *s
     Plan pl;
     rc = make_plan(h, b, mode, x.shard_mode != 0, x.global_vocab, pl);
     if (rc) return rc;
-    if (pl.smem > h->smem_optin) return fail(h, STG_ERR_CAPACITY, "shared memory needed exceeds the device limit");
+    if (pl.smem > h->smem_optin || kRowArenaBytes > h->smem_optin) return fail(h, STG_ERR_CAPACITY, "shared memory needed exceeds the device limit");
     const RowPlan *d_rows; const WorkItem *d_items; const float *d_pow;
     rc = upload_plan(h, pl, stream, &d_rows, &d_items, &d_pow);
     if (rc) return rc;
@@ -346,6 +349,8 @@ int run_batch(StgHandle h, const StgSampleBatch *b, const BatchExtra &x, void *s
     a.cand_count = (int32_t *)h->cand_count.p;
     a.tickets = (uint32_t *)h->tickets.p;
     a.work_counter = (uint32_t *)h->work_counter.p;
+    a.phase_ticks = (unsigned long long *)h->ticks.p;
+    h->ticks_items = (int)pl.items.size();
     a.escratch = (float *)h->escratch.p;
     a.keyscratch = (unsigned long long *)h->keyscratch.p;
     a.dists = x.dists_out;
@@ -379,15 +384,45 @@ int run_batch(StgHandle h, const StgSampleBatch *b, const BatchExtra &x, void *s
         }
         return STG_OK;
     }
-    const int grid = std::min(a.n_items, h->sm_count);
-    cudaError_t e = launch_sample(a, grid, pl.smem, stream);
+    // two persistent kernels: the row items (long, one SM each) on a high-priority side stream so
+    // that they take their SMs first, the chunk items on the caller's stream beside them
+    const int n_rows_items = pl.n_row_items, n_chunk_items = (int)pl.items.size() - pl.n_row_items;
+    cudaError_t e = cudaSuccess;
+    const bool both = n_rows_items > 0 && n_chunk_items > 0;
+    if (both) {
+        e = cudaEventRecord(h->ev_fork, stream);
+        if (e == cudaSuccess) e = cudaStreamWaitEvent(h->aux_stream, h->ev_fork, 0);
+    }
+    int launches = 0;
+    if (e == cudaSuccess && n_rows_items > 0) {
+        SampleArgs r = a;
+        r.n_items = n_rows_items;
+        r.item_base = 0;
+        r.work_counter = (uint32_t *)h->work_counter.p + 1;
+        r.work_base = h->work_base_rows;
+        const int grid = std::min(n_rows_items, h->sm_count);
+        e = launch_sample_rows(r, grid, both ? h->aux_stream : stream);
+        if (e == cudaSuccess) { h->work_base_rows += (uint32_t)n_rows_items + (uint32_t)grid; launches++; }
+        if (e == cudaSuccess && both) e = cudaEventRecord(h->ev_join, h->aux_stream);
+    }
+    if (e == cudaSuccess && n_chunk_items > 0) {
+        SampleArgs c = a;
+        c.items = a.items + n_rows_items;
+        c.n_items = n_chunk_items;
+        c.item_base = n_rows_items;
+        const int grid = std::min(n_chunk_items, h->sm_count);
+        e = launch_sample_chunks(c, grid, pl.smem, stream);
+        if (e == cudaSuccess) { h->work_base += (uint32_t)n_chunk_items + (uint32_t)grid; launches++; }
+    }
+    if (e == cudaSuccess && both) e = cudaStreamWaitEvent(stream, h->ev_join, 0);
     if (e != cudaSuccess) {
-        cudaMemsetAsync(h->work_counter.p, 0, 4, stream);
+        cudaMemsetAsync(h->work_counter.p, 0, 8, stream);
         cudaMemsetAsync(h->tickets.p, 0, h->tickets.bytes, stream);
         h->work_base = 0;
-        return cuda_fail(h, e, "k_sample launch");
+        h->work_base_rows = 0;
+        return cuda_fail(h, e, "sampling kernel launch");
     }
-    h->work_base += (uint32_t)a.n_items + (uint32_t)grid;
+    h->stats.kernel_launches += launches - 1;  // the call below counts one
     h->stats.calls++;
     h->stats.kernel_launches++;
     h->stats.rows_sampled += rows;
@@ -439,7 +474,7 @@ int stg_create(const StgConfig *cfg, StgHandle *out)
     h->smem_optin = prop.sharedMemPerBlockOptin > 4096 ? prop.sharedMemPerBlockOptin - 4096 : 0;
     const size_t R = (size_t)cfg->max_rows, V = (size_t)cfg->max_vocab;
     const size_t sel_max = std::max<size_t>(1, (size_t)cfg->max_top_k + cfg->max_history);
-    h->cand_entries = R * std::max<size_t>(4 * sel_max, 64);
+    h->cand_entries = R * std::max<size_t>(8 * sel_max, 64);
     h->escratch_stride = (int64_t)round_up(V + 8, 64);
     h->key_stride = (int64_t)round_up(V + 8, 64);
     h->plan_bytes_cap = round_up(R * sizeof(RowPlan), 256) + round_up((R * 65) * sizeof(WorkItem), 256) +
@@ -462,6 +497,7 @@ int stg_create(const StgConfig *cfg, StgHandle *out)
     A(h->o_tokens, R * 4); A(h->o_probs, R * 4); A(h->o_flags, R * 4);
     const size_t tk = R * std::max<size_t>(cfg->max_top_k, 1) * 4;
     A(h->o_topk_ids, tk); A(h->o_topk_vals, tk); A(h->o_topk_probs, tk);
+    if (getenv("STG_PHASE_TICKS") && getenv("STG_PHASE_TICKS")[0] == '1') A(h->ticks, R * 65 * 32 * 8);
     if (cfg->max_spec_draft > 0) {
         const size_t L = (size_t)cfg->max_spec_draft;
         A(h->sp_draft, R * L * 4); A(h->sp_uniforms, R * (L + 2) * 8);
@@ -471,6 +507,14 @@ int stg_create(const StgConfig *cfg, StgHandle *out)
     if (rc == STG_OK) {
         e = cudaHostAlloc((void **)&h->plan_host, h->plan_bytes_cap * 4, cudaHostAllocDefault);
         if (e != cudaSuccess) rc = cuda_fail(nullptr, e, "cudaHostAlloc");
+    }
+    if (rc == STG_OK) {
+        int lo = 0, hi = 0;
+        cudaDeviceGetStreamPriorityRange(&lo, &hi);
+        e = cudaStreamCreateWithPriority(&h->aux_stream, cudaStreamNonBlocking, hi);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->ev_fork, cudaEventDisableTiming);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->ev_join, cudaEventDisableTiming);
+        if (e != cudaSuccess) rc = cuda_fail(nullptr, e, "side stream");
     }
     for (int i = 0; i < 4 && rc == STG_OK; i++) {
         e = cudaEventCreateWithFlags(&h->plan_ev[i], cudaEventDisableTiming);
@@ -498,12 +542,15 @@ int stg_destroy(StgHandle h)
     stg_comm_destroy(h);
     DevBuf *all[] = {&h->plan_dev, &h->cand, &h->cand_count, &h->tickets, &h->work_counter, &h->escratch, &h->keyscratch,
                      &h->dists, &h->st_hist, &h->st_bias_ids, &h->st_bias_vals, &h->st_uniforms, &h->st_mask, &h->st_logits,
-                     &h->o_tokens, &h->o_probs, &h->o_flags, &h->o_topk_ids, &h->o_topk_vals, &h->o_topk_probs, &h->o_pairs,
+                     &h->o_tokens, &h->o_probs, &h->o_flags, &h->o_topk_ids, &h->o_topk_vals, &h->o_topk_probs, &h->o_pairs, &h->ticks,
                      &h->sp_draft, &h->sp_uniforms, &h->sp_accepted, &h->sp_correction, &h->sp_aprobs, &h->sp_flags,
                      &h->sp_rowstats, &h->xchg_local, &h->xchg_gather, &h->xchg_count_local, &h->xchg_count_gather};
     for (DevBuf *b : all) dev_free(*b);
     if (h->plan_host) cudaFreeHost(h->plan_host);
     for (auto &ev : h->plan_ev) if (ev) cudaEventDestroy(ev);
+    if (h->ev_fork) cudaEventDestroy(h->ev_fork);
+    if (h->ev_join) cudaEventDestroy(h->ev_join);
+    if (h->aux_stream) cudaStreamDestroy(h->aux_stream);
     delete h;
     return STG_OK;
 }
@@ -517,6 +564,18 @@ size_t stg_last_error(StgHandle h, char *buf, size_t len)
         buf[n] = 0;
     }
     return s.size() + 1;
+}
+
+int stg_debug_phase_ticks(StgHandle h, uint64_t *out, int32_t max_items, int32_t *n_items)
+{
+    if (!h || !out || !n_items) return STG_ERR_INVALID_ARGUMENT;
+    if (!h->ticks.p) return fail(h, STG_ERR_UNSUPPORTED, "create the handle with STG_PHASE_TICKS=1 in the environment");
+    CK(cudaSetDevice(h->cfg.device));
+    CK(cudaDeviceSynchronize());
+    const int n = std::min(max_items, h->ticks_items);
+    CK(cudaMemcpy(out, h->ticks.p, (size_t)n * 32 * 8, cudaMemcpyDeviceToHost));
+    *n_items = n;
+    return STG_OK;
 }
 
 int stg_get_stats(StgHandle h, StgStats *out)

@@ -1,0 +1,368 @@
+// Segment-parallel form of the sequential-fp32-sum emulation (see stg_emul.cuh for the arithmetic).
+//
+// The sequence is cut into sub-tiles of 256 elements.  All warps first reduce their sub-tiles to a
+// plain sum; a block scan (fp64) of those gives, for every sub-tile, a good guess of the binade the
+// running sum is in when the sequential loop reaches it.  All warps then reduce each sub-tile to
+// its composite increment (for an even / odd start) under that guess.  One warp finally walks the
+// sub-tiles in order with the EXACT running sum: a sub-tile whose composite keeps the sum inside
+// the binade it was computed for (and below the target) is consumed whole - 32 of them per warp
+// scan - and only a sub-tile in which the sum leaves its binade, meets the target, or was guessed
+// wrongly is replayed with real fp32 additions, one element after the other.  The result is
+// bit-identical to the one-by-one loop; the guesses only decide how much is replayed.
+//
+// Per element the hot phases cost a handful of instructions: with u = 2^(E-23) the unit of the
+// running sum, the increment of x is rint(x / u) (round-half-even, one multiply by a power of two
+// and one convert), and exact ties - where the parity of the running sum decides - are detected
+// by their fraction of exactly one half and handled on a slow path.
+#pragma once
+#include "stg_emul.cuh"
+
+namespace stg {
+
+constexpr int kSub = 256;           // elements per sub-tile (8 consecutive per lane)
+constexpr int kMaxSubTiles = 1024;  // => sequences of up to 262144 elements
+
+struct Emul2Work {                  // lives in dynamic shared memory (20 KB)
+    double sums[kMaxSubTiles];      // sum of each sub-tile
+    int comp[kMaxSubTiles][2];      // composite increment under the guessed binade: even / odd start
+    int guess[kMaxSubTiles];        // guessed biased exponent of the running sum at the sub-tile
+};
+
+struct Emul2Ctl {
+    double wsum[32];
+    float s;
+    int hit;
+    int abort_at;                   // sub-tile that needed a replay the caller had forbidden, or -1
+};
+
+// increment of x (>= 0) in units of 1/scale, for an even (d0) and an odd (d1) running sum
+__device__ __forceinline__ void unit_incr_fast(float x, float scale, int &d0, int &d1, bool &tie)
+{
+    const float xs = x * scale;            // exact: scale is a power of two
+    int d = __float2int_rn(xs);            // round half to even, saturating
+    d = d > (1 << 24) ? (1 << 24) : d;
+    const float tr = truncf(xs);
+    tie = (xs - tr) == 0.5f;               // exact below 2^24; 0 above
+    d0 = d;
+    d1 = tie ? 2 * (int)tr + 1 - d : d;
+}
+
+__device__ __forceinline__ int exp_of_double(double v)
+{
+    if (!(v > 0.0)) return 1;
+    int e = ilogb(v) + 127;
+    return e < 1 ? 1 : (e > 254 ? 254 : e);
+}
+
+__device__ __forceinline__ long long target_units(float target, bool has_target, int eb)
+{
+    if (!has_target) return LLONG_MAX;
+    if (eb >= 24) {
+        const float ts = target * __int_as_float((277 - eb) << 23);  // target * 2^(150-eb)
+        return ts >= 33554432.f ? (1ll << 25) : (long long)__float2int_ru(ts);
+    }
+    double td = ceil(ldexp((double)target, 150 - eb));
+    return td >= 1073741824.0 ? (1ll << 30) : (td <= -1073741824.0 ? -(1ll << 30) : (long long)td);
+}
+
+// composite of one sub-tile (8 consecutive elements per lane) under binade `eb`; all lanes get it.
+// FORCE: a tie inside the sub-tile makes the composite "unknown" (saturated), which forces a replay.
+template <bool FORCE>
+__device__ __forceinline__ void subtile_composite(const float x[8], int eb, int &r0, int &r1)
+{
+    if (eb >= 24) {
+        // common case first: no element is an exact tie, so the increment does not depend on the
+        // parity of the running sum and the composite is a plain integer sum
+        const float scale = __int_as_float((277 - eb) << 23);
+        int a = 0;
+        bool any_tie = false;
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const float xs = x[j] * scale;
+            a += min(__float2int_rn(xs), 1 << 24);
+            any_tie |= (xs - truncf(xs)) == 0.5f;
+        }
+        a = min(a, 1 << 24);
+        if (__ballot_sync(0xFFFFFFFFu, any_tie) == 0u) {
+            r0 = r1 = __reduce_add_sync(0xFFFFFFFFu, a);
+            return;
+        }
+    }
+    if (FORCE) { r0 = r1 = 1 << 28; return; }
+    int a0 = 0, a1 = 0;
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        int d0, d1;
+        unit_incr(x[j], eb, d0, d1);
+        a0 += (a0 & 1) ? d1 : d0;
+        a1 += ((1 + a1) & 1) ? d1 : d0;
+    }
+    a0 = min(a0, 1 << 24);
+    a1 = min(a1, 1 << 24);
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        int p0 = __shfl_down_sync(0xFFFFFFFFu, a0, o);
+        int p1 = __shfl_down_sync(0xFFFFFFFFu, a1, o);
+        int n0, n1;
+        comp(a0, a1, p0, p1, n0, n1);
+        a0 = n0; a1 = n1;  // only lane 0's chain is meaningful
+    }
+    r0 = __shfl_sync(0xFFFFFFFFu, a0, 0);
+    r1 = __shfl_sync(0xFFFFFFFFu, a1, 0);
+}
+
+// Replays one sub-tile exactly (one warp, 8 consecutive elements per lane).  Lanes are consumed in
+// order: a warp scan of the lanes' composites under the current binade finds the first lane in which
+// the sum leaves the binade or meets the target; the lanes before it are taken whole, that lane
+// adds its 8 elements with real fp32 additions, and the scan restarts behind it in the new binade.
+// `s` is the exact running sum before the sub-tile; returns the hit index or -1.
+template <bool POS_ONLY>
+__device__ __forceinline__ int replay_subtile(const float x[8], int base, int n, float target, bool has_target,
+                                              float &s)
+{
+    const int lane = threadIdx.x & 31;
+    const int g0 = base + lane * 8;
+    int start_lane = 0;
+    for (;;) {
+        const uint32_t sb = __float_as_uint(s);
+        const int ef = (int)(sb >> 23) & 255;
+        const int eb = ef ? ef : 1;
+        const int sint = (int)((sb & 0x7FFFFFu) | (ef ? 0x800000u : 0u));
+        if (ef == 255) return -1;
+        const long long tint = target_units(target, has_target, eb);
+        int a0 = 0, a1 = 0;
+        if (lane >= start_lane) {
+            if (eb >= 24) {
+                const float scale = __int_as_float((277 - eb) << 23);
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    int d0, d1;
+                    bool tie;
+                    const float v = (g0 + j < n && (!POS_ONLY || x[j] > 0.f)) ? x[j] : 0.f;
+                    unit_incr_fast(v, scale, d0, d1, tie);
+                    a0 += (a0 & 1) ? d1 : d0;
+                    a1 += ((1 + a1) & 1) ? d1 : d0;
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    int d0, d1;
+                    const float v = (g0 + j < n && (!POS_ONLY || x[j] > 0.f)) ? x[j] : 0.f;
+                    unit_incr(v, eb, d0, d1);
+                    a0 += (a0 & 1) ? d1 : d0;
+                    a1 += ((1 + a1) & 1) ? d1 : d0;
+                }
+            }
+            a0 = min(a0, 1 << 25);
+            a1 = min(a1, 1 << 25);
+        }
+        int i0 = a0, i1 = a1;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            int p0 = __shfl_up_sync(0xFFFFFFFFu, i0, o);
+            int p1 = __shfl_up_sync(0xFFFFFFFFu, i1, o);
+            if (lane >= o) { int r0, r1; comp(p0, p1, i0, i1, r0, r1); i0 = r0; i1 = r1; }
+        }
+        const int S = sat_add(sint, (sint & 1) ? i1 : i0);  // sum after lanes 0 .. lane
+        // a target that is already met fires at the first element still to come
+        const bool fire = lane >= start_lane && (S >= (1 << 24) || (long long)S >= tint);
+        const unsigned fm = __ballot_sync(0xFFFFFFFFu, fire);
+        if (fm == 0u) {
+            const int send = __shfl_sync(0xFFFFFFFFu, S, 31);
+            s = ldexpf((float)send, eb - 150);
+            return -1;
+        }
+        const int L = __ffs(fm) - 1;
+        int sprev = __shfl_sync(0xFFFFFFFFu, S, L > 0 ? L - 1 : 0);
+        if (L == 0) sprev = sint;
+        float acc = ldexpf((float)sprev, eb - 150);
+        int hit = -1;
+        if (lane == L) {
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                if (g0 + j < n && (!POS_ONLY || x[j] > 0.f) && hit < 0) {
+                    acc = __fadd_rn(acc, x[j]);
+                    if (has_target && acc >= target) hit = g0 + j;
+                }
+            }
+        }
+        s = __shfl_sync(0xFFFFFFFFu, acc, L);
+        hit = __shfl_sync(0xFFFFFFFFu, hit, L);
+        if (hit >= 0) return hit;
+        start_lane = L + 1;
+        if (start_lane >= 32) return -1;
+    }
+}
+
+// Same contract as emul_scan (stg_emul.cuh), for n <= kSub * kMaxSubTiles.  `Prov::load` may have
+// side effects and is called exactly once per element; `Prov::reload` must be pure.
+// FORCE: the elements are only partially ordered (ordered between groups, arbitrary inside a
+// group): any sub-tile that needs its internal order - a replay, or a parity tie - is checked
+// against replay_ok[sub-tile]; when that says 0 the scan stops and returns -2 with the sub-tile in
+// c->abort_at, so that the caller can order that part and run again.
+template <class Prov, bool POS_ONLY, bool FORCE, int UN = 2>
+__device__ int emul_scan2(Emul2Ctl *c, Emul2Work *wk, const Prov &pv, int n, float target, bool has_target,
+                          float *sum_out, const unsigned char *replay_ok, unsigned long long *tk)
+{
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int nsub = (n + kSub - 1) / kSub;
+    __syncthreads();
+    // phase A: sum of every sub-tile (4 sub-tiles per warp in flight)
+    constexpr int W = kThreads / 32;
+    for (int t = warp; t < nsub; t += UN * W) {
+        float x[UN][8];
+#pragma unroll
+        for (int h = 0; h < UN; h++)
+            if (t + h * W < nsub) pv.load((t + h * W) * kSub + lane * 8, n, x[h]);
+#pragma unroll
+        for (int h = 0; h < UN; h++) {
+            if (t + h * W < nsub) {
+                float acc = 0.f;
+#pragma unroll
+                for (int j = 0; j < 8; j++) acc += (x[h][j] > 0.f) ? x[h][j] : 0.f;
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
+                if (lane == 0) wk->sums[t + h * W] = (double)acc;  // a guess only needs float accuracy
+            }
+        }
+    }
+    __syncthreads();
+    tick(tk, 0);
+    // phase B: exclusive prefix of the sub-tile sums -> guessed binade per sub-tile
+    {
+        double v = tid < nsub ? wk->sums[tid] : 0.0;
+        double inc = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            double t = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+            if (lane >= o) inc += t;
+        }
+        if (lane == 31) c->wsum[warp] = inc;
+        __syncthreads();
+        if (warp == 0) {
+            double w = c->wsum[lane];
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                double t = __shfl_up_sync(0xFFFFFFFFu, w, o);
+                if (lane >= o) w += t;
+            }
+            c->wsum[lane] = w;
+        }
+        __syncthreads();
+        double excl = inc - v + (warp ? c->wsum[warp - 1] : 0.0);
+        if (tid < nsub) wk->guess[tid] = exp_of_double(excl);
+    }
+    __syncthreads();
+    tick(tk, 1);
+    // phase C: composite of every sub-tile under its guessed binade
+    for (int t = warp; t < nsub; t += UN * W) {
+        float x[UN][8];
+        bool z[UN];
+#pragma unroll
+        for (int h = 0; h < UN; h++) {
+            const int tt = t + h * W;
+            z[h] = tt >= nsub || wk->sums[tt] == 0.0;  // nothing to add: composite 0
+            if (!z[h]) pv.reload(tt * kSub + lane * 8, n, x[h]);
+        }
+#pragma unroll
+        for (int h = 0; h < UN; h++) {
+            const int tt = t + h * W;
+            if (tt < nsub) {
+                int a0 = 0, a1 = 0;
+                if (!z[h]) {
+                    if (POS_ONLY) {
+#pragma unroll
+                        for (int j = 0; j < 8; j++) x[h][j] = x[h][j] > 0.f ? x[h][j] : 0.f;
+                    }
+                    subtile_composite<FORCE>(x[h], wk->guess[tt], a0, a1);
+                }
+                if (lane == 0) { wk->comp[tt][0] = a0; wk->comp[tt][1] = a1; }
+            }
+        }
+    }
+    __syncthreads();
+    tick(tk, 2);
+    // phase D: one warp walks the sub-tiles with the exact sum
+    if (warp == 0) {
+        float s = 0.f;
+        int hit = -1;
+        int t = 0;
+        int abort_at = -1;
+        int n_iter = 0, n_replay = 0;
+        while (t < nsub && hit < 0) {
+            n_iter++;
+            const uint32_t sb = __float_as_uint(s);
+            const int ef = (int)(sb >> 23) & 255;
+            const int eb = ef ? ef : 1;
+            const int sint = (int)((sb & 0x7FFFFFu) | (ef ? 0x800000u : 0u));
+            if (ef == 255) break;  // inf / NaN: nothing changes any more
+            const long long tint = target_units(target, has_target, eb);
+            // lane l proposes sub-tile t + l
+            const int tt = t + lane;
+            int a0 = 0, a1 = 0;
+            bool valid = false;
+            if (tt < nsub) {
+                a0 = wk->comp[tt][0];
+                a1 = wk->comp[tt][1];
+                valid = (wk->guess[tt] == eb) || (a0 == 0 && a1 == 0 && wk->sums[tt] == 0.0);
+            }
+            int i0 = a0, i1 = a1;
+            if (__any_sync(0xFFFFFFFFu, a0 != a1)) {
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    int p0 = __shfl_up_sync(0xFFFFFFFFu, i0, o);
+                    int p1 = __shfl_up_sync(0xFFFFFFFFu, i1, o);
+                    if (lane >= o) { int r0, r1; comp(p0, p1, i0, i1, r0, r1); i0 = r0; i1 = r1; }
+                }
+            } else {
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    int p0 = __shfl_up_sync(0xFFFFFFFFu, i0, o);
+                    if (lane >= o) i0 = sat_add(i0, p0);
+                }
+                i1 = i0;
+            }
+            const int S = sat_add(sint, (sint & 1) ? i1 : i0);  // sum after sub-tiles t .. t+lane
+            const bool bad = tt >= nsub || !valid || S >= (1 << 24) || (long long)S >= tint;
+            const unsigned badmask = __ballot_sync(0xFFFFFFFFu, bad);
+            const int ok = badmask ? __ffs(badmask) - 1 : 32;  // sub-tiles consumed whole
+            if (ok > 0) {
+                const int send = __shfl_sync(0xFFFFFFFFu, S, ok - 1);
+                s = ldexpf((float)send, eb - 150);
+                t += ok;
+            }
+            if (ok < 32 && t < nsub) {
+                if (FORCE && replay_ok != nullptr && !replay_ok[t]) { abort_at = t; break; }
+                float x[8];
+                pv.reload(t * kSub + lane * 8, n, x);
+                hit = replay_subtile<POS_ONLY>(x, t * kSub, n, target, has_target, s);
+                t += 1;
+                n_replay++;
+            }
+        }
+        if (lane == 0) { c->s = s; c->hit = abort_at >= 0 ? -2 : hit; c->abort_at = abort_at; }
+        tick(tk, 3);
+        if (tk && lane == 0) { tk[4] = (unsigned long long)n_iter; tk[5] = (unsigned long long)n_replay; }
+    }
+    __syncthreads();
+    if (sum_out) *sum_out = c->s;
+    const int h = c->hit;
+    __syncthreads();
+    return h;
+}
+
+// picks the segment-parallel form whenever the sequence fits it
+template <class Prov, bool POS_ONLY>
+__device__ int emul_any(EmulCtl *c1, Emul2Ctl *c2, Emul2Work *wk, const Prov &pv, int n, float target,
+                        bool has_target, float *sum_out, unsigned long long *tk = nullptr)
+{
+    if (n <= kSub * kMaxSubTiles && wk != nullptr)
+        return emul_scan2<Prov, POS_ONLY, false>(c2, wk, pv, n, target, has_target, sum_out, nullptr, tk);
+#ifndef NO_OLD_EMUL
+    return emul_scan<Prov, POS_ONLY>(c1, pv, n, target, has_target, sum_out);
+#else
+    return -1;
+#endif
+}
+
+}  // namespace stg

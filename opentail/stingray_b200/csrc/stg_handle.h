@@ -35,10 +35,14 @@ struct StgSampler_ {
     stg::DevBuf cand, cand_count, tickets, work_counter, escratch, keyscratch, dists;
     stg::DevBuf st_hist, st_bias_ids, st_bias_vals, st_uniforms, st_mask, st_logits;
     stg::DevBuf o_tokens, o_probs, o_flags, o_topk_ids, o_topk_vals, o_topk_probs, o_pairs;
+    stg::DevBuf ticks;                   // diagnostic phase stamps (STG_PHASE_TICKS=1)
+    int ticks_items = 0;
     stg::DevBuf sp_draft, sp_uniforms, sp_accepted, sp_correction, sp_aprobs, sp_flags, sp_rowstats;
     int64_t escratch_stride = 0, key_stride = 0;
     size_t cand_entries = 0;
-    uint32_t work_base = 0;
+    uint32_t work_base = 0, work_base_rows = 0;
+    cudaStream_t aux_stream = nullptr;   // the row kernel runs here, beside the chunk kernel
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
     size_t plan_bytes_cap = 0;
     // exchange buffers of the vocabulary-sharded mode
     stg::DevBuf xchg_local, xchg_gather, xchg_count_local, xchg_count_gather;

@@ -16,6 +16,8 @@
 
 namespace stg {
 
+static_assert(kRowArenaEnd == (int)kRowArenaBytes, "row arena layout and its launch size disagree");
+
 struct ItemShared {
     int item;
     int last;
@@ -94,9 +96,11 @@ __device__ __forceinline__ void write_greedy(const SampleArgs &a, int row, u64 k
 }
 
 template <int VEC, bool BF16>
-__device__ void run_chunk(const SampleArgs &a, int row, int chunk, SelCtl *ctl, ItemShared *ish,
+__device__ void run_chunk(const SampleArgs &a, int row, int chunk, int item, SelCtl *ctl, ItemShared *ish,
                           unsigned char *arena)
 {
+    u64 *tk = a.phase_ticks ? a.phase_ticks + (int64_t)item * 32 : nullptr;
+    tick(tk, 0);
     const RowPlan rp = a.plans[row];
     const int esz = BF16 ? 2 : 4;
     const void *rowp = (const char *)a.logits + (int64_t)row * a.row_stride * esz;
@@ -150,9 +154,10 @@ __device__ void run_chunk(const SampleArgs &a, int row, int chunk, SelCtl *ctl, 
     s.idx_off = a.vocab_offset;
     sel_reset(s);
     sel_stream<VEC, BF16>(s, rowp, mrow, begin, end);
+    tick(tk, 1);
     if (rp.n_chunks > 1) {
         const int cnt = ctl->cnt;
-        u64 *dst = a.cand + rp.cand_off + (int64_t)chunk * rp.sel;
+        u64 *dst = a.cand + rp.cand_off + (int64_t)chunk * 2 * rp.sel;
         const u64 *src = s.buf[ctl->cur];
         for (int e = threadIdx.x; e < cnt; e += kThreads) dst[e] = src[e];
         __threadfence();
@@ -170,11 +175,12 @@ __device__ void run_chunk(const SampleArgs &a, int row, int chunk, SelCtl *ctl, 
         sel_reset(s);
         for (int c = 0; c < rp.n_chunks; c++) {
             int m = __ldcg(a.cand_count + rp.slot + c);
-            sel_append_keys(s, a.cand + rp.cand_off + (int64_t)c * rp.sel, m);
+            sel_append_keys(s, a.cand + rp.cand_off + (int64_t)c * 2 * rp.sel, m);
         }
     }
     if (a.shard_mode == 1) {
-        // vocabulary-sharded mode: hand this rank's survivors to the exchange buffer
+        // vocabulary-sharded mode: hand this rank's best `sel` survivors to the exchange buffer
+        if (ctl->cnt > rp.sel) sel_compact(s);
         const int cnt = ctl->cnt;
         const u64 *src = s.buf[ctl->cur];
         u64 *dst = a.xchg_local + (int64_t)row * a.xchg_stride;
@@ -183,6 +189,7 @@ __device__ void run_chunk(const SampleArgs &a, int row, int chunk, SelCtl *ctl, 
         __syncthreads();
         return;
     }
+    tick(tk, 2);
     const int32_t *hist = a.hist_ids ? a.hist_ids + rp.hist_off : nullptr;
     const float *ptab = (a.pow_tab && rp.pow_off >= 0) ? a.pow_tab + rp.pow_off : nullptr;
     float u = a.uniforms ? __ldg(a.uniforms + row) : 0.5f;
@@ -194,11 +201,13 @@ __device__ void run_chunk(const SampleArgs &a, int row, int chunk, SelCtl *ctl, 
         if (a.token_probs) a.token_probs[row] = ish->fout.prob;
         if (a.row_flags) a.row_flags[row] = ish->fout.flags;
     }
+    tick(tk, 3);
     __syncthreads();
 }
 
+// Chunk items: the streaming arg-max / top-N selection (HBM-bound).
 template <int VEC, bool BF16>
-__global__ void __launch_bounds__(kThreads, 1) k_sample(const __grid_constant__ SampleArgs a)
+__global__ void __launch_bounds__(kThreads, 1) k_sample_chunks(const __grid_constant__ SampleArgs a)
 {
     extern __shared__ __align__(16) unsigned char arena[];
     __shared__ SelCtl ctl;
@@ -210,10 +219,26 @@ __global__ void __launch_bounds__(kThreads, 1) k_sample(const __grid_constant__ 
         __syncthreads();
         if ((unsigned)item >= (unsigned)a.n_items) break;
         const WorkItem w = a.items[item];
-        if (w.chunk >= 0)
-            run_chunk<VEC, BF16>(a, w.row, w.chunk, &ctl, &ish, arena);
-        else
-            run_row<BF16>(a, w.row, &ctl, arena);
+        run_chunk<VEC, BF16>(a, w.row, w.chunk, a.item_base + item, &ctl, &ish, arena);
+        __syncthreads();
+    }
+}
+
+// Row items: the full-vocabulary pipeline, one row per CTA at a time.
+template <bool BF16>
+__global__ void __launch_bounds__(kThreads, 1) k_sample_rows(const __grid_constant__ SampleArgs a)
+{
+    extern __shared__ __align__(16) unsigned char arena[];
+    __shared__ SelCtl ctl;
+    __shared__ int sh_item;
+    for (;;) {
+        if (threadIdx.x == 0) sh_item = (int)(atomicAdd(a.work_counter, 1u) - a.work_base);
+        __syncthreads();
+        const int item = sh_item;
+        __syncthreads();
+        if ((unsigned)item >= (unsigned)a.n_items) break;
+        const WorkItem w = a.items[item];
+        run_row<BF16>(a, w.row, a.item_base + item, &ctl, arena);
         __syncthreads();
     }
 }
@@ -277,16 +302,25 @@ cudaError_t launch_shard_finish(const SampleArgs &a, const void *gather, const i
     return cudaGetLastError();
 }
 
-cudaError_t launch_sample(const SampleArgs &a, int grid, size_t smem, cudaStream_t stream)
+cudaError_t launch_sample_chunks(const SampleArgs &a, int grid, size_t smem, cudaStream_t stream)
 {
     void (*fn)(const SampleArgs);
     if (a.dtype == 1)
-        fn = a.vec == 4 ? k_sample<4, true> : k_sample<1, true>;
+        fn = a.vec == 4 ? k_sample_chunks<4, true> : k_sample_chunks<1, true>;
     else
-        fn = a.vec == 4 ? k_sample<4, false> : k_sample<1, false>;
+        fn = a.vec == 4 ? k_sample_chunks<4, false> : k_sample_chunks<1, false>;
     cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     fn<<<grid, kThreads, smem, stream>>>(a);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_sample_rows(const SampleArgs &a, int grid, cudaStream_t stream)
+{
+    void (*fn)(const SampleArgs) = a.dtype == 1 ? k_sample_rows<true> : k_sample_rows<false>;
+    cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRowArenaBytes);
+    if (e != cudaSuccess) return e;
+    fn<<<grid, kThreads, kRowArenaBytes, stream>>>(a);
     return cudaGetLastError();
 }
 

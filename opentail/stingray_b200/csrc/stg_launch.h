@@ -7,9 +7,10 @@
 namespace stg {
 
 // shared memory a row-type work item needs: sort keys + exp-value histogram
-constexpr size_t kRowArenaBytes = (size_t)kSortCap * 4 + 2048 * 4 + 2048 * 8;
+constexpr size_t kRowArenaBytes = 201728;  // layout in stg_rowdist.cuh (checked there)
 
-cudaError_t launch_sample(const SampleArgs &a, int grid, size_t smem, cudaStream_t stream);
+cudaError_t launch_sample_chunks(const SampleArgs &a, int grid, size_t smem, cudaStream_t stream);
+cudaError_t launch_sample_rows(const SampleArgs &a, int grid, cudaStream_t stream);
 cudaError_t launch_shard_finish(const SampleArgs &a, const void *gather, const int32_t *gcount, size_t smem,
                                 cudaStream_t stream);
 

@@ -1,41 +1,101 @@
 // The full-vocabulary pipeline for one row, run by one 1024-thread CTA:
-//   bias -> history penalties -> 1/T -> softmax -> min-p -> top-p -> normalise -> inverse-CDF draw
+//   bias -> history penalties -> 1/T -> softmax -> [top-k] -> min-p -> top-p -> normalise -> draw
 // (Sampler.Sample's slow path, src/OpenTail.Stingray.Engine/Sampler.cs:41-95, and
 // BuildFilteredDistribution, :118-163), plus GreedyWithHistoryPenalties (:421-437).
 //
 // The row is read from HBM once; later passes re-read it (or the exp values kept in a per-CTA
 // scratch row) from L2.  Every sum the reference accumulates sequentially in fp32 is reproduced
-// bit for bit by emul_scan; the one vectorised sum (Normalize's TensorPrimitives.Sum, whose order
-// the reference does not pin) is accumulated in fp64 and rounded once.
+// bit for bit (stg_emul2.cuh); the one vectorised sum (Normalize's TensorPrimitives.Sum, whose
+// order the reference does not pin) is accumulated in fp64 and rounded once.
 //
-// top-p is sort-free over the vocabulary: a histogram of the exp values bounds the nucleus, only
-// the candidates above that bound are sorted (in shared memory), and the reference's sequential
-// cumulative cut is then emulated over them.
+// History and bias adjustments touch a few hundred tokens: they are gathered into a shared-memory
+// hash table (token -> adjusted logit) that the first pass consults through a folded bitmap.
+//
+// top-p is sort-free over the vocabulary.  A histogram of the exp values (4096 bins: exponent and
+// 5 mantissa bits) bounds the nucleus; the candidates above the bound are scattered into bin order
+// (largest bin first, arbitrary order inside a bin); only the bins in which the reference's
+// sequential cumulative sum can change binade or reach top_p are sorted; the emulated sum then
+// runs over that partially ordered sequence and refuses to replay an unsorted stretch element by
+// element - in that case the stretch is sorted and the sum run again.
 #pragma once
 #include <cuda_runtime.h>
 #include <limits.h>
 #include <math_constants.h>
 #include <stdint.h>
+#include <string.h>
 
 #include "stg_emul.cuh"
+#include "stg_emul2.cuh"
 #include "stg_select.cuh"
 #include "stg_types.h"
 
 namespace stg {
 
-constexpr int kBins = 2048;  // exp-value histogram: 8 exponent + 4 mantissa bits of a float <= 1
+constexpr int kBins = 4096;        // exp-value histogram: 8 exponent + 5 mantissa bits of a float <= 1
+constexpr int kBinShift = 18;
+constexpr int kMaxDirty = 512;     // bins sorted individually before giving up on the partial order
+constexpr int kDirtyRound = 2048;  // elements rank-sorted per round
+constexpr int kMaxOvSlots = 4096;  // hash slots => at most 2048 history + bias entries per row
+static_assert(kBins == 4 * kThreads, "the bin scans assign 4 bins to a thread");
+
+// shared-memory arena of a row item
+constexpr int kOffKeys = 0;                                      // u32[kSortCap] | hash table | Sel buffers
+constexpr int kOffCount = kSortCap * 4;                          // u32[kBins]
+constexpr int kOffMass = kOffCount + kBins * 4;                  // float[kBins]
+constexpr int kOffBinOff = kOffMass + kBins * 4;                 // u32[kBins]: start of each bin in the list
+constexpr int kOffEmul = kOffBinOff + kBins * 4;                 // Emul2Work
+constexpr int kOffReplayOk = kOffEmul + (int)sizeof(Emul2Work);  // u8[kMaxSubTiles]
+constexpr int kRowArenaEnd = kOffReplayOk + kMaxSubTiles;
 
 struct RowCtl {
     EmulCtl em;
+    Emul2Ctl em2;
     double red_d[32];
     int red_i[32];
     u64 red_k[32];
+    float red_f[32];
     RowDist dist;
-    int n_cand;       // candidates written by the compaction
-    int n_surv;       // survivors of min-p over the whole row
+    int n_cand;       // candidates in the bin-ordered list
+    int bound;        // their number as the histogram counted them
     int c_lo;         // lowest histogram bin among the candidates
     int found;        // find_kth_match result
     int running;
+    int n_dirty;      // bins waiting to be sorted
+    int give_up;      // partial order abandoned: sort everything
+    unsigned short dirty[kMaxDirty];
+    int dirty_cum[kMaxDirty + 1];
+    unsigned sorted_bits[kBins / 32];  // bins already sorted
+};
+
+// ---- hash table of adjusted logits ---------------------------------------------------------------
+struct OvTable {
+    int *key;          // token id or -1
+    int *cnt_all;      // occurrences in the whole history
+    int *cnt_w;        // occurrences inside the repetition window
+    int *n_bias;       // bias entries for this token
+    float *bias;       // their sum
+    float *adj;        // adjusted (unscaled) logit
+    unsigned char *bitmap;  // 65536 folded bits: bit (id & 0xFFFF) set when id may be in the table
+    int mask;          // slots - 1
+    __device__ __forceinline__ int find(int id) const
+    {
+        int h = (int)(((unsigned)id * 2654435761u) >> 7) & mask;
+        for (;;) {
+            int k = key[h];
+            if (k == id) return h;
+            if (k == -1) return -1;
+            h = (h + 1) & mask;
+        }
+    }
+    __device__ __forceinline__ int insert(int id)
+    {
+        int h = (int)(((unsigned)id * 2654435761u) >> 7) & mask;
+        for (;;) {
+            int old = atomicCAS(&key[h], -1, id);
+            if (old == -1 || old == id) return h;
+            h = (h + 1) & mask;
+        }
+    }
 };
 
 // ---- sources of the row's adjusted, temperature-scaled logits ---------------------------------
@@ -46,7 +106,7 @@ struct SrcLogits {
     int aligned;
     float inv_t;
     bool scale;
-    __device__ __forceinline__ void get8(int base, int n, float x[8]) const
+    __device__ __forceinline__ void get8raw(int base, int n, float x[8]) const
     {
         if (aligned && base + 8 <= n) {
             load_vec4<BF16, false>(rowp, base, x);
@@ -69,6 +129,10 @@ struct SrcLogits {
                 x[j] = v;
             }
         }
+    }
+    __device__ __forceinline__ void get8(int base, int n, float x[8]) const
+    {
+        get8raw(base, n, x);
         if (scale) {
 #pragma unroll
             for (int j = 0; j < 8; j++) x[j] = __fmul_rn(x[j], inv_t);
@@ -98,8 +162,20 @@ struct SrcScratch {
     }
 };
 
+__device__ __forceinline__ void store8(float *p, int base, int n, const float x[8])
+{
+    if (base + 8 <= n) {
+        __stcg((float4 *)(p + base), make_float4(x[0], x[1], x[2], x[3]));
+        __stcg((float4 *)(p + base + 4), make_float4(x[4], x[5], x[6], x[7]));
+    } else {
+#pragma unroll
+        for (int j = 0; j < 8; j++)
+            if (base + j < n) __stcg(p + base + j, x[j]);
+    }
+}
+
 // ---- probability of an element from its exp value -----------------------------------------------
-static __device__ __forceinline__ float eval_p2(float e, const RowDist &d)  // after softmax and min-p
+__device__ __forceinline__ float eval_p2(float e, const RowDist &d)  // softmax, top-k, min-p
 {
     float p = (d.flags & kDistScale1) ? __fmul_rn(e, d.inv1) : e;
     if (d.flags & kDistTopK) {
@@ -109,7 +185,7 @@ static __device__ __forceinline__ float eval_p2(float e, const RowDist &d)  // a
     if ((d.flags & kDistMinP) && p < d.minp_thr) p = 0.f;
     return p;
 }
-static __device__ __forceinline__ float eval_p3(float e, int i, const RowDist &d)  // final probability
+__device__ __forceinline__ float eval_p3(float e, int i, const RowDist &d)  // final probability
 {
     float p = eval_p2(e, d);
     if (d.flags & kDistTopP) {
@@ -119,7 +195,7 @@ static __device__ __forceinline__ float eval_p3(float e, int i, const RowDist &d
     return p;
 }
 
-// ---- emul_scan providers -------------------------------------------------------------------------
+// ---- providers of the emulated sums ----------------------------------------------------------------
 // exp pass: computes e_i = expf(x_i - max), stores it in the scratch row, feeds the histogram.
 template <class Src>
 struct ProvExp {
@@ -127,7 +203,7 @@ struct ProvExp {
     float mx;
     float *scratch;
     unsigned *hcount;   // null: no histogram wanted
-    u64 *hmass;
+    unsigned *hmass;    // per bin: sum of the top 12 mantissa bits (all values in a bin share the exponent)
     __device__ __forceinline__ void load(int base, int n, float x[8]) const
     {
         if (base >= n) {
@@ -141,39 +217,32 @@ struct ProvExp {
             float e = (base + j < n) ? expf(__fsub_rn(x[j], mx)) : 0.f;
             x[j] = e;
             if (hcount && e > 0.f) {
-                unsigned bin = __float_as_uint(e) >> 19;
+                unsigned bin = __float_as_uint(e) >> kBinShift;
                 bin = bin < (unsigned)kBins ? bin : (unsigned)(kBins - 1);
                 atomicAdd(&hcount[bin], 1u);
-                atomicAdd(&hmass[bin], (u64)((double)e * 1099511627776.0));
+                atomicAdd(&hmass[bin], ((__float_as_uint(e) & 0x7FFFFFu) | 0x800000u) >> 12);
             }
         }
-        if (base + 8 <= n) {
-            __stcg((float4 *)(scratch + base), make_float4(x[0], x[1], x[2], x[3]));
-            __stcg((float4 *)(scratch + base + 4), make_float4(x[4], x[5], x[6], x[7]));
-        } else {
-#pragma unroll
-            for (int j = 0; j < 8; j++)
-                if (base + j < n) __stcg(scratch + base + j, x[j]);
-        }
+        store8(scratch, base, n, x);
     }
-};
-
-struct ProvConstFill {  // every token has the same probability (no finite logit)
-    float value;
-    float *scratch;
-    __device__ __forceinline__ void load(int base, int n, float x[8]) const
+    __device__ __forceinline__ void reload(int base, int n, float x[8]) const
     {
+        if (base >= n) {
 #pragma unroll
-        for (int j = 0; j < 8; j++) {
-            x[j] = (base + j < n) ? value : 0.f;
-            if (base + j < n) __stcg(scratch + base + j, value);
+            for (int j = 0; j < 8; j++) x[j] = 0.f;
+            return;
         }
+        SrcScratch s{scratch, 1.f, false};
+        s.get8(base, n, x);
+#pragma unroll
+        for (int j = 0; j < 8; j++)
+            if (base + j >= n) x[j] = 0.f;
     }
 };
 
 struct ProvFinal {  // final probabilities from the scratch row of exp values
     const float *scratch;
-    const RowDist *d;
+    RowDist d;        // by value: lives in registers
     float *dist_out;  // optional: materialise the distribution
     __device__ __forceinline__ void load(int base, int n, float x[8]) const
     {
@@ -186,19 +255,32 @@ struct ProvFinal {  // final probabilities from the scratch row of exp values
         s.get8(base, n, x);
 #pragma unroll
         for (int j = 0; j < 8; j++) {
-            x[j] = (base + j < n) ? eval_p3(x[j], base + j, *d) : 0.f;
+            x[j] = (base + j < n) ? eval_p3(x[j], base + j, d) : 0.f;
             if (dist_out && base + j < n) dist_out[base + j] = x[j];
         }
     }
+    __device__ __forceinline__ void reload(int base, int n, float x[8]) const
+    {
+        if (base >= n) {
+#pragma unroll
+            for (int j = 0; j < 8; j++) x[j] = 0.f;
+            return;
+        }
+        SrcScratch s{scratch, 1.f, false};
+        s.get8(base, n, x);
+#pragma unroll
+        for (int j = 0; j < 8; j++) x[j] = (base + j < n) ? eval_p3(x[j], base + j, d) : 0.f;
+    }
 };
 
-struct ProvKeys {  // descending sorted probability bit patterns
+struct ProvKeys {  // probability bit patterns in (partial) descending order
     const uint32_t *keys;
     __device__ __forceinline__ void load(int base, int n, float x[8]) const
     {
 #pragma unroll
         for (int j = 0; j < 8; j++) x[j] = (base + j < n) ? __uint_as_float(keys[base + j]) : 0.f;
     }
+    __device__ __forceinline__ void reload(int base, int n, float x[8]) const { load(base, n, x); }
 };
 
 // ---- block-wide helpers ----------------------------------------------------------------------------
@@ -219,7 +301,7 @@ static __device__ void bitonic_sort_desc_t(T *a, int p2)
     }
 }
 
-static __device__ __forceinline__ u64 block_max_key_r(u64 k, u64 *scratch)
+__device__ __forceinline__ u64 block_max_key_r(u64 k, u64 *scratch)
 {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -244,28 +326,49 @@ static __device__ __forceinline__ u64 block_max_key_r(u64 k, u64 *scratch)
     return k;
 }
 
+__device__ __forceinline__ float block_max_float(float v, float *scratch)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, o));
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+    __syncthreads();
+    v = scratch[threadIdx.x & 31];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, o));
+    __syncthreads();
+    return v;
+}
+
 // (max value, lowest index of it) of the source as a key; 0 when nothing is > -infinity
 template <class Src>
 static __device__ u64 pass_max(const Src &src, int n, u64 *red)
 {
     float best = -CUDART_INF_F;
     int best_i = -1;
-    for (int base = threadIdx.x * 8; base < n; base += kThreads * 8) {
-        float x[8];
-        src.get8(base, n, x);
+    for (int base = threadIdx.x * 8; base < n; base += kThreads * 8 * 2) {
+        float x[2][8];
+        const int b1 = base + kThreads * 8;
+        src.get8(base, n, x[0]);
+        if (b1 < n) src.get8(b1, n, x[1]);
 #pragma unroll
         for (int j = 0; j < 8; j++)
-            if (x[j] > best) { best = x[j]; best_i = base + j; }
+            if (x[0][j] > best) { best = x[0][j]; best_i = base + j; }
+        if (b1 < n) {
+#pragma unroll
+            for (int j = 0; j < 8; j++)
+                if (x[1][j] > best) { best = x[1][j]; best_i = b1 + j; }
+        }
     }
-    // a thread's elements are not contiguous across tiles, but each thread keeps its own lowest
-    // index per value and the key order (value, then lower index) resolves ties across threads
+    // each thread keeps its own lowest index per value (it visits ascending indices), and the key
+    // order (value, then lower index) resolves ties across threads
     u64 k = best_i >= 0 ? make_key(best, best_i) : 0ull;
     return block_max_key_r(k, red);
 }
 
-// index of the `kth` (1-based) element, in token order, whose post-min-p probability equals tstar
+// index of the `kth` (1-based) element, in token order, whose pre-top-p probability equals tstar
 static __device__ int find_kth_match(RowCtl *rc, const float *scratch, int n, const RowDist &d, float tstar,
-                              int kth)
+                                     int kth)
 {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     __syncthreads();
@@ -319,86 +422,206 @@ static __device__ int find_kth_match(RowCtl *rc, const float *scratch, int n, co
     return INT_MAX;
 }
 
-// ---- history / bias overrides, applied to a raw copy of the row in the scratch row -----------------
-// ApplyHistoryPenalties (Sampler.cs:367-419) after the logit bias (Sampler.cs:50-56): entries are
-// sorted by token so that one thread owns each distinct token and applies, in the reference's
-// order, the bias additions, the per-occurrence repetition penalty inside the window, and the
-// presence/frequency penalty over the whole history.
-static __device__ void apply_overrides(const SampleArgs &a, const RowPlan &rp, float *scratch, int n,
-                                bool with_bias, u64 *keys /* arena */)
+// ---- history / bias overrides ------------------------------------------------------------------------
+// ApplyHistoryPenalties (Sampler.cs:367-419) after the logit bias (Sampler.cs:50-56).  One hash
+// slot per distinct token: its bias sum, its occurrence counts, then - by the slot's owner thread,
+// in the reference's order - bias additions, the per-occurrence repetition penalty inside the
+// window, and the presence/frequency penalty over the whole history.  Requires
+// 2 * (history + bias entries) <= slots <= kMaxOvSlots.
+template <bool BF16>
+static __device__ void build_overrides(const SampleArgs &a, const RowPlan &rp, const void *rowp,
+                                       const uint32_t *mrow, int n, bool with_hist, bool with_bias, OvTable &ov,
+                                       unsigned char *arena, int slots)
 {
     const int tid = threadIdx.x;
-    const int nh = rp.hist_len;
+    ov.key = (int *)arena;
+    ov.cnt_all = ov.key + slots;
+    ov.cnt_w = ov.cnt_all + slots;
+    ov.n_bias = ov.cnt_w + slots;
+    ov.bias = (float *)(ov.n_bias + slots);
+    ov.adj = ov.bias + slots;
+    ov.bitmap = (unsigned char *)(ov.adj + slots);
+    ov.mask = slots - 1;
+    for (int t = tid; t < slots; t += kThreads) {
+        ov.key[t] = -1; ov.cnt_all[t] = 0; ov.cnt_w[t] = 0; ov.n_bias[t] = 0; ov.bias[t] = 0.f;
+    }
+    for (int t = tid; t < 2048; t += kThreads) ((uint32_t *)ov.bitmap)[t] = 0u;
+    __syncthreads();
+    const int nh = with_hist ? rp.hist_len : 0;
     const int nb = with_bias ? rp.bias_len : 0;
-    const int ne = nh + nb;
-    if (ne == 0) return;
-    const int p2 = pow2_ceil(max(ne, 2));
-    const int32_t *hist = a.hist_ids + rp.hist_off;
-    for (int t = tid; t < p2; t += kThreads) {
-        u64 k = 0ull;
-        if (t < nb) {
-            int id = __ldg(a.bias_ids + rp.bias_off + t);
-            if ((unsigned)id < (unsigned)n) k = ~(((u64)(uint32_t)id << 32) | (u64)(uint32_t)t);
-        } else if (t < ne) {
-            int pos = t - nb;
-            int id = __ldg(hist + pos);
-            if ((unsigned)id < (unsigned)n) k = ~(((u64)(uint32_t)id << 32) | (u64)(0x80000000u | (uint32_t)pos));
+    for (int t = tid; t < nh + nb; t += kThreads) {
+        if (t < nh) {
+            int id = __ldg(a.hist_ids + rp.hist_off + t);
+            if ((unsigned)id >= (unsigned)n) continue;
+            int h = ov.insert(id);
+            atomicAdd(&ov.cnt_all[h], 1);
+            if (t >= rp.window_start) atomicAdd(&ov.cnt_w[h], 1);
+        } else {
+            int b = t - nh;
+            int id = __ldg(a.bias_ids + rp.bias_off + b);
+            if ((unsigned)id >= (unsigned)n) continue;
+            int h = ov.insert(id);
+            atomicAdd(&ov.n_bias[h], 1);
+            atomicAdd(&ov.bias[h], __ldg(a.bias_vals + rp.bias_off + b));
         }
-        keys[t] = k;
     }
     __syncthreads();
-    bitonic_sort_desc(keys, p2);
-    const bool has_hist_pen = nh > 0;
-    for (int t = tid; t < ne; t += kThreads) {
-        u64 kk = keys[t];
-        if (kk == 0ull) continue;
-        u64 k = ~kk;
-        uint32_t id = (uint32_t)(k >> 32);
-        if (t > 0 && keys[t - 1] != 0ull && (uint32_t)((~keys[t - 1]) >> 32) == id) continue;  // not a run start
-        float x = __ldcg(scratch + id);
-        int occ_all = 0, occ_w = 0;
-        for (int r = t; r < ne; r++) {
-            u64 rk = keys[r];
-            if (rk == 0ull) break;
-            u64 q = ~rk;
-            if ((uint32_t)(q >> 32) != id) break;
-            uint32_t sub = (uint32_t)q;
-            if (sub & 0x80000000u) {
-                occ_all++;
-                if ((int)(sub & 0x7FFFFFFFu) >= rp.window_start) occ_w++;
-            } else {
-                x = __fadd_rn(x, __ldg(a.bias_vals + rp.bias_off + (int)sub));
-            }
-        }
-        if (has_hist_pen && occ_all > 0) {
+    for (int h = tid; h < slots; h += kThreads) {
+        int id = ov.key[h];
+        if (id < 0) continue;
+        float x = load_one<BF16>(rowp, id);
+        if (mrow && !mask_bit(mrow, id)) x = -CUDART_INF_F;
+        if (ov.n_bias[h] > 0) x = __fadd_rn(x, ov.bias[h]);
+        const int occ_all = ov.cnt_all[h], occ_w = ov.cnt_w[h];
+        if (occ_all > 0) {
             if (rp.rep != 1.0f)
                 for (int r = 0; r < occ_w; r++) x = x > 0.f ? __fdiv_rn(x, rp.rep) : __fmul_rn(x, rp.rep);
             if (!(rp.pres == 0.f && rp.freq == 0.f))
                 x = __fsub_rn(x, __fadd_rn(rp.pres, __fmul_rn(rp.freq, (float)occ_all)));
         }
-        __stcg(scratch + id, x);
+        ov.adj[h] = x;
+        atomicOr((unsigned *)ov.bitmap + ((id & 0xFFFF) >> 5), 1u << (id & 31));
     }
-    __threadfence_block();
     __syncthreads();
+}
+
+// first pass of a row with overrides: adjusted, scaled logits into the scratch row, and their maximum
+template <bool BF16>
+static __device__ float pass_adjust(const SrcLogits<BF16> &raw, const OvTable &ov, float inv_t, bool scale, int n,
+                                    float *scratch, float *red)
+{
+    float best = -CUDART_INF_F;
+    for (int base = threadIdx.x * 8; base < n; base += kThreads * 8 * 2) {
+        float x[2][8];
+        const int b1 = base + kThreads * 8;
+        raw.get8raw(base, n, x[0]);
+        if (b1 < n) raw.get8raw(b1, n, x[1]);
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int b = h ? b1 : base;
+            if (b >= n) break;
+            unsigned m = ov.bitmap[(b & 0xFFFF) >> 3];
+            while (m) {
+                int j = __ffs(m) - 1;
+                m &= m - 1;
+                if (b + j < n) {
+                    int slot = ov.find(b + j);
+                    if (slot >= 0) x[h][j] = ov.adj[slot];
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                if (scale) x[h][j] = __fmul_rn(x[h][j], inv_t);
+                if (b + j < n) best = fmaxf(best, x[h][j]);
+            }
+            store8(scratch, b, n, x[h]);
+        }
+    }
+    return block_max_float(best, red);
+}
+
+// mass of a histogram bin in exp-value units: every value in bin b has the biased exponent b >> 5, and
+// hmass holds the sum of the top 12 bits of their 24-bit mantissas
+__device__ __forceinline__ double bin_mass(const unsigned *hmass, int b)
+{
+    const int ex = b >> 5;  // biased exponent (0: denormals, treated as exponent 1)
+    return ldexp((double)hmass[b], (ex ? ex : 1) - 127 - 11);  // truncation makes it up to 2^-12 low
+}
+
+// ---- top-p over a partially ordered candidate list ---------------------------------------------------
+// rank-sorts (descending) every bin on the dirty list, kDirtyRound elements per round
+static __device__ void sort_dirty_bins(RowCtl *rc, uint32_t *keys, const unsigned *bstart, const unsigned *hcount,
+                                       uint32_t *tmp_key, int *tmp_dst)
+{
+    const int tid = threadIdx.x;
+    const int nd = rc->n_dirty;
+    __syncthreads();
+    if (tid == 0) {
+        int acc = 0;
+        for (int i = 0; i < nd; i++) { rc->dirty_cum[i] = acc; acc += (int)hcount[rc->dirty[i]]; }
+        rc->dirty_cum[nd] = acc;
+    }
+    __syncthreads();
+    const int total = rc->dirty_cum[nd];
+    for (int round0 = 0; round0 < total; round0 += kDirtyRound) {
+        const int m = min(kDirtyRound, total - round0);
+        for (int e = tid; e < m; e += kThreads) {
+            const int g = round0 + e;
+            int lo = 0, hi = nd;  // last i with dirty_cum[i] <= g
+            while (hi - lo > 1) {
+                int mid = (lo + hi) >> 1;
+                if (rc->dirty_cum[mid] <= g) lo = mid; else hi = mid;
+            }
+            const int b = rc->dirty[lo];
+            const int off = (int)bstart[b], cnt = (int)hcount[b];
+            const int pos = g - rc->dirty_cum[lo];
+            const uint32_t k = keys[off + pos];
+            int rank = 0;
+            for (int j = 0; j < cnt; j++) {
+                const uint32_t o = keys[off + j];
+                rank += (o > k || (o == k && j < pos)) ? 1 : 0;
+            }
+            tmp_key[e] = k;
+            tmp_dst[e] = off + rank;
+        }
+        __syncthreads();
+        for (int e = tid; e < m; e += kThreads) keys[tmp_dst[e]] = tmp_key[e];
+        __syncthreads();
+    }
+}
+
+__device__ __forceinline__ double scan4_double(double tot, RowCtl *rc)  // inclusive block scan of per-thread totals
+{
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    double run = tot;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        double t = __shfl_up_sync(0xFFFFFFFFu, run, o);
+        if (lane >= o) run += t;
+    }
+    __syncthreads();
+    if (lane == 31) rc->red_d[warp] = run;
+    __syncthreads();
+    if (warp == 0) {
+        double w = rc->red_d[lane];
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            double t = __shfl_up_sync(0xFFFFFFFFu, w, o);
+            if (lane >= o) w += t;
+        }
+        rc->red_d[lane] = w;
+    }
+    __syncthreads();
+    return run + (warp ? rc->red_d[warp - 1] : 0.0);
 }
 
 // ---- the distribution of one row --------------------------------------------------------------------
 // Leaves the exp values in `scratch` and the descriptor in rc->dist.  `src` yields the adjusted,
-// temperature-scaled logits.
+// temperature-scaled logits; `mx_known` is their maximum when the caller already has it.
 template <class Src>
 static __device__ void build_dist(RowCtl *rc, SelCtl *sctl, const Src &src, const RowPlan &rp, int n,
-                           float *scratch, unsigned char *arena, uint32_t *gkeys, int gkeys_cap,
-                           uint32_t *flags_out)
+                                  float *scratch, unsigned char *arena, uint32_t *gkeys, int gkeys_cap,
+                                  uint32_t *flags_out, u64 *tk, bool have_max, float mx_known)
 {
     const int tid = threadIdx.x;
-    uint32_t *skeys = (uint32_t *)arena;                       // kSortCap u32
-    unsigned *hcount = (unsigned *)(arena + kSortCap * 4);     // kBins u32
-    u64 *hmass = (u64 *)(arena + kSortCap * 4 + kBins * 4);    // kBins u64
+    uint32_t *skeys = (uint32_t *)(arena + kOffKeys);
+    unsigned *hcount = (unsigned *)(arena + kOffCount);
+    unsigned *hmass = (unsigned *)(arena + kOffMass);
+    unsigned *bstart = (unsigned *)(arena + kOffBinOff);
+    Emul2Work *wk2 = (Emul2Work *)(arena + kOffEmul);
+    unsigned char *replay_ok = arena + kOffReplayOk;
     const bool want_topp = rp.top_p < 1.0f && rp.top_p > 0.f;
     const bool want_minp = rp.min_p > 0.f;
     const bool want_topk = rp.top_k > 0 && rp.top_k < n;
 
-    u64 mk = pass_max(src, n, rc->red_k);
+    float mx;
+    if (have_max) {
+        mx = mx_known;
+    } else {
+        u64 mk = pass_max(src, n, rc->red_k);
+        mx = mk ? key_val(mk) : -CUDART_INF_F;
+    }
+    tick(tk, 2);
     RowDist d;
     d.flags = 0;
     d.inv_t = src.inv_t;
@@ -406,30 +629,32 @@ static __device__ void build_dist(RowCtl *rc, SelCtl *sctl, const Src &src, cons
     d.kth = 0.f; d.inv2 = 1.f; d.minp_thr = 0.f; d.tstar = 0.f; d.inv3 = 1.f; d.inv1 = 1.f;
     d.uniform_p = 0.f; d.sum_end = 0.f; d.argmax = 0;
     if (want_topp) {
-        for (int t = tid; t < kBins; t += kThreads) { hcount[t] = 0u; hmass[t] = 0ull; }
+        for (int t = tid; t < kBins; t += kThreads) { hcount[t] = 0u; hmass[t] = 0u; }
     }
     __syncthreads();
     float sum = 0.f;
-    if (mk == 0ull) {
+    const bool uniform = !(mx > -CUDART_INF_F);  // also covers NaN
+    if (uniform) {
         // Softmax's fully masked case (Sampler.cs:452-458): every token gets 1/V, no rescale
         d.flags |= kDistUniform;
         d.max_x = -CUDART_INF_F;
         d.uniform_p = __fdiv_rn(1.0f, (float)n);
-        ProvConstFill pc{d.uniform_p, scratch};
-        for (int base = tid * 8; base < n; base += kThreads * 8) { float x[8]; pc.load(base, n, x); }
+        for (int i = tid; i < n; i += kThreads) __stcg(scratch + i, d.uniform_p);
         if (want_topp && tid == 0) {
-            unsigned bin = __float_as_uint(d.uniform_p) >> 19;
+            unsigned bin = __float_as_uint(d.uniform_p) >> kBinShift;
             hcount[bin] = (unsigned)n;
-            hmass[bin] = (u64)((double)d.uniform_p * 1099511627776.0) * (u64)n;
+            hmass[bin] = (unsigned)min((unsigned long long)n * ((((unsigned long long)__float_as_uint(d.uniform_p) & 0x7FFFFFu) | 0x800000u) >> 12), 0xFFFFFFFFull);
         }
         __syncthreads();
     } else {
-        d.max_x = key_val(mk);
-        ProvExp<Src> pe{src, d.max_x, scratch, want_topp ? hcount : nullptr, hmass};
-        emul_scan<ProvExp<Src>, false>(&rc->em, pe, n, 0.f, false, &sum);
+        d.max_x = mx;
+        ProvExp<Src> pe{src, mx, scratch, want_topp ? hcount : nullptr, hmass};
+        emul_any<ProvExp<Src>, false>(&rc->em, &rc->em2, wk2, pe, n, 0.f, false, &sum, tk ? tk + 12 : nullptr);
         if (sum > 0.f && sum != 1.0f) { d.flags |= kDistScale1; d.inv1 = __fdiv_rn(1.0f, sum); }
     }
     __syncthreads();
+    tick(tk, 3);
+#ifndef NO_TOPK
     if (want_topk) {
         // ApplyTopK + Normalize (Sampler.cs:477-488, :71-81): the k-th largest probability, counted
         // with multiplicity; everything below it is dropped, ties at it all survive.  Selected on
@@ -437,12 +662,13 @@ static __device__ void build_dist(RowCtl *rc, SelCtl *sctl, const Src &src, cons
         Sel s;
         s.c = sctl;
         s.cap = 8192;
-        s.buf[0] = (u64 *)arena;
+        s.buf[0] = (u64 *)(arena + kOffKeys);
         s.buf[1] = s.buf[0] + s.cap;
         s.n = rp.top_k;
         s.idx_off = 0;
         sel_reset(s);
         sel_stream<4, false>(s, scratch, nullptr, 0, n);
+        if (sctl->cnt > s.n) sel_compact(s);  // exactly the best k: their minimum is the k-th largest
         const u64 *b = s.buf[sctl->cur];
         u64 inv_min = 0ull;
         for (int e = tid; e < sctl->cnt; e += kThreads) { u64 t = ~b[e]; inv_min = t > inv_min ? t : inv_min; }
@@ -463,9 +689,11 @@ static __device__ void build_dist(RowCtl *rc, SelCtl *sctl, const Src &src, cons
         if (s2 > 0.f && s2 != 1.0f) { d.flags |= kDistScale2; d.inv2 = __fdiv_rn(1.0f, s2); }
         __syncthreads();
     }
+#endif
+    tick(tk, 4);
     if (want_minp) {
         // ApplyMinP (Sampler.cs:493-503): the largest probability belongs to exp value 1 (or 1/V)
-        float emax = (d.flags & kDistUniform) ? d.uniform_p : 1.0f;
+        float emax = uniform ? d.uniform_p : 1.0f;
         float pmax = (d.flags & kDistScale1) ? __fmul_rn(emax, d.inv1) : emax;
         if (d.flags & kDistScale2) pmax = __fmul_rn(pmax, d.inv2);
         d.minp_thr = __fmul_rn(rp.min_p, pmax);
@@ -474,73 +702,206 @@ static __device__ void build_dist(RowCtl *rc, SelCtl *sctl, const Src &src, cons
 
     double sum3 = 0.0;
     if (want_topp) {
-        // bound the nucleus from the histogram (exact enough to be a superset; the cut itself is
-        // decided below by the emulated sequential sum)
+        const double scale_p = ((d.flags & kDistScale1) ? (double)d.inv1 : 1.0) *
+                               ((d.flags & kDistScale2) ? (double)d.inv2 : 1.0);
         for (int attempt = 0; attempt < 2; attempt++) {
-            if (tid == 0) {
-                int c_lo = 0;
-                if (attempt == 0) {
-                    double scale_p = ((d.flags & kDistScale1) ? (double)d.inv1 : 1.0) *
-                                     ((d.flags & kDistScale2) ? (double)d.inv2 : 1.0) / 1099511627776.0;
-                    u64 acc_m = 0ull;
-                    unsigned acc_c = 0u;
-                    for (int b = kBins - 1; b >= 0; --b) {
-                        acc_c += hcount[b];
-                        acc_m += hmass[b];
-                        // estimate only: a bound that proves too tight is caught below (the
-                        // emulated sum then never reaches top_p) and the cut is redone over all
-                        double need = (double)rp.top_p * (1.0 + 1.0 / 65536.0) +
-                                      16.0 * sqrt((double)acc_c) * 2.98e-8 + 1e-7;
-                        if ((double)acc_m * scale_p >= need) { c_lo = b > 0 ? b - 1 : 0; break; }
+            // (1) bound the nucleus: bins from the top until the estimated mass clears top_p.  An
+            // estimate suffices: a bound that proves too tight is caught below (the emulated sum
+            // then never reaches top_p although survivors remain) and everything is taken.
+            if (tid == 0) { rc->c_lo = 0; rc->give_up = 0; rc->n_dirty = 0; }
+            __syncthreads();
+            if (attempt == 0) {
+                // mass and count of the bins above each bin (4 bins per thread, highest bins first)
+                double lm[4], tm = 0.0, tc = 0.0;
+                unsigned lc[4];
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const int b = kBins - 1 - (tid * 4 + j);
+                    lc[j] = hcount[b];
+                    lm[j] = lc[j] ? bin_mass(hmass, b) : 0.0;
+                    tm += lm[j];
+                    tc += (double)lc[j];
+                }
+                double am = scan4_double(tm, rc) - tm;
+                double ac = scan4_double(tc, rc) - tc;
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const int b = kBins - 1 - (tid * 4 + j);
+                    am += lm[j];
+                    ac += (double)lc[j];
+                    if (lc[j]) {
+                        const double need = (double)rp.top_p * (1.0 + 1.0 / 65536.0) + 16.0 * sqrt(ac) * 2.98e-8 + 1e-7;
+                        if (am * scale_p >= need) atomicMax(&rc->c_lo, b > 0 ? b - 1 : 0);
                     }
                 }
-                rc->c_lo = c_lo;
-                rc->n_cand = 0;
-                rc->n_surv = 0;
+                __syncthreads();
             }
+            for (int t = tid; t < kBins / 32; t += kThreads) rc->sorted_bits[t] = 0u;
             __syncthreads();
-            const uint32_t lo_bits = (uint32_t)rc->c_lo << 19;
-            // how many candidates at most? decides shared vs global key storage
-            int bound = 0;
-            for (int b = rc->c_lo + tid; b < kBins; b += kThreads) bound += (int)hcount[b];
-            bound = block_sum_int(bound, rc->red_i);
+            tick(tk, 5);
+            const int c_lo = rc->c_lo;
+            // (2) start of every candidate bin in the bin-ordered list (largest bin first)
+            unsigned *cursor = (unsigned *)wk2;  // kBins u32 = 16 KB over Emul2Work's sums + comp, free here
+            {
+                unsigned loc[4], tot = 0;
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    int b = kBins - 1 - (tid * 4 + j);
+                    loc[j] = b >= c_lo ? hcount[b] : 0u;
+                    cursor[b] = 0u;
+                    tot += loc[j];
+                }
+                const double incl = scan4_double((double)tot, rc);
+                unsigned run = (unsigned)(incl - (double)tot);
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    int b = kBins - 1 - (tid * 4 + j);
+                    bstart[b] = run;
+                    run += loc[j];
+                }
+                if (tid == kThreads - 1) rc->bound = (int)run;
+                __syncthreads();
+            }
+            const int bound = rc->bound;
             uint32_t *keys = skeys;
             int cap = kSortCap;
             if (bound > kSortCap) { keys = gkeys; cap = gkeys_cap; *flags_out |= (1u << 7); }
-            // compaction: probability bit patterns of the survivors above the bound
+            // (3) scatter the survivors above the bound into bin order; count all survivors
             int my_surv = 0;
-            for (int base = tid * 8; base < n; base += kThreads * 8) {
-                float x[8];
-                SrcScratch s{scratch, 1.f, false};
-                s.get8(base, n, x);
+            const uint32_t lo_bits = (uint32_t)c_lo << kBinShift;
+            for (int base = tid * 8; base < n; base += kThreads * 8 * 2) {
+                float x[2][8];
+                const int b1 = base + kThreads * 8;
+                SrcScratch sc{scratch, 1.f, false};
+                sc.get8(base, n, x[0]);
+                if (b1 < n) sc.get8(b1, n, x[1]);
 #pragma unroll
-                for (int j = 0; j < 8; j++) {
-                    if (base + j >= n) continue;
-                    float p = eval_p2(x[j], d);
-                    if (p > 0.f) {
-                        my_surv++;
-                        if (__float_as_uint(x[j]) >= lo_bits) {
-                            int slot = atomicAdd(&rc->n_cand, 1);
-                            if (slot < cap) keys[slot] = __float_as_uint(p);
+                for (int h = 0; h < 2; h++) {
+                    const int bb = h ? b1 : base;
+                    if (bb >= n) break;
+#pragma unroll
+                    for (int j = 0; j < 8; j++) {
+                        if (bb + j >= n) continue;
+                        const float e = x[h][j];
+                        const float p = eval_p2(e, d);
+                        if (p > 0.f) {
+                            my_surv++;
+                            const uint32_t ebits = __float_as_uint(e);
+                            if (ebits >= lo_bits) {
+                                unsigned bin = ebits >> kBinShift;
+                                bin = bin < (unsigned)kBins ? bin : (unsigned)(kBins - 1);
+                                unsigned pos = bstart[bin] + atomicAdd(&cursor[bin], 1u);
+                                if (pos < (unsigned)cap) keys[pos] = __float_as_uint(p);
+                            }
                         }
                     }
                 }
             }
             my_surv = block_sum_int(my_surv, rc->red_i);
+            // The filters before top-p drop the smallest values only, so the bins that lost
+            // elements are the last ones of the list: it stays dense.  From here on the histogram
+            // describes the list.
+            int mine = 0;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                int b = kBins - 1 - (tid * 4 + j);
+                unsigned have = b >= c_lo ? cursor[b] : 0u;
+                hcount[b] = have;
+                mine += (int)have;
+            }
+            const int nc = min(block_sum_int(mine, rc->red_i), cap);
             __syncthreads();
-            const int nc = min(rc->n_cand, cap);
+            tick(tk, 6);
             if (nc == 0) break;
-            const int p2 = pow2_ceil(max(nc, 2));
-            for (int t = nc + tid; t < p2; t += kThreads) keys[t] = 0u;
-            __syncthreads();
-            if (!(d.flags & kDistUniform)) bitonic_sort_desc_t<uint32_t>(keys, p2);
-            ProvKeys pk{keys};
+            // (4) bins in which the sequential sum may change binade or meet top_p, judged from
+            // the estimated mass before and after each bin: they are sorted up front
+            {
+                double loc[4], tot = 0.0;
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    int b = kBins - 1 - (tid * 4 + j);
+                    loc[j] = (b >= c_lo && hcount[b]) ? bin_mass(hmass, b) * scale_p : 0.0;
+                    tot += loc[j];
+                }
+                double before = scan4_double(tot, rc) - tot;
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    int b = kBins - 1 - (tid * 4 + j);
+                    if (b >= c_lo && hcount[b] >= 2u) {
+                        // the estimate is low by at most 2^-12 (mantissa truncation) and the
+                        // emulated sum drifts by ~1e-5; a miss is caught by the scan itself
+                        const double lo = before * (1.0 - 1.0 / 32768.0), hi = (before + loc[j]) * (1.0 + 1.0 / 2048.0);
+                        const bool crosses = exp_of_double(lo) != exp_of_double(hi);
+                        const bool cut = lo <= (double)rp.top_p && hi >= (double)rp.top_p;
+                        if (crosses || cut) {
+                            int slot = atomicAdd(&rc->n_dirty, 1);
+                            if (slot < kMaxDirty) rc->dirty[slot] = (unsigned short)b; else rc->give_up = 1;
+                        }
+                    }
+                    before += loc[j];
+                }
+                __syncthreads();
+            }
+            int hit = -1;
             float cum = 0.f;
-            int hit = emul_scan<ProvKeys, false>(&rc->em, pk, nc, rp.top_p, true, &cum);
+            bool sorted_all = uniform;  // all keys equal: any order is sorted
+            for (int pass = 0; pass < 64; pass++) {
+                if (!sorted_all && (rc->give_up || pass == 63)) {
+                    // partial order abandoned: sort the whole list
+                    const int p2 = pow2_ceil(max(nc, 2));
+                    for (int t = nc + tid; t < p2; t += kThreads) keys[t] = 0u;
+                    __syncthreads();
+                    bitonic_sort_desc_t<uint32_t>(keys, p2);
+                    sorted_all = true;
+                } else if (!sorted_all && rc->n_dirty > 0) {
+                    sort_dirty_bins(rc, keys, bstart, hcount, (uint32_t *)wk2, (int *)wk2 + kDirtyRound);
+                    for (int i = tid; i < min(rc->n_dirty, kMaxDirty); i += kThreads)
+                        atomicOr(&rc->sorted_bits[rc->dirty[i] >> 5], 1u << (rc->dirty[i] & 31));
+                    __syncthreads();
+                    if (tid == 0) rc->n_dirty = 0;
+                }
+                __syncthreads();
+                if (!sorted_all) {
+                    // a sub-tile that overlaps an unsorted bin of two or more keys may not be replayed
+                    for (int t = tid; t < kMaxSubTiles; t += kThreads) replay_ok[t] = 1;
+                    __syncthreads();
+                    for (int b = c_lo + tid; b < kBins; b += kThreads) {
+                        const unsigned cnt = hcount[b];
+                        if (cnt >= 2u && !((rc->sorted_bits[b >> 5] >> (b & 31)) & 1u)) {
+                            const int t0 = (int)bstart[b] >> 8, t1 = (int)(bstart[b] + cnt - 1) >> 8;
+                            for (int t = t0; t <= t1 && t < kMaxSubTiles; t++) replay_ok[t] = 0;
+                        }
+                    }
+                    __syncthreads();
+                }
+                ProvKeys pk{keys};
+                if (nc <= kSub * kMaxSubTiles) {
+                    hit = emul_scan2<ProvKeys, false, true, 4>(&rc->em2, wk2, pk, nc, rp.top_p, true, &cum,
+                                                            sorted_all ? nullptr : replay_ok, nullptr);
+                } else {
+                    if (!sorted_all) { if (tid == 0) rc->give_up = 1; __syncthreads(); continue; }
+                    hit = emul_scan<ProvKeys, false>(&rc->em, pk, nc, rp.top_p, true, &cum);
+                }
+                if (hit != -2) break;
+                // the sum needed the internal order of an unsorted stretch: sort its bins and rerun
+                const int t_abort = rc->em2.abort_at;
+                for (int b = c_lo + tid; b < kBins; b += kThreads) {
+                    const unsigned cnt = hcount[b];
+                    if (cnt >= 2u && !((rc->sorted_bits[b >> 5] >> (b & 31)) & 1u)) {
+                        const int t0 = (int)bstart[b] >> 8, t1 = (int)(bstart[b] + cnt - 1) >> 8;
+                        if (t0 <= t_abort && t_abort <= t1) {
+                            int slot = atomicAdd(&rc->n_dirty, 1);
+                            if (slot < kMaxDirty) rc->dirty[slot] = (unsigned short)b; else rc->give_up = 1;
+                        }
+                    }
+                }
+                __syncthreads();
+            }
+            tick(tk, 8);
             if (hit < 0 && nc < my_surv && attempt == 0) continue;  // bound was too tight: take all
             const int last = hit >= 0 ? hit : nc - 1;
             const float tstar = __uint_as_float(keys[last]);
-            // ties at the cut: kept ones are a prefix (by token id) of the equal probabilities
+            // ties at the cut: the kept ones are a prefix (by token id) of the equal probabilities
             int keep = 0, all = 0;
             for (int t = tid; t < nc; t += kThreads) {
                 if (keys[t] == __float_as_uint(tstar)) { all++; keep += (t <= last) ? 1 : 0; }
@@ -571,6 +932,7 @@ static __device__ void build_dist(RowCtl *rc, SelCtl *sctl, const Src &src, cons
         }
         sum3 = block_sum_double(part, rc->red_d);
     }
+    tick(tk, 9);
     // Normalize (Sampler.cs:553-562)
     float s3 = (float)sum3;
     if (s3 > 0.f && s3 != 1.0f) { d.flags |= kDistScale3; d.inv3 = __fdiv_rn(1.0f, s3); }
@@ -580,11 +942,17 @@ static __device__ void build_dist(RowCtl *rc, SelCtl *sctl, const Src &src, cons
 }
 
 template <bool BF16>
-static __device__ void run_row(const SampleArgs &a, int row, SelCtl *sctl, unsigned char *arena)
+static __device__ void run_row(const SampleArgs &a, int row, int item, SelCtl *sctl, unsigned char *arena)
 {
+    u64 *tk = a.phase_ticks ? a.phase_ticks + (int64_t)item * 32 : nullptr;
+    tick(tk, 0);
     __shared__ RowCtl rc;
+    __shared__ RowPlan sh_rp;  // kept in shared memory: the row's parameters are read rarely
     const int tid = threadIdx.x;
-    const RowPlan rp = a.plans[row];
+    __syncthreads();
+    if (tid == 0) sh_rp = a.plans[row];
+    __syncthreads();
+    const RowPlan &rp = sh_rp;
     const int n = a.vocab;
     const int esz = BF16 ? 2 : 4;
     const void *rowp = (const char *)a.logits + (int64_t)row * a.row_stride * esz;
@@ -594,38 +962,34 @@ static __device__ void run_row(const SampleArgs &a, int row, SelCtl *sctl, unsig
     const int gkeys_cap = (int)(a.key_stride * 2);
     const bool greedy = rp.temperature <= 0.f;
     const bool with_bias = !greedy && rp.bias_len > 0;
-    const bool overrides = (rp.has_penalty && rp.hist_len > 0) || with_bias;
+    const bool with_hist = rp.has_penalty && rp.hist_len > 0;
+    const bool overrides = with_hist || with_bias;
     __shared__ uint32_t sh_flags;
     if (tid == 0) sh_flags = 0;
     __syncthreads();
 
+    const float inv_t = (!greedy && rp.temperature != 1.0f) ? __fdiv_rn(1.0f, rp.temperature) : 1.0f;
+    const bool scale = !greedy && rp.temperature != 1.0f;
+    SrcLogits<BF16> raw{rowp, mrow, a.vec == 4, 1.f, false};
+    float mx = 0.f;
     if (overrides) {
-        // raw masked copy of the row, then the per-token adjustments
-        SrcLogits<BF16> raw{rowp, mrow, a.vec == 4, 1.f, false};
-        for (int base = tid * 8; base < n; base += kThreads * 8) {
-            float x[8];
-            raw.get8(base, n, x);
-            if (base + 8 <= n) {
-                __stcg((float4 *)(scratch + base), make_float4(x[0], x[1], x[2], x[3]));
-                __stcg((float4 *)(scratch + base + 4), make_float4(x[4], x[5], x[6], x[7]));
-            } else {
-#pragma unroll
-                for (int j = 0; j < 8; j++)
-                    if (base + j < n) __stcg(scratch + base + j, x[j]);
-            }
-        }
+        // adjusted (and scaled) logits into the scratch row
+        const int entries = (with_hist ? rp.hist_len : 0) + (with_bias ? rp.bias_len : 0);
+        int slots = 64;
+        while (slots < 2 * entries) slots <<= 1;
+        OvTable ov;
+        build_overrides<BF16>(a, rp, rowp, mrow, n, with_hist, with_bias, ov, arena, slots);
+        mx = pass_adjust<BF16>(raw, ov, inv_t, scale, n, scratch, rc.red_f);
         __threadfence_block();
         __syncthreads();
-        RowPlan eff = rp;
-        if (!rp.has_penalty) eff.hist_len = 0;
-        apply_overrides(a, eff, scratch, n, with_bias, (u64 *)arena);
     }
+    tick(tk, 1);
 
     if (greedy) {
         // Greedy / GreedyWithHistoryPenalties; in distribution mode a one-hot row
         u64 mk;
         if (overrides) { SrcScratch s{scratch, 1.f, false}; mk = pass_max(s, n, rc.red_k); }
-        else { SrcLogits<BF16> s{rowp, mrow, a.vec == 4, 1.f, false}; mk = pass_max(s, n, rc.red_k); }
+        else mk = pass_max(raw, n, rc.red_k);
         int tok = mk ? key_idx(mk) : 0;
         if (a.mode == 2) {
             if (tid == 0) {
@@ -653,18 +1017,16 @@ static __device__ void run_row(const SampleArgs &a, int row, SelCtl *sctl, unsig
         return;
     }
 
-    const float inv_t = rp.temperature != 1.0f ? __fdiv_rn(1.0f, rp.temperature) : 1.0f;
-    const bool scale = rp.temperature != 1.0f;
     if (overrides) {
-        SrcScratch s{scratch, inv_t, scale};
-        build_dist(&rc, sctl, s, rp, n, scratch, arena, gkeys, gkeys_cap, &sh_flags);
+        // the scratch row is scaled already; the descriptor still records the scale
+        SrcScratch s{scratch, inv_t, false};
+        build_dist(&rc, sctl, s, rp, n, scratch, arena, gkeys, gkeys_cap, &sh_flags, tk, true, mx);
     } else {
         SrcLogits<BF16> s{rowp, mrow, a.vec == 4, inv_t, scale};
-        build_dist(&rc, sctl, s, rp, n, scratch, arena, gkeys, gkeys_cap, &sh_flags);
+        build_dist(&rc, sctl, s, rp, n, scratch, arena, gkeys, gkeys_cap, &sh_flags, tk, false, 0.f);
     }
     if (a.mode == 2) {
         // descriptor only; the raw arg-max goes with it (the looser accept rule compares against it)
-        SrcLogits<BF16> raw{rowp, mrow, a.vec == 4, 1.f, false};
         u64 mk = pass_max(raw, n, rc.red_k);
         if (tid == 0) {
             rc.dist.argmax = mk ? key_idx(mk) : 0;
@@ -676,7 +1038,7 @@ static __device__ void run_row(const SampleArgs &a, int row, SelCtl *sctl, unsig
 
     // draw: SampleFromDistribution (Sampler.cs:564-576)
     float *dout = (a.mode == 1 && a.dist_out) ? a.dist_out + (int64_t)row * n : nullptr;
-    ProvFinal pf{scratch, &rc.dist, dout};
+    ProvFinal pf{scratch, rc.dist, dout};
     if (a.mode == 1) {
         for (int base = tid * 8; base < n; base += kThreads * 8) { float x[8]; pf.load(base, n, x); }
         if (tid == 0 && a.row_flags) a.row_flags[row] = kPathFull | sh_flags;
@@ -685,7 +1047,8 @@ static __device__ void run_row(const SampleArgs &a, int row, SelCtl *sctl, unsig
     }
     const float u = a.uniforms ? __ldg(a.uniforms + row) : 0.5f;
     float cum = 0.f;
-    int hit = emul_scan<ProvFinal, false>(&rc.em, pf, n, u, true, &cum);
+    Emul2Work *wk2 = (Emul2Work *)(arena + kOffEmul);
+    int hit = emul_any<ProvFinal, false>(&rc.em, &rc.em2, wk2, pf, n, u, true, &cum, tk ? tk + 20 : nullptr);
     if (tid == 0) {
         uint32_t fl = kPathFull | sh_flags;
         if (rc.dist.flags & kDistUniform) fl |= (1u << 6);
@@ -695,6 +1058,7 @@ static __device__ void run_row(const SampleArgs &a, int row, SelCtl *sctl, unsig
         if (a.token_probs) a.token_probs[row] = eval_p3(__ldcg(scratch + tok), tok, rc.dist);
         if (a.row_flags) a.row_flags[row] = fl;
     }
+    tick(tk, 10);
     __syncthreads();
 }
 

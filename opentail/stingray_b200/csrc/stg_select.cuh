@@ -128,6 +128,10 @@ struct SelCtl {
     u64 thr;
     u64 minkey;
     unsigned hist[256];
+    unsigned red[32];     // block reductions
+    unsigned ord_lo;      // lower end and shift of the coarse histogram of an approximate compaction
+    int shift;
+    int cut;              // its boundary bin
 };
 
 struct Sel {
@@ -224,11 +228,108 @@ static __device__ void sel_compact(Sel &s)
     __syncthreads();
 }
 
+// Cheap compaction: raises tau without finding the exact N-th key.  The keys are binned by value
+// into 256 bins covering the top 4 binades below the buffer's maximum; the highest boundary that
+// still keeps at least N keys becomes the cut, the keys below it are dropped, and tau becomes the
+// smallest surviving value (at least N better-or-earlier keys are held, so the strict `> tau`
+// test stays exact).  Leaves between N and N + (one bin) keys.  Falls back to the exact
+// selection when the binning cannot separate the keys (heavy ties, or the N-th key far below the
+// maximum).  Requires cnt > N.  All threads call it.
+static __device__ void sel_compact(Sel &s);
+static __device__ void sel_raise(Sel &s)
+{
+    SelCtl *c = s.c;
+    const int tid = threadIdx.x;
+    const int cnt = c->cnt;
+    const u64 *src = s.buf[c->cur];
+    u64 *dst = s.buf[c->cur ^ 1];
+    __syncthreads();
+    // maximum value (as ordered bits) in the buffer
+    unsigned mx = 0u;
+    for (int e = tid; e < cnt; e += kThreads) mx = max(mx, (unsigned)(src[e] >> 32));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = max(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+    if ((tid & 31) == 0) c->red[tid >> 5] = mx;
+    if (tid < 256) c->hist[tid] = 0;
+    __syncthreads();
+    if (tid < 32) {
+        mx = c->red[tid];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = max(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+        if (tid == 0) {
+            // 256 bins of 2^18 ordered-bit units (1/32 of a binade) below the maximum
+            const unsigned span = 256u << 18;
+            c->ord_lo = mx >= span ? mx - span + 1u : 0u;
+            c->shift = 18;
+            c->cnt2 = 0;
+            c->minkey = ~0ull;
+        }
+    }
+    __syncthreads();
+    const unsigned lo = c->ord_lo;
+    const int sh = c->shift;
+    for (int e = tid; e < cnt; e += kThreads) {
+        const unsigned o = (unsigned)(src[e] >> 32);
+        const unsigned b = o >= lo ? min((o - lo) >> sh, 255u) : 0u;
+        atomicAdd(&c->hist[b], 1u);
+    }
+    __syncthreads();
+    if (tid < 32) {
+        unsigned h[8];
+        unsigned local = 0;
+#pragma unroll
+        for (int j = 0; j < 8; j++) { h[j] = c->hist[tid * 8 + j]; local += h[j]; }
+        unsigned run = local;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            unsigned t = __shfl_down_sync(0xFFFFFFFFu, run, o);
+            if (tid + o < 32) run += t;
+        }
+        const unsigned above = run - local;
+        const unsigned want = (unsigned)s.n;
+        if (above < want && want <= above + local) {
+            unsigned acc = above;
+            for (int j = 7; j >= 0; --j) {
+                if (want <= acc + h[j]) { c->cut = tid * 8 + j; c->want = (int)(acc + h[j]); break; }
+                acc += h[j];
+            }
+        }
+    }
+    __syncthreads();
+    const int cut = c->cut;
+    const int kept = c->want;  // keys in bins >= cut
+    if (cut == 0 || kept > s.n + ((s.cap - s.n) >> 2)) {
+        // bin 0 collects everything below the window, and a crowded boundary bin means ties:
+        // let the exact selection handle those
+        sel_compact(s);
+        return;
+    }
+    u64 mymin = ~0ull;
+    for (int e = tid; e < cnt; e += kThreads) {
+        const u64 k = src[e];
+        const unsigned o = (unsigned)(k >> 32);
+        const unsigned b = o >= lo ? min((o - lo) >> sh, 255u) : 0u;
+        if ((int)b >= cut) {
+            int slot = atomicAdd(&c->cnt2, 1);
+            dst[slot] = k;
+            if (k < mymin) mymin = k;
+        }
+    }
+    if (mymin != ~0ull) atomicMin(&c->minkey, mymin);
+    __syncthreads();
+    if (tid == 0) {
+        c->cnt = c->cnt2;
+        c->cur ^= 1;
+        c->tau = key_val(c->minkey);
+    }
+    __syncthreads();
+}
+
 // Appends the caller's up-to-4 passing elements; exact (counted) form used when room is short.
 static __device__ __forceinline__ void sel_append_exact(Sel &s, const float v[4], const int idx[4], int end)
 {
     SelCtl *c = s.c;
-    for (;;) {
+    for (int attempt = 0;; attempt++) {
         const float tau = c->tau;
         int n = 0;
 #pragma unroll
@@ -241,7 +342,9 @@ static __device__ __forceinline__ void sel_append_exact(Sel &s, const float v[4]
         __syncthreads();
         if (threadIdx.x == 0) c->tmp = 0;
         if (cnt + total > s.cap) {
-            sel_compact(s);  // cnt > N here because cap >= N + kSubTile >= N + total
+            // cnt > N here because cap >= N + kSubTile >= N + total; the exact selection leaves
+            // exactly N keys, after which a sub-tile always fits
+            if (attempt == 0) sel_raise(s); else sel_compact(s);
             continue;
         }
         if (n) {
@@ -256,52 +359,110 @@ static __device__ __forceinline__ void sel_append_exact(Sel &s, const float v[4]
     }
 }
 
+// token index of element e of sub-step u in the iteration starting at base (see load_items)
+template <int VEC>
+static __device__ __forceinline__ int item_index(int base, int u, int e)
+{
+    return VEC == 4 ? base + (u * kThreads + (int)threadIdx.x) * 4 + e
+                    : base + (u * 4 + e) * kThreads + (int)threadIdx.x;
+}
+
+template <int VEC, bool BF16>
+static __device__ __forceinline__ void sel_load_iter(const void *rowp, const uint32_t *mrow, int base, int end,
+                                                     float v[4][4])
+{
+    int idx[4];
+#pragma unroll
+    for (int u = 0; u < 4; u++) load_items<VEC, BF16, true>(rowp, mrow, base, u, end, v[u], idx);
+}
+
+// filters one 16384-element iteration into the buffer; returns with the block in step
+template <int VEC>
+static __device__ __forceinline__ void sel_process_iter(Sel &s, const float v[4][4], int base, int end, int &cnt0)
+{
+    SelCtl *c = s.c;
+    const float tau = c->tau;
+    int n = 0;
+#pragma unroll
+    for (int u = 0; u < 4; u++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) n += (v[u][e] > tau) ? 1 : 0;  // out of range reads -inf
+    if (n) {
+        int slot = atomicAdd(&c->cnt, n);
+        if (slot + n > s.cap) {
+            c->overflow = 1;
+        } else {
+            u64 *b = s.buf[c->cur];
+#pragma unroll
+            for (int u = 0; u < 4; u++)
+#pragma unroll
+                for (int e = 0; e < 4; e++)
+                    if (v[u][e] > tau) b[slot++] = make_key(v[u][e], item_index<VEC>(base, u, e) + s.idx_off);
+        }
+    }
+    __syncthreads();
+    if (c->overflow) {
+        __syncthreads();
+        if (threadIdx.x == 0) { c->cnt = cnt0; c->overflow = 0; }
+        __syncthreads();
+        if (c->cnt > s.n) sel_raise(s);
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            int idx[4];
+#pragma unroll
+            for (int e = 0; e < 4; e++) idx[e] = item_index<VEC>(base, u, e);
+            sel_append_exact(s, v[u], idx, end);
+        }
+    } else if (c->cnt > s.n + ((s.cap - s.n) >> 1)) {
+        // keep head-room so that the optimistic append rarely has to be rolled back
+        sel_raise(s);
+    }
+    cnt0 = c->cnt;
+    __syncthreads();
+}
+
 // Streams elements [begin, end) of one row through the selection.  Elements are visited in
 // ascending token order per 16384-element iteration, which is what makes the strict `> tau` test
 // exact: an element equal to the N-th best value arrives after N better-or-earlier ones.
+// The first 4096 elements are appended exactly and tau raised from them, so that it is a real
+// bound before the bulk arrives; after that the loads of the next iteration are issued before the
+// current one is filtered (two iterations, 128 KB, in flight per CTA).  On return the buffer
+// holds a superset of the best N keys of the range, at most 2N of them.
 template <int VEC, bool BF16>
 static __device__ void sel_stream(Sel &s, const void *rowp, const uint32_t *mrow, int begin, int end)
 {
     SelCtl *c = s.c;
-    constexpr int U = 4;
-    int cnt0 = c->cnt;
-    for (int base = begin; base < end; base += kThreads * 4 * U) {
-        float v[U][4];
-        int idx[U][4];
-#pragma unroll
-        for (int u = 0; u < U; u++) load_items<VEC, BF16, true>(rowp, mrow, base, u, end, v[u], idx[u]);
-        const float tau = c->tau;
-        int n = 0;
-#pragma unroll
-        for (int u = 0; u < U; u++)
-#pragma unroll
-            for (int e = 0; e < 4; e++) n += (v[u][e] > tau) ? 1 : 0;  // out of range reads -inf
-        if (n) {
-            int slot = atomicAdd(&c->cnt, n);
-            if (slot + n > s.cap) {
-                c->overflow = 1;
-            } else {
-                u64 *b = s.buf[c->cur];
-#pragma unroll
-                for (int u = 0; u < U; u++)
-#pragma unroll
-                    for (int e = 0; e < 4; e++)
-                        if (v[u][e] > tau) b[slot++] = make_key(v[u][e], idx[u][e] + s.idx_off);
-            }
-        }
-        __syncthreads();
-        if (c->overflow) {
-            __syncthreads();
-            if (threadIdx.x == 0) { c->cnt = cnt0; c->overflow = 0; }
-            __syncthreads();
-            if (c->cnt > s.n) sel_compact(s);
-#pragma unroll
-            for (int u = 0; u < U; u++) sel_append_exact(s, v[u], idx[u], end);
-        }
-        cnt0 = c->cnt;
-        __syncthreads();
+    constexpr int STEP = kThreads * 16;
+    const int first_end = min(end, begin + kSubTile);
+    {
+        float v[4];
+        int idx[4];
+        load_items<VEC, BF16, true>(rowp, mrow, begin, 0, first_end, v, idx);
+        sel_append_exact(s, v, idx, first_end);
+        if (c->cnt > s.n) sel_raise(s);
     }
-    if (c->cnt > s.n) sel_compact(s);
+    int cnt0 = c->cnt;
+    int base = first_end;
+    if (base < end) {
+        float va[4][4], vb[4][4];
+        sel_load_iter<VEC, BF16>(rowp, mrow, base, end, va);
+        for (;;) {
+            int nb = base + STEP;
+            bool more = nb < end;
+            if (more) sel_load_iter<VEC, BF16>(rowp, mrow, nb, end, vb);
+            sel_process_iter<VEC>(s, va, base, end, cnt0);
+            if (!more) break;
+            base = nb;
+            nb = base + STEP;
+            more = nb < end;
+            if (more) sel_load_iter<VEC, BF16>(rowp, mrow, nb, end, va);
+            sel_process_iter<VEC>(s, vb, base, end, cnt0);
+            if (!more) break;
+            base = nb;
+        }
+    }
+    if (c->cnt > 2 * s.n) sel_raise(s);
+    if (c->cnt > 2 * s.n) sel_compact(s);
 }
 
 // Appends `count` keys from global memory (another chunk's survivors).
@@ -311,7 +472,7 @@ static __device__ void sel_append_keys(Sel &s, const u64 *keys, int count)
     for (int base = 0; base < count; base += kSubTile) {
         int m = min(kSubTile, count - base);
         __syncthreads();
-        if (c->cnt + m > s.cap) sel_compact(s);
+        if (c->cnt + m > s.cap) sel_raise(s);
         u64 *b = s.buf[c->cur];
         const int cnt = c->cnt;
         __syncthreads();
@@ -320,7 +481,8 @@ static __device__ void sel_append_keys(Sel &s, const u64 *keys, int count)
         if (threadIdx.x == 0) c->cnt = cnt + m;
         __syncthreads();
     }
-    if (c->cnt > s.n) sel_compact(s);
+    if (c->cnt > 2 * s.n) sel_raise(s);
+    if (c->cnt > 2 * s.n) sel_compact(s);
 }
 
 // ---- block-wide bitonic sort, descending, of `p2` (power of two) 64-bit keys in shared memory --
@@ -338,6 +500,19 @@ static __device__ void bitonic_sort_desc(u64 *a, int p2)
             __syncthreads();
         }
     }
+}
+
+// descending rank sort of `cnt` distinct keys from src into dst (quadratic work, two barriers):
+// cheaper than the bitonic network for the few hundred candidates of a typical row
+static __device__ void rank_sort_desc(const u64 *src, u64 *dst, int cnt)
+{
+    for (int t = threadIdx.x; t < cnt; t += kThreads) {
+        const u64 k = src[t];
+        int rank = 0;
+        for (int j = 0; j < cnt; j++) rank += (src[j] > k) ? 1 : 0;
+        dst[rank] = k;
+    }
+    __syncthreads();
 }
 
 static __device__ __forceinline__ int pow2_ceil(int n)
@@ -386,7 +561,7 @@ static __device__ void finish_topk(Sel &s, const RowPlan &rp, const int32_t *his
 {
     SelCtl *c = s.c;
     const int tid = threadIdx.x;
-    const int cnt = c->cnt;
+    int cnt = c->cnt;
     u64 *a = s.buf[c->cur];
     u64 *b = s.buf[c->cur ^ 1];
     const int k = rp.top_k;
@@ -401,35 +576,85 @@ static __device__ void finish_topk(Sel &s, const RowPlan &rp, const int32_t *his
         __syncthreads();
         return;
     }
+    // raw order (Sampler.cs:242-249): descending value, ascending token on ties
+    const bool small = cnt <= 192;  // the quadratic rank sort only wins for a handful of keys
     const int p2 = pow2_ceil(max(cnt, 2));
-    for (int t = cnt + tid; t < p2; t += kThreads) a[t] = 0ull;
-    __syncthreads();
-    bitonic_sort_desc(a, p2);
+    u64 *raw;    // sorted raw candidates
+    u64 *work;   // the other buffer
+    if (small) {
+        rank_sort_desc(a, b, cnt);
+        raw = b; work = a;
+    } else {
+        for (int t = cnt + tid; t < p2; t += kThreads) a[t] = 0ull;
+        __syncthreads();
+        bitonic_sort_desc(a, p2);
+        raw = a; work = b;
+    }
+    u64 *pen = work;  // sorted penalised keys when has_penalty
+    const int m_all = cnt;
+    cnt = min(cnt, sel);  // the reference's candidates: the best `sel` raw logits (Sampler.cs:225)
 
     if (rp.has_penalty) {
         // penalise each candidate (Sampler.cs:263-287), then stable re-sort by penalised value
-        // (Sampler.cs:289-294): key = (penalised value, raw rank)
-        for (int t = tid; t < p2; t += kThreads) {
+        // (Sampler.cs:289-294): key = (penalised value, raw rank).  Occurrence counts come from a
+        // hash of the history built once (token -> count, count inside the window) when it fits
+        // behind the keys, else from a scan of the history per candidate.
+        u64 *unsorted = small ? raw + m_all : work;
+        const int m = small ? cnt : p2;
+        int hslots = 64;
+        while (hslots < 2 * rp.hist_len) hslots <<= 1;
+        int *hkey = (int *)(unsorted + m);
+        int *hall = hkey + hslots, *hwin = hall + hslots;
+        const bool use_hash = (char *)(hwin + hslots) <= (char *)(s.buf[unsorted >= s.buf[1] ? 1 : 0] + s.cap);
+        if (use_hash) {
+            for (int t = tid; t < hslots; t += kThreads) { hkey[t] = -1; hall[t] = 0; hwin[t] = 0; }
+            __syncthreads();
+            for (int t = tid; t < rp.hist_len; t += kThreads) {
+                const int id = __ldg(hist + t);
+                if (id < 0) continue;  // never a candidate, and -1 marks an empty slot
+                int h = (int)(((unsigned)id * 2654435761u) >> 7) & (hslots - 1);
+                for (;;) {
+                    int old = atomicCAS(&hkey[h], -1, id);
+                    if (old == -1 || old == id) break;
+                    h = (h + 1) & (hslots - 1);
+                }
+                atomicAdd(&hall[h], 1);
+                if (t >= rp.window_start) atomicAdd(&hwin[h], 1);
+            }
+            __syncthreads();
+        }
+        for (int t = tid; t < m; t += kThreads) {
             u64 key2 = 0ull;
             if (t < cnt) {
-                float v = key_val(a[t]);
-                int id = key_idx(a[t]);
-                int occ_all, occ_w;
-                count_occurrences(hist, rp.hist_len, rp.window_start, id, occ_all, occ_w);
+                float v = key_val(raw[t]);
+                int id = key_idx(raw[t]);
+                int occ_all = 0, occ_w = 0;
+                if (use_hash) {
+                    int h = (int)(((unsigned)id * 2654435761u) >> 7) & (hslots - 1);
+                    for (;;) {
+                        const int kx = hkey[h];
+                        if (kx == id) { occ_all = hall[h]; occ_w = hwin[h]; break; }
+                        if (kx == -1) break;
+                        h = (h + 1) & (hslots - 1);
+                    }
+                } else {
+                    count_occurrences(hist, rp.hist_len, rp.window_start, id, occ_all, occ_w);
+                }
                 if (occ_all > 0) {
                     if (rp.rep != 1.0f && occ_w > 0) {
-                        float pen = pow_rep(pow_tab, rp.rep, occ_w);
-                        v = v > 0.f ? __fdiv_rn(v, pen) : __fmul_rn(v, pen);
+                        float pw = pow_rep(pow_tab, rp.rep, occ_w);
+                        v = v > 0.f ? __fdiv_rn(v, pw) : __fmul_rn(v, pw);
                     }
                     float add = __fadd_rn(rp.pres, __fmul_rn(rp.freq, (float)occ_all));
                     v = __fsub_rn(v, add);
                 }
                 key2 = ((u64)ord32(v) << 32) | (u64)(0xFFFFFFFFu - (uint32_t)t);
             }
-            b[t] = key2;
+            unsorted[t] = key2;
         }
         __syncthreads();
-        bitonic_sort_desc(b, p2);
+        if (small) rank_sort_desc(unsorted, work, cnt);
+        else bitonic_sort_desc(work, p2);
     }
 
     // first k candidates -> registers -> compact arrays over the buffer that is no longer needed
@@ -443,18 +668,18 @@ static __device__ void finish_topk(Sel &s, const RowPlan &rp, const int32_t *his
         ri[j] = -1;
         if (t < k && t < cnt) {
             if (rp.has_penalty) {
-                u64 k2 = b[t];
+                u64 k2 = pen[t];
                 int raw_rank = (int)(0xFFFFFFFFu - (uint32_t)k2);
                 rv[j] = unord32((uint32_t)(k2 >> 32));
-                ri[j] = key_idx(a[raw_rank]);
+                ri[j] = key_idx(raw[raw_rank]);
             } else {
-                rv[j] = key_val(a[t]);
-                ri[j] = key_idx(a[t]);
+                rv[j] = key_val(raw[t]);
+                ri[j] = key_idx(raw[t]);
             }
         }
     }
     __syncthreads();
-    float *vals = (float *)b;
+    float *vals = (float *)work;
     int *ids = (int *)(vals + k);
     float *probs = (float *)(ids + k);
     const float inv_t = rp.temperature == 1.0f ? 1.0f : __fdiv_rn(1.0f, rp.temperature);

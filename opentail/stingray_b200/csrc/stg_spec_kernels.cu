@@ -34,7 +34,7 @@ __device__ __forceinline__ float eval_point(const void *rowp, int i, const RowDi
 template <bool BF16>
 struct ProvRow {
     SrcLogits<BF16> src;
-    const RowDist *d;
+    RowDist d;  // by value: lives in registers
     __device__ __forceinline__ void load(int base, int n, float x[8]) const
     {
         if (base >= n) {
@@ -42,18 +42,19 @@ struct ProvRow {
             for (int j = 0; j < 8; j++) x[j] = 0.f;
             return;
         }
-        if (d->flags & kDistOneHot) {
+        if (d.flags & kDistOneHot) {
 #pragma unroll
-            for (int j = 0; j < 8; j++) x[j] = (base + j == d->tie_idx_max) ? 1.f : 0.f;
+            for (int j = 0; j < 8; j++) x[j] = (base + j == d.tie_idx_max) ? 1.f : 0.f;
             return;
         }
         src.get8(base, n, x);
 #pragma unroll
         for (int j = 0; j < 8; j++) {
-            float e = (d->flags & kDistUniform) ? d->uniform_p : expf(__fsub_rn(x[j], d->max_x));
-            x[j] = (base + j < n) ? eval_p3(e, base + j, *d) : 0.f;
+            float e = (d.flags & kDistUniform) ? d.uniform_p : expf(__fsub_rn(x[j], d.max_x));
+            x[j] = (base + j < n) ? eval_p3(e, base + j, d) : 0.f;
         }
     }
+    __device__ __forceinline__ void reload(int base, int n, float x[8]) const { load(base, n, x); }
 };
 
 // positive part of p - q (ResampleResidual's terms)
@@ -71,10 +72,12 @@ struct ProvResidual {
             x[j] = r > 0.f ? r : 0.f;
         }
     }
+    __device__ __forceinline__ void reload(int base, int n, float x[8]) const { load(base, n, x); }
 };
 
 struct SpecShared {
     EmulCtl em;
+    Emul2Ctl em2;
     int accepted;
     int red_i[32];
 };
@@ -83,6 +86,8 @@ template <bool BF16>
 __global__ void __launch_bounds__(kThreads, 1) k_spec_finish(const __grid_constant__ SpecArgs a)
 {
     __shared__ SpecShared sh;
+    extern __shared__ __align__(16) unsigned char spec_dyn[];
+    Emul2Work *wk2 = (Emul2Work *)spec_dyn;
     const int tid = threadIdx.x;
     const int s = blockIdx.x;
     const int L = a.n_draft, V = a.vocab;
@@ -134,28 +139,28 @@ __global__ void __launch_bounds__(kThreads, 1) k_spec_finish(const __grid_consta
     } else {
         const bool al = a.vec == 4;
         const void *prow = trows + (int64_t)acc * V * esz;
-        ProvRow<BF16> pp{SrcLogits<BF16>{prow, nullptr, al, td[acc].inv_t, td[acc].inv_t != 1.0f}, &td[acc]};
+        ProvRow<BF16> pp{SrcLogits<BF16>{prow, nullptr, al, td[acc].inv_t, td[acc].inv_t != 1.0f}, td[acc]};
         const float u0 = __double2float_rn(u[L]);
         const float u1 = __double2float_rn(u[L + 1]);
         float cum;
         if (acc == L || a.mode == 1) {
             // bonus draw from the last target row (:555-559), or a draw from p after a looser-rule
             // rejection (:552): SampleFromDistribution, Sampler.cs:564-576
-            corr = emul_scan<ProvRow<BF16>, false>(&sh.em, pp, V, u0, true, &cum);
+            corr = emul_any<ProvRow<BF16>, false>(&sh.em, &sh.em2, wk2, pp, V, u0, true, &cum);
             if (corr < 0) { corr = V - 1; fl |= (1u << 5); }
         } else {
             const void *qrow = drows + (int64_t)acc * V * esz;
-            ProvRow<BF16> qq{SrcLogits<BF16>{qrow, nullptr, al, dd[acc].inv_t, dd[acc].inv_t != 1.0f}, &dd[acc]};
+            ProvRow<BF16> qq{SrcLogits<BF16>{qrow, nullptr, al, dd[acc].inv_t, dd[acc].inv_t != 1.0f}, dd[acc]};
             ProvResidual<BF16> rr{pp, qq};
             float sum;
-            emul_scan<ProvResidual<BF16>, true>(&sh.em, rr, V, 0.f, false, &sum);
+            emul_any<ProvResidual<BF16>, true>(&sh.em, &sh.em2, wk2, rr, V, 0.f, false, &sum);
             if (sum <= 0.f || isnan(sum)) {
-                corr = emul_scan<ProvRow<BF16>, false>(&sh.em, pp, V, u0, true, &cum);
+                corr = emul_any<ProvRow<BF16>, false>(&sh.em, &sh.em2, wk2, pp, V, u0, true, &cum);
                 if (corr < 0) { corr = V - 1; fl |= (1u << 5); }
                 fl |= (1u << 8);  // empty residual
             } else {
                 const float target = __fmul_rn(u0, sum);
-                corr = emul_scan<ProvResidual<BF16>, true>(&sh.em, rr, V, target, true, &cum);
+                corr = emul_any<ProvResidual<BF16>, true>(&sh.em, &sh.em2, wk2, rr, V, target, true, &cum);
                 if (corr < 0) {
                     // rounding fallback: the last token with a positive residual
                     int lastp = -1;
@@ -177,7 +182,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_spec_finish(const __grid_consta
                     if (lastp >= 0) {
                         corr = lastp;
                     } else {
-                        corr = emul_scan<ProvRow<BF16>, false>(&sh.em, pp, V, u1, true, &cum);
+                        corr = emul_any<ProvRow<BF16>, false>(&sh.em, &sh.em2, wk2, pp, V, u1, true, &cum);
                         if (corr < 0) corr = V - 1;
                     }
                 }
@@ -193,8 +198,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_spec_finish(const __grid_consta
 
 cudaError_t launch_spec_finish(const SpecArgs &a, cudaStream_t stream)
 {
-    if (a.dtype == 1) k_spec_finish<true><<<a.n_seq, kThreads, 0, stream>>>(a);
-    else k_spec_finish<false><<<a.n_seq, kThreads, 0, stream>>>(a);
+    if (a.dtype == 1) k_spec_finish<true><<<a.n_seq, kThreads, sizeof(Emul2Work), stream>>>(a);
+    else k_spec_finish<false><<<a.n_seq, kThreads, sizeof(Emul2Work), stream>>>(a);
     return cudaGetLastError();
 }
 

@@ -12,7 +12,7 @@ constexpr int kEmulItems = 8;           // consecutive elements per thread in th
 constexpr int kEmulTile = kThreads * kEmulItems;
 constexpr int kSortCap = 32768;         // top-p candidate keys sorted in shared memory
 constexpr int kHistBins = 4096;         // probability histogram bins (exponent + 4 mantissa bits)
-constexpr int kMaxOverride = 16384;     // history + bias entries per row on the full-vocabulary path
+constexpr int kMaxOverride = 2048;      // history + bias entries per row on the full-vocabulary path
 
 enum Path : int32_t {
     kPathGreedy = 0,        // Sampler.Greedy
@@ -83,6 +83,7 @@ struct SampleArgs {
     int32_t *cand_count;             // per (row, chunk) entry counts
     uint32_t *tickets;               // per-row arrival counters (self-resetting)
     uint32_t *work_counter;
+    unsigned long long *phase_ticks; // diagnostic: 32 globaltimer stamps per work item, or null
     float *escratch;                 // per-CTA exp scratch rows [grid, escratch_stride]
     unsigned long long *keyscratch;  // per-CTA wide-nucleus key scratch [grid, key_stride]
     RowDist *dists;                  // per-row distribution descriptors (optional output)
@@ -95,6 +96,7 @@ struct SampleArgs {
     int64_t key_stride;
     uint32_t work_base;
     int32_t n_items;
+    int32_t item_base;               // index of this launch's first item in the step's item list
     int32_t rows, vocab, dtype, topk_stride;
     int32_t chunk_len;               // elements per chunk work item (multiple of kSubTile)
     int32_t cap;                     // entries per candidate buffer in shared memory
@@ -104,5 +106,17 @@ struct SampleArgs {
     int32_t shard_mode;              // 0 off, 1 select only (write candidates), 2 finish from gather
     int32_t n_ranks;
 };
+
+#ifdef __CUDACC__
+// diagnostic time stamp (nanoseconds) of phase k of the current work item; a no-op when disabled
+__device__ __forceinline__ void tick(unsigned long long *t, int k)
+{
+    if (t != nullptr && threadIdx.x == 0) {
+        unsigned long long v;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(v));
+        t[k] = v;
+    }
+}
+#endif
 
 }  // namespace stg
