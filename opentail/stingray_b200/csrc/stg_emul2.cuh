@@ -201,9 +201,13 @@ __device__ __forceinline__ int replay_subtile(const float x[8], int base, int n,
 // against replay_ok[sub-tile]; when that says 0 the scan stops and returns -2 with the sub-tile in
 // c->abort_at, so that the caller can order that part and run again.
 template <class Prov, bool POS_ONLY, bool FORCE, int UN = 2>
-__device__ int emul_scan2(Emul2Ctl *c, Emul2Work *wk, const Prov &pv, int n, float target, bool has_target,
-                          float *sum_out, const unsigned char *replay_ok, unsigned long long *tk)
+__device__ __noinline__ int emul_scan2(Emul2Ctl *c, Emul2Work *wk, const Prov &pv_in, int n, float target,
+                                       bool has_target, float *sum_out, const unsigned char *replay_ok,
+                                       unsigned long long *tk)
 {
+    // out of line, with its own copy of the provider: the loops below then get a register
+    // allocation of their own instead of sharing one with the caller's other phases
+    const Prov pv = pv_in;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int nsub = (n + kSub - 1) / kSub;
     __syncthreads();
@@ -332,6 +336,21 @@ __device__ int emul_scan2(Emul2Ctl *c, Emul2Work *wk, const Prov &pv, int n, flo
                 t += ok;
             }
             if (ok < 32 && t < nsub) {
+                if (wk->guess[t] != eb && !(wk->sums[t] == 0.0)) {
+                    // the binade was guessed wrongly for this sub-tile (it follows a crossing closely):
+                    // its composite under the actual binade needs no order, so recompute it and retry
+                    float x[8];
+                    pv.reload(t * kSub + lane * 8, n, x);
+                    if (POS_ONLY) {
+#pragma unroll
+                        for (int j = 0; j < 8; j++) x[j] = x[j] > 0.f ? x[j] : 0.f;
+                    }
+                    int a0, a1;
+                    subtile_composite<FORCE>(x, eb, a0, a1);
+                    if (lane == 0) { wk->comp[t][0] = a0; wk->comp[t][1] = a1; wk->guess[t] = eb; }
+                    __syncwarp();
+                    continue;
+                }
                 if (FORCE && replay_ok != nullptr && !replay_ok[t]) { abort_at = t; break; }
                 float x[8];
                 pv.reload(t * kSub + lane * 8, n, x);

@@ -500,13 +500,15 @@ static __device__ float pass_adjust(const SrcLogits<BF16> &raw, const OvTable &o
         for (int h = 0; h < 2; h++) {
             const int b = h ? b1 : base;
             if (b >= n) break;
-            unsigned m = ov.bitmap[(b & 0xFFFF) >> 3];
-            while (m) {
-                int j = __ffs(m) - 1;
-                m &= m - 1;
-                if (b + j < n) {
-                    int slot = ov.find(b + j);
-                    if (slot >= 0) x[h][j] = ov.adj[slot];
+            const unsigned m = ov.bitmap[(b & 0xFFFF) >> 3];
+            if (m) {
+                // static indices only: a runtime index would push the whole array into local memory
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    if (((m >> j) & 1u) && b + j < n) {
+                        int slot = ov.find(b + j);
+                        if (slot >= 0) x[h][j] = ov.adj[slot];
+                    }
                 }
             }
 #pragma unroll
@@ -520,6 +522,16 @@ static __device__ float pass_adjust(const SrcLogits<BF16> &raw, const OvTable &o
     return block_max_float(best, red);
 }
 
+template <bool BF16>
+static __device__ __noinline__ float adjust_row(const SampleArgs &a, const RowPlan &rp, const SrcLogits<BF16> &raw, int n,
+                                                bool with_hist, bool with_bias, unsigned char *arena, int slots,
+                                                float inv_t, bool scale, float *scratch, float *red)
+{
+    OvTable ov;
+    build_overrides<BF16>(a, rp, raw.rowp, raw.mrow, n, with_hist, with_bias, ov, arena, slots);
+    return pass_adjust<BF16>(raw, ov, inv_t, scale, n, scratch, red);
+}
+
 // mass of a histogram bin in exp-value units: every value in bin b has the biased exponent b >> 5, and
 // hmass holds the sum of the top 12 bits of their 24-bit mantissas
 __device__ __forceinline__ double bin_mass(const unsigned *hmass, int b)
@@ -529,32 +541,42 @@ __device__ __forceinline__ double bin_mass(const unsigned *hmass, int b)
 }
 
 // ---- top-p over a partially ordered candidate list ---------------------------------------------------
-// rank-sorts (descending) every bin on the dirty list, kDirtyRound elements per round
+// rank-sorts (descending) every bin on the dirty list.  The bins are taken in rounds of whole bins
+// holding at most kDirtyRound keys together (the sort is in place, so a bin must not be split over
+// rounds); a single bin larger than that makes the caller give the partial order up.
 static __device__ void sort_dirty_bins(RowCtl *rc, uint32_t *keys, const unsigned *bstart, const unsigned *hcount,
                                        uint32_t *tmp_key, int *tmp_dst)
 {
     const int tid = threadIdx.x;
-    const int nd = rc->n_dirty;
+    const int nd = min(rc->n_dirty, kMaxDirty);
     __syncthreads();
-    if (tid == 0) {
-        int acc = 0;
-        for (int i = 0; i < nd; i++) { rc->dirty_cum[i] = acc; acc += (int)hcount[rc->dirty[i]]; }
-        rc->dirty_cum[nd] = acc;
-    }
-    __syncthreads();
-    const int total = rc->dirty_cum[nd];
-    for (int round0 = 0; round0 < total; round0 += kDirtyRound) {
-        const int m = min(kDirtyRound, total - round0);
+    int first = 0;
+    while (first < nd) {
+        // round: bins first .. last-1
+        if (tid == 0) {
+            int acc = 0, i = first;
+            for (; i < nd; i++) {
+                const int c = (int)hcount[rc->dirty[i]];
+                if (acc + c > kDirtyRound) break;
+                rc->dirty_cum[i] = acc;
+                acc += c;
+            }
+            if (i == first) { rc->give_up = 1; i = nd; acc = 0; }  // one bin alone is too large
+            rc->dirty_cum[i] = acc;
+            rc->running = i;
+        }
+        __syncthreads();
+        const int last = rc->running;
+        const int m = rc->give_up ? 0 : rc->dirty_cum[last];
         for (int e = tid; e < m; e += kThreads) {
-            const int g = round0 + e;
-            int lo = 0, hi = nd;  // last i with dirty_cum[i] <= g
+            int lo = first, hi = last;  // last i in [first, last) with dirty_cum[i] <= e
             while (hi - lo > 1) {
                 int mid = (lo + hi) >> 1;
-                if (rc->dirty_cum[mid] <= g) lo = mid; else hi = mid;
+                if (rc->dirty_cum[mid] <= e) lo = mid; else hi = mid;
             }
             const int b = rc->dirty[lo];
             const int off = (int)bstart[b], cnt = (int)hcount[b];
-            const int pos = g - rc->dirty_cum[lo];
+            const int pos = e - rc->dirty_cum[lo];
             const uint32_t k = keys[off + pos];
             int rank = 0;
             for (int j = 0; j < cnt; j++) {
@@ -567,6 +589,7 @@ static __device__ void sort_dirty_bins(RowCtl *rc, uint32_t *keys, const unsigne
         __syncthreads();
         for (int e = tid; e < m; e += kThreads) keys[tmp_dst[e]] = tmp_key[e];
         __syncthreads();
+        first = last;
     }
 }
 
@@ -595,67 +618,14 @@ __device__ __forceinline__ double scan4_double(double tot, RowCtl *rc)  // inclu
     return run + (warp ? rc->red_d[warp - 1] : 0.0);
 }
 
-// ---- the distribution of one row --------------------------------------------------------------------
-// Leaves the exp values in `scratch` and the descriptor in rc->dist.  `src` yields the adjusted,
-// temperature-scaled logits; `mx_known` is their maximum when the caller already has it.
-template <class Src>
-static __device__ void build_dist(RowCtl *rc, SelCtl *sctl, const Src &src, const RowPlan &rp, int n,
-                                  float *scratch, unsigned char *arena, uint32_t *gkeys, int gkeys_cap,
-                                  uint32_t *flags_out, u64 *tk, bool have_max, float mx_known)
+// top-k of the full-vocabulary pipeline (ApplyTopK + Normalize); updates rc->dist.  Out of line
+// for the same reason as topp_cut.
+static __device__ __noinline__ void topk_cut(RowCtl *rc, SelCtl *sctl, const RowPlan &rp, int n, const float *scratch,
+                                             unsigned char *arena)
 {
     const int tid = threadIdx.x;
-    uint32_t *skeys = (uint32_t *)(arena + kOffKeys);
-    unsigned *hcount = (unsigned *)(arena + kOffCount);
-    unsigned *hmass = (unsigned *)(arena + kOffMass);
-    unsigned *bstart = (unsigned *)(arena + kOffBinOff);
-    Emul2Work *wk2 = (Emul2Work *)(arena + kOffEmul);
-    unsigned char *replay_ok = arena + kOffReplayOk;
-    const bool want_topp = rp.top_p < 1.0f && rp.top_p > 0.f;
-    const bool want_minp = rp.min_p > 0.f;
-    const bool want_topk = rp.top_k > 0 && rp.top_k < n;
-
-    float mx;
-    if (have_max) {
-        mx = mx_known;
-    } else {
-        u64 mk = pass_max(src, n, rc->red_k);
-        mx = mk ? key_val(mk) : -CUDART_INF_F;
-    }
-    tick(tk, 2);
-    RowDist d;
-    d.flags = 0;
-    d.inv_t = src.inv_t;
-    d.tie_idx_max = INT_MAX;
-    d.kth = 0.f; d.inv2 = 1.f; d.minp_thr = 0.f; d.tstar = 0.f; d.inv3 = 1.f; d.inv1 = 1.f;
-    d.uniform_p = 0.f; d.sum_end = 0.f; d.argmax = 0;
-    if (want_topp) {
-        for (int t = tid; t < kBins; t += kThreads) { hcount[t] = 0u; hmass[t] = 0u; }
-    }
-    __syncthreads();
-    float sum = 0.f;
-    const bool uniform = !(mx > -CUDART_INF_F);  // also covers NaN
-    if (uniform) {
-        // Softmax's fully masked case (Sampler.cs:452-458): every token gets 1/V, no rescale
-        d.flags |= kDistUniform;
-        d.max_x = -CUDART_INF_F;
-        d.uniform_p = __fdiv_rn(1.0f, (float)n);
-        for (int i = tid; i < n; i += kThreads) __stcg(scratch + i, d.uniform_p);
-        if (want_topp && tid == 0) {
-            unsigned bin = __float_as_uint(d.uniform_p) >> kBinShift;
-            hcount[bin] = (unsigned)n;
-            hmass[bin] = (unsigned)min((unsigned long long)n * ((((unsigned long long)__float_as_uint(d.uniform_p) & 0x7FFFFFu) | 0x800000u) >> 12), 0xFFFFFFFFull);
-        }
-        __syncthreads();
-    } else {
-        d.max_x = mx;
-        ProvExp<Src> pe{src, mx, scratch, want_topp ? hcount : nullptr, hmass};
-        emul_any<ProvExp<Src>, false>(&rc->em, &rc->em2, wk2, pe, n, 0.f, false, &sum, tk ? tk + 12 : nullptr);
-        if (sum > 0.f && sum != 1.0f) { d.flags |= kDistScale1; d.inv1 = __fdiv_rn(1.0f, sum); }
-    }
-    __syncthreads();
-    tick(tk, 3);
-#ifndef NO_TOPK
-    if (want_topk) {
+    RowDist d = rc->dist;
+    {
         // ApplyTopK + Normalize (Sampler.cs:477-488, :71-81): the k-th largest probability, counted
         // with multiplicity; everything below it is dropped, ties at it all survive.  Selected on
         // the exp values, of which the probabilities are a monotone image.
@@ -689,19 +659,30 @@ static __device__ void build_dist(RowCtl *rc, SelCtl *sctl, const Src &src, cons
         if (s2 > 0.f && s2 != 1.0f) { d.flags |= kDistScale2; d.inv2 = __fdiv_rn(1.0f, s2); }
         __syncthreads();
     }
-#endif
-    tick(tk, 4);
-    if (want_minp) {
-        // ApplyMinP (Sampler.cs:493-503): the largest probability belongs to exp value 1 (or 1/V)
-        float emax = uniform ? d.uniform_p : 1.0f;
-        float pmax = (d.flags & kDistScale1) ? __fmul_rn(emax, d.inv1) : emax;
-        if (d.flags & kDistScale2) pmax = __fmul_rn(pmax, d.inv2);
-        d.minp_thr = __fmul_rn(rp.min_p, pmax);
-        d.flags |= kDistMinP;
-    }
+    __syncthreads();
+    if (tid == 0) rc->dist = d;
+    __syncthreads();
+}
 
+// top-p (ApplyTopP, Sampler.cs:516-551): finds the cut of the reference's sorted sequential
+// cumulative sum without sorting the vocabulary; updates rc->dist (tstar, tie_idx_max) and
+// returns the fp64 sum of the kept probabilities.  Kept out of line: it is long, runs once per
+// row, and would otherwise dominate the register allocation of the streaming phases around it.
+static __device__ __noinline__ double topp_cut(RowCtl *rc, const RowPlan &rp, int n, const float *scratch,
+                                               unsigned char *arena, uint32_t *gkeys, int gkeys_cap,
+                                               uint32_t *flags_out, u64 *tk)
+{
+    const int tid = threadIdx.x;
+    uint32_t *skeys = (uint32_t *)(arena + kOffKeys);
+    unsigned *hcount = (unsigned *)(arena + kOffCount);
+    unsigned *hmass = (unsigned *)(arena + kOffMass);
+    unsigned *bstart = (unsigned *)(arena + kOffBinOff);
+    Emul2Work *wk2 = (Emul2Work *)(arena + kOffEmul);
+    unsigned char *replay_ok = arena + kOffReplayOk;
+    RowDist d = rc->dist;
+    const bool uniform = (d.flags & kDistUniform) != 0;
     double sum3 = 0.0;
-    if (want_topp) {
+    {
         const double scale_p = ((d.flags & kDistScale1) ? (double)d.inv1 : 1.0) *
                                ((d.flags & kDistScale2) ? (double)d.inv2 : 1.0);
         for (int attempt = 0; attempt < 2; attempt++) {
@@ -833,7 +814,8 @@ static __device__ void build_dist(RowCtl *rc, SelCtl *sctl, const Src &src, cons
                         const double lo = before * (1.0 - 1.0 / 32768.0), hi = (before + loc[j]) * (1.0 + 1.0 / 2048.0);
                         const bool crosses = exp_of_double(lo) != exp_of_double(hi);
                         const bool cut = lo <= (double)rp.top_p && hi >= (double)rp.top_p;
-                        if (crosses || cut) {
+                        const bool head = bstart[b] < 2048u;  // the sum changes binade every few keys here
+                        if (crosses || cut || head) {
                             int slot = atomicAdd(&rc->n_dirty, 1);
                             if (slot < kMaxDirty) rc->dirty[slot] = (unsigned short)b; else rc->give_up = 1;
                         }
@@ -845,7 +827,10 @@ static __device__ void build_dist(RowCtl *rc, SelCtl *sctl, const Src &src, cons
             int hit = -1;
             float cum = 0.f;
             bool sorted_all = uniform;  // all keys equal: any order is sorted
+            tick(tk, 24);
+            if (tk && tid == 0) { tk[28] = (u64)rc->n_dirty; tk[29] = (u64)nc; tk[30] = 0; tk[31] = 0; }
             for (int pass = 0; pass < 64; pass++) {
+                if (tk && tid == 0) tk[30] = (u64)(pass + 1);
                 if (!sorted_all && (rc->give_up || pass == 63)) {
                     // partial order abandoned: sort the whole list
                     const int p2 = pow2_ceil(max(nc, 2));
@@ -854,7 +839,11 @@ static __device__ void build_dist(RowCtl *rc, SelCtl *sctl, const Src &src, cons
                     bitonic_sort_desc_t<uint32_t>(keys, p2);
                     sorted_all = true;
                 } else if (!sorted_all && rc->n_dirty > 0) {
+                    if (tk && tid == 0) tk[31] += 1;
                     sort_dirty_bins(rc, keys, bstart, hcount, (uint32_t *)wk2, (int *)wk2 + kDirtyRound);
+                    if (pass == 0) tick(tk, 25);
+                    __syncthreads();
+                    if (rc->give_up) continue;  // a bin was too large for the in-place sort: sort everything
                     for (int i = tid; i < min(rc->n_dirty, kMaxDirty); i += kThreads)
                         atomicOr(&rc->sorted_bits[rc->dirty[i] >> 5], 1u << (rc->dirty[i] & 31));
                     __syncthreads();
@@ -882,6 +871,7 @@ static __device__ void build_dist(RowCtl *rc, SelCtl *sctl, const Src &src, cons
                     if (!sorted_all) { if (tid == 0) rc->give_up = 1; __syncthreads(); continue; }
                     hit = emul_scan<ProvKeys, false>(&rc->em, pk, nc, rp.top_p, true, &cum);
                 }
+                if (pass == 0) tick(tk, 26);
                 if (hit != -2) break;
                 // the sum needed the internal order of an unsorted stretch: sort its bins and rerun
                 const int t_abort = rc->em2.abort_at;
@@ -920,7 +910,102 @@ static __device__ void build_dist(RowCtl *rc, SelCtl *sctl, const Src &src, cons
             }
             break;
         }
+    }
+    __syncthreads();
+    if (tid == 0) rc->dist = d;
+    __syncthreads();
+    return sum3;
+}
+
+// ---- the distribution of one row --------------------------------------------------------------------
+// Leaves the exp values in `scratch` and the descriptor in rc->dist.  `src` yields the adjusted,
+// temperature-scaled logits; `mx_known` is their maximum when the caller already has it.
+template <class Src>
+static __device__ void build_dist(RowCtl *rc, SelCtl *sctl, const Src &src, const RowPlan &rp, int n,
+                                  float *scratch, unsigned char *arena, uint32_t *gkeys, int gkeys_cap,
+                                  uint32_t *flags_out, u64 *tk, bool have_max, float mx_known)
+{
+    const int tid = threadIdx.x;
+    uint32_t *skeys = (uint32_t *)(arena + kOffKeys);
+    unsigned *hcount = (unsigned *)(arena + kOffCount);
+    unsigned *hmass = (unsigned *)(arena + kOffMass);
+    unsigned *bstart = (unsigned *)(arena + kOffBinOff);
+    Emul2Work *wk2 = (Emul2Work *)(arena + kOffEmul);
+    unsigned char *replay_ok = arena + kOffReplayOk;
+    const bool want_topp = rp.top_p < 1.0f && rp.top_p > 0.f;
+    const bool want_minp = rp.min_p > 0.f;
+    const bool want_topk = rp.top_k > 0 && rp.top_k < n;
+
+    float mx;
+    if (have_max) {
+        mx = mx_known;
     } else {
+        u64 mk = pass_max(src, n, rc->red_k);
+        mx = mk ? key_val(mk) : -CUDART_INF_F;
+    }
+    tick(tk, 2);
+    RowDist d;
+    d.flags = 0;
+    d.inv_t = src.inv_t;
+    d.tie_idx_max = INT_MAX;
+    d.kth = 0.f; d.inv2 = 1.f; d.minp_thr = 0.f; d.tstar = 0.f; d.inv3 = 1.f; d.inv1 = 1.f;
+    d.uniform_p = 0.f; d.sum_end = 0.f; d.argmax = 0;
+    if (want_topp) {
+        for (int t = tid; t < kBins; t += kThreads) { hcount[t] = 0u; hmass[t] = 0u; }
+    }
+    __syncthreads();
+    float sum = 0.f;
+    const bool uniform = !(mx > -CUDART_INF_F);  // also covers NaN
+    if (uniform) {
+        // Softmax's fully masked case (Sampler.cs:452-458): every token gets 1/V, no rescale
+        d.flags |= kDistUniform;
+        d.max_x = -CUDART_INF_F;
+        d.uniform_p = __fdiv_rn(1.0f, (float)n);
+        for (int i = tid; i < n; i += kThreads) __stcg(scratch + i, d.uniform_p);
+        if (want_topp && tid == 0) {
+            unsigned bin = __float_as_uint(d.uniform_p) >> kBinShift;
+            hcount[bin] = (unsigned)n;
+            hmass[bin] = (unsigned)min((unsigned long long)n * ((((unsigned long long)__float_as_uint(d.uniform_p) & 0x7FFFFFu) | 0x800000u) >> 12), 0xFFFFFFFFull);
+        }
+        __syncthreads();
+    } else {
+        d.max_x = mx;
+        ProvExp<Src> pe{src, mx, scratch, want_topp ? hcount : nullptr, hmass};
+        emul_any<ProvExp<Src>, false>(&rc->em, &rc->em2, wk2, pe, n, 0.f, false, &sum, tk ? tk + 12 : nullptr);
+        if (sum > 0.f && sum != 1.0f) { d.flags |= kDistScale1; d.inv1 = __fdiv_rn(1.0f, sum); }
+    }
+    __syncthreads();
+    tick(tk, 3);
+#ifndef NO_TOPK
+    if (want_topk) {
+        __syncthreads();
+        if (tid == 0) rc->dist = d;
+        __syncthreads();
+        topk_cut(rc, sctl, rp, n, scratch, arena);
+        d = rc->dist;
+    }
+#endif
+    tick(tk, 4);
+    if (want_minp) {
+        // ApplyMinP (Sampler.cs:493-503): the largest probability belongs to exp value 1 (or 1/V)
+        float emax = uniform ? d.uniform_p : 1.0f;
+        float pmax = (d.flags & kDistScale1) ? __fmul_rn(emax, d.inv1) : emax;
+        if (d.flags & kDistScale2) pmax = __fmul_rn(pmax, d.inv2);
+        d.minp_thr = __fmul_rn(rp.min_p, pmax);
+        d.flags |= kDistMinP;
+    }
+
+    double sum3 = 0.0;
+#ifndef NO_TOPP
+    if (want_topp) {
+        __syncthreads();
+        if (tid == 0) rc->dist = d;
+        __syncthreads();
+        sum3 = topp_cut(rc, rp, n, scratch, arena, gkeys, gkeys_cap, flags_out, tk);
+        d = rc->dist;
+    } else
+#endif
+    {
         double part = 0.0;
         for (int base = tid * 8; base < n; base += kThreads * 8) {
             float x[8];
@@ -972,17 +1057,17 @@ static __device__ void run_row(const SampleArgs &a, int row, int item, SelCtl *s
     const bool scale = !greedy && rp.temperature != 1.0f;
     SrcLogits<BF16> raw{rowp, mrow, a.vec == 4, 1.f, false};
     float mx = 0.f;
+#ifndef NO_OVERRIDES
     if (overrides) {
         // adjusted (and scaled) logits into the scratch row
         const int entries = (with_hist ? rp.hist_len : 0) + (with_bias ? rp.bias_len : 0);
         int slots = 64;
         while (slots < 2 * entries) slots <<= 1;
-        OvTable ov;
-        build_overrides<BF16>(a, rp, rowp, mrow, n, with_hist, with_bias, ov, arena, slots);
-        mx = pass_adjust<BF16>(raw, ov, inv_t, scale, n, scratch, rc.red_f);
+        mx = adjust_row<BF16>(a, rp, raw, n, with_hist, with_bias, arena, slots, inv_t, scale, scratch, rc.red_f);
         __threadfence_block();
         __syncthreads();
     }
+#endif
     tick(tk, 1);
 
     if (greedy) {

@@ -191,6 +191,7 @@ static __device__ void sel_compact(Sel &s)
             bool mine = above < want && want <= above + local;
             if (mine) {
                 unsigned acc = above;
+#pragma unroll
                 for (int j = 7; j >= 0; --j) {
                     if (want <= acc + h[j]) {
                         c->prefix = (prefix << 8) | (u64)(tid * 8 + j);
@@ -289,8 +290,10 @@ static __device__ void sel_raise(Sel &s)
         const unsigned want = (unsigned)s.n;
         if (above < want && want <= above + local) {
             unsigned acc = above;
+            bool found = false;
+#pragma unroll
             for (int j = 7; j >= 0; --j) {
-                if (want <= acc + h[j]) { c->cut = tid * 8 + j; c->want = (int)(acc + h[j]); break; }
+                if (!found && want <= acc + h[j]) { c->cut = tid * 8 + j; c->want = (int)(acc + h[j]); found = true; }
                 acc += h[j];
             }
         }
