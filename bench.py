@@ -53,7 +53,7 @@ def ncu_traffic(name: str):
     path = os.path.join(ROOT, "profiles", f"{name}.traffic.json")
     try:
         with open(path) as f:
-            return json.load(f)
+            return int(json.load(f)["bytes_per_step"])
     except Exception:
         return None
 
