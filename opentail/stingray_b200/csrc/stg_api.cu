@@ -353,6 +353,7 @@ int run_batch(StgHandle h, const StgSampleBatch *b, const BatchExtra &x, void *s
     h->ticks_items = (int)pl.items.size();
     a.escratch = (float *)h->escratch.p;
     a.keyscratch = (unsigned long long *)h->keyscratch.p;
+    a.listscratch = (unsigned long long *)h->listscratch.p;
     a.dists = x.dists_out;
     a.xchg_local = (unsigned long long *)h->xchg_local.p;
     a.xchg_count = (int32_t *)h->xchg_count_local.p;
@@ -488,6 +489,7 @@ int stg_create(const StgConfig *cfg, StgHandle *out)
     A(h->work_counter, 256);
     A(h->escratch, (size_t)h->sm_count * h->escratch_stride * 4);
     A(h->keyscratch, (size_t)h->sm_count * h->key_stride * 8);
+    A(h->listscratch, (size_t)h->sm_count * h->key_stride * 8);
     A(h->st_hist, R * std::max<size_t>(cfg->max_history, 1) * 4);
     A(h->st_bias_ids, R * std::max<size_t>(cfg->max_bias, 1) * 4);
     A(h->st_bias_vals, R * std::max<size_t>(cfg->max_bias, 1) * 4);
@@ -540,7 +542,7 @@ int stg_destroy(StgHandle h)
     cudaSetDevice(h->cfg.device);
     cudaDeviceSynchronize();
     stg_comm_destroy(h);
-    DevBuf *all[] = {&h->plan_dev, &h->cand, &h->cand_count, &h->tickets, &h->work_counter, &h->escratch, &h->keyscratch,
+    DevBuf *all[] = {&h->plan_dev, &h->cand, &h->cand_count, &h->tickets, &h->work_counter, &h->escratch, &h->keyscratch, &h->listscratch,
                      &h->dists, &h->st_hist, &h->st_bias_ids, &h->st_bias_vals, &h->st_uniforms, &h->st_mask, &h->st_logits,
                      &h->o_tokens, &h->o_probs, &h->o_flags, &h->o_topk_ids, &h->o_topk_vals, &h->o_topk_probs, &h->o_pairs, &h->ticks,
                      &h->sp_draft, &h->sp_uniforms, &h->sp_accepted, &h->sp_correction, &h->sp_aprobs, &h->sp_flags,

@@ -15,9 +15,38 @@
 // and one convert), and exact ties - where the parity of the running sum decides - are detected
 // by their fraction of exactly one half and handled on a slow path.
 #pragma once
+#include <type_traits>
+
 #include "stg_emul.cuh"
 
 namespace stg {
+
+// ---- staged reads ----------------------------------------------------------------------------------
+// A provider whose elements sit in global memory as 16-byte quads (kQuadsLoad / kQuadsReload per
+// thread and sub-tile) can have them copied to shared memory a few sub-tiles ahead with cp.async,
+// so that the latency of L2 is not paid with registers.  Every thread copies and reads only its
+// own slots: no block-wide synchronisation is involved.
+constexpr int kStageBytes = 131072;  // shared memory the staged loops may use
+template <class P, class = void>
+struct StageQ { static constexpr int load = 0, reload = 0; };
+template <class P>
+struct StageQ<P, std::void_t<decltype(P::kQuadsLoad)>> {
+    static constexpr int load = P::kQuadsLoad, reload = P::kQuadsReload;
+};
+__device__ __forceinline__ void cp_async16(void *smem, const void *gmem)
+{
+    const unsigned sa = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sa), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+// quad q of stage s of this thread: consecutive threads are 16 bytes apart (conflict-free LDS.128)
+template <int NQ>
+__device__ __forceinline__ float4 *stage_slot(unsigned char *stage, int s, int q)
+{
+    return (float4 *)(stage + ((size_t)(s * NQ + q) * kThreads + threadIdx.x) * 16);
+}
 
 constexpr int kSub = 256;           // elements per sub-tile (8 consecutive per lane)
 constexpr int kMaxSubTiles = 1024;  // => sequences of up to 262144 elements
@@ -203,7 +232,7 @@ __device__ __forceinline__ int replay_subtile(const float x[8], int base, int n,
 template <class Prov, bool POS_ONLY, bool FORCE, int UN = 2>
 __device__ __noinline__ int emul_scan2(Emul2Ctl *c, Emul2Work *wk, const Prov &pv_in, int n, float target,
                                        bool has_target, float *sum_out, const unsigned char *replay_ok,
-                                       unsigned long long *tk)
+                                       unsigned long long *tk, unsigned char *stage = nullptr)
 {
     // out of line, with its own copy of the provider: the loops below then get a register
     // allocation of their own instead of sharing one with the caller's other phases
@@ -211,9 +240,58 @@ __device__ __noinline__ int emul_scan2(Emul2Ctl *c, Emul2Work *wk, const Prov &p
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int nsub = (n + kSub - 1) / kSub;
     __syncthreads();
-    // phase A: sum of every sub-tile (4 sub-tiles per warp in flight)
+    // phase A: sum of every sub-tile
     constexpr int W = kThreads / 32;
-    for (int t = warp; t < nsub; t += UN * W) {
+    constexpr int QL = StageQ<Prov>::load, QR = StageQ<Prov>::reload;
+    bool staged = false;
+    if constexpr (QL > 0) staged = stage != nullptr && pv.stage_ok();
+    if constexpr (QL > 0) {
+        if (staged) {
+            constexpr int D = (kStageBytes / (QL * 16 * kThreads)) < 4 ? (kStageBytes / (QL * 16 * kThreads)) : 4;
+            int tq = warp;
+#pragma unroll
+            for (int sidx = 0; sidx < D; sidx++, tq += W) {
+                const int b = tq * kSub + lane * 8;
+                if (tq < nsub && b + 8 <= n) {
+                    const char *g = pv.stage_src(b, false);
+#pragma unroll
+                    for (int q = 0; q < QL; q++) cp_async16(stage_slot<QL>(stage, sidx, q), g + q * 16);
+                }
+                cp_async_commit();
+            }
+            int sidx = 0;
+            for (int t = warp; t < nsub; t += W) {
+                cp_async_wait<D - 1>();
+                const int b = t * kSub + lane * 8;
+                float x[8];
+                if (b + 8 <= n) {
+                    float4 qd[QL];
+#pragma unroll
+                    for (int q = 0; q < QL; q++) qd[q] = *stage_slot<QL>(stage, sidx, q);
+                    pv.load_from(b, n, qd, x);
+                } else {
+                    pv.load(b, n, x);
+                }
+                float acc = 0.f;
+#pragma unroll
+                for (int j = 0; j < 8; j++) acc += (x[j] > 0.f) ? x[j] : 0.f;
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
+                if (lane == 0) wk->sums[t] = (double)acc;
+                const int bq = tq * kSub + lane * 8;
+                if (tq < nsub && bq + 8 <= n) {
+                    const char *g = pv.stage_src(bq, false);
+#pragma unroll
+                    for (int q = 0; q < QL; q++) cp_async16(stage_slot<QL>(stage, sidx, q), g + q * 16);
+                }
+                cp_async_commit();
+                tq += W;
+                sidx = sidx + 1 == D ? 0 : sidx + 1;
+            }
+            cp_async_wait<0>();
+        }
+    }
+    for (int t = warp; t < nsub && !staged; t += UN * W) {
         float x[UN][8];
 #pragma unroll
         for (int h = 0; h < UN; h++)
@@ -259,7 +337,56 @@ __device__ __noinline__ int emul_scan2(Emul2Ctl *c, Emul2Work *wk, const Prov &p
     __syncthreads();
     tick(tk, 1);
     // phase C: composite of every sub-tile under its guessed binade
-    for (int t = warp; t < nsub; t += UN * W) {
+    if constexpr (QR > 0) {
+        if (staged) {
+            constexpr int D = (kStageBytes / (QR * 16 * kThreads)) < 4 ? (kStageBytes / (QR * 16 * kThreads)) : 4;
+            int tq = warp;
+#pragma unroll
+            for (int sidx = 0; sidx < D; sidx++, tq += W) {
+                const int b = tq * kSub + lane * 8;
+                if (tq < nsub && b + 8 <= n && !(wk->sums[tq] == 0.0)) {
+                    const char *g = pv.stage_src(b, true);
+#pragma unroll
+                    for (int q = 0; q < QR; q++) cp_async16(stage_slot<QR>(stage, sidx, q), g + q * 16);
+                }
+                cp_async_commit();
+            }
+            int sidx = 0;
+            for (int t = warp; t < nsub; t += W) {
+                cp_async_wait<D - 1>();
+                const int b = t * kSub + lane * 8;
+                int a0 = 0, a1 = 0;
+                if (!(wk->sums[t] == 0.0)) {
+                    float x[8];
+                    if (b + 8 <= n) {
+                        float4 qd[QR];
+#pragma unroll
+                        for (int q = 0; q < QR; q++) qd[q] = *stage_slot<QR>(stage, sidx, q);
+                        pv.reload_from(b, n, qd, x);
+                    } else {
+                        pv.reload(b, n, x);
+                    }
+                    if (POS_ONLY) {
+#pragma unroll
+                        for (int j = 0; j < 8; j++) x[j] = x[j] > 0.f ? x[j] : 0.f;
+                    }
+                    subtile_composite<FORCE>(x, wk->guess[t], a0, a1);
+                }
+                if (lane == 0) { wk->comp[t][0] = a0; wk->comp[t][1] = a1; }
+                const int bq = tq * kSub + lane * 8;
+                if (tq < nsub && bq + 8 <= n && !(wk->sums[tq] == 0.0)) {
+                    const char *g = pv.stage_src(bq, true);
+#pragma unroll
+                    for (int q = 0; q < QR; q++) cp_async16(stage_slot<QR>(stage, sidx, q), g + q * 16);
+                }
+                cp_async_commit();
+                tq += W;
+                sidx = sidx + 1 == D ? 0 : sidx + 1;
+            }
+            cp_async_wait<0>();
+        }
+    }
+    for (int t = warp; t < nsub && !staged; t += UN * W) {
         float x[UN][8];
         bool z[UN];
 #pragma unroll
@@ -373,10 +500,11 @@ __device__ __noinline__ int emul_scan2(Emul2Ctl *c, Emul2Work *wk, const Prov &p
 // picks the segment-parallel form whenever the sequence fits it
 template <class Prov, bool POS_ONLY>
 __device__ int emul_any(EmulCtl *c1, Emul2Ctl *c2, Emul2Work *wk, const Prov &pv, int n, float target,
-                        bool has_target, float *sum_out, unsigned long long *tk = nullptr)
+                        bool has_target, float *sum_out, unsigned long long *tk = nullptr,
+                        unsigned char *stage = nullptr)
 {
     if (n <= kSub * kMaxSubTiles && wk != nullptr)
-        return emul_scan2<Prov, POS_ONLY, false>(c2, wk, pv, n, target, has_target, sum_out, nullptr, tk);
+        return emul_scan2<Prov, POS_ONLY, false>(c2, wk, pv, n, target, has_target, sum_out, nullptr, tk, stage);
 #ifndef NO_OLD_EMUL
     return emul_scan<Prov, POS_ONLY>(c1, pv, n, target, has_target, sum_out);
 #else

@@ -32,7 +32,7 @@ struct StgSampler_ {
     cudaEvent_t plan_ev[4]{};
     int plan_slot = 0;
     std::vector<unsigned char> plan_cache;  // bytes of the plan last uploaded
-    stg::DevBuf cand, cand_count, tickets, work_counter, escratch, keyscratch, dists;
+    stg::DevBuf cand, cand_count, tickets, work_counter, escratch, keyscratch, listscratch, dists;
     stg::DevBuf st_hist, st_bias_ids, st_bias_vals, st_uniforms, st_mask, st_logits;
     stg::DevBuf o_tokens, o_probs, o_flags, o_topk_ids, o_topk_vals, o_topk_probs, o_pairs;
     stg::DevBuf ticks;                   // diagnostic phase stamps (STG_PHASE_TICKS=1)

@@ -31,11 +31,12 @@
 
 namespace stg {
 
-constexpr int kBins = 4096;        // exp-value histogram: 8 exponent + 5 mantissa bits of a float <= 1
-constexpr int kBinShift = 18;
-constexpr int kMaxDirty = 512;     // bins sorted individually before giving up on the partial order
+constexpr int kBins = 4096;        // exp-value histogram: 32 binades below 2.0, 7 mantissa bits each
+constexpr int kBinExp0 = 96;       // biased exponent of the lowest binade with bins of its own
+constexpr int kMaxDirty = 1024;    // bins sorted individually before giving up on the partial order
 constexpr int kDirtyRound = 2048;  // elements rank-sorted per round
 constexpr int kMaxOvSlots = 4096;  // hash slots => at most 2048 history + bias entries per row
+static_assert(kSortCap * 4 >= kStageBytes, "the staged loops borrow the key region");
 static_assert(kBins == 4 * kThreads, "the bin scans assign 4 bins to a thread");
 
 // shared-memory arena of a row item
@@ -45,7 +46,20 @@ constexpr int kOffMass = kOffCount + kBins * 4;                  // float[kBins]
 constexpr int kOffBinOff = kOffMass + kBins * 4;                 // u32[kBins]: start of each bin in the list
 constexpr int kOffEmul = kOffBinOff + kBins * 4;                 // Emul2Work
 constexpr int kOffReplayOk = kOffEmul + (int)sizeof(Emul2Work);  // u8[kMaxSubTiles]
-constexpr int kRowArenaEnd = kOffReplayOk + kMaxSubTiles;
+constexpr int kOffBinExp = kOffReplayOk + kMaxSubTiles;          // u8[kBins]: binade of the running sum at each bin
+constexpr int kRowArenaEnd = kOffBinExp + kBins;
+
+// histogram bin of an exp value (0 < e <= 1): values below 2^-31 share bin 0
+__device__ __forceinline__ unsigned bin_of(uint32_t ebits)
+{
+    const int b = (int)(ebits >> 16) - (kBinExp0 << 7);
+    return (unsigned)min(max(b, 0), kBins - 1);
+}
+// smallest bit pattern that falls into bin b or above
+__device__ __forceinline__ uint32_t bin_floor_bits(int b)
+{
+    return b > 0 ? (uint32_t)(b + (kBinExp0 << 7)) << 16 : 0u;
+}
 
 struct RowCtl {
     EmulCtl em;
@@ -62,6 +76,8 @@ struct RowCtl {
     int running;
     int n_dirty;      // bins waiting to be sorted
     int give_up;      // partial order abandoned: sort everything
+    int n_list;       // candidates in the token-ordered list (-1: no list)
+    unsigned flag_bits[kBins / 32];    // bins in which the sum may change binade, meet top_p or hit a tie
     unsigned short dirty[kMaxDirty];
     int dirty_cum[kMaxDirty + 1];
     unsigned sorted_bits[kBins / 32];  // bins already sorted
@@ -138,6 +154,34 @@ struct SrcLogits {
             for (int j = 0; j < 8; j++) x[j] = __fmul_rn(x[j], inv_t);
         }
     }
+    // staged reads (stg_emul2.cuh): the thread's 8 elements as 16-byte quads copied to shared memory
+    static constexpr int kQuads = BF16 ? 1 : 2;
+    __device__ __forceinline__ bool stage_ok() const { return aligned != 0; }
+    __device__ __forceinline__ const char *stage_src(int base) const
+    {
+        return (const char *)rowp + (size_t)base * (BF16 ? 2 : 4);
+    }
+    __device__ __forceinline__ void decode(int base, const float4 *q, float x[8]) const
+    {
+        if (BF16) {
+            const uint4 t = *(const uint4 *)q;
+            x[0] = bf16_lo(t.x); x[1] = bf16_hi(t.x); x[2] = bf16_lo(t.y); x[3] = bf16_hi(t.y);
+            x[4] = bf16_lo(t.z); x[5] = bf16_hi(t.z); x[6] = bf16_lo(t.w); x[7] = bf16_hi(t.w);
+        } else {
+            x[0] = q[0].x; x[1] = q[0].y; x[2] = q[0].z; x[3] = q[0].w;
+            x[4] = q[1].x; x[5] = q[1].y; x[6] = q[1].z; x[7] = q[1].w;
+        }
+        if (mrow) {
+            uint32_t bits = __ldg(mrow + (base >> 5)) >> (base & 31);
+#pragma unroll
+            for (int j = 0; j < 8; j++)
+                if (!((bits >> j) & 1u)) x[j] = -CUDART_INF_F;
+        }
+        if (scale) {
+#pragma unroll
+            for (int j = 0; j < 8; j++) x[j] = __fmul_rn(x[j], inv_t);
+        }
+    }
 };
 
 struct SrcScratch {
@@ -155,6 +199,18 @@ struct SrcScratch {
 #pragma unroll
             for (int j = 0; j < 8; j++) x[j] = (base + j < n) ? __ldcg(p + base + j) : -CUDART_INF_F;
         }
+        if (scale) {
+#pragma unroll
+            for (int j = 0; j < 8; j++) x[j] = __fmul_rn(x[j], inv_t);
+        }
+    }
+    static constexpr int kQuads = 2;
+    __device__ __forceinline__ bool stage_ok() const { return true; }
+    __device__ __forceinline__ const char *stage_src(int base) const { return (const char *)(p + base); }
+    __device__ __forceinline__ void decode(int base, const float4 *q, float x[8]) const
+    {
+        x[0] = q[0].x; x[1] = q[0].y; x[2] = q[0].z; x[3] = q[0].w;
+        x[4] = q[1].x; x[5] = q[1].y; x[6] = q[1].z; x[7] = q[1].w;
         if (scale) {
 #pragma unroll
             for (int j = 0; j < 8; j++) x[j] = __fmul_rn(x[j], inv_t);
@@ -197,33 +253,40 @@ __device__ __forceinline__ float eval_p3(float e, int i, const RowDist &d)  // f
 
 // ---- providers of the emulated sums ----------------------------------------------------------------
 // exp pass: computes e_i = expf(x_i - max), stores it in the scratch row, feeds the histogram.
+// `load` is called by whole warps (the histogram update of bin 0 is aggregated over the warp:
+// a peaked row sends nearly every value there).
 template <class Src>
 struct ProvExp {
     Src src;
     float mx;
     float *scratch;
-    unsigned *hcount;   // null: no histogram wanted
-    unsigned *hmass;    // per bin: sum of the top 12 mantissa bits (all values in a bin share the exponent)
-    __device__ __forceinline__ void load(int base, int n, float x[8]) const
+    unsigned long long *hist;  // null: no histogram wanted.  Per bin: count << 40 | sum of the top 12
+                               // mantissa bits (all values in a bin share the exponent)
+    __device__ __forceinline__ void finish(int base, int n, float x[8]) const
     {
-        if (base >= n) {
-#pragma unroll
-            for (int j = 0; j < 8; j++) x[j] = 0.f;
-            return;
-        }
-        src.get8(base, n, x);
+        int low = 0;
 #pragma unroll
         for (int j = 0; j < 8; j++) {
             float e = (base + j < n) ? expf(__fsub_rn(x[j], mx)) : 0.f;
             x[j] = e;
-            if (hcount && e > 0.f) {
-                unsigned bin = __float_as_uint(e) >> kBinShift;
-                bin = bin < (unsigned)kBins ? bin : (unsigned)(kBins - 1);
-                atomicAdd(&hcount[bin], 1u);
-                atomicAdd(&hmass[bin], ((__float_as_uint(e) & 0x7FFFFFu) | 0x800000u) >> 12);
+            if (hist && e > 0.f) {
+                const uint32_t eb = __float_as_uint(e);
+                const unsigned bin = bin_of(eb);
+                if (bin == 0u) low++;
+                else atomicAdd(&hist[bin], (1ull << 40) | (unsigned long long)(((eb & 0x7FFFFFu) | 0x800000u) >> 12));
             }
         }
-        store8(scratch, base, n, x);
+        if (hist) {
+            low = __reduce_add_sync(0xFFFFFFFFu, low);
+            if (low && (threadIdx.x & 31) == 0)
+                atomicAdd(&hist[0], ((unsigned long long)low << 40) | ((unsigned long long)low * 0xFFFull));
+        }
+        if (base < n) store8(scratch, base, n, x);
+    }
+    __device__ __forceinline__ void load(int base, int n, float x[8]) const
+    {
+        if (base < n) src.get8(base, n, x);
+        finish(base, n, x);
     }
     __device__ __forceinline__ void reload(int base, int n, float x[8]) const
     {
@@ -237,6 +300,23 @@ struct ProvExp {
 #pragma unroll
         for (int j = 0; j < 8; j++)
             if (base + j >= n) x[j] = 0.f;
+    }
+    // staged reads
+    static constexpr int kQuadsLoad = Src::kQuads, kQuadsReload = 2;
+    __device__ __forceinline__ bool stage_ok() const { return src.stage_ok(); }
+    __device__ __forceinline__ const char *stage_src(int base, bool re) const
+    {
+        return re ? (const char *)(scratch + base) : src.stage_src(base);
+    }
+    __device__ __forceinline__ void load_from(int base, int n, const float4 *q, float x[8]) const
+    {
+        src.decode(base, q, x);
+        finish(base, n, x);
+    }
+    __device__ __forceinline__ void reload_from(int base, int n, const float4 *q, float x[8]) const
+    {
+        x[0] = q[0].x; x[1] = q[0].y; x[2] = q[0].z; x[3] = q[0].w;
+        x[4] = q[1].x; x[5] = q[1].y; x[6] = q[1].z; x[7] = q[1].w;
     }
 };
 
@@ -271,6 +351,24 @@ struct ProvFinal {  // final probabilities from the scratch row of exp values
 #pragma unroll
         for (int j = 0; j < 8; j++) x[j] = (base + j < n) ? eval_p3(x[j], base + j, d) : 0.f;
     }
+};
+
+struct ProvList {  // final probabilities of the top-p candidates, in token order (id << 32 | exp bits)
+    const u64 *list;
+    RowDist d;
+    __device__ __forceinline__ void load(int base, int n, float x[8]) const
+    {
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            float v = 0.f;
+            if (base + j < n) {
+                const u64 c = __ldcg(list + base + j);
+                v = eval_p3(__uint_as_float((uint32_t)c), (int)(c >> 32), d);
+            }
+            x[j] = v;
+        }
+    }
+    __device__ __forceinline__ void reload(int base, int n, float x[8]) const { load(base, n, x); }
 };
 
 struct ProvKeys {  // probability bit patterns in (partial) descending order
@@ -532,12 +630,12 @@ static __device__ __noinline__ float adjust_row(const SampleArgs &a, const RowPl
     return pass_adjust<BF16>(raw, ov, inv_t, scale, n, scratch, red);
 }
 
-// mass of a histogram bin in exp-value units: every value in bin b has the biased exponent b >> 5, and
-// hmass holds the sum of the top 12 bits of their 24-bit mantissas
+// mass of a histogram bin in exp-value units: every value in bin b >= 1 has the biased exponent
+// kBinExp0 + (b >> 7), and hmass holds the sum of the top 12 bits of their 24-bit mantissas (the
+// smaller values gathered in bin 0 are overestimated, which only widens the nucleus bound)
 __device__ __forceinline__ double bin_mass(const unsigned *hmass, int b)
 {
-    const int ex = b >> 5;  // biased exponent (0: denormals, treated as exponent 1)
-    return ldexp((double)hmass[b], (ex ? ex : 1) - 127 - 11);  // truncation makes it up to 2^-12 low
+    return ldexp((double)hmass[b], kBinExp0 + (b >> 7) - 127 - 11);  // truncation makes it up to 2^-12 low
 }
 
 // ---- top-p over a partially ordered candidate list ---------------------------------------------------
@@ -669,7 +767,7 @@ static __device__ __noinline__ void topk_cut(RowCtl *rc, SelCtl *sctl, const Row
 // returns the fp64 sum of the kept probabilities.  Kept out of line: it is long, runs once per
 // row, and would otherwise dominate the register allocation of the streaming phases around it.
 static __device__ __noinline__ double topp_cut(RowCtl *rc, const RowPlan &rp, int n, const float *scratch,
-                                               unsigned char *arena, uint32_t *gkeys, int gkeys_cap,
+                                               unsigned char *arena, uint32_t *gkeys, int gkeys_cap, u64 *list,
                                                uint32_t *flags_out, u64 *tk)
 {
     const int tid = threadIdx.x;
@@ -679,6 +777,7 @@ static __device__ __noinline__ double topp_cut(RowCtl *rc, const RowPlan &rp, in
     unsigned *bstart = (unsigned *)(arena + kOffBinOff);
     Emul2Work *wk2 = (Emul2Work *)(arena + kOffEmul);
     unsigned char *replay_ok = arena + kOffReplayOk;
+    unsigned char *bin_exp = arena + kOffBinExp;
     RowDist d = rc->dist;
     const bool uniform = (d.flags & kDistUniform) != 0;
     double sum3 = 0.0;
@@ -747,19 +846,58 @@ static __device__ __noinline__ double topp_cut(RowCtl *rc, const RowPlan &rp, in
             uint32_t *keys = skeys;
             int cap = kSortCap;
             if (bound > kSortCap) { keys = gkeys; cap = gkeys_cap; *flags_out |= (1u << 7); }
-            // (3) scatter the survivors above the bound into bin order; count all survivors
+            // (3) per bin, from the estimated mass before and after it: the binade the sequential sum
+            // is in when it reaches the bin, and whether it may change binade or meet top_p inside
+            // the bin.  Such bins - and the head of the list, where the sum changes binade every few
+            // keys - must be in exact order before the sum is emulated.
+            for (int t = tid; t < kBins / 32; t += kThreads) rc->flag_bits[t] = 0u;
+            __syncthreads();
+            {
+                double loc[4], tot = 0.0;
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    int b = kBins - 1 - (tid * 4 + j);
+                    loc[j] = (b >= c_lo && hcount[b]) ? bin_mass(hmass, b) * scale_p : 0.0;
+                    tot += loc[j];
+                }
+                double before = scan4_double(tot, rc) - tot;
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    int b = kBins - 1 - (tid * 4 + j);
+                    // the estimate is low by at most 2^-12 (mantissa truncation) and the emulated
+                    // sum drifts by ~1e-5; a miss is caught by the scan itself
+                    const double lo = before * (1.0 - 1.0 / 32768.0), hi = (before + loc[j]) * (1.0 + 1.0 / 2048.0);
+                    const int e_lo = exp_of_double(lo);
+                    bin_exp[b] = (unsigned char)e_lo;
+                    if (b >= c_lo && hcount[b]) {
+                        const bool crosses = e_lo != exp_of_double(hi);
+                        const bool cut = lo <= (double)rp.top_p && hi >= (double)rp.top_p;
+                        const bool head = bstart[b] < 2048u;
+                        if (crosses || cut || head) atomicOr(&rc->flag_bits[b >> 5], 1u << (b & 31));
+                    }
+                    before += loc[j];
+                }
+                __syncthreads();
+            }
+            // (4) scatter the survivors above the bound into bin order, and - in token order - into
+            // the candidate list the draw later walks; count all survivors.  A key whose addition
+            // would be an exact tie (where the parity of the running sum decides the rounding, so
+            // the order inside its bin matters) flags its bin.
             int my_surv = 0;
-            const uint32_t lo_bits = (uint32_t)c_lo << kBinShift;
-            for (int base = tid * 8; base < n; base += kThreads * 8 * 2) {
+            int list_run = 0;
+            const uint32_t lo_bits = bin_floor_bits(c_lo);
+            for (int it0 = 0; it0 < n; it0 += kThreads * 8 * 2) {
                 float x[2][8];
+                const int base = it0 + tid * 8;
                 const int b1 = base + kThreads * 8;
                 SrcScratch sc{scratch, 1.f, false};
-                sc.get8(base, n, x[0]);
+                if (base < n) sc.get8(base, n, x[0]);
                 if (b1 < n) sc.get8(b1, n, x[1]);
+                unsigned take[2] = {0u, 0u};
 #pragma unroll
                 for (int h = 0; h < 2; h++) {
                     const int bb = h ? b1 : base;
-                    if (bb >= n) break;
+                    if (bb >= n) continue;
 #pragma unroll
                     for (int j = 0; j < 8; j++) {
                         if (bb + j >= n) continue;
@@ -769,16 +907,61 @@ static __device__ __noinline__ double topp_cut(RowCtl *rc, const RowPlan &rp, in
                             my_surv++;
                             const uint32_t ebits = __float_as_uint(e);
                             if (ebits >= lo_bits) {
-                                unsigned bin = ebits >> kBinShift;
-                                bin = bin < (unsigned)kBins ? bin : (unsigned)(kBins - 1);
+                                take[h] |= 1u << j;
+                                const unsigned bin = bin_of(ebits);
                                 unsigned pos = bstart[bin] + atomicAdd(&cursor[bin], 1u);
-                                if (pos < (unsigned)cap) keys[pos] = __float_as_uint(p);
+                                const uint32_t pbits = __float_as_uint(p);
+                                if (pos < (unsigned)cap) keys[pos] = pbits;
+                                const int k = (int)bin_exp[bin] - (int)((pbits >> 23) & 255u);
+                                if (k >= 1 && k <= 24) {
+                                    const uint32_t m = (pbits & 0x7FFFFFu) | 0x800000u;
+                                    if ((m & ((1u << k) - 1u)) == (1u << (k - 1)))
+                                        atomicOr(&rc->flag_bits[bin >> 5], 1u << (bin & 31));
+                                }
                             }
                         }
                     }
                 }
+                // token-ordered list: exclusive block scan of (count of half 0, count of half 1)
+                const int lane = tid & 31, warp = tid >> 5;
+                const int mine = __popc(take[0]) | (__popc(take[1]) << 16);
+                int inc = mine;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    int t = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+                    if (lane >= o) inc += t;
+                }
+                if (lane == 31) rc->red_i[warp] = inc;
+                __syncthreads();
+                if (warp == 0) {
+                    int wv = rc->red_i[lane];
+#pragma unroll
+                    for (int o = 1; o < 32; o <<= 1) {
+                        int t = __shfl_up_sync(0xFFFFFFFFu, wv, o);
+                        if (lane >= o) wv += t;
+                    }
+                    rc->red_i[lane] = wv;
+                }
+                __syncthreads();
+                const int excl = inc - mine + (warp ? rc->red_i[warp - 1] : 0);
+                const int total = rc->red_i[31];
+                int pos0 = list_run + (excl & 0xFFFF);
+                int pos1 = list_run + (total & 0xFFFF) + (excl >> 16);
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    if ((take[0] >> j) & 1u)
+                        list[pos0++] = ((u64)(uint32_t)(base + j) << 32) | __float_as_uint(x[0][j]);
+                }
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    if ((take[1] >> j) & 1u)
+                        list[pos1++] = ((u64)(uint32_t)(b1 + j) << 32) | __float_as_uint(x[1][j]);
+                }
+                list_run += (total & 0xFFFF) + (total >> 16);
+                __syncthreads();  // red_i is reused by the next round
             }
             my_surv = block_sum_int(my_surv, rc->red_i);
+            if (tid == 0) rc->n_list = list_run;
             // The filters before top-p drop the smallest values only, so the bins that lost
             // elements are the last ones of the list: it stays dense.  From here on the histogram
             // describes the list.
@@ -793,41 +976,35 @@ static __device__ __noinline__ double topp_cut(RowCtl *rc, const RowPlan &rp, in
             const int nc = min(block_sum_int(mine, rc->red_i), cap);
             __syncthreads();
             tick(tk, 6);
-            if (nc == 0) break;
-            // (4) bins in which the sequential sum may change binade or meet top_p, judged from
-            // the estimated mass before and after each bin: they are sorted up front
-            {
-                double loc[4], tot = 0.0;
-#pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    int b = kBins - 1 - (tid * 4 + j);
-                    loc[j] = (b >= c_lo && hcount[b]) ? bin_mass(hmass, b) * scale_p : 0.0;
-                    tot += loc[j];
+            if (nc == 0) { if (tid == 0) rc->n_list = -1; __syncthreads(); break; }
+            // (5) a sub-tile of the emulated sum is replayed whole, so every bin that shares a
+            // sub-tile with a flagged bin has to be sorted with it
+            for (int t = tid; t < kMaxSubTiles; t += kThreads) replay_ok[t] = 0;
+            __syncthreads();
+            for (int b = c_lo + tid; b < kBins; b += kThreads) {
+                const unsigned cnt = hcount[b];
+                if (cnt && ((rc->flag_bits[b >> 5] >> (b & 31)) & 1u)) {
+                    const int t0 = (int)bstart[b] >> 8, t1 = (int)(bstart[b] + cnt - 1) >> 8;
+                    for (int t = t0; t <= t1 && t < kMaxSubTiles; t++) replay_ok[t] = 1;
                 }
-                double before = scan4_double(tot, rc) - tot;
-#pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    int b = kBins - 1 - (tid * 4 + j);
-                    if (b >= c_lo && hcount[b] >= 2u) {
-                        // the estimate is low by at most 2^-12 (mantissa truncation) and the
-                        // emulated sum drifts by ~1e-5; a miss is caught by the scan itself
-                        const double lo = before * (1.0 - 1.0 / 32768.0), hi = (before + loc[j]) * (1.0 + 1.0 / 2048.0);
-                        const bool crosses = exp_of_double(lo) != exp_of_double(hi);
-                        const bool cut = lo <= (double)rp.top_p && hi >= (double)rp.top_p;
-                        const bool head = bstart[b] < 2048u;  // the sum changes binade every few keys here
-                        if (crosses || cut || head) {
-                            int slot = atomicAdd(&rc->n_dirty, 1);
-                            if (slot < kMaxDirty) rc->dirty[slot] = (unsigned short)b; else rc->give_up = 1;
-                        }
-                    }
-                    before += loc[j];
-                }
-                __syncthreads();
             }
+            __syncthreads();
+            for (int b = c_lo + tid; b < kBins; b += kThreads) {
+                const unsigned cnt = hcount[b];
+                if (cnt >= 2u) {
+                    const int t0 = (int)bstart[b] >> 8, t1 = (int)(bstart[b] + cnt - 1) >> 8;
+                    bool need = false;
+                    for (int t = t0; t <= t1 && t < kMaxSubTiles; t++) need |= replay_ok[t] != 0;
+                    if (need) {
+                        int slot = atomicAdd(&rc->n_dirty, 1);
+                        if (slot < kMaxDirty) rc->dirty[slot] = (unsigned short)b; else rc->give_up = 1;
+                    }
+                }
+            }
+            __syncthreads();
             int hit = -1;
             float cum = 0.f;
             bool sorted_all = uniform;  // all keys equal: any order is sorted
-            tick(tk, 24);
             if (tk && tid == 0) { tk[28] = (u64)rc->n_dirty; tk[29] = (u64)nc; tk[30] = 0; tk[31] = 0; }
             for (int pass = 0; pass < 64; pass++) {
                 if (tk && tid == 0) tk[30] = (u64)(pass + 1);
@@ -841,7 +1018,6 @@ static __device__ __noinline__ double topp_cut(RowCtl *rc, const RowPlan &rp, in
                 } else if (!sorted_all && rc->n_dirty > 0) {
                     if (tk && tid == 0) tk[31] += 1;
                     sort_dirty_bins(rc, keys, bstart, hcount, (uint32_t *)wk2, (int *)wk2 + kDirtyRound);
-                    if (pass == 0) tick(tk, 25);
                     __syncthreads();
                     if (rc->give_up) continue;  // a bin was too large for the in-place sort: sort everything
                     for (int i = tid; i < min(rc->n_dirty, kMaxDirty); i += kThreads)
@@ -871,7 +1047,6 @@ static __device__ __noinline__ double topp_cut(RowCtl *rc, const RowPlan &rp, in
                     if (!sorted_all) { if (tid == 0) rc->give_up = 1; __syncthreads(); continue; }
                     hit = emul_scan<ProvKeys, false>(&rc->em, pk, nc, rp.top_p, true, &cum);
                 }
-                if (pass == 0) tick(tk, 26);
                 if (hit != -2) break;
                 // the sum needed the internal order of an unsorted stretch: sort its bins and rerun
                 const int t_abort = rc->em2.abort_at;
@@ -922,7 +1097,7 @@ static __device__ __noinline__ double topp_cut(RowCtl *rc, const RowPlan &rp, in
 // temperature-scaled logits; `mx_known` is their maximum when the caller already has it.
 template <class Src>
 static __device__ void build_dist(RowCtl *rc, SelCtl *sctl, const Src &src, const RowPlan &rp, int n,
-                                  float *scratch, unsigned char *arena, uint32_t *gkeys, int gkeys_cap,
+                                  float *scratch, unsigned char *arena, uint32_t *gkeys, int gkeys_cap, u64 *list,
                                   uint32_t *flags_out, u64 *tk, bool have_max, float mx_known)
 {
     const int tid = threadIdx.x;
@@ -963,16 +1138,32 @@ static __device__ void build_dist(RowCtl *rc, SelCtl *sctl, const Src &src, cons
         d.uniform_p = __fdiv_rn(1.0f, (float)n);
         for (int i = tid; i < n; i += kThreads) __stcg(scratch + i, d.uniform_p);
         if (want_topp && tid == 0) {
-            unsigned bin = __float_as_uint(d.uniform_p) >> kBinShift;
+            unsigned bin = bin_of(__float_as_uint(d.uniform_p));
             hcount[bin] = (unsigned)n;
             hmass[bin] = (unsigned)min((unsigned long long)n * ((((unsigned long long)__float_as_uint(d.uniform_p) & 0x7FFFFFu) | 0x800000u) >> 12), 0xFFFFFFFFull);
         }
         __syncthreads();
     } else {
         d.max_x = mx;
-        ProvExp<Src> pe{src, mx, scratch, want_topp ? hcount : nullptr, hmass};
-        emul_any<ProvExp<Src>, false>(&rc->em, &rc->em2, wk2, pe, n, 0.f, false, &sum, tk ? tk + 12 : nullptr);
+        // the histogram is accumulated as one packed 64-bit word per bin (count << 40 | mass) over
+        // the two 32-bit arrays, which are adjacent, and unpacked afterwards
+        static_assert(kOffMass == kOffCount + kBins * 4, "count and mass arrays must be adjacent");
+        unsigned long long *hist = (unsigned long long *)hcount;
+        ProvExp<Src> pe{src, mx, scratch, want_topp ? hist : nullptr};
+        emul_any<ProvExp<Src>, false>(&rc->em, &rc->em2, wk2, pe, n, 0.f, false, &sum, tk ? tk + 12 : nullptr,
+                                      arena + kOffKeys);
         if (sum > 0.f && sum != 1.0f) { d.flags |= kDistScale1; d.inv1 = __fdiv_rn(1.0f, sum); }
+        if (want_topp) {
+            unsigned long long v[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) v[j] = hist[tid * 4 + j];
+            __syncthreads();
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                hcount[tid * 4 + j] = (unsigned)(v[j] >> 40);
+                hmass[tid * 4 + j] = (unsigned)(v[j] & 0xFFFFFFFFull);
+            }
+        }
     }
     __syncthreads();
     tick(tk, 3);
@@ -1001,7 +1192,7 @@ static __device__ void build_dist(RowCtl *rc, SelCtl *sctl, const Src &src, cons
         __syncthreads();
         if (tid == 0) rc->dist = d;
         __syncthreads();
-        sum3 = topp_cut(rc, rp, n, scratch, arena, gkeys, gkeys_cap, flags_out, tk);
+        sum3 = topp_cut(rc, rp, n, scratch, arena, gkeys, gkeys_cap, list, flags_out, tk);
         d = rc->dist;
     } else
 #endif
@@ -1045,12 +1236,13 @@ static __device__ void run_row(const SampleArgs &a, int row, int item, SelCtl *s
     float *scratch = a.escratch + (int64_t)blockIdx.x * a.escratch_stride;
     uint32_t *gkeys = (uint32_t *)(a.keyscratch + (int64_t)blockIdx.x * a.key_stride);
     const int gkeys_cap = (int)(a.key_stride * 2);
+    u64 *list = a.listscratch + (int64_t)blockIdx.x * a.key_stride;
     const bool greedy = rp.temperature <= 0.f;
     const bool with_bias = !greedy && rp.bias_len > 0;
     const bool with_hist = rp.has_penalty && rp.hist_len > 0;
     const bool overrides = with_hist || with_bias;
     __shared__ uint32_t sh_flags;
-    if (tid == 0) sh_flags = 0;
+    if (tid == 0) { sh_flags = 0; rc.n_list = -1; }
     __syncthreads();
 
     const float inv_t = (!greedy && rp.temperature != 1.0f) ? __fdiv_rn(1.0f, rp.temperature) : 1.0f;
@@ -1105,10 +1297,10 @@ static __device__ void run_row(const SampleArgs &a, int row, int item, SelCtl *s
     if (overrides) {
         // the scratch row is scaled already; the descriptor still records the scale
         SrcScratch s{scratch, inv_t, false};
-        build_dist(&rc, sctl, s, rp, n, scratch, arena, gkeys, gkeys_cap, &sh_flags, tk, true, mx);
+        build_dist(&rc, sctl, s, rp, n, scratch, arena, gkeys, gkeys_cap, list, &sh_flags, tk, true, mx);
     } else {
         SrcLogits<BF16> s{rowp, mrow, a.vec == 4, inv_t, scale};
-        build_dist(&rc, sctl, s, rp, n, scratch, arena, gkeys, gkeys_cap, &sh_flags, tk, false, 0.f);
+        build_dist(&rc, sctl, s, rp, n, scratch, arena, gkeys, gkeys_cap, list, &sh_flags, tk, false, 0.f);
     }
     if (a.mode == 2) {
         // descriptor only; the raw arg-max goes with it (the looser accept rule compares against it)
@@ -1133,7 +1325,19 @@ static __device__ void run_row(const SampleArgs &a, int row, int item, SelCtl *s
     const float u = a.uniforms ? __ldg(a.uniforms + row) : 0.5f;
     float cum = 0.f;
     Emul2Work *wk2 = (Emul2Work *)(arena + kOffEmul);
-    int hit = emul_any<ProvFinal, false>(&rc.em, &rc.em2, wk2, pf, n, u, true, &cum, tk ? tk + 20 : nullptr);
+    int hit;
+    const int n_list = rc.n_list;
+    if (n_list >= 0) {
+        // after top-p only the listed candidates can be non-zero, and adding a zero neither changes
+        // the running sum nor can be the first element to reach the target (unless the target is
+        // not positive, which the first token meets whatever its probability)
+        ProvList pl{list, rc.dist};
+        hit = emul_any<ProvList, false>(&rc.em, &rc.em2, wk2, pl, n_list, u, true, &cum, tk ? tk + 20 : nullptr);
+        if (hit >= 0) hit = (int)(__ldcg(list + hit) >> 32);
+        if (!(u > 0.f)) hit = 0;
+    } else {
+        hit = emul_any<ProvFinal, false>(&rc.em, &rc.em2, wk2, pf, n, u, true, &cum, tk ? tk + 20 : nullptr);
+    }
     if (tid == 0) {
         uint32_t fl = kPathFull | sh_flags;
         if (rc.dist.flags & kDistUniform) fl |= (1u << 6);

@@ -86,6 +86,7 @@ struct SampleArgs {
     unsigned long long *phase_ticks; // diagnostic: 32 globaltimer stamps per work item, or null
     float *escratch;                 // per-CTA exp scratch rows [grid, escratch_stride]
     unsigned long long *keyscratch;  // per-CTA wide-nucleus key scratch [grid, key_stride]
+    unsigned long long *listscratch; // per-CTA top-p candidates in token order [grid, key_stride]: id << 32 | exp bits
     RowDist *dists;                  // per-row distribution descriptors (optional output)
     unsigned long long *xchg_local;  // vocabulary-sharded mode: this rank's candidates [rows, xchg_stride]
     int32_t *xchg_count;             // ... and how many each row has
