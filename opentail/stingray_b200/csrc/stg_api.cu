@@ -489,7 +489,7 @@ int stg_create(const StgConfig *cfg, StgHandle *out)
     A(h->work_counter, 256);
     A(h->escratch, (size_t)h->sm_count * h->escratch_stride * 4);
     A(h->keyscratch, (size_t)h->sm_count * h->key_stride * 8);
-    A(h->listscratch, (size_t)h->sm_count * h->key_stride * 8);
+    A(h->listscratch, (size_t)h->sm_count * (h->key_stride + 512) * 8);  // + 2 sub-tiles: padded reads
     A(h->st_hist, R * std::max<size_t>(cfg->max_history, 1) * 4);
     A(h->st_bias_ids, R * std::max<size_t>(cfg->max_bias, 1) * 4);
     A(h->st_bias_vals, R * std::max<size_t>(cfg->max_bias, 1) * 4);

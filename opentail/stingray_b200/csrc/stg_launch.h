@@ -7,7 +7,7 @@
 namespace stg {
 
 // shared memory a row-type work item needs: sort keys + exp-value histogram
-constexpr size_t kRowArenaBytes = 205824;  // layout in stg_rowdist.cuh (checked there)
+constexpr size_t kRowArenaBytes = 211968;  // layout in stg_rowdist.cuh (checked there)
 
 cudaError_t launch_sample_chunks(const SampleArgs &a, int grid, size_t smem, cudaStream_t stream);
 cudaError_t launch_sample_rows(const SampleArgs &a, int grid, cudaStream_t stream);

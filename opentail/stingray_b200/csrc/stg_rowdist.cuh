@@ -47,7 +47,9 @@ constexpr int kOffBinOff = kOffMass + kBins * 4;                 // u32[kBins]: 
 constexpr int kOffEmul = kOffBinOff + kBins * 4;                 // Emul2Work
 constexpr int kOffReplayOk = kOffEmul + (int)sizeof(Emul2Work);  // u8[kMaxSubTiles]
 constexpr int kOffBinExp = kOffReplayOk + kMaxSubTiles;          // u8[kBins]: binade of the running sum at each bin
-constexpr int kRowArenaEnd = kOffBinExp + kBins;
+constexpr int kOffSubSrc = kOffBinExp + kBins;                   // int[kMaxSubTiles]: list offset of each list sub-tile
+constexpr int kOffSubCnt = kOffSubSrc + kMaxSubTiles * 4;        // u16[kMaxSubTiles]: entries in it
+constexpr int kRowArenaEnd = kOffSubCnt + kMaxSubTiles * 2;
 
 // histogram bin of an exp value (0 < e <= 1): values below 2^-31 share bin 0
 __device__ __forceinline__ unsigned bin_of(uint32_t ebits)
@@ -353,22 +355,49 @@ struct ProvFinal {  // final probabilities from the scratch row of exp values
     }
 };
 
-struct ProvList {  // final probabilities of the top-p candidates, in token order (id << 32 | exp bits)
+struct ProvList {  // final probabilities of the top-p candidates, in token order (id << 32 | exp bits).
+    // The sequence is made of sub-tiles of kSub entries: sub-tile t starts at list[sub_src[t]] and
+    // holds sub_cnt[t] entries; the rest of it counts as zeros.
     const u64 *list;
+    const int *sub_src;
+    const unsigned short *sub_cnt;
     RowDist d;
+    __device__ __forceinline__ const u64 *at(int pos) const { return list + sub_src[pos >> 8] + (pos & (kSub - 1)); }
     __device__ __forceinline__ void load(int base, int n, float x[8]) const
     {
+        const int t = base >> 8, off = base & (kSub - 1);
+        const int cnt = base < n ? (int)sub_cnt[t] : 0;
+        const u64 *p = list + (base < n ? sub_src[t] : 0) + off;
 #pragma unroll
         for (int j = 0; j < 8; j++) {
             float v = 0.f;
-            if (base + j < n) {
-                const u64 c = __ldcg(list + base + j);
+            if (off + j < cnt) {
+                const u64 c = __ldcg(p + j);
                 v = eval_p3(__uint_as_float((uint32_t)c), (int)(c >> 32), d);
             }
             x[j] = v;
         }
     }
     __device__ __forceinline__ void reload(int base, int n, float x[8]) const { load(base, n, x); }
+    // staged reads: 8 entries of 8 bytes
+    static constexpr int kQuadsLoad = 4, kQuadsReload = 4;
+    __device__ __forceinline__ bool stage_ok() const { return true; }
+    __device__ __forceinline__ const char *stage_src(int base, bool) const { return (const char *)at(base); }
+    __device__ __forceinline__ void load_from(int base, int n, const float4 *q, float x[8]) const
+    {
+        const int off = base & (kSub - 1);
+        const int cnt = (int)sub_cnt[base >> 8];
+#pragma unroll
+        for (int h = 0; h < 4; h++) {
+            const uint4 v = *(const uint4 *)&q[h];
+            x[2 * h] = (off + 2 * h < cnt) ? eval_p3(__uint_as_float(v.x), (int)v.y, d) : 0.f;
+            x[2 * h + 1] = (off + 2 * h + 1 < cnt) ? eval_p3(__uint_as_float(v.z), (int)v.w, d) : 0.f;
+        }
+    }
+    __device__ __forceinline__ void reload_from(int base, int n, const float4 *q, float x[8]) const
+    {
+        load_from(base, n, q, x);
+    }
 };
 
 struct ProvKeys {  // probability bit patterns in (partial) descending order
@@ -583,38 +612,73 @@ static __device__ void build_overrides(const SampleArgs &a, const RowPlan &rp, c
     __syncthreads();
 }
 
-// first pass of a row with overrides: adjusted, scaled logits into the scratch row, and their maximum
+// first pass of a row with overrides: adjusted, scaled logits into the scratch row, and their maximum.
+// `stage` (may be null) is shared memory for `depth` stages of cp.async reads ahead.
 template <bool BF16>
 static __device__ float pass_adjust(const SrcLogits<BF16> &raw, const OvTable &ov, float inv_t, bool scale, int n,
-                                    float *scratch, float *red)
+                                    float *scratch, float *red, unsigned char *stage, int depth)
 {
     float best = -CUDART_INF_F;
-    for (int base = threadIdx.x * 8; base < n; base += kThreads * 8 * 2) {
-        float x[2][8];
-        const int b1 = base + kThreads * 8;
-        raw.get8raw(base, n, x[0]);
-        if (b1 < n) raw.get8raw(b1, n, x[1]);
-#pragma unroll
-        for (int h = 0; h < 2; h++) {
-            const int b = h ? b1 : base;
-            if (b >= n) break;
-            const unsigned m = ov.bitmap[(b & 0xFFFF) >> 3];
-            if (m) {
-                // static indices only: a runtime index would push the whole array into local memory
-#pragma unroll
-                for (int j = 0; j < 8; j++) {
-                    if (((m >> j) & 1u) && b + j < n) {
-                        int slot = ov.find(b + j);
-                        if (slot >= 0) x[h][j] = ov.adj[slot];
-                    }
-                }
-            }
+    auto body = [&](int b, float x[8]) {
+        const unsigned m = ov.bitmap[(b & 0xFFFF) >> 3];
+        if (m) {
+            // static indices only: a runtime index would push the whole array into local memory
 #pragma unroll
             for (int j = 0; j < 8; j++) {
-                if (scale) x[h][j] = __fmul_rn(x[h][j], inv_t);
-                if (b + j < n) best = fmaxf(best, x[h][j]);
+                if (((m >> j) & 1u) && b + j < n) {
+                    int slot = ov.find(b + j);
+                    if (slot >= 0) x[j] = ov.adj[slot];
+                }
             }
-            store8(scratch, b, n, x[h]);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            if (scale) x[j] = __fmul_rn(x[j], inv_t);
+            if (b + j < n) best = fmaxf(best, x[j]);
+        }
+        store8(scratch, b, n, x);
+    };
+    constexpr int NQ = SrcLogits<BF16>::kQuads;
+    constexpr int step = kThreads * 8;
+    if (stage != nullptr && depth >= 2 && raw.stage_ok()) {
+        if (depth > 4) depth = 4;
+        int bq = threadIdx.x * 8;
+        for (int sidx = 0; sidx < depth; sidx++, bq += step) {
+            if (bq + 8 <= n) {
+                const char *g = raw.stage_src(bq);
+#pragma unroll
+                for (int q = 0; q < NQ; q++) cp_async16(stage_slot<NQ>(stage, sidx, q), g + q * 16);
+            }
+            cp_async_commit();
+        }
+        int sidx = 0;
+        for (int base = threadIdx.x * 8; base < n; base += step) {
+            if (depth == 4) cp_async_wait<3>(); else if (depth == 3) cp_async_wait<2>(); else cp_async_wait<1>();
+            float x[8];
+            if (base + 8 <= n) {
+                float4 qd[NQ];
+#pragma unroll
+                for (int q = 0; q < NQ; q++) qd[q] = *stage_slot<NQ>(stage, sidx, q);
+                raw.decode(base, qd, x);
+            } else {
+                raw.get8raw(base, n, x);
+            }
+            body(base, x);
+            if (bq + 8 <= n) {
+                const char *g = raw.stage_src(bq);
+#pragma unroll
+                for (int q = 0; q < NQ; q++) cp_async16(stage_slot<NQ>(stage, sidx, q), g + q * 16);
+            }
+            cp_async_commit();
+            bq += step;
+            sidx = sidx + 1 == depth ? 0 : sidx + 1;
+        }
+        cp_async_wait<0>();
+    } else {
+        for (int base = threadIdx.x * 8; base < n; base += step) {
+            float x[8];
+            raw.get8raw(base, n, x);
+            body(base, x);
         }
     }
     return block_max_float(best, red);
@@ -627,7 +691,12 @@ static __device__ __noinline__ float adjust_row(const SampleArgs &a, const RowPl
 {
     OvTable ov;
     build_overrides<BF16>(a, rp, raw.rowp, raw.mrow, n, with_hist, with_bias, ov, arena, slots);
-    return pass_adjust<BF16>(raw, ov, inv_t, scale, n, scratch, red);
+    // the table takes 24 bytes per slot and 8 KB of bitmap at the bottom of the key region; what
+    // is left of that region stages the reads
+    const int table_bytes = (slots * 24 + 8192 + 1023) & ~1023;
+    constexpr int stage_bytes = SrcLogits<BF16>::kQuads * 16 * kThreads;
+    const int depth = (kSortCap * 4 - table_bytes) / stage_bytes;
+    return pass_adjust<BF16>(raw, ov, inv_t, scale, n, scratch, red, arena + table_bytes, depth);
 }
 
 // mass of a histogram bin in exp-value units: every value in bin b >= 1 has the biased exponent
@@ -645,36 +714,62 @@ __device__ __forceinline__ double bin_mass(const unsigned *hmass, int b)
 static __device__ void sort_dirty_bins(RowCtl *rc, uint32_t *keys, const unsigned *bstart, const unsigned *hcount,
                                        uint32_t *tmp_key, int *tmp_dst)
 {
-    const int tid = threadIdx.x;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int nd = min(rc->n_dirty, kMaxDirty);
+    static_assert(kMaxDirty <= kThreads, "one dirty bin per thread in the prefix sum");
     __syncthreads();
-    int first = 0;
-    while (first < nd) {
-        // round: bins first .. last-1
-        if (tid == 0) {
-            int acc = 0, i = first;
-            for (; i < nd; i++) {
-                const int c = (int)hcount[rc->dirty[i]];
-                if (acc + c > kDirtyRound) break;
-                rc->dirty_cum[i] = acc;
-                acc += c;
+    // exclusive prefix of the dirty bins' key counts
+    {
+        const int c = tid < nd ? (int)hcount[rc->dirty[tid]] : 0;
+        int inc = c;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            int v = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+            if (lane >= o) inc += v;
+        }
+        if (lane == 31) rc->red_i[warp] = inc;
+        __syncthreads();
+        if (warp == 0) {
+            int w = rc->red_i[lane];
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                int v = __shfl_up_sync(0xFFFFFFFFu, w, o);
+                if (lane >= o) w += v;
             }
-            if (i == first) { rc->give_up = 1; i = nd; acc = 0; }  // one bin alone is too large
-            rc->dirty_cum[i] = acc;
-            rc->running = i;
+            rc->red_i[lane] = w;
         }
         __syncthreads();
-        const int last = rc->running;
-        const int m = rc->give_up ? 0 : rc->dirty_cum[last];
+        const int excl = inc - c + (warp ? rc->red_i[warp - 1] : 0);
+        if (tid < nd) rc->dirty_cum[tid] = excl;
+        if (tid == nd - 1) rc->dirty_cum[nd] = excl + c;
+        __syncthreads();
+    }
+    int first = 0;
+    while (first < nd) {
+        // round: the longest run of bins first .. last-1 holding at most kDirtyRound keys
+        const int base_cum = rc->dirty_cum[first];
+        int lo = first, hi = nd + 1;  // largest i with dirty_cum[i] - base_cum <= kDirtyRound
+        while (hi - lo > 1) {
+            int mid = (lo + hi) >> 1;
+            if (rc->dirty_cum[mid] - base_cum <= kDirtyRound) lo = mid; else hi = mid;
+        }
+        const int last = lo;
+        if (last == first) {  // one bin alone is too large for the in-place sort
+            __syncthreads();
+            if (tid == 0) rc->give_up = 1;
+            __syncthreads();
+            return;
+        }
+        const int m = rc->dirty_cum[last] - base_cum;
         for (int e = tid; e < m; e += kThreads) {
-            int lo = first, hi = last;  // last i in [first, last) with dirty_cum[i] <= e
-            while (hi - lo > 1) {
-                int mid = (lo + hi) >> 1;
-                if (rc->dirty_cum[mid] <= e) lo = mid; else hi = mid;
+            int l2 = first, h2 = last;  // last i in [first, last) with dirty_cum[i] - base_cum <= e
+            while (h2 - l2 > 1) {
+                int mid = (l2 + h2) >> 1;
+                if (rc->dirty_cum[mid] - base_cum <= e) l2 = mid; else h2 = mid;
             }
-            const int b = rc->dirty[lo];
+            const int b = rc->dirty[l2];
             const int off = (int)bstart[b], cnt = (int)hcount[b];
-            const int pos = e - rc->dirty_cum[lo];
+            const int pos = e - (rc->dirty_cum[l2] - base_cum);
             const uint32_t k = keys[off + pos];
             int rank = 0;
             for (int j = 0; j < cnt; j++) {
@@ -778,6 +873,8 @@ static __device__ __noinline__ double topp_cut(RowCtl *rc, const RowPlan &rp, in
     Emul2Work *wk2 = (Emul2Work *)(arena + kOffEmul);
     unsigned char *replay_ok = arena + kOffReplayOk;
     unsigned char *bin_exp = arena + kOffBinExp;
+    int *sub_src = (int *)(arena + kOffSubSrc);
+    unsigned short *sub_cnt = (unsigned short *)(arena + kOffSubCnt);
     RowDist d = rc->dist;
     const bool uniform = (d.flags & kDistUniform) != 0;
     double sum3 = 0.0;
@@ -884,20 +981,28 @@ static __device__ __noinline__ double topp_cut(RowCtl *rc, const RowPlan &rp, in
             // would be an exact tie (where the parity of the running sum decides the rounding, so
             // the order inside its bin matters) flags its bin.
             int my_surv = 0;
-            int list_run = 0;
             const uint32_t lo_bits = bin_floor_bits(c_lo);
-            for (int it0 = 0; it0 < n; it0 += kThreads * 8 * 2) {
+            // every warp owns a contiguous run of sub-tiles and compacts its candidates to the front
+            // of the same stretch of the list: token order is kept without a block-wide scan
+            const int lane = tid & 31, warp = tid >> 5;
+            const int nsub_v = (n + kSub - 1) / kSub;
+            const int per_warp = (nsub_v + (kThreads / 32) - 1) / (kThreads / 32);
+            const int t_begin = warp * per_warp, t_end = min(t_begin + per_warp, nsub_v);
+            u64 *seg = list + (size_t)t_begin * kSub;
+            int seg_cnt = 0;
+            for (int t = t_begin; t < t_end; t += 2) {
                 float x[2][8];
-                const int base = it0 + tid * 8;
-                const int b1 = base + kThreads * 8;
+                const int base = t * kSub + lane * 8;
+                const int b1 = base + kSub;
+                const bool has1 = t + 1 < t_end;
                 SrcScratch sc{scratch, 1.f, false};
                 if (base < n) sc.get8(base, n, x[0]);
-                if (b1 < n) sc.get8(b1, n, x[1]);
+                if (has1 && b1 < n) sc.get8(b1, n, x[1]);
                 unsigned take[2] = {0u, 0u};
 #pragma unroll
                 for (int h = 0; h < 2; h++) {
                     const int bb = h ? b1 : base;
-                    if (bb >= n) continue;
+                    if ((h && !has1) || bb >= n) continue;
 #pragma unroll
                     for (int j = 0; j < 8; j++) {
                         if (bb + j >= n) continue;
@@ -922,46 +1027,49 @@ static __device__ __noinline__ double topp_cut(RowCtl *rc, const RowPlan &rp, in
                         }
                     }
                 }
-                // token-ordered list: exclusive block scan of (count of half 0, count of half 1)
-                const int lane = tid & 31, warp = tid >> 5;
                 const int mine = __popc(take[0]) | (__popc(take[1]) << 16);
                 int inc = mine;
 #pragma unroll
                 for (int o = 1; o < 32; o <<= 1) {
-                    int t = __shfl_up_sync(0xFFFFFFFFu, inc, o);
-                    if (lane >= o) inc += t;
+                    int v = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+                    if (lane >= o) inc += v;
                 }
-                if (lane == 31) rc->red_i[warp] = inc;
-                __syncthreads();
-                if (warp == 0) {
-                    int wv = rc->red_i[lane];
-#pragma unroll
-                    for (int o = 1; o < 32; o <<= 1) {
-                        int t = __shfl_up_sync(0xFFFFFFFFu, wv, o);
-                        if (lane >= o) wv += t;
-                    }
-                    rc->red_i[lane] = wv;
-                }
-                __syncthreads();
-                const int excl = inc - mine + (warp ? rc->red_i[warp - 1] : 0);
-                const int total = rc->red_i[31];
-                int pos0 = list_run + (excl & 0xFFFF);
-                int pos1 = list_run + (total & 0xFFFF) + (excl >> 16);
+                const int total = __shfl_sync(0xFFFFFFFFu, inc, 31);
+                const int excl = inc - mine;
+                int pos0 = seg_cnt + (excl & 0xFFFF);
+                int pos1 = seg_cnt + (total & 0xFFFF) + (excl >> 16);
 #pragma unroll
                 for (int j = 0; j < 8; j++) {
                     if ((take[0] >> j) & 1u)
-                        list[pos0++] = ((u64)(uint32_t)(base + j) << 32) | __float_as_uint(x[0][j]);
+                        seg[pos0++] = ((u64)(uint32_t)(base + j) << 32) | __float_as_uint(x[0][j]);
                 }
 #pragma unroll
                 for (int j = 0; j < 8; j++) {
                     if ((take[1] >> j) & 1u)
-                        list[pos1++] = ((u64)(uint32_t)(b1 + j) << 32) | __float_as_uint(x[1][j]);
+                        seg[pos1++] = ((u64)(uint32_t)(b1 + j) << 32) | __float_as_uint(x[1][j]);
                 }
-                list_run += (total & 0xFFFF) + (total >> 16);
-                __syncthreads();  // red_i is reused by the next round
+                seg_cnt += (total & 0xFFFF) + (total >> 16);
+            }
+            // the list as a sequence of sub-tiles: each warp's stretch, padded to whole sub-tiles
+            __syncthreads();
+            if (lane == 0) rc->red_i[warp] = (seg_cnt + kSub - 1) / kSub;
+            __syncthreads();
+            {
+                int first = 0, all = 0;
+                for (int w = 0; w < kThreads / 32; w++) {
+                    const int c = rc->red_i[w];
+                    if (w < warp) first += c;
+                    all += c;
+                }
+                const int mine_tiles = (seg_cnt + kSub - 1) / kSub;
+                for (int k = lane; k < mine_tiles && first + k < kMaxSubTiles; k += 32) {
+                    sub_src[first + k] = (t_begin + k) * kSub;
+                    sub_cnt[first + k] = (unsigned short)min(kSub, seg_cnt - k * kSub);
+                }
+                __syncthreads();
+                if (tid == 0) rc->n_list = all <= kMaxSubTiles ? all * kSub : -1;  // -1: the draw walks the row instead
             }
             my_surv = block_sum_int(my_surv, rc->red_i);
-            if (tid == 0) rc->n_list = list_run;
             // The filters before top-p drop the smallest values only, so the bins that lost
             // elements are the last ones of the list: it stays dense.  From here on the histogram
             // describes the list.
@@ -1236,7 +1344,7 @@ static __device__ void run_row(const SampleArgs &a, int row, int item, SelCtl *s
     float *scratch = a.escratch + (int64_t)blockIdx.x * a.escratch_stride;
     uint32_t *gkeys = (uint32_t *)(a.keyscratch + (int64_t)blockIdx.x * a.key_stride);
     const int gkeys_cap = (int)(a.key_stride * 2);
-    u64 *list = a.listscratch + (int64_t)blockIdx.x * a.key_stride;
+    u64 *list = a.listscratch + (int64_t)blockIdx.x * (a.key_stride + 2 * kSub);
     const bool greedy = rp.temperature <= 0.f;
     const bool with_bias = !greedy && rp.bias_len > 0;
     const bool with_hist = rp.has_penalty && rp.hist_len > 0;
@@ -1331,9 +1439,10 @@ static __device__ void run_row(const SampleArgs &a, int row, int item, SelCtl *s
         // after top-p only the listed candidates can be non-zero, and adding a zero neither changes
         // the running sum nor can be the first element to reach the target (unless the target is
         // not positive, which the first token meets whatever its probability)
-        ProvList pl{list, rc.dist};
-        hit = emul_any<ProvList, false>(&rc.em, &rc.em2, wk2, pl, n_list, u, true, &cum, tk ? tk + 20 : nullptr);
-        if (hit >= 0) hit = (int)(__ldcg(list + hit) >> 32);
+        ProvList pl{list, (const int *)(arena + kOffSubSrc), (const unsigned short *)(arena + kOffSubCnt), rc.dist};
+        hit = emul_any<ProvList, false>(&rc.em, &rc.em2, wk2, pl, n_list, u, true, &cum, tk ? tk + 20 : nullptr,
+                                        arena + kOffKeys);
+        if (hit >= 0) hit = (int)(__ldcg(pl.at(hit)) >> 32);
         if (!(u > 0.f)) hit = 0;
     } else {
         hit = emul_any<ProvFinal, false>(&rc.em, &rc.em2, wk2, pf, n, u, true, &cum, tk ? tk + 20 : nullptr);
