@@ -385,8 +385,9 @@ int run_batch(StgHandle h, const StgSampleBatch *b, const BatchExtra &x, void *s
         }
         return STG_OK;
     }
-    // two persistent kernels: the row items (long, one SM each) on a high-priority side stream so
-    // that they take their SMs first, the chunk items on the caller's stream beside them
+    // two persistent kernels side by side: the row items (long, one SM each) go first on the
+    // caller's stream so that they take their SMs at once; the chunk items follow on a side stream
+    // with a grid that fits the SMs left over
     const int n_rows_items = pl.n_row_items, n_chunk_items = (int)pl.items.size() - pl.n_row_items;
     cudaError_t e = cudaSuccess;
     const bool both = n_rows_items > 0 && n_chunk_items > 0;
@@ -395,25 +396,27 @@ int run_batch(StgHandle h, const StgSampleBatch *b, const BatchExtra &x, void *s
         if (e == cudaSuccess) e = cudaStreamWaitEvent(h->aux_stream, h->ev_fork, 0);
     }
     int launches = 0;
+    int row_grid = 0;
     if (e == cudaSuccess && n_rows_items > 0) {
         SampleArgs r = a;
         r.n_items = n_rows_items;
         r.item_base = 0;
         r.work_counter = (uint32_t *)h->work_counter.p + 1;
         r.work_base = h->work_base_rows;
-        const int grid = std::min(n_rows_items, h->sm_count);
-        e = launch_sample_rows(r, grid, both ? h->aux_stream : stream);
-        if (e == cudaSuccess) { h->work_base_rows += (uint32_t)n_rows_items + (uint32_t)grid; launches++; }
-        if (e == cudaSuccess && both) e = cudaEventRecord(h->ev_join, h->aux_stream);
+        row_grid = std::min(n_rows_items, h->sm_count);
+        e = launch_sample_rows(r, row_grid, stream);
+        if (e == cudaSuccess) { h->work_base_rows += (uint32_t)n_rows_items + (uint32_t)row_grid; launches++; }
     }
     if (e == cudaSuccess && n_chunk_items > 0) {
         SampleArgs c = a;
         c.items = a.items + n_rows_items;
         c.n_items = n_chunk_items;
         c.item_base = n_rows_items;
-        const int grid = std::min(n_chunk_items, h->sm_count);
-        e = launch_sample_chunks(c, grid, pl.smem, stream);
+        const int room = h->sm_count - row_grid >= 16 ? h->sm_count - row_grid : h->sm_count;
+        const int grid = std::min(n_chunk_items, room);
+        e = launch_sample_chunks(c, grid, pl.smem, both ? h->aux_stream : stream);
         if (e == cudaSuccess) { h->work_base += (uint32_t)n_chunk_items + (uint32_t)grid; launches++; }
+        if (e == cudaSuccess && both) e = cudaEventRecord(h->ev_join, h->aux_stream);
     }
     if (e == cudaSuccess && both) e = cudaStreamWaitEvent(stream, h->ev_join, 0);
     if (e != cudaSuccess) {
