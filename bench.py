@@ -191,6 +191,100 @@ def run_reference(args, rank, world):
     print(json.dumps(line))
 
 
+def run_spec(args, rank, local, world):
+    """Config 4: one speculative verification step (32 sequences x (9 target + 8 draft) rows of
+    151,936 fp32 logits).  The unit is a verified sequence; same timing rules as the sampling step."""
+    import torch
+    import torch.distributed as dist
+
+    from opentail.stingray_b200 import BatchSampler
+    from opentail.stingray_b200 import workloads as W
+
+    torch.cuda.set_device(local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
+    w = W.config4(seed=3 + 100 * rank)
+    n_seq, lp1, vocab = w.target.shape
+    L = lp1 - 1
+    bs = BatchSampler(max_rows=n_seq * lp1, max_vocab=vocab, max_history=1, max_top_k=8, max_spec_draft=L, device=local)
+    n_copies = 2  # 2 x 331 MB > 126 MB L2
+    devs = [(torch.from_numpy(w.target).cuda(), torch.from_numpy(w.draft).cuda(),
+             torch.from_numpy(w.draft_tokens).cuda(), torch.from_numpy(w.uniforms).cuda()) for _ in range(n_copies)]
+
+    def step(i):
+        t, d, tok, u = devs[i % n_copies]
+        return bs.spec_verify(t, d, tok, w.params, u)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    barrier()
+    launches0 = bs.stats()["kernel_launches"]
+    clocks = ClockSampler(local)
+    clocks.start()
+    time.sleep(0.25)
+    barrier()
+    t_wall0 = time.time()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for i in range(args.steps):
+        step(i)
+    ev1.record()
+    torch.cuda.synchronize()
+    clock_info = clocks.stop(t_wall0, time.time())
+    ms_step = ev0.elapsed_time(ev1) / args.steps
+    launches = bs.stats()["kernel_launches"] - launches0
+    # end to end: pinned host logits in, accepted lengths and correction tokens out
+    pt, pd = torch.from_numpy(w.target).pin_memory(), torch.from_numpy(w.draft).pin_memory()
+    dt, dd = torch.empty_like(devs[0][0]), torch.empty_like(devs[0][1])
+    e2e_steps = max(3, min(args.steps, 5))
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(e2e_steps):
+        dt.copy_(pt, non_blocking=True)
+        dd.copy_(pd, non_blocking=True)
+        out = bs.spec_verify(dt, dd, w.draft_tokens, w.params, w.uniforms)
+        acc = out["accepted"].cpu()
+        corr = out["correction"].cpu()
+    e1.record()
+    torch.cuda.synchronize()
+    e2e_ms = e0.elapsed_time(e1) / e2e_steps
+    t = torch.tensor([ms_step, e2e_ms], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step, e2e_ms = [float(x) for x in t.cpu()]
+    peak, peak_kind = measured_peak()
+    alg = w.algorithmic_bytes()
+    if rank == 0:
+        line = {
+            "metric": "verified sequences/s (32 seq x (9 target + 8 draft) x V=151,936 fp32 per GPU)",
+            "value": n_seq * world / (ms_step / 1000.0), "unit": "sequences/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": w.name, "sequences_per_gpu": n_seq, "draft_len": L, "vocab": vocab,
+                       "sharding": f"sequences x{world}", "l2": f"{n_copies} rotating input copies, "
+                       f"{n_copies * (w.target.nbytes + w.draft.nbytes) / 1e6:.0f} MB > 126 MB L2"},
+            "roofline": {"bound": "hbm", "achieved": alg / (ms_step / 1000.0) / 1e9, "peak": peak, "unit": "GB/s",
+                         "frac": alg / (ms_step / 1000.0) / 1e9 / peak, "peak_kind": peak_kind,
+                         "algorithmic_bytes_per_launch": alg, "traffic": None},
+            "e2e": {"value": n_seq * world / (e2e_ms / 1000.0), "unit": "sequences/s",
+                    "h2d_bytes_per_step": w.target.nbytes + w.draft.nbytes + w.draft_tokens.nbytes + w.uniforms.nbytes,
+                    "d2h_bytes_per_step": 8 * n_seq, "ms_per_step": e2e_ms},
+            "gpu_launches": launches, "clocks": clock_info,
+            "accepted_mean": float(acc.float().mean()),
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -213,6 +307,9 @@ def main():
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the sampling path has no CPU fallback")
+    if args.config == "c4":
+        run_spec(args, rank, local, world)
+        return
     torch.cuda.set_device(local)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")

@@ -505,11 +505,7 @@ __device__ int emul_any(EmulCtl *c1, Emul2Ctl *c2, Emul2Work *wk, const Prov &pv
 {
     if (n <= kSub * kMaxSubTiles && wk != nullptr)
         return emul_scan2<Prov, POS_ONLY, false>(c2, wk, pv, n, target, has_target, sum_out, nullptr, tk, stage);
-#ifndef NO_OLD_EMUL
     return emul_scan<Prov, POS_ONLY>(c1, pv, n, target, has_target, sum_out);
-#else
-    return -1;
-#endif
 }
 
 }  // namespace stg

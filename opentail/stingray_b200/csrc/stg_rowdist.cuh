@@ -687,10 +687,11 @@ static __device__ float pass_adjust(const SrcLogits<BF16> &raw, const OvTable &o
 template <bool BF16>
 static __device__ __noinline__ float adjust_row(const SampleArgs &a, const RowPlan &rp, const SrcLogits<BF16> &raw, int n,
                                                 bool with_hist, bool with_bias, unsigned char *arena, int slots,
-                                                float inv_t, bool scale, float *scratch, float *red)
+                                                float inv_t, bool scale, float *scratch, float *red, u64 *tk)
 {
     OvTable ov;
     build_overrides<BF16>(a, rp, raw.rowp, raw.mrow, n, with_hist, with_bias, ov, arena, slots);
+    tick(tk, 11);
     // the table takes 24 bytes per slot and 8 KB of bitmap at the bottom of the key region; what
     // is left of that region stages the reads
     const int table_bytes = (slots * 24 + 8192 + 1023) & ~1023;
@@ -1209,12 +1210,9 @@ static __device__ void build_dist(RowCtl *rc, SelCtl *sctl, const Src &src, cons
                                   uint32_t *flags_out, u64 *tk, bool have_max, float mx_known)
 {
     const int tid = threadIdx.x;
-    uint32_t *skeys = (uint32_t *)(arena + kOffKeys);
     unsigned *hcount = (unsigned *)(arena + kOffCount);
     unsigned *hmass = (unsigned *)(arena + kOffMass);
-    unsigned *bstart = (unsigned *)(arena + kOffBinOff);
     Emul2Work *wk2 = (Emul2Work *)(arena + kOffEmul);
-    unsigned char *replay_ok = arena + kOffReplayOk;
     const bool want_topp = rp.top_p < 1.0f && rp.top_p > 0.f;
     const bool want_minp = rp.min_p > 0.f;
     const bool want_topk = rp.top_k > 0 && rp.top_k < n;
@@ -1275,7 +1273,6 @@ static __device__ void build_dist(RowCtl *rc, SelCtl *sctl, const Src &src, cons
     }
     __syncthreads();
     tick(tk, 3);
-#ifndef NO_TOPK
     if (want_topk) {
         __syncthreads();
         if (tid == 0) rc->dist = d;
@@ -1283,7 +1280,6 @@ static __device__ void build_dist(RowCtl *rc, SelCtl *sctl, const Src &src, cons
         topk_cut(rc, sctl, rp, n, scratch, arena);
         d = rc->dist;
     }
-#endif
     tick(tk, 4);
     if (want_minp) {
         // ApplyMinP (Sampler.cs:493-503): the largest probability belongs to exp value 1 (or 1/V)
@@ -1295,7 +1291,6 @@ static __device__ void build_dist(RowCtl *rc, SelCtl *sctl, const Src &src, cons
     }
 
     double sum3 = 0.0;
-#ifndef NO_TOPP
     if (want_topp) {
         __syncthreads();
         if (tid == 0) rc->dist = d;
@@ -1303,7 +1298,6 @@ static __device__ void build_dist(RowCtl *rc, SelCtl *sctl, const Src &src, cons
         sum3 = topp_cut(rc, rp, n, scratch, arena, gkeys, gkeys_cap, list, flags_out, tk);
         d = rc->dist;
     } else
-#endif
     {
         double part = 0.0;
         for (int base = tid * 8; base < n; base += kThreads * 8) {
@@ -1357,17 +1351,15 @@ static __device__ void run_row(const SampleArgs &a, int row, int item, SelCtl *s
     const bool scale = !greedy && rp.temperature != 1.0f;
     SrcLogits<BF16> raw{rowp, mrow, a.vec == 4, 1.f, false};
     float mx = 0.f;
-#ifndef NO_OVERRIDES
     if (overrides) {
         // adjusted (and scaled) logits into the scratch row
         const int entries = (with_hist ? rp.hist_len : 0) + (with_bias ? rp.bias_len : 0);
         int slots = 64;
         while (slots < 2 * entries) slots <<= 1;
-        mx = adjust_row<BF16>(a, rp, raw, n, with_hist, with_bias, arena, slots, inv_t, scale, scratch, rc.red_f);
+        mx = adjust_row<BF16>(a, rp, raw, n, with_hist, with_bias, arena, slots, inv_t, scale, scratch, rc.red_f, tk);
         __threadfence_block();
         __syncthreads();
     }
-#endif
     tick(tk, 1);
 
     if (greedy) {

@@ -548,14 +548,211 @@ static __device__ __forceinline__ float pow_rep(const float *tab, float rep, int
     return (float)pow((double)rep, (double)occ);
 }
 
+// Threshold of the `want` largest values of P[0..cnt) (block-wide radix select, most significant
+// byte first).  On return every P > *thr belongs to the `want` largest, and *need of the entries
+// equal to *thr complete them (which ones is the caller's tie rule).  All threads call it;
+// 1 <= want <= cnt.
+static __device__ void select_thr32(SelCtl *c, const uint32_t *P, int cnt, int want_in, uint32_t *thr, int *need)
+{
+    const int tid = threadIdx.x;
+    __syncthreads();
+    if (tid == 0) { c->want = want_in; c->prefix = 0; c->stop = 0; }
+    for (int pass = 3; pass >= 0; --pass) {
+        if (tid < 256) c->hist[tid] = 0;
+        __syncthreads();
+        const uint32_t prefix = (uint32_t)c->prefix;
+        const int sh = 8 * pass;
+        for (int e = tid; e < cnt; e += kThreads) {
+            const uint32_t k = P[e];
+            if (pass == 3 || (k >> (sh + 8)) == prefix) atomicAdd(&c->hist[(k >> sh) & 255u], 1u);
+        }
+        __syncthreads();
+        if (tid < 32) {
+            unsigned h[8];
+            unsigned local = 0;
+#pragma unroll
+            for (int j = 0; j < 8; j++) { h[j] = c->hist[tid * 8 + j]; local += h[j]; }
+            const unsigned want = (unsigned)c->want;  // read before the shuffles order the lanes
+            unsigned run = local;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                unsigned t = __shfl_down_sync(0xFFFFFFFFu, run, o);
+                if (tid + o < 32) run += t;
+            }
+            const unsigned above = run - local;
+            if (above < want && want <= above + local) {
+                unsigned acc = above;
+#pragma unroll
+                for (int j = 7; j >= 0; --j) {
+                    if (want <= acc + h[j]) {
+                        const uint32_t np = (prefix << 8) | (uint32_t)(tid * 8 + j);
+                        c->prefix = np;
+                        c->want = (int)(want - acc);
+                        if (pass == 0) {
+                            c->stop = 1;  // np is the exact threshold value
+                        } else if (h[j] == want - acc) {
+                            c->stop = 2;  // the whole bucket is taken: no ties to resolve
+                            c->thr = (u64)np << sh;
+                        }
+                        break;
+                    }
+                    acc += h[j];
+                }
+            }
+        }
+        __syncthreads();
+        if (c->stop) break;
+    }
+    if (c->stop == 2) {
+        const uint32_t lo = (uint32_t)c->thr;  // everything >= lo is taken
+        *thr = lo ? lo - 1u : 0u;
+        *need = lo ? 0 : 0x7FFFFFFF;           // lo == 0: every entry, also those equal to 0
+    } else {
+        *thr = (uint32_t)c->prefix;
+        *need = c->want;
+    }
+    __syncthreads();
+}
+
 struct FinishOut {
     int token;
     float prob;
     uint32_t flags;
 };
 
-// Finishes the top-k path for one row whose exact top-`sel` raw candidates sit (unsorted) in the
-// active buffer: sort, penalise, stable re-sort, softmax over the first k, min-p, top-p, draw.
+constexpr int kFastFinishK = 256;  // up to this top_k the candidates are selected, not sorted
+
+static __device__ void finish_topk_sort(Sel &s, const RowPlan &rp, const int32_t *hist, const float *pow_tab);
+static __device__ void finish_topk_draw(Sel &s, const RowPlan &rp, float uniform, FinishOut *out_sh, int32_t *o_ids,
+                                        float *o_vals, float *o_probs);
+
+// Candidate order for a small k without sorting the candidates: the exact candidate set by radix
+// select on the raw keys (Sampler.cs:225, :242-249), their penalised values (Sampler.cs:263-287),
+// the k best of those by a second radix select, and a rank sort of just these k in the stable
+// order of Sampler.cs:289-294 (penalised value descending, raw order among equals).  Leaves vals /
+// ids of the first k at the start of the buffer that is not active.
+static __device__ void finish_topk_select(Sel &s, const RowPlan &rp, const int32_t *hist, const float *pow_tab)
+{
+    SelCtl *c = s.c;
+    const int tid = threadIdx.x;
+    const int k = rp.top_k;
+    const int keep = rp.has_penalty ? rp.sel : k;
+    if (c->cnt > keep) {
+        const int n_saved = s.n;
+        s.n = keep;
+        sel_compact(s);
+        s.n = n_saved;
+    }
+    const int cnt = c->cnt;
+    const u64 *a = s.buf[c->cur];
+    unsigned char *bb = (unsigned char *)s.buf[c->cur ^ 1];
+    float *vals = (float *)bb;
+    int *ids = (int *)(vals + k);
+    const int ke = min(k, cnt);
+    if (!rp.has_penalty) {
+        for (int t = tid; t < k; t += kThreads) {
+            if (t >= cnt) { vals[t] = -CUDART_INF_F; ids[t] = -1; continue; }
+            const u64 key = a[t];
+            int rank = 0;
+            for (int j = 0; j < cnt; j++) rank += (a[j] > key) ? 1 : 0;
+            vals[rank] = key_val(key);
+            ids[rank] = key_idx(key);
+        }
+        __syncthreads();
+        return;
+    }
+    // scratch behind vals / ids / probs
+    uint32_t *P = (uint32_t *)(bb + (((size_t)3 * k * 4 + 15) & ~(size_t)15));  // penalised values, ordered bits
+    uint32_t *SP = P + ((cnt + 3) & ~3);                                        // ... of the k selected
+    u64 *SK = (u64 *)(SP + ((k + 3) & ~3));                                     // their raw keys
+    int hslots = 64;
+    while (hslots < 2 * rp.hist_len) hslots <<= 1;
+    int *hkey = (int *)(SK + k);
+    int *hall = hkey + hslots, *hwin = hall + hslots;
+    const bool use_hash = (char *)(hwin + hslots) <= (char *)(s.buf[c->cur ^ 1] + s.cap);
+    if (use_hash) {
+        for (int t = tid; t < hslots; t += kThreads) { hkey[t] = -1; hall[t] = 0; hwin[t] = 0; }
+        __syncthreads();
+        for (int t = tid; t < rp.hist_len; t += kThreads) {
+            const int id = __ldg(hist + t);
+            if (id < 0) continue;  // never a candidate, and -1 marks an empty slot
+            int h = (int)(((unsigned)id * 2654435761u) >> 7) & (hslots - 1);
+            for (;;) {
+                int old = atomicCAS(&hkey[h], -1, id);
+                if (old == -1 || old == id) break;
+                h = (h + 1) & (hslots - 1);
+            }
+            atomicAdd(&hall[h], 1);
+            if (t >= rp.window_start) atomicAdd(&hwin[h], 1);
+        }
+        __syncthreads();
+    }
+    for (int t = tid; t < cnt; t += kThreads) {
+        float v = key_val(a[t]);
+        const int id = key_idx(a[t]);
+        int occ_all = 0, occ_w = 0;
+        if (use_hash) {
+            int h = (int)(((unsigned)id * 2654435761u) >> 7) & (hslots - 1);
+            for (;;) {
+                const int kx = hkey[h];
+                if (kx == id) { occ_all = hall[h]; occ_w = hwin[h]; break; }
+                if (kx == -1) break;
+                h = (h + 1) & (hslots - 1);
+            }
+        } else {
+            count_occurrences(hist, rp.hist_len, rp.window_start, id, occ_all, occ_w);
+        }
+        if (occ_all > 0) {
+            if (rp.rep != 1.0f && occ_w > 0) {
+                float pw = pow_rep(pow_tab, rp.rep, occ_w);
+                v = v > 0.f ? __fdiv_rn(v, pw) : __fmul_rn(v, pw);
+            }
+            float add = __fadd_rn(rp.pres, __fmul_rn(rp.freq, (float)occ_all));
+            v = __fsub_rn(v, add);
+        }
+        P[t] = ord32(v);
+    }
+    __syncthreads();
+    uint32_t thr;
+    int need;
+    select_thr32(c, P, cnt, ke, &thr, &need);
+    if (tid == 0) c->cnt2 = 0;
+    __syncthreads();
+    for (int t = tid; t < cnt; t += kThreads) {
+        const uint32_t pv = P[t];
+        bool take = pv > thr;
+        if (pv == thr && need > 0) {
+            // ties at the k-th penalised value: the earlier ones in raw order complete the k
+            const u64 key = a[t];
+            int r = 0;
+            for (int j = 0; j < cnt; j++) r += (P[j] == thr && a[j] > key) ? 1 : 0;
+            take = r < need;
+        }
+        if (take) {
+            const int slot = atomicAdd(&c->cnt2, 1);
+            if (slot < k) { SP[slot] = pv; SK[slot] = a[t]; }
+        }
+    }
+    __syncthreads();
+    const int got = min(c->cnt2, k);
+    for (int t = tid; t < k; t += kThreads) {
+        if (t >= got) { vals[t] = -CUDART_INF_F; ids[t] = -1; continue; }
+        const uint32_t pv = SP[t];
+        const u64 key = SK[t];
+        int rank = 0;
+        for (int j = 0; j < got; j++) {
+            const uint32_t pj = SP[j];
+            rank += (pj > pv || (pj == pv && SK[j] > key)) ? 1 : 0;
+        }
+        vals[rank] = unord32(pv);
+        ids[rank] = key_idx(key);
+    }
+    __syncthreads();
+}
+
+// Finishes the top-k path for one row whose candidates - the exact top-`sel` raw logits, possibly
+// with some extra ones below them - sit (unsorted) in the active buffer: order the k best by
+// penalised value, softmax over them, min-p, top-p, draw.
 // Every fp32 operation is issued separately (no fused multiply-add), in the order of
 // Sampler.cs:257-349.  `vals`/`ids`/`probs` views alias the inactive buffer.
 static __device__ void finish_topk(Sel &s, const RowPlan &rp, const int32_t *hist, const float *pow_tab,
@@ -564,11 +761,8 @@ static __device__ void finish_topk(Sel &s, const RowPlan &rp, const int32_t *his
 {
     SelCtl *c = s.c;
     const int tid = threadIdx.x;
-    int cnt = c->cnt;
-    u64 *a = s.buf[c->cur];
-    u64 *b = s.buf[c->cur ^ 1];
+    const int cnt = c->cnt;
     const int k = rp.top_k;
-    const int sel = rp.sel;
     if (cnt == 0) {  // Sampler.cs:254-255: no finite logit -> Greedy(raw) == token 0
         if (tid == 0) { out_sh->token = 0; out_sh->prob = 0.f; out_sh->flags = kPathTopKNoFinite | (1u << 6); }
         for (int t = tid; t < k; t += kThreads) {
@@ -579,6 +773,25 @@ static __device__ void finish_topk(Sel &s, const RowPlan &rp, const int32_t *his
         __syncthreads();
         return;
     }
+    if (k <= kFastFinishK) {
+        finish_topk_select(s, rp, hist, pow_tab);
+    } else {
+        finish_topk_sort(s, rp, hist, pow_tab);
+    }
+    finish_topk_draw(s, rp, uniform, out_sh, o_ids, o_vals, o_probs);
+}
+
+// Candidate order by sorting everything (any k): leaves vals / ids of the first k in the buffer
+// that is not active.
+static __device__ void finish_topk_sort(Sel &s, const RowPlan &rp, const int32_t *hist, const float *pow_tab)
+{
+    SelCtl *c = s.c;
+    const int tid = threadIdx.x;
+    int cnt = c->cnt;
+    u64 *a = s.buf[c->cur];
+    u64 *b = s.buf[c->cur ^ 1];
+    const int k = rp.top_k;
+    const int sel = rp.sel;
     // raw order (Sampler.cs:242-249): descending value, ascending token on ties
     const bool small = cnt <= 192;  // the quadratic rank sort only wins for a handful of keys
     const int p2 = pow2_ceil(max(cnt, 2));
@@ -682,16 +895,31 @@ static __device__ void finish_topk(Sel &s, const RowPlan &rp, const int32_t *his
         }
     }
     __syncthreads();
+    // the draw reads vals / ids from the buffer that is not active
+    if (tid == 0 && work != b) c->cur ^= 1;
+    __syncthreads();
     float *vals = (float *)work;
     int *ids = (int *)(vals + k);
-    float *probs = (float *)(ids + k);
-    const float inv_t = rp.temperature == 1.0f ? 1.0f : __fdiv_rn(1.0f, rp.temperature);
 #pragma unroll
     for (int j = 0; j < R; j++) {
         int t = tid + j * kThreads;
         if (t < k) { vals[t] = rv[j]; ids[t] = ri[j]; }
     }
     __syncthreads();
+}
+
+// Softmax over the k ordered candidates, min-p, top-p and the draw (Sampler.cs:296-349).  vals / ids
+// sit at the start of the buffer that is not active.
+static __device__ void finish_topk_draw(Sel &s, const RowPlan &rp, float uniform, FinishOut *out_sh, int32_t *o_ids,
+                                        float *o_vals, float *o_probs)
+{
+    SelCtl *c = s.c;
+    const int tid = threadIdx.x;
+    const int k = rp.top_k;
+    float *vals = (float *)s.buf[c->cur ^ 1];
+    int *ids = (int *)(vals + k);
+    float *probs = (float *)(ids + k);
+    const float inv_t = rp.temperature == 1.0f ? 1.0f : __fdiv_rn(1.0f, rp.temperature);
     const float mx = __fmul_rn(vals[0], inv_t);
     for (int t = tid; t < k; t += kThreads) {
         float v = vals[t];
