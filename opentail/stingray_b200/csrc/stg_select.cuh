@@ -638,10 +638,27 @@ static __device__ void finish_topk_select(Sel &s, const RowPlan &rp, const int32
     const int k = rp.top_k;
     const int keep = rp.has_penalty ? rp.sel : k;
     if (c->cnt > keep) {
-        const int n_saved = s.n;
-        s.n = keep;
-        sel_compact(s);
-        s.n = n_saved;
+        if (c->cnt <= 512) {
+            // few candidates: rank them directly (fewer barriers than the radix passes)
+            const int m = c->cnt;
+            const u64 *src = s.buf[c->cur];
+            u64 *dst = s.buf[c->cur ^ 1];
+            __syncthreads();
+            for (int t = tid; t < m; t += kThreads) {
+                const u64 key = src[t];
+                int rank = 0;
+                for (int j = 0; j < m; j++) rank += (src[j] > key) ? 1 : 0;
+                if (rank < keep) dst[rank] = key;
+            }
+            __syncthreads();
+            if (tid == 0) { c->cnt = keep; c->cur ^= 1; }
+            __syncthreads();
+        } else {
+            const int n_saved = s.n;
+            s.n = keep;
+            sel_compact(s);
+            s.n = n_saved;
+        }
     }
     const int cnt = c->cnt;
     const u64 *a = s.buf[c->cur];
@@ -713,6 +730,24 @@ static __device__ void finish_topk_select(Sel &s, const RowPlan &rp, const int32
         P[t] = ord32(v);
     }
     __syncthreads();
+    if (cnt <= 256) {
+        // few candidates: the rank in the stable order is the position
+        for (int t = tid; t < k; t += kThreads) {
+            if (t >= ke) { vals[t] = -CUDART_INF_F; ids[t] = -1; }
+        }
+        for (int t = tid; t < cnt; t += kThreads) {
+            const uint32_t pv = P[t];
+            const u64 key = a[t];
+            int rank = 0;
+            for (int j = 0; j < cnt; j++) {
+                const uint32_t pj = P[j];
+                rank += (pj > pv || (pj == pv && a[j] > key)) ? 1 : 0;
+            }
+            if (rank < ke) { vals[rank] = unord32(pv); ids[rank] = key_idx(key); }
+        }
+        __syncthreads();
+        return;
+    }
     uint32_t thr;
     int need;
     select_thr32(c, P, cnt, ke, &thr, &need);
