@@ -26,7 +26,20 @@ namespace stg {
 // thread and sub-tile) can have them copied to shared memory a few sub-tiles ahead with cp.async,
 // so that the latency of L2 is not paid with registers.  Every thread copies and reads only its
 // own slots: no block-wide synchronisation is involved.
-constexpr int kStageBytes = 131072;  // shared memory the staged loops may use
+constexpr int kStageBytes = 131072;  // shared memory the staged loops use at most (4 stages of 32 bytes per thread)
+__device__ __forceinline__ void cp_async_wait_dyn(int pending)
+{
+    if (pending >= 3) asm volatile("cp.async.wait_group 3;" ::: "memory");
+    else if (pending == 2) asm volatile("cp.async.wait_group 2;" ::: "memory");
+    else if (pending == 1) asm volatile("cp.async.wait_group 1;" ::: "memory");
+    else asm volatile("cp.async.wait_group 0;" ::: "memory");
+}
+// stages of Q quads per thread that fit `bytes` of shared memory (at most 4; below 2 staging is off)
+__device__ __forceinline__ int stage_depth(int bytes, int quads)
+{
+    const int d = bytes / (quads * 16 * kThreads);
+    return d > 4 ? 4 : d;
+}
 template <class P, class = void>
 struct StageQ { static constexpr int load = 0, reload = 0; };
 template <class P>
@@ -232,7 +245,8 @@ __device__ __forceinline__ int replay_subtile(const float x[8], int base, int n,
 template <class Prov, bool POS_ONLY, bool FORCE, int UN = 2>
 __device__ __noinline__ int emul_scan2(Emul2Ctl *c, Emul2Work *wk, const Prov &pv_in, int n, float target,
                                        bool has_target, float *sum_out, const unsigned char *replay_ok,
-                                       unsigned long long *tk, unsigned char *stage = nullptr)
+                                       unsigned long long *tk, unsigned char *stage = nullptr,
+                                       int stage_bytes = kStageBytes)
 {
     // out of line, with its own copy of the provider: the loops below then get a register
     // allocation of their own instead of sharing one with the caller's other phases
@@ -244,12 +258,12 @@ __device__ __noinline__ int emul_scan2(Emul2Ctl *c, Emul2Work *wk, const Prov &p
     constexpr int W = kThreads / 32;
     constexpr int QL = StageQ<Prov>::load, QR = StageQ<Prov>::reload;
     bool staged = false;
-    if constexpr (QL > 0) staged = stage != nullptr && pv.stage_ok();
+    if constexpr (QL > 0)
+        staged = stage != nullptr && pv.stage_ok() && stage_depth(stage_bytes, QL) >= 2 && stage_depth(stage_bytes, QR) >= 2;
     if constexpr (QL > 0) {
         if (staged) {
-            constexpr int D = (kStageBytes / (QL * 16 * kThreads)) < 4 ? (kStageBytes / (QL * 16 * kThreads)) : 4;
+            const int D = stage_depth(stage_bytes, QL);
             int tq = warp;
-#pragma unroll
             for (int sidx = 0; sidx < D; sidx++, tq += W) {
                 const int b = tq * kSub + lane * 8;
                 if (tq < nsub && b + 8 <= n) {
@@ -261,7 +275,7 @@ __device__ __noinline__ int emul_scan2(Emul2Ctl *c, Emul2Work *wk, const Prov &p
             }
             int sidx = 0;
             for (int t = warp; t < nsub; t += W) {
-                cp_async_wait<D - 1>();
+                cp_async_wait_dyn(D - 1);
                 const int b = t * kSub + lane * 8;
                 float x[8];
                 if (b + 8 <= n) {
@@ -339,9 +353,8 @@ __device__ __noinline__ int emul_scan2(Emul2Ctl *c, Emul2Work *wk, const Prov &p
     // phase C: composite of every sub-tile under its guessed binade
     if constexpr (QR > 0) {
         if (staged) {
-            constexpr int D = (kStageBytes / (QR * 16 * kThreads)) < 4 ? (kStageBytes / (QR * 16 * kThreads)) : 4;
+            const int D = stage_depth(stage_bytes, QR);
             int tq = warp;
-#pragma unroll
             for (int sidx = 0; sidx < D; sidx++, tq += W) {
                 const int b = tq * kSub + lane * 8;
                 if (tq < nsub && b + 8 <= n && !(wk->sums[tq] == 0.0)) {
@@ -353,7 +366,7 @@ __device__ __noinline__ int emul_scan2(Emul2Ctl *c, Emul2Work *wk, const Prov &p
             }
             int sidx = 0;
             for (int t = warp; t < nsub; t += W) {
-                cp_async_wait<D - 1>();
+                cp_async_wait_dyn(D - 1);
                 const int b = t * kSub + lane * 8;
                 int a0 = 0, a1 = 0;
                 if (!(wk->sums[t] == 0.0)) {
@@ -501,10 +514,11 @@ __device__ __noinline__ int emul_scan2(Emul2Ctl *c, Emul2Work *wk, const Prov &p
 template <class Prov, bool POS_ONLY>
 __device__ int emul_any(EmulCtl *c1, Emul2Ctl *c2, Emul2Work *wk, const Prov &pv, int n, float target,
                         bool has_target, float *sum_out, unsigned long long *tk = nullptr,
-                        unsigned char *stage = nullptr)
+                        unsigned char *stage = nullptr, int stage_bytes = kStageBytes)
 {
     if (n <= kSub * kMaxSubTiles && wk != nullptr)
-        return emul_scan2<Prov, POS_ONLY, false>(c2, wk, pv, n, target, has_target, sum_out, nullptr, tk, stage);
+        return emul_scan2<Prov, POS_ONLY, false>(c2, wk, pv, n, target, has_target, sum_out, nullptr, tk, stage,
+                                                 stage_bytes);
     return emul_scan<Prov, POS_ONLY>(c1, pv, n, target, has_target, sum_out);
 }
 

@@ -220,6 +220,46 @@ struct SrcScratch {
     }
 };
 
+// the row's logits with the history / bias overrides applied on the fly (then temperature-scaled)
+template <bool BF16>
+struct SrcLogitsOv {
+    SrcLogits<BF16> raw;  // unscaled
+    OvTable ov;
+    float inv_t;
+    bool scale;
+    __device__ __forceinline__ void adjust(int base, int n, float x[8]) const
+    {
+        const unsigned m = ov.bitmap[(base & 0xFFFF) >> 3];
+        if (m) {
+            // static indices only: a runtime index would push the whole array into local memory
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                if (((m >> j) & 1u) && base + j < n) {
+                    int slot = ov.find(base + j);
+                    if (slot >= 0) x[j] = ov.adj[slot];
+                }
+            }
+        }
+        if (scale) {
+#pragma unroll
+            for (int j = 0; j < 8; j++) x[j] = __fmul_rn(x[j], inv_t);
+        }
+    }
+    __device__ __forceinline__ void get8(int base, int n, float x[8]) const
+    {
+        raw.get8raw(base, n, x);
+        adjust(base, n, x);
+    }
+    static constexpr int kQuads = SrcLogits<BF16>::kQuads;
+    __device__ __forceinline__ bool stage_ok() const { return raw.stage_ok(); }
+    __device__ __forceinline__ const char *stage_src(int base) const { return raw.stage_src(base); }
+    __device__ __forceinline__ void decode(int base, const float4 *q, float x[8]) const
+    {
+        raw.decode(base, q, x);
+        adjust(base, base + 8, x);
+    }
+};
+
 __device__ __forceinline__ void store8(float *p, int base, int n, const float x[8])
 {
     if (base + 8 <= n) {
@@ -612,40 +652,23 @@ static __device__ void build_overrides(const SampleArgs &a, const RowPlan &rp, c
     __syncthreads();
 }
 
-// first pass of a row with overrides: adjusted, scaled logits into the scratch row, and their maximum.
-// `stage` (may be null) is shared memory for `depth` stages of cp.async reads ahead.
+// First pass of a row with overrides: (maximum, lowest index of it) of the adjusted, scaled logits as
+// a key; 0 when nothing is > -infinity.  `stage` is shared memory for cp.async reads ahead.
 template <bool BF16>
-static __device__ float pass_adjust(const SrcLogits<BF16> &raw, const OvTable &ov, float inv_t, bool scale, int n,
-                                    float *scratch, float *red, unsigned char *stage, int depth)
+static __device__ __noinline__ u64 pass_max_ov(const SrcLogitsOv<BF16> &src_in, int n, u64 *red, unsigned char *stage,
+                                               int stage_bytes)
 {
+    const SrcLogitsOv<BF16> src = src_in;
     float best = -CUDART_INF_F;
-    auto body = [&](int b, float x[8]) {
-        const unsigned m = ov.bitmap[(b & 0xFFFF) >> 3];
-        if (m) {
-            // static indices only: a runtime index would push the whole array into local memory
-#pragma unroll
-            for (int j = 0; j < 8; j++) {
-                if (((m >> j) & 1u) && b + j < n) {
-                    int slot = ov.find(b + j);
-                    if (slot >= 0) x[j] = ov.adj[slot];
-                }
-            }
-        }
-#pragma unroll
-        for (int j = 0; j < 8; j++) {
-            if (scale) x[j] = __fmul_rn(x[j], inv_t);
-            if (b + j < n) best = fmaxf(best, x[j]);
-        }
-        store8(scratch, b, n, x);
-    };
-    constexpr int NQ = SrcLogits<BF16>::kQuads;
+    int best_i = -1;
+    constexpr int NQ = SrcLogitsOv<BF16>::kQuads;
     constexpr int step = kThreads * 8;
-    if (stage != nullptr && depth >= 2 && raw.stage_ok()) {
-        if (depth > 4) depth = 4;
+    const int depth = stage_depth(stage_bytes, NQ);
+    if (stage != nullptr && depth >= 2 && src.stage_ok()) {
         int bq = threadIdx.x * 8;
         for (int sidx = 0; sidx < depth; sidx++, bq += step) {
             if (bq + 8 <= n) {
-                const char *g = raw.stage_src(bq);
+                const char *g = src.stage_src(bq);
 #pragma unroll
                 for (int q = 0; q < NQ; q++) cp_async16(stage_slot<NQ>(stage, sidx, q), g + q * 16);
             }
@@ -653,19 +676,21 @@ static __device__ float pass_adjust(const SrcLogits<BF16> &raw, const OvTable &o
         }
         int sidx = 0;
         for (int base = threadIdx.x * 8; base < n; base += step) {
-            if (depth == 4) cp_async_wait<3>(); else if (depth == 3) cp_async_wait<2>(); else cp_async_wait<1>();
+            cp_async_wait_dyn(depth - 1);
             float x[8];
             if (base + 8 <= n) {
                 float4 qd[NQ];
 #pragma unroll
                 for (int q = 0; q < NQ; q++) qd[q] = *stage_slot<NQ>(stage, sidx, q);
-                raw.decode(base, qd, x);
+                src.decode(base, qd, x);
             } else {
-                raw.get8raw(base, n, x);
+                src.get8(base, n, x);
             }
-            body(base, x);
+#pragma unroll
+            for (int j = 0; j < 8; j++)
+                if (base + j < n && x[j] > best) { best = x[j]; best_i = base + j; }
             if (bq + 8 <= n) {
-                const char *g = raw.stage_src(bq);
+                const char *g = src.stage_src(bq);
 #pragma unroll
                 for (int q = 0; q < NQ; q++) cp_async16(stage_slot<NQ>(stage, sidx, q), g + q * 16);
             }
@@ -677,27 +702,14 @@ static __device__ float pass_adjust(const SrcLogits<BF16> &raw, const OvTable &o
     } else {
         for (int base = threadIdx.x * 8; base < n; base += step) {
             float x[8];
-            raw.get8raw(base, n, x);
-            body(base, x);
+            src.get8(base, n, x);
+#pragma unroll
+            for (int j = 0; j < 8; j++)
+                if (base + j < n && x[j] > best) { best = x[j]; best_i = base + j; }
         }
     }
-    return block_max_float(best, red);
-}
-
-template <bool BF16>
-static __device__ __noinline__ float adjust_row(const SampleArgs &a, const RowPlan &rp, const SrcLogits<BF16> &raw, int n,
-                                                bool with_hist, bool with_bias, unsigned char *arena, int slots,
-                                                float inv_t, bool scale, float *scratch, float *red, u64 *tk)
-{
-    OvTable ov;
-    build_overrides<BF16>(a, rp, raw.rowp, raw.mrow, n, with_hist, with_bias, ov, arena, slots);
-    tick(tk, 11);
-    // the table takes 24 bytes per slot and 8 KB of bitmap at the bottom of the key region; what
-    // is left of that region stages the reads
-    const int table_bytes = (slots * 24 + 8192 + 1023) & ~1023;
-    constexpr int stage_bytes = SrcLogits<BF16>::kQuads * 16 * kThreads;
-    const int depth = (kSortCap * 4 - table_bytes) / stage_bytes;
-    return pass_adjust<BF16>(raw, ov, inv_t, scale, n, scratch, red, arena + table_bytes, depth);
+    u64 k = best_i >= 0 ? make_key(best, best_i) : 0ull;
+    return block_max_key_r(k, red);
 }
 
 // mass of a histogram bin in exp-value units: every value in bin b >= 1 has the biased exponent
@@ -1207,7 +1219,8 @@ static __device__ __noinline__ double topp_cut(RowCtl *rc, const RowPlan &rp, in
 template <class Src>
 static __device__ void build_dist(RowCtl *rc, SelCtl *sctl, const Src &src, const RowPlan &rp, int n,
                                   float *scratch, unsigned char *arena, uint32_t *gkeys, int gkeys_cap, u64 *list,
-                                  uint32_t *flags_out, u64 *tk, bool have_max, float mx_known)
+                                  uint32_t *flags_out, u64 *tk, bool have_max, float mx_known,
+                                  unsigned char *stage, int stage_bytes)
 {
     const int tid = threadIdx.x;
     unsigned *hcount = (unsigned *)(arena + kOffCount);
@@ -1257,7 +1270,7 @@ static __device__ void build_dist(RowCtl *rc, SelCtl *sctl, const Src &src, cons
         unsigned long long *hist = (unsigned long long *)hcount;
         ProvExp<Src> pe{src, mx, scratch, want_topp ? hist : nullptr};
         emul_any<ProvExp<Src>, false>(&rc->em, &rc->em2, wk2, pe, n, 0.f, false, &sum, tk ? tk + 12 : nullptr,
-                                      arena + kOffKeys);
+                                      stage, stage_bytes);
         if (sum > 0.f && sum != 1.0f) { d.flags |= kDistScale1; d.inv1 = __fdiv_rn(1.0f, sum); }
         if (want_topp) {
             unsigned long long v[4];
@@ -1350,23 +1363,29 @@ static __device__ void run_row(const SampleArgs &a, int row, int item, SelCtl *s
     const float inv_t = (!greedy && rp.temperature != 1.0f) ? __fdiv_rn(1.0f, rp.temperature) : 1.0f;
     const bool scale = !greedy && rp.temperature != 1.0f;
     SrcLogits<BF16> raw{rowp, mrow, a.vec == 4, 1.f, false};
-    float mx = 0.f;
+    // rows with history penalties or logit bias: the adjusted logits of the few tokens concerned
+    // go into a hash table at the bottom of the key region; every later read of the row applies
+    // them on the fly.  What is left of the region stages the reads.
+    SrcLogitsOv<BF16> adj;
+    adj.raw = raw;
+    adj.inv_t = inv_t;
+    adj.scale = scale;
+    int table_bytes = 0;
+    u64 mk_adj = 0ull;
     if (overrides) {
-        // adjusted (and scaled) logits into the scratch row
         const int entries = (with_hist ? rp.hist_len : 0) + (with_bias ? rp.bias_len : 0);
         int slots = 64;
         while (slots < 2 * entries) slots <<= 1;
-        mx = adjust_row<BF16>(a, rp, raw, n, with_hist, with_bias, arena, slots, inv_t, scale, scratch, rc.red_f, tk);
-        __threadfence_block();
-        __syncthreads();
+        build_overrides<BF16>(a, rp, rowp, mrow, n, with_hist, with_bias, adj.ov, arena, slots);
+        table_bytes = (slots * 24 + 8192 + 1023) & ~1023;
+        tick(tk, 11);
+        mk_adj = pass_max_ov<BF16>(adj, n, rc.red_k, arena + table_bytes, kSortCap * 4 - table_bytes);
     }
     tick(tk, 1);
 
     if (greedy) {
         // Greedy / GreedyWithHistoryPenalties; in distribution mode a one-hot row
-        u64 mk;
-        if (overrides) { SrcScratch s{scratch, 1.f, false}; mk = pass_max(s, n, rc.red_k); }
-        else mk = pass_max(raw, n, rc.red_k);
+        const u64 mk = overrides ? mk_adj : pass_max(raw, n, rc.red_k);
         int tok = mk ? key_idx(mk) : 0;
         if (a.mode == 2) {
             if (tid == 0) {
@@ -1395,12 +1414,12 @@ static __device__ void run_row(const SampleArgs &a, int row, int item, SelCtl *s
     }
 
     if (overrides) {
-        // the scratch row is scaled already; the descriptor still records the scale
-        SrcScratch s{scratch, inv_t, false};
-        build_dist(&rc, sctl, s, rp, n, scratch, arena, gkeys, gkeys_cap, list, &sh_flags, tk, true, mx);
+        build_dist(&rc, sctl, adj, rp, n, scratch, arena, gkeys, gkeys_cap, list, &sh_flags, tk, true,
+                   mk_adj ? key_val(mk_adj) : -CUDART_INF_F, arena + table_bytes, kSortCap * 4 - table_bytes);
     } else {
         SrcLogits<BF16> s{rowp, mrow, a.vec == 4, inv_t, scale};
-        build_dist(&rc, sctl, s, rp, n, scratch, arena, gkeys, gkeys_cap, list, &sh_flags, tk, false, 0.f);
+        build_dist(&rc, sctl, s, rp, n, scratch, arena, gkeys, gkeys_cap, list, &sh_flags, tk, false, 0.f,
+                   arena + kOffKeys, kSortCap * 4);
     }
     if (a.mode == 2) {
         // descriptor only; the raw arg-max goes with it (the looser accept rule compares against it)
