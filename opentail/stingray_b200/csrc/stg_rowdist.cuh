@@ -116,6 +116,28 @@ struct OvTable {
     }
 };
 
+// What the streaming passes need of the table, in three registers: the arrays follow one another
+// (key, cnt_all, cnt_w, n_bias, bias, adj: `slots` words each, then the bitmap).
+struct OvView {
+    const int *key;
+    int mask;  // slots - 1
+    __device__ __forceinline__ int find(int id) const
+    {
+        int h = (int)(((unsigned)id * 2654435761u) >> 7) & mask;
+        for (;;) {
+            int k = key[h];
+            if (k == id) return h;
+            if (k == -1) return -1;
+            h = (h + 1) & mask;
+        }
+    }
+    __device__ __forceinline__ float adj(int slot) const { return ((const float *)key)[5 * (mask + 1) + slot]; }
+    __device__ __forceinline__ unsigned bitmap_byte(int i) const
+    {
+        return ((const unsigned char *)(key + 6 * (mask + 1)))[(i & 0xFFFF) >> 3];
+    }
+};
+
 // ---- sources of the row's adjusted, temperature-scaled logits ---------------------------------
 template <bool BF16>
 struct SrcLogits {
@@ -224,19 +246,19 @@ struct SrcScratch {
 template <bool BF16>
 struct SrcLogitsOv {
     SrcLogits<BF16> raw;  // unscaled
-    OvTable ov;
+    OvView ov;
     float inv_t;
     bool scale;
     __device__ __forceinline__ void adjust(int base, int n, float x[8]) const
     {
-        const unsigned m = ov.bitmap[(base & 0xFFFF) >> 3];
+        const unsigned m = ov.bitmap_byte(base);
         if (m) {
             // static indices only: a runtime index would push the whole array into local memory
 #pragma unroll
             for (int j = 0; j < 8; j++) {
                 if (((m >> j) & 1u) && base + j < n) {
                     int slot = ov.find(base + j);
-                    if (slot >= 0) x[j] = ov.adj[slot];
+                    if (slot >= 0) x[j] = ov.adj(slot);
                 }
             }
         }
@@ -1376,7 +1398,10 @@ static __device__ void run_row(const SampleArgs &a, int row, int item, SelCtl *s
         const int entries = (with_hist ? rp.hist_len : 0) + (with_bias ? rp.bias_len : 0);
         int slots = 64;
         while (slots < 2 * entries) slots <<= 1;
-        build_overrides<BF16>(a, rp, rowp, mrow, n, with_hist, with_bias, adj.ov, arena, slots);
+        OvTable table;
+        build_overrides<BF16>(a, rp, rowp, mrow, n, with_hist, with_bias, table, arena, slots);
+        adj.ov.key = table.key;
+        adj.ov.mask = table.mask;
         table_bytes = (slots * 24 + 8192 + 1023) & ~1023;
         tick(tk, 11);
         mk_adj = pass_max_ov<BF16>(adj, n, rc.red_k, arena + table_bytes, kSortCap * 4 - table_bytes);
