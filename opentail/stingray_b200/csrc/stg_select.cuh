@@ -432,7 +432,8 @@ static __device__ __forceinline__ void sel_process_iter(Sel &s, const float v[4]
 // current one is filtered (two iterations, 128 KB, in flight per CTA).  On return the buffer
 // holds a superset of the best N keys of the range, at most 2N of them.
 template <int VEC, bool BF16>
-static __device__ void sel_stream(Sel &s, const void *rowp, const uint32_t *mrow, int begin, int end)
+static __device__ void sel_stream_pass(Sel &s, const void *rowp, const uint32_t *mrow, int begin, int end,
+                                       bool optimistic)
 {
     SelCtl *c = s.c;
     constexpr int STEP = kThreads * 16;
@@ -442,7 +443,17 @@ static __device__ void sel_stream(Sel &s, const void *rowp, const uint32_t *mrow
         int idx[4];
         load_items<VEC, BF16, true>(rowp, mrow, begin, 0, first_end, v, idx);
         sel_append_exact(s, v, idx, first_end);
-        if (c->cnt > s.n) sel_raise(s);
+        if (c->cnt > s.n) {
+            // optimistic bound: the first sub-tile taken as a sample of the range, tau is set where
+            // about 2.5 N elements of the whole range should pass (the caller checks the outcome)
+            const int n_saved = s.n;
+            if (optimistic) {
+                const long long m = (5ll * s.n * kSubTile) / (2ll * (long long)(end - begin));
+                s.n = (int)max(32ll, min((long long)s.n, m));
+            }
+            sel_raise(s);
+            s.n = n_saved;
+        }
     }
     int cnt0 = c->cnt;
     int base = first_end;
@@ -462,6 +473,27 @@ static __device__ void sel_stream(Sel &s, const void *rowp, const uint32_t *mrow
             sel_process_iter<VEC>(s, vb, base, end, cnt0);
             if (!more) break;
             base = nb;
+        }
+    }
+}
+
+template <int VEC, bool BF16>
+static __device__ void sel_stream(Sel &s, const void *rowp, const uint32_t *mrow, int begin, int end)
+{
+    SelCtl *c = s.c;
+    // With a bound guessed from the first sub-tile the buffer rarely fills and tau is rarely raised
+    // again.  The guess is checked: the survivors are exactly the elements above the final tau, so
+    // N or more of them contain the best N; fewer (the first sub-tile was not representative) and
+    // the range is streamed again with the safe bound, the N-th best seen so far.
+    const bool try_optimistic = end - begin >= 4 * kSubTile;
+    sel_stream_pass<VEC, BF16>(s, rowp, mrow, begin, end, try_optimistic);
+    if (try_optimistic) {
+        __syncthreads();
+        const bool short_of = c->cnt < s.n && c->tau > -CUDART_INF_F;
+        __syncthreads();
+        if (short_of) {
+            sel_reset(s);
+            sel_stream_pass<VEC, BF16>(s, rowp, mrow, begin, end, false);
         }
     }
     if (c->cnt > 2 * s.n) sel_raise(s);

@@ -221,6 +221,41 @@ def test_promoting_penalties_two_stage_selection(bs):
     parity.compare(w, gpu)
 
 
+def test_sorted_and_drifting_rows_selection_retry(bs):
+    """Rows whose first elements are not representative of the rest (descending, ascending, a step):
+    the streaming selection guesses its threshold from the first sub-tile and must notice a guess
+    that keeps too few candidates."""
+    rng = np.random.default_rng(21)
+    vocab = 151936
+    base = rng.normal(0, 2.5, (6, vocab)).astype(np.float32)
+    logits = base.copy()
+    logits[0] = np.sort(base[0])[::-1]                      # largest values first
+    logits[1] = np.sort(base[1])                            # largest values last
+    logits[2, :8192] += 6.0                                 # a block of large values at the start
+    logits[3, 8192:] += 6.0                                 # ... everywhere but the start
+    logits[4] = np.round(base[4])                           # heavy ties
+    logits[4, :4096] = 9.0                                  # the whole first sub-tile is one tied maximum
+    p = _params(6, temperature=0.9, top_k=64, top_p=0.95, repetition_penalty=1.1, frequency_penalty=0.2)
+    hist = [rng.integers(0, vocab, 200) for _ in range(6)]
+    from opentail.stingray_b200 import workloads as W
+
+    w = _wl(logits, p, W.uniforms24(rng, 6), hist)
+    gpu = parity.run_gpu(bs, w, want_topk=64)
+    stats = parity.compare(w, gpu)
+    assert stats["mismatch"] == stats["boundary_draws"]
+    # the same rows as many-row batch (one chunk per row: long ranges)
+    from opentail.stingray_b200 import BatchSampler
+
+    big = np.tile(logits, (50, 1))
+    pb = np.tile(p, 50)
+    wb = _wl(big, pb, W.uniforms24(rng, 300), [hist[i % 6] for i in range(300)])
+    bs2 = BatchSampler(max_rows=300, max_vocab=vocab, max_history=256, max_top_k=64)
+    gb = parity.run_gpu(bs2, wb, want_topk=64)
+    bs2.close()
+    for r in range(300):
+        assert np.array_equal(gb["topk_ids"][r, :64], gpu["topk_ids"][r % 6, :64]), r
+
+
 def test_config1_single_row_and_greedy(bs):
     from opentail.stingray_b200 import workloads as W
 
