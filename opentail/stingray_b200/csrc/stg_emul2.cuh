@@ -64,14 +64,27 @@ __device__ __forceinline__ float4 *stage_slot(unsigned char *stage, int s, int q
 constexpr int kSub = 256;           // elements per sub-tile (8 consecutive per lane)
 constexpr int kMaxSubTiles = 1024;  // => sequences of up to 262144 elements
 
-struct Emul2Work {                  // lives in dynamic shared memory (20 KB)
-    double sums[kMaxSubTiles];      // sum of each sub-tile
-    int comp[kMaxSubTiles][2];      // composite increment under the guessed binade: even / odd start
-    int guess[kMaxSubTiles];        // guessed biased exponent of the running sum at the sub-tile
+constexpr int kMaxCross = 12;       // sub-tiles per scan with a prepared binade crossing
+
+// per-lane composites of a sub-tile in which the running sum is expected to pass from binade g to
+// g + 1: with them the walk crosses without touching the sub-tile's elements (except one lane's 8)
+struct CrossSlot {
+    int lo[32][2];                  // lane composite (even / odd start) under binade g
+    int hi[32][2];                  // ... under binade g + 1
 };
+
+struct Emul2Work {                  // lives in dynamic shared memory (20 KB)
+    float sums[kMaxSubTiles];       // sum of each sub-tile (a guess only needs float accuracy)
+    int comp[kMaxSubTiles][2];      // composite increment under the guessed binade: even / odd start
+    unsigned char guess[kMaxSubTiles];  // guessed biased exponent of the running sum at the sub-tile
+    unsigned char xslot[kMaxSubTiles];  // 1 + index of the sub-tile's CrossSlot, 0: none
+    CrossSlot xs[kMaxCross];
+};
+static_assert(sizeof(Emul2Work) >= 16384, "other phases borrow 16 KB of this area");
 
 struct Emul2Ctl {
     double wsum[32];
+    int n_cross;                    // CrossSlots handed out
     float s;
     int hit;
     int abort_at;                   // sub-tile that needed a replay the caller had forbidden, or -1
@@ -87,6 +100,21 @@ __device__ __forceinline__ void unit_incr_fast(float x, float scale, int &d0, in
     tie = (xs - tr) == 0.5f;               // exact below 2^24; 0 above
     d0 = d;
     d1 = tie ? 2 * (int)tr + 1 - d : d;
+}
+
+// composite of a lane's 8 consecutive elements under binade eb (saturating)
+__device__ __forceinline__ void lane_composite(const float x[8], int eb, int &a0, int &a1)
+{
+    a0 = 0; a1 = 0;
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        int d0, d1;
+        unit_incr(x[j], eb, d0, d1);
+        a0 += (a0 & 1) ? d1 : d0;
+        a1 += ((1 + a1) & 1) ? d1 : d0;
+    }
+    a0 = min(a0, 1 << 25);
+    a1 = min(a1, 1 << 25);
 }
 
 __device__ __forceinline__ int exp_of_double(double v)
@@ -291,7 +319,7 @@ __device__ __noinline__ int emul_scan2(Emul2Ctl *c, Emul2Work *wk, const Prov &p
                 for (int j = 0; j < 8; j++) acc += (x[j] > 0.f) ? x[j] : 0.f;
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
-                if (lane == 0) wk->sums[t] = (double)acc;
+                if (lane == 0) wk->sums[t] = acc;
                 const int bq = tq * kSub + lane * 8;
                 if (tq < nsub && bq + 8 <= n) {
                     const char *g = pv.stage_src(bq, false);
@@ -318,7 +346,7 @@ __device__ __noinline__ int emul_scan2(Emul2Ctl *c, Emul2Work *wk, const Prov &p
                 for (int j = 0; j < 8; j++) acc += (x[h][j] > 0.f) ? x[h][j] : 0.f;
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
-                if (lane == 0) wk->sums[t + h * W] = (double)acc;  // a guess only needs float accuracy
+                if (lane == 0) wk->sums[t + h * W] = acc;
             }
         }
     }
@@ -326,7 +354,7 @@ __device__ __noinline__ int emul_scan2(Emul2Ctl *c, Emul2Work *wk, const Prov &p
     tick(tk, 0);
     // phase B: exclusive prefix of the sub-tile sums -> guessed binade per sub-tile
     {
-        double v = tid < nsub ? wk->sums[tid] : 0.0;
+        double v = tid < nsub ? (double)wk->sums[tid] : 0.0;
         double inc = v;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
@@ -346,7 +374,14 @@ __device__ __noinline__ int emul_scan2(Emul2Ctl *c, Emul2Work *wk, const Prov &p
         }
         __syncthreads();
         double excl = inc - v + (warp ? c->wsum[warp - 1] : 0.0);
-        if (tid < nsub) wk->guess[tid] = exp_of_double(excl);
+        if (tid < nsub) { wk->guess[tid] = (unsigned char)exp_of_double(excl); wk->xslot[tid] = 0; }
+        if (tid == 0) c->n_cross = 0;
+    }
+    __syncthreads();
+    // sub-tiles in which the sum should pass into the next binade get a CrossSlot
+    if (tid + 1 < nsub && (int)wk->guess[tid + 1] == (int)wk->guess[tid] + 1 && wk->sums[tid] > 0.f) {
+        const int slot = atomicAdd(&c->n_cross, 1);
+        if (slot < kMaxCross) wk->xslot[tid] = (unsigned char)(slot + 1);
     }
     __syncthreads();
     tick(tk, 1);
@@ -357,7 +392,7 @@ __device__ __noinline__ int emul_scan2(Emul2Ctl *c, Emul2Work *wk, const Prov &p
             int tq = warp;
             for (int sidx = 0; sidx < D; sidx++, tq += W) {
                 const int b = tq * kSub + lane * 8;
-                if (tq < nsub && b + 8 <= n && !(wk->sums[tq] == 0.0)) {
+                if (tq < nsub && b + 8 <= n && !(wk->sums[tq] == 0.f)) {
                     const char *g = pv.stage_src(b, true);
 #pragma unroll
                     for (int q = 0; q < QR; q++) cp_async16(stage_slot<QR>(stage, sidx, q), g + q * 16);
@@ -369,7 +404,7 @@ __device__ __noinline__ int emul_scan2(Emul2Ctl *c, Emul2Work *wk, const Prov &p
                 cp_async_wait_dyn(D - 1);
                 const int b = t * kSub + lane * 8;
                 int a0 = 0, a1 = 0;
-                if (!(wk->sums[t] == 0.0)) {
+                if (!(wk->sums[t] == 0.f)) {
                     float x[8];
                     if (b + 8 <= n) {
                         float4 qd[QR];
@@ -384,10 +419,19 @@ __device__ __noinline__ int emul_scan2(Emul2Ctl *c, Emul2Work *wk, const Prov &p
                         for (int j = 0; j < 8; j++) x[j] = x[j] > 0.f ? x[j] : 0.f;
                     }
                     subtile_composite<FORCE>(x, wk->guess[t], a0, a1);
+                    const int xsl = wk->xslot[t];
+                    if (xsl) {
+                        CrossSlot &cs = wk->xs[xsl - 1];
+                        int l0, l1, h0, h1;
+                        lane_composite(x, wk->guess[t], l0, l1);
+                        lane_composite(x, wk->guess[t] + 1, h0, h1);
+                        cs.lo[lane][0] = l0; cs.lo[lane][1] = l1;
+                        cs.hi[lane][0] = h0; cs.hi[lane][1] = h1;
+                    }
                 }
                 if (lane == 0) { wk->comp[t][0] = a0; wk->comp[t][1] = a1; }
                 const int bq = tq * kSub + lane * 8;
-                if (tq < nsub && bq + 8 <= n && !(wk->sums[tq] == 0.0)) {
+                if (tq < nsub && bq + 8 <= n && !(wk->sums[tq] == 0.f)) {
                     const char *g = pv.stage_src(bq, true);
 #pragma unroll
                     for (int q = 0; q < QR; q++) cp_async16(stage_slot<QR>(stage, sidx, q), g + q * 16);
@@ -405,7 +449,7 @@ __device__ __noinline__ int emul_scan2(Emul2Ctl *c, Emul2Work *wk, const Prov &p
 #pragma unroll
         for (int h = 0; h < UN; h++) {
             const int tt = t + h * W;
-            z[h] = tt >= nsub || wk->sums[tt] == 0.0;  // nothing to add: composite 0
+            z[h] = tt >= nsub || wk->sums[tt] == 0.f;  // nothing to add: composite 0
             if (!z[h]) pv.reload(tt * kSub + lane * 8, n, x[h]);
         }
 #pragma unroll
@@ -419,6 +463,15 @@ __device__ __noinline__ int emul_scan2(Emul2Ctl *c, Emul2Work *wk, const Prov &p
                         for (int j = 0; j < 8; j++) x[h][j] = x[h][j] > 0.f ? x[h][j] : 0.f;
                     }
                     subtile_composite<FORCE>(x[h], wk->guess[tt], a0, a1);
+                    const int xsl = wk->xslot[tt];
+                    if (xsl) {
+                        CrossSlot &cs = wk->xs[xsl - 1];
+                        int l0, l1, h0, h1;
+                        lane_composite(x[h], wk->guess[tt], l0, l1);
+                        lane_composite(x[h], wk->guess[tt] + 1, h0, h1);
+                        cs.lo[lane][0] = l0; cs.lo[lane][1] = l1;
+                        cs.hi[lane][0] = h0; cs.hi[lane][1] = h1;
+                    }
                 }
                 if (lane == 0) { wk->comp[tt][0] = a0; wk->comp[tt][1] = a1; }
             }
@@ -432,7 +485,7 @@ __device__ __noinline__ int emul_scan2(Emul2Ctl *c, Emul2Work *wk, const Prov &p
         int hit = -1;
         int t = 0;
         int abort_at = -1;
-        int n_iter = 0, n_replay = 0;
+        int n_iter = 0, n_replay = 0, n_fast = 0;
         while (t < nsub && hit < 0) {
             n_iter++;
             const uint32_t sb = __float_as_uint(s);
@@ -448,7 +501,7 @@ __device__ __noinline__ int emul_scan2(Emul2Ctl *c, Emul2Work *wk, const Prov &p
             if (tt < nsub) {
                 a0 = wk->comp[tt][0];
                 a1 = wk->comp[tt][1];
-                valid = (wk->guess[tt] == eb) || (a0 == 0 && a1 == 0 && wk->sums[tt] == 0.0);
+                valid = (wk->guess[tt] == eb) || (a0 == 0 && a1 == 0 && wk->sums[tt] == 0.f);
             }
             int i0 = a0, i1 = a1;
             if (__any_sync(0xFFFFFFFFu, a0 != a1)) {
@@ -476,7 +529,7 @@ __device__ __noinline__ int emul_scan2(Emul2Ctl *c, Emul2Work *wk, const Prov &p
                 t += ok;
             }
             if (ok < 32 && t < nsub) {
-                if (wk->guess[t] != eb && !(wk->sums[t] == 0.0)) {
+                if (wk->guess[t] != eb && !(wk->sums[t] == 0.f)) {
                     // the binade was guessed wrongly for this sub-tile (it follows a crossing closely):
                     // its composite under the actual binade needs no order, so recompute it and retry
                     float x[8];
@@ -487,21 +540,83 @@ __device__ __noinline__ int emul_scan2(Emul2Ctl *c, Emul2Work *wk, const Prov &p
                     }
                     int a0, a1;
                     subtile_composite<FORCE>(x, eb, a0, a1);
-                    if (lane == 0) { wk->comp[t][0] = a0; wk->comp[t][1] = a1; wk->guess[t] = eb; }
+                    if (lane == 0) { wk->comp[t][0] = a0; wk->comp[t][1] = a1; wk->guess[t] = (unsigned char)eb; wk->xslot[t] = 0; }
                     __syncwarp();
                     continue;
                 }
                 if (FORCE && replay_ok != nullptr && !replay_ok[t]) { abort_at = t; break; }
                 float x[8];
                 pv.reload(t * kSub + lane * 8, n, x);
-                hit = replay_subtile<POS_ONLY>(x, t * kSub, n, target, has_target, s);
+                // prepared crossing: the lanes before the one in which the sum leaves the binade are
+                // taken by their composites, that lane adds its 8 elements for real, the lanes behind
+                // it are taken by their composites under the next binade
+                bool crossed = false;
+                const int xsl = wk->xslot[t];
+                if (xsl && eb < 253) {
+                    const CrossSlot &cs = wk->xs[xsl - 1];
+                    int i0 = cs.lo[lane][0], i1 = cs.lo[lane][1];
+#pragma unroll
+                    for (int o = 1; o < 32; o <<= 1) {
+                        int p0 = __shfl_up_sync(0xFFFFFFFFu, i0, o);
+                        int p1 = __shfl_up_sync(0xFFFFFFFFu, i1, o);
+                        if (lane >= o) { int r0, r1; comp(p0, p1, i0, i1, r0, r1); i0 = r0; i1 = r1; }
+                    }
+                    const uint32_t sb1 = __float_as_uint(s);  // s has moved on since the top of the round
+                    const int sint1 = (int)((sb1 & 0x7FFFFFu) | (((sb1 >> 23) & 255u) ? 0x800000u : 0u));
+                    const int S1 = sat_add(sint1, (sint1 & 1) ? i1 : i0);  // sum after lanes 0 .. lane
+                    const unsigned over = __ballot_sync(0xFFFFFFFFu, S1 >= (1 << 24));
+                    const unsigned tgt = __ballot_sync(0xFFFFFFFFu, (long long)S1 >= tint);
+                    const int L = over ? __ffs(over) - 1 : 32;
+                    if (L < 32 && (tgt & ((1u << L) - 1u)) == 0u) {
+                        int sprev = __shfl_sync(0xFFFFFFFFu, S1, L > 0 ? L - 1 : 0);
+                        if (L == 0) sprev = sint1;
+                        float acc = ldexpf((float)sprev, eb - 150);
+                        int hit_l = -1;
+                        if (lane == L) {
+                            const int g0 = t * kSub + lane * 8;
+#pragma unroll
+                            for (int j = 0; j < 8; j++) {
+                                if (g0 + j < n && (!POS_ONLY || x[j] > 0.f) && hit_l < 0) {
+                                    acc = __fadd_rn(acc, x[j]);
+                                    if (has_target && acc >= target) hit_l = g0 + j;
+                                }
+                            }
+                        }
+                        acc = __shfl_sync(0xFFFFFFFFu, acc, L);
+                        hit_l = __shfl_sync(0xFFFFFFFFu, hit_l, L);
+                        const uint32_t ab = __float_as_uint(acc);
+                        const int ef2 = (int)(ab >> 23) & 255;
+                        if (hit_l >= 0) {
+                            s = acc; hit = hit_l; crossed = true;
+                        } else if (ef2 == eb + 1) {
+                            const int sint2 = (int)((ab & 0x7FFFFFu) | 0x800000u);
+                            const long long tint2 = target_units(target, has_target, ef2);
+                            int j0 = lane > L ? cs.hi[lane][0] : 0, j1 = lane > L ? cs.hi[lane][1] : 0;
+#pragma unroll
+                            for (int o = 1; o < 32; o <<= 1) {
+                                int p0 = __shfl_up_sync(0xFFFFFFFFu, j0, o);
+                                int p1 = __shfl_up_sync(0xFFFFFFFFu, j1, o);
+                                if (lane >= o) { int r0, r1; comp(p0, p1, j0, j1, r0, r1); j0 = r0; j1 = r1; }
+                            }
+                            const int S2 = sat_add(sint2, (sint2 & 1) ? j1 : j0);
+                            const bool fire2 = S2 >= (1 << 24) || (long long)S2 >= tint2;
+                            if (__ballot_sync(0xFFFFFFFFu, fire2) == 0u) {
+                                const int send = __shfl_sync(0xFFFFFFFFu, S2, 31);
+                                s = ldexpf((float)send, ef2 - 150);
+                                crossed = true;
+                                n_fast++;
+                            }
+                        }
+                    }
+                }
+                if (!crossed) hit = replay_subtile<POS_ONLY>(x, t * kSub, n, target, has_target, s);
                 t += 1;
                 n_replay++;
             }
         }
         if (lane == 0) { c->s = s; c->hit = abort_at >= 0 ? -2 : hit; c->abort_at = abort_at; }
         tick(tk, 3);
-        if (tk && lane == 0) { tk[4] = (unsigned long long)n_iter; tk[5] = (unsigned long long)n_replay; }
+        if (tk && lane == 0) { tk[4] = (unsigned long long)n_iter; tk[5] = (unsigned long long)n_replay; tk[6] = (unsigned long long)n_fast; }
     }
     __syncthreads();
     if (sum_out) *sum_out = c->s;
