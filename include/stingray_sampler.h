@@ -255,6 +255,17 @@ STG_API int stg_mtp_accept(StgHandle handle, const void *logits, int32_t logits_
                            float p_min, int32_t *accept, int32_t *argmax, float *draft_prob,
                            void *stream);
 
+/* Composes the allowed-token bitmasks of several constraints of each row into one: the AND of the
+ * inners' words, AndTokenConstraint.Filter (src/OpenTail.Stingray.Core/Grammar/
+ * AndTokenConstraint.cs:44-86).  masks: device [n_masks, rows, mask_row_stride] words (n_masks <=
+ * 32), same bit convention as StgSampleBatch.mask.  An inner that allows nothing is skipped; when
+ * no inner constrains, or the intersection is empty, the row comes out as all ones (= unmasked)
+ * and out_uses_mask[row] (device uint8 [rows], may be NULL) is 0, else 1.  The result can be passed
+ * as StgSampleBatch.mask as it is. */
+STG_API int stg_and_masks(StgHandle handle, const uint32_t *masks, int32_t n_masks, int32_t rows,
+                          int32_t vocab, int64_t mask_row_stride, uint32_t *out,
+                          int64_t out_row_stride, uint8_t *out_uses_mask, void *stream);
+
 /* ---- vocabulary-sharded mode (no counterpart in the reference, which is single-device:
  *      src/OpenTail.Stingray.Cli/RunCommand.cs:100) ------------------------------------------------
  * Each rank holds the column slice [vocab_offset, vocab_offset + batch->vocab) of every row, the

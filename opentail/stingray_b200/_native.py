@@ -19,7 +19,7 @@ MEM_HOST_UNIFORMS, MEM_HOST_OUTPUTS, MEM_HOST_DRAFT = 16, 32, 64
 EXPORTS = [
     "stg_abi_version", "stg_create", "stg_destroy", "stg_last_error", "stg_get_stats", "stg_debug_phase_ticks",
     "stg_argmax_rows", "stg_argmax_rows_static", "stg_sample_rows", "stg_build_distribution", "stg_spec_verify",
-    "stg_mtp_accept", "stg_comm_unique_id", "stg_comm_init", "stg_comm_destroy",
+    "stg_mtp_accept", "stg_and_masks", "stg_comm_unique_id", "stg_comm_init", "stg_comm_destroy",
     "stg_shard_select", "stg_shard_allgather", "stg_shard_finish", "stg_shard_gather_local",
 ]
 
@@ -97,6 +97,7 @@ def load() -> C.CDLL:
     lib.stg_build_distribution.argtypes = [vp, C.POINTER(StgSampleBatch), vp, vp]
     lib.stg_spec_verify.argtypes = [vp, C.POINTER(StgSpecBatch), vp]
     lib.stg_mtp_accept.argtypes = [vp, vp, i32, i32, i32, i64, vp, f32, vp, vp, vp, vp]
+    lib.stg_and_masks.argtypes = [vp, vp, i32, i32, i32, i64, vp, i64, vp, vp]
     lib.stg_comm_unique_id.argtypes = [vp]
     lib.stg_comm_init.argtypes = [vp, vp, i32, i32]
     lib.stg_comm_destroy.argtypes = [vp]

@@ -14,7 +14,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libstingray_sampler.so")
-SOURCES = ["stg_kernels.cu", "stg_api.cu", "stg_spec.cu", "stg_spec_kernels.cu", "stg_static.cu"]
+SOURCES = ["stg_kernels.cu", "stg_api.cu", "stg_spec.cu", "stg_spec_kernels.cu", "stg_static.cu", "stg_mask.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC,-fvisibility=hidden", "-shared", "-cudart", "shared",

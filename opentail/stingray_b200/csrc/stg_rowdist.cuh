@@ -464,12 +464,25 @@ struct ProvList {  // final probabilities of the top-p candidates, in token orde
 
 struct ProvKeys {  // probability bit patterns in (partial) descending order
     const uint32_t *keys;
+    bool global;  // the list sits in global memory (a nucleus too wide for shared memory): staged reads pay
     __device__ __forceinline__ void load(int base, int n, float x[8]) const
     {
 #pragma unroll
         for (int j = 0; j < 8; j++) x[j] = (base + j < n) ? __uint_as_float(keys[base + j]) : 0.f;
     }
     __device__ __forceinline__ void reload(int base, int n, float x[8]) const { load(base, n, x); }
+    static constexpr int kQuadsLoad = 2, kQuadsReload = 2;
+    __device__ __forceinline__ bool stage_ok() const { return global; }
+    __device__ __forceinline__ const char *stage_src(int base, bool) const { return (const char *)(keys + base); }
+    __device__ __forceinline__ void load_from(int base, int n, const float4 *q, float x[8]) const
+    {
+        x[0] = q[0].x; x[1] = q[0].y; x[2] = q[0].z; x[3] = q[0].w;
+        x[4] = q[1].x; x[5] = q[1].y; x[6] = q[1].z; x[7] = q[1].w;
+    }
+    __device__ __forceinline__ void reload_from(int base, int n, const float4 *q, float x[8]) const
+    {
+        load_from(base, n, q, x);
+    }
 };
 
 // ---- block-wide helpers ----------------------------------------------------------------------------
@@ -1182,10 +1195,11 @@ static __device__ __noinline__ double topp_cut(RowCtl *rc, const RowPlan &rp, in
                     }
                     __syncthreads();
                 }
-                ProvKeys pk{keys};
+                ProvKeys pk{keys, keys != skeys};
                 if (nc <= kSub * kMaxSubTiles) {
                     hit = emul_scan2<ProvKeys, false, true, 4>(&rc->em2, wk2, pk, nc, rp.top_p, true, &cum,
-                                                            sorted_all ? nullptr : replay_ok, nullptr);
+                                                            sorted_all ? nullptr : replay_ok, nullptr,
+                                                            keys != skeys ? arena + kOffKeys : nullptr, kSortCap * 4);
                 } else {
                     if (!sorted_all) { if (tid == 0) rc->give_up = 1; __syncthreads(); continue; }
                     hit = emul_scan<ProvKeys, false>(&rc->em, pk, nc, rp.top_p, true, &cum);

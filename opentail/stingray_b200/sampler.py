@@ -327,6 +327,20 @@ class BatchSampler:
                                              am.data_ptr(), pr.data_ptr(), self._stream(stream)))
         return acc, am, pr
 
+    def and_masks(self, masks, vocab: int, stream=None):
+        """``AndTokenConstraint.Filter`` in bitmask form (``stg_and_masks``): ``masks`` is a CUDA int32
+        tensor ``[n_masks, rows, words]`` of allowed-token bits; returns (mask ``[rows, words]``,
+        uses ``[rows]`` uint8: 0 where the row comes out unmasked)."""
+        import torch
+
+        n_masks, rows, words = masks.shape
+        assert masks.is_contiguous() and masks.dtype == torch.int32
+        out = torch.empty((rows, words), dtype=torch.int32, device=masks.device)
+        uses = torch.empty(rows, dtype=torch.uint8, device=masks.device)
+        self._check(self._lib.stg_and_masks(self._h, C.c_void_p(masks.data_ptr()), n_masks, rows, vocab,
+                                            C.c_int64(words), C.c_void_p(out.data_ptr()), C.c_int64(words),
+                                            C.c_void_p(uses.data_ptr()), self._stream(stream)))
+        return out, uses
 
     # -- vocabulary-sharded mode ---------------------------------------------------------------------
     @staticmethod

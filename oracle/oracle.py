@@ -196,6 +196,26 @@ def sample(logits, params: OrcParams, u: float = 0.5, history=None, bias=None, s
     return SampleResult(tok, tr, cid, cv, cp, probs)
 
 
+def sample_bias_arrays(logits, params: OrcParams, u, history, bias_ids, bias_vals, sum_mode=0) -> SampleResult:
+    """``sample`` with the logit bias given as parallel arrays (duplicate ids are added one after the
+    other, as the reference's loop over the dictionary entries would for distinct keys)."""
+    a, pa = _f32(logits)
+    h, ph = _i32(history)
+    hc = 0 if h is None else h.size
+    bi, pbi = _i32(bias_ids)
+    bv, pbv = _f32(bias_vals)
+    tr = OrcTrace()
+    k = max(int(params.top_k), 1)
+    cid = np.full(k, -1, np.int32)
+    cv = np.zeros(k, np.float32)
+    cp = np.zeros(k, np.float32)
+    tok = lib().orc_sample(
+        pa, a.size, C.byref(params), ph, hc, pbi, pbv, bi.size, sum_mode, float(u), C.byref(tr),
+        cid.ctypes.data_as(C.POINTER(C.c_int32)), cv.ctypes.data_as(C.POINTER(C.c_float)),
+        cp.ctypes.data_as(C.POINTER(C.c_float)), None)
+    return SampleResult(tok, tr, cid, cv, cp, None)
+
+
 def build_filtered_distribution(logits, params: OrcParams, history=None, bias=None, sum_mode=0):
     a, pa = _f32(logits)
     h, ph = _i32(history)

@@ -256,6 +256,59 @@ def test_sorted_and_drifting_rows_selection_retry(bs):
         assert np.array_equal(gb["topk_ids"][r, :64], gpu["topk_ids"][r % 6, :64]), r
 
 
+def test_logit_bias_rows_against_oracle(bs):
+    """Rows with logit bias take the full-vocabulary path, where top-k is ApplyTopK + Normalize
+    (Sampler.cs:41-95): bias entries (duplicates, out-of-range ids, promoting and demoting values),
+    histories, top-k / min-p / top-p on and off, on a full-size vocabulary."""
+    import torch
+
+    rng = np.random.default_rng(31)
+    rows, vocab = 24, 151936
+    logits = rng.normal(0, 2.5, (rows, vocab)).astype(np.float32)
+    p = _params(rows, temperature=0.9, top_p=0.92)
+    p["temperature"] = rng.uniform(0.4, 1.3, rows).astype(np.float32)
+    p["top_k"] = rng.choice([0, 0, 30, 200], rows)
+    p["min_p"] = rng.choice([0.0, 0.0, 0.02], rows).astype(np.float32)
+    p["top_p"] = rng.choice([1.0, 0.9, 0.97], rows).astype(np.float32)
+    p["repetition_penalty"] = rng.choice([1.0, 1.15], rows).astype(np.float32)
+    p["frequency_penalty"] = rng.choice([0.0, 0.4], rows).astype(np.float32)
+    hist = [rng.integers(0, vocab, 100) for _ in range(rows)]
+    bias = []
+    for r in range(rows):
+        n = int(rng.integers(3, 40))
+        ids = rng.integers(-5, vocab + 5, n)
+        top = np.argsort(logits[r])[-3:]
+        ids[-3:] = top                                           # push the best tokens around
+        ids = np.unique(ids)                                     # LogitBias is a dictionary: distinct keys
+        vals = rng.choice([-100.0, -3.0, 2.5, 8.0], ids.size).astype(np.float32)
+        bias.append((ids.astype(np.int32), vals))
+    bi = np.concatenate([b[0] for b in bias])
+    bv = np.concatenate([b[1] for b in bias])
+    bo = np.concatenate([[0], np.cumsum([len(b[0]) for b in bias])]).astype(np.int32)
+    from opentail.stingray_b200 import workloads as W
+
+    u = W.uniforms24(rng, rows)
+    w = _wl(logits, p, u, hist)
+    out = bs.sample_rows(torch.from_numpy(logits).cuda(), p, history_ids=torch.from_numpy(w.history_ids).cuda(),
+                         history_offsets=w.history_offsets, bias=(torch.from_numpy(bi).cuda(), torch.from_numpy(bv).cuda(), bo),
+                         uniforms=torch.from_numpy(u).cuda(), want_probs=True, want_flags=True)
+    tok = out["tokens"].cpu().numpy()
+    prob = out["probs"].cpu().numpy()
+    flags = out["flags"].cpu().numpy().view(np.uint32)
+    mismatch = 0
+    for r in range(rows):
+        op = orc.OrcParams(*[p[r][n].item() for n in p.dtype.names])
+        ids, vals = bias[r]
+        res = orc.sample_bias_arrays(logits[r], op, float(u[r]), hist[r], ids, vals)
+        assert (flags[r] & 7) == 3
+        if tok[r] != res.token:
+            assert float(res.trace.margin) <= parity.BOUNDARY, (r, tok[r], res.token, res.trace.margin)
+            mismatch += 1
+        else:
+            np.testing.assert_allclose(prob[r], res.trace.prob, rtol=2e-5)
+    assert mismatch <= 1
+
+
 def test_config1_single_row_and_greedy(bs):
     from opentail.stingray_b200 import workloads as W
 

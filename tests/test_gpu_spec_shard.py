@@ -192,3 +192,34 @@ def test_vocab_sharded_equals_unsharded(n_ranks):
     assert np.array_equal(got["topk_ids"][4:], ref["topk_ids"][4:])
     assert np.array_equal(got["topk_logits"][4:], ref["topk_logits"][4:])
     assert np.array_equal(got["topk_probs"][4:], ref["topk_probs"][4:])
+
+
+def test_and_masks_matches_and_constraint_rules():
+    """AndTokenConstraint semantics (AndTokenConstraintTests.cs:132-216): intersection of the inners,
+    a dead inner is skipped, an empty intersection or no live inner leaves the row unmasked."""
+    import torch
+    from opentail.stingray_b200 import BatchSampler
+
+    rng = np.random.default_rng(9)
+    for vocab in (70, 1000, 151936, 262144):
+        words = (vocab + 31) // 32
+        rows, K = 7, 3
+        m = rng.integers(0, 2 ** 32, (K, rows, words), dtype=np.uint64).astype(np.uint32)
+        m[0, 1] = 0                                   # a dead inner in row 1
+        m[:, 2] = 0                                   # every inner dead in row 2
+        m[0, 3] = 0x55555555; m[1, 3] = 0xAAAAAAAA    # empty intersection in row 3
+        m[:, 4] = 0; m[0, 4, words - 1] = 1 << 31     # only a bit beyond the vocabulary (when vocab % 32 != 0)
+        m[1, 5] = 0xFFFFFFFF                          # an inner that allows everything
+        bs = BatchSampler(max_rows=rows, max_vocab=vocab, max_history=1, max_top_k=8)
+        out, uses = bs.and_masks(torch.from_numpy(m.view(np.int32)).cuda(), vocab)
+        out = out.cpu().numpy().view(np.uint32)
+        uses = uses.cpu().numpy()
+        bs.close()
+        tail = ((1 << (vocab & 31)) - 1) if vocab & 31 else 0xFFFFFFFF
+        for r in range(rows):
+            want, masking = orc.and_masks([m[k, r] for k in range(K)], vocab)
+            assert bool(uses[r]) == masking, (vocab, r)
+            got = out[r].copy()
+            got[-1] &= tail
+            want[-1] &= tail
+            assert np.array_equal(got, want), (vocab, r)
