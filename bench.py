@@ -125,6 +125,21 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
+def to_device(w):
+    """Device copies of a workload's arrays (the timed region starts with inputs resident in HBM)."""
+    import torch
+
+    dev = {}
+    lg = torch.from_numpy(w.logits.view(np.int16) if w.logits.dtype == np.uint16 else w.logits).cuda()
+    dev["logits"] = lg.view(torch.bfloat16) if w.logits.dtype == np.uint16 else lg
+    dev["uniforms"] = torch.from_numpy(w.uniforms).cuda()
+    if w.history_ids is not None:
+        dev["history_ids"] = torch.from_numpy(w.history_ids).cuda()
+    if w.mask is not None:
+        dev["mask"] = torch.from_numpy(w.mask.view(np.int32)).cuda()
+    return dev
+
+
 def make_workload(name: str, rank: int):
     from opentail.stingray_b200 import workloads as W
 
@@ -324,14 +339,13 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
 
     from opentail.stingray_b200 import BatchSampler
-    from tests import parity
 
     w = make_workload(args.config, rank)
     hist_max = int(np.diff(w.history_offsets).max()) if w.history_offsets is not None else 0
     bs = BatchSampler(max_rows=w.rows, max_vocab=w.vocab, max_history=max(hist_max, 1),
                       max_top_k=max(int(w.params["top_k"].max()), 1), device=local)
     n_copies = 3
-    devs = [parity.to_device(w) for _ in range(n_copies)]
+    devs = [to_device(w) for _ in range(n_copies)]
 
     def step(i):
         d = devs[i % n_copies]

@@ -1221,8 +1221,11 @@ static __device__ __noinline__ double topp_cut(RowCtl *rc, const RowPlan &rp, in
             }
             tick(tk, 8);
             if (hit < 0 && nc < my_surv && attempt == 0) continue;  // bound was too tight: take all
+            // no hit: the running sum never reaches top_p (min-p or top-k removed too much mass), and
+            // ApplyTopP then cuts nothing (Sampler.cs:536-549).  The list is only partially ordered,
+            // so its last key is not its smallest: the threshold is simply zero.
             const int last = hit >= 0 ? hit : nc - 1;
-            const float tstar = __uint_as_float(keys[last]);
+            const float tstar = hit >= 0 ? __uint_as_float(keys[last]) : 0.f;
             // ties at the cut: the kept ones are a prefix (by token id) of the equal probabilities
             int keep = 0, all = 0;
             for (int t = tid; t < nc; t += kThreads) {

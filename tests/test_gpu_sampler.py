@@ -309,6 +309,27 @@ def test_logit_bias_rows_against_oracle(bs):
     assert mismatch <= 1
 
 
+def test_top_p_never_reached_after_min_p(bs):
+    """min-p can remove so much mass that the running sum of ApplyTopP never reaches top_p; nothing
+    is cut then (Sampler.cs:536-549).  Also the wide-nucleus case (keys outside shared memory)."""
+    from opentail.stingray_b200 import workloads as W
+
+    rng = np.random.default_rng(41)
+    for vocab, sigma, temp, top_p, min_p in ((200003, 6.0, 0.7, 0.5, 0.2), (32000, 2.0, 1.5, 0.99, 0.01),
+                                              (151936, 1.0, 1.5, 0.9999, 0.001)):
+        rows = 6
+        logits = rng.normal(0, sigma, (rows, vocab)).astype(np.float32)
+        p = _params(rows, temperature=temp, top_p=top_p, min_p=min_p, repetition_penalty=1.1, presence_penalty=-0.5,
+                    repeat_last_n=0)
+        hist = [rng.integers(0, vocab, 300) for _ in range(rows)]
+        w = _wl(logits, p, W.uniforms24(rng, rows), hist)
+        first = parity.run_gpu(bs, w)
+        stats = parity.compare(w, first)
+        assert stats["mismatch"] == 0
+        again = parity.run_gpu(bs, w)
+        assert np.array_equal(first["tokens"], again["tokens"])
+
+
 def test_config1_single_row_and_greedy(bs):
     from opentail.stingray_b200 import workloads as W
 
