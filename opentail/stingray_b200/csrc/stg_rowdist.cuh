@@ -1126,7 +1126,7 @@ static __device__ __noinline__ double topp_cut(RowCtl *rc, const RowPlan &rp, in
             for (int j = 0; j < 4; j++) {
                 int b = kBins - 1 - (tid * 4 + j);
                 unsigned have = b >= c_lo ? cursor[b] : 0u;
-                hcount[b] = have;
+                if (b >= c_lo) hcount[b] = have;  // the bins below keep their counts for a second attempt
                 mine += (int)have;
             }
             const int nc = min(block_sum_int(mine, rc->red_i), cap);

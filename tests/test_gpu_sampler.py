@@ -316,7 +316,8 @@ def test_top_p_never_reached_after_min_p(bs):
 
     rng = np.random.default_rng(41)
     for vocab, sigma, temp, top_p, min_p in ((200003, 6.0, 0.7, 0.5, 0.2), (32000, 2.0, 1.5, 0.99, 0.01),
-                                              (151936, 1.0, 1.5, 0.9999, 0.001)):
+                                              (151936, 1.0, 1.5, 0.9999, 0.001), (262144, 2.0, 1.5, 0.9999, 0.0),
+                                              (200003, 3.5, 1.5, 0.9999, 0.0)):
         rows = 6
         logits = rng.normal(0, sigma, (rows, vocab)).astype(np.float32)
         p = _params(rows, temperature=temp, top_p=top_p, min_p=min_p, repetition_penalty=1.1, presence_penalty=-0.5,
