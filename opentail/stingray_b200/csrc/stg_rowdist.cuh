@@ -687,16 +687,16 @@ static __device__ void build_overrides(const SampleArgs &a, const RowPlan &rp, c
     __syncthreads();
 }
 
-// First pass of a row with overrides: (maximum, lowest index of it) of the adjusted, scaled logits as
+// First pass of a row: (maximum, lowest index of it) of the (adjusted,) scaled logits as
 // a key; 0 when nothing is > -infinity.  `stage` is shared memory for cp.async reads ahead.
-template <bool BF16>
-static __device__ __noinline__ u64 pass_max_ov(const SrcLogitsOv<BF16> &src_in, int n, u64 *red, unsigned char *stage,
-                                               int stage_bytes)
+template <class Src>
+static __device__ __noinline__ u64 pass_max_staged(const Src &src_in, int n, u64 *red, unsigned char *stage,
+                                                   int stage_bytes)
 {
-    const SrcLogitsOv<BF16> src = src_in;
+    const Src src = src_in;
     float best = -CUDART_INF_F;
     int best_i = -1;
-    constexpr int NQ = SrcLogitsOv<BF16>::kQuads;
+    constexpr int NQ = Src::kQuads;
     constexpr int step = kThreads * 8;
     const int depth = stage_depth(stage_bytes, NQ);
     if (stage != nullptr && depth >= 2 && src.stage_ok()) {
@@ -1273,7 +1273,7 @@ static __device__ void build_dist(RowCtl *rc, SelCtl *sctl, const Src &src, cons
     if (have_max) {
         mx = mx_known;
     } else {
-        u64 mk = pass_max(src, n, rc->red_k);
+        u64 mk = pass_max_staged(src, n, rc->red_k, stage, stage_bytes);
         mx = mk ? key_val(mk) : -CUDART_INF_F;
     }
     tick(tk, 2);
@@ -1421,7 +1421,7 @@ static __device__ void run_row(const SampleArgs &a, int row, int item, SelCtl *s
         adj.ov.mask = table.mask;
         table_bytes = (slots * 24 + 8192 + 1023) & ~1023;
         tick(tk, 11);
-        mk_adj = pass_max_ov<BF16>(adj, n, rc.red_k, arena + table_bytes, kSortCap * 4 - table_bytes);
+        mk_adj = pass_max_staged(adj, n, rc.red_k, arena + table_bytes, kSortCap * 4 - table_bytes);
     }
     tick(tk, 1);
 
