@@ -1228,13 +1228,14 @@ static __device__ __noinline__ double topp_cut(RowCtl *rc, const RowPlan &rp, in
             const float tstar = hit >= 0 ? __uint_as_float(keys[last]) : 0.f;
             // ties at the cut: the kept ones are a prefix (by token id) of the equal probabilities
             int keep = 0, all = 0;
+            double part = 0.0;
             for (int t = tid; t < nc; t += kThreads) {
-                if (keys[t] == __float_as_uint(tstar)) { all++; keep += (t <= last) ? 1 : 0; }
+                const uint32_t kb = keys[t];
+                if (kb == __float_as_uint(tstar)) { all++; keep += (t <= last) ? 1 : 0; }
+                if (t <= last) part += (double)__uint_as_float(kb);
             }
             keep = block_sum_int(keep, rc->red_i);
             all = block_sum_int(all, rc->red_i);
-            double part = 0.0;
-            for (int t = tid; t <= last; t += kThreads) part += (double)__uint_as_float(keys[t]);
             sum3 = block_sum_double(part, rc->red_d);
             d.flags |= kDistTopP;
             d.tstar = tstar;
