@@ -75,6 +75,23 @@ enum {
     STG_ROW_WIDE_NUCLEUS = 1u << 7   /* top-p candidates did not fit on chip; global-memory sort */
 };
 
+/* ---- per-sequence flags written to StgSpecBatch.seq_flags (STG_ROW_CDF_FALLBACK applies too) --- */
+enum {
+    STG_SEQ_EMPTY_RESIDUAL = 1u << 8, /* max(p - q, 0) summed to nothing: the correction was drawn from p
+                                         with the second spare uniform (Sampler.cs:598-599) */
+    STG_SEQ_BAD_DRAFT = 1u << 9       /* a draft token lay outside [0, vocab): it was rejected unread (the
+                                         reference throws there, SpeculativeDecoder.cs:534) */
+};
+
+/* ---- StgConfig.flags ---------------------------------------------------------------------------- */
+enum {
+    STG_CFG_HOST_LOGITS = 1u << 0,   /* reserve device staging for max_rows x max_vocab fp32 logits and the
+                                        matching mask words at stg_create, so that calls with
+                                        STG_MEM_HOST_LOGITS / STG_MEM_HOST_MASK never allocate; without
+                                        it that staging grows on the first such call (which then
+                                        synchronises the stream once) */
+};
+
 typedef struct StgSampler_ *StgHandle;
 
 /* Capacities fixed at creation; all device workspace is allocated once from them, so that no
@@ -89,7 +106,7 @@ typedef struct StgConfig {
     int32_t max_top_k;
     int32_t max_bias;     /* logit-bias entries per row */
     int32_t max_spec_draft; /* draft length of stg_spec_verify (0 = entry point unused) */
-    uint32_t flags;       /* reserved, 0 */
+    uint32_t flags;       /* STG_CFG_* */
 } StgConfig;
 
 /* SamplingParams of the reference (src/OpenTail.Stingray.Engine/Sampler.cs:648-686), the fields
@@ -137,7 +154,8 @@ typedef struct StgSampleBatch {
                                        path after the penalty re-sort (-1 = unused slot) */
     float *topk_logits;             /* out, same shape or NULL: their penalised logits */
     float *topk_probs;              /* out, same shape or NULL: softmax over the k candidates */
-    int32_t topk_stride;
+    int32_t topk_stride;            /* >= the largest top_k of any row on the top-k path when a topk_*
+                                       output is given (STG_ERR_INVALID_ARGUMENT otherwise) */
     uint32_t mem_flags;             /* STG_MEM_HOST_* */
 } StgSampleBatch;
 
@@ -156,7 +174,9 @@ typedef struct StgSpecBatch {
                                        1: looser accept p >= p_min || draft == argmax, draw from p */
     const void *target_logits;
     const void *draft_logits;       /* may be NULL when mode == 1 */
-    const int32_t *draft_tokens;    /* [n_seq, n_draft] */
+    const int32_t *draft_tokens;    /* [n_seq, n_draft]; ids outside [0, vocab) are an error when the
+                                       array is in host memory and are rejected with STG_SEQ_BAD_DRAFT
+                                       when it is in device memory */
     const StgRowParams *params;     /* host [n_seq]; histories and bias do not apply here (the
                                        reference turns speculation off when they are set,
                                        src/OpenTail.Stingray.Cli/RunCommand.cs:1651-1678) */
@@ -272,7 +292,7 @@ STG_API int stg_and_masks(StgHandle handle, const uint32_t *masks, int32_t n_mas
  * layout a tensor-parallel lm-head leaves behind.  stg_shard_select picks, per row, the local
  * candidates of the top-k path (batch->vocab is the slice width, history ids are global token
  * ids) into the handle's exchange buffer; stg_shard_allgather exchanges them between ranks with
- * one ncclAllGather; stg_shard_finish merges the gathered candidates and finishes the sampling
+ * ONE ncclAllGather per step; stg_shard_finish merges the gathered candidates and finishes the sampling
  * chain.  Only rows on the top-k path or greedy rows without penalties are supported; other rows
  * return STG_ERR_UNSUPPORTED (use row sharding for those). */
 STG_API int stg_comm_unique_id(void *out_id128); /* 128 bytes; call on rank 0, then broadcast */
@@ -281,6 +301,9 @@ STG_API int stg_comm_destroy(StgHandle handle);
 STG_API int stg_shard_select(StgHandle handle, const StgSampleBatch *batch, int32_t vocab_offset,
                              int32_t global_vocab, void *stream);
 STG_API int stg_shard_allgather(StgHandle handle, void *stream);
+/* Bytes this rank contributes to the all-gather of the step last selected (keys and counts of
+ * every row in one block, sized by the step's largest selection count). */
+STG_API int stg_shard_exchange_bytes(StgHandle handle, uint64_t *out_bytes);
 STG_API int stg_shard_finish(StgHandle handle, const StgSampleBatch *batch, int32_t global_vocab,
                              void *stream);
 /* Single-process variant of the exchange for tests: copies `n_ranks` handles' local candidate

@@ -15,12 +15,14 @@ ERR_NAMES = {
 DTYPE_F32, DTYPE_BF16 = 0, 1
 MEM_HOST_LOGITS, MEM_HOST_HISTORY, MEM_HOST_MASK, MEM_HOST_BIAS = 1, 2, 4, 8
 MEM_HOST_UNIFORMS, MEM_HOST_OUTPUTS, MEM_HOST_DRAFT = 16, 32, 64
+CFG_HOST_LOGITS = 1
+SEQ_EMPTY_RESIDUAL, SEQ_BAD_DRAFT = 1 << 8, 1 << 9
 
 EXPORTS = [
     "stg_abi_version", "stg_create", "stg_destroy", "stg_last_error", "stg_get_stats", "stg_debug_phase_ticks",
     "stg_argmax_rows", "stg_argmax_rows_static", "stg_sample_rows", "stg_build_distribution", "stg_spec_verify",
     "stg_mtp_accept", "stg_and_masks", "stg_comm_unique_id", "stg_comm_init", "stg_comm_destroy",
-    "stg_shard_select", "stg_shard_allgather", "stg_shard_finish", "stg_shard_gather_local",
+    "stg_shard_select", "stg_shard_allgather", "stg_shard_exchange_bytes", "stg_shard_finish", "stg_shard_gather_local",
 ]
 
 
@@ -103,6 +105,7 @@ def load() -> C.CDLL:
     lib.stg_comm_destroy.argtypes = [vp]
     lib.stg_shard_select.argtypes = [vp, C.POINTER(StgSampleBatch), i32, i32, vp]
     lib.stg_shard_allgather.argtypes = [vp, vp]
+    lib.stg_shard_exchange_bytes.argtypes = [vp, C.POINTER(C.c_uint64)]
     lib.stg_shard_finish.argtypes = [vp, C.POINTER(StgSampleBatch), i32, vp]
     lib.stg_shard_gather_local.argtypes = [vp, C.POINTER(vp), i32, vp]
     for name in EXPORTS:

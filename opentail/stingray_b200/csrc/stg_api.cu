@@ -64,6 +64,8 @@ struct Plan {
     int n_row_items = 0;
     size_t smem = 0;
     uint64_t n_greedy = 0, n_topk = 0, n_full = 0;
+    int max_topk_path_k = 0;  // largest top_k among the rows on the top-k path
+    int max_sel = 1;          // largest selection count of a chunked row
 };
 
 // Resolves every row's path exactly as Sampler.Sample dispatches (Sampler.cs:19-39) and lays out
@@ -108,6 +110,7 @@ int make_plan(StgHandle h, const StgSampleBatch *b, int mode, bool shard, int gl
             rp.path = rp.has_penalty ? kPathGreedyPen : kPathGreedy;
         } else if (p.top_k > 0 && p.top_k < GV && blen == 0) {
             rp.path = kPathTopK;
+            pl.max_topk_path_k = std::max(pl.max_topk_path_k, (int)p.top_k);
             int64_t want = (int64_t)p.top_k + (rp.has_penalty ? hlen : 0);
             rp.sel = (int)std::min<int64_t>(want, GV);
             if (p.top_k > h->cfg.max_top_k) return fail(h, STG_ERR_CAPACITY, "top_k larger than max_top_k");
@@ -174,6 +177,7 @@ int make_plan(StgHandle h, const StgSampleBatch *b, int mode, bool shard, int gl
     for (int r = 0; r < rows; r++)
         for (int c = 0; c < pl.rows[r].n_chunks; c++) pl.items.push_back({r, c});
     // room for two 4096-element sub-tiles beyond the selection when shared memory allows it: fewer compactions
+    pl.max_sel = max_sel;
     pl.cap = max_sel + 2 * kSubTile;
     if ((size_t)pl.cap * 16 > h->smem_optin) pl.cap = max_sel + kSubTile;
     pl.smem = std::max<size_t>((size_t)pl.cap * 16, 1024);  // chunk kernel; the row kernel has a fixed arena
@@ -220,8 +224,9 @@ int stage_in(StgHandle h, const void *src, size_t bytes, bool on_host, DevBuf &s
     if (src == nullptr || bytes == 0) { *out = src; return STG_OK; }
     if (!on_host) { *out = src; return STG_OK; }
     if (bytes > stage.bytes) {
-        // staging for host arrays is sized at creation from the handle's capacities; only the
-        // logits staging (the one large array) is grown on first use
+        // staging for host arrays is sized at creation from the handle's capacities; the logits and
+        // mask staging (the large ones) are sized there too with STG_CFG_HOST_LOGITS, and otherwise
+        // grown on first use
         if (&stage != &h->st_logits && &stage != &h->st_mask)
             return fail(h, STG_ERR_CAPACITY, "host array larger than the staging buffer");
         CK(cudaStreamSynchronize(stream));
@@ -317,6 +322,9 @@ int run_batch(StgHandle h, const StgSampleBatch *b, const BatchExtra &x, void *s
     const bool host_out = mf & STG_MEM_HOST_OUTPUTS;
     const int ts = b->topk_stride;
     if ((b->topk_ids || b->topk_logits || b->topk_probs) && ts < 1) return fail(h, STG_ERR_INVALID_ARGUMENT, "topk_stride must be positive");
+    // every top-k-path row writes top_k entries of each requested top-k output at row * topk_stride
+    if ((b->topk_ids || b->topk_logits || b->topk_probs) && pl.max_topk_path_k > ts)
+        return fail(h, STG_ERR_INVALID_ARGUMENT, "topk_stride is smaller than a row's top_k");
     if (host_out && (b->topk_ids || b->topk_logits || b->topk_probs) && (size_t)rows * ts * 4 > h->o_topk_ids.bytes)
         return fail(h, STG_ERR_CAPACITY, "topk outputs exceed max_rows * max_top_k");
     a.tokens = host_out ? (int32_t *)h->o_tokens.p : b->tokens;
@@ -355,9 +363,14 @@ int run_batch(StgHandle h, const StgSampleBatch *b, const BatchExtra &x, void *s
     a.keyscratch = (unsigned long long *)h->keyscratch.p;
     a.listscratch = (unsigned long long *)h->listscratch.p;
     a.dists = x.dists_out;
+    // vocabulary-sharded mode: one block per rank, [rows, stride] keys followed by [rows] counts,
+    // with the stride of this step (its largest selection count), so that one all-gather of
+    // exactly the bytes in use moves both
+    const int xstride = pl.max_sel;
+    const size_t xblock = round_up((size_t)rows * xstride * 8 + (size_t)rows * 4, 16);
     a.xchg_local = (unsigned long long *)h->xchg_local.p;
-    a.xchg_count = (int32_t *)h->xchg_count_local.p;
-    a.xchg_stride = h->shard_sel;
+    a.xchg_count = (int32_t *)((char *)h->xchg_local.p + (size_t)rows * xstride * 8);
+    a.xchg_stride = xstride;
     a.row_stride = b->row_stride;
     a.mask_stride = b->mask_row_stride;
     a.escratch_stride = h->escratch_stride;
@@ -371,10 +384,12 @@ int run_batch(StgHandle h, const StgSampleBatch *b, const BatchExtra &x, void *s
     a.mode = mode;
     a.vocab_offset = x.vocab_offset; a.shard_mode = x.shard_mode; a.n_ranks = h->n_ranks;
 
-    if (x.shard_mode == 1) h->shard_rows_used = rows;
+    if (x.shard_mode && xblock > h->xchg_local.bytes) return fail(h, STG_ERR_CAPACITY, "exchange buffers are too small");
+    if (x.shard_mode == 1) { h->shard_rows_used = rows; h->shard_stride_used = xstride; h->shard_block_bytes = xblock; }
     if (x.shard_mode == 2) {
-        if (rows != h->shard_rows_used) return fail(h, STG_ERR_INVALID_ARGUMENT, "batch differs from the one selected");
-        cudaError_t e2 = launch_shard_finish(a, h->xchg_gather.p, (const int32_t *)h->xchg_count_gather.p, (size_t)pl.cap * 16, stream);
+        if (rows != h->shard_rows_used || xstride != h->shard_stride_used)
+            return fail(h, STG_ERR_INVALID_ARGUMENT, "batch differs from the one selected");
+        cudaError_t e2 = launch_shard_finish(a, h->xchg_gather.p, xblock, (size_t)pl.cap * 16, stream);
         if (e2 != cudaSuccess) return cuda_fail(h, e2, "k_shard_finish launch");
         h->stats.kernel_launches++;
         if (host_out) {
@@ -497,8 +512,13 @@ int stg_create(const StgConfig *cfg, StgHandle *out)
     A(h->st_bias_ids, R * std::max<size_t>(cfg->max_bias, 1) * 4);
     A(h->st_bias_vals, R * std::max<size_t>(cfg->max_bias, 1) * 4);
     A(h->st_uniforms, R * 4);
-    A(h->st_mask, 256);
-    A(h->st_logits, 256);
+    if (cfg->flags & STG_CFG_HOST_LOGITS) {
+        A(h->st_mask, R * ((V + 31) / 32) * 4);
+        A(h->st_logits, R * V * 4);
+    } else {
+        A(h->st_mask, 256);
+        A(h->st_logits, 256);
+    }
     A(h->o_tokens, R * 4); A(h->o_probs, R * 4); A(h->o_flags, R * 4);
     const size_t tk = R * std::max<size_t>(cfg->max_top_k, 1) * 4;
     A(h->o_topk_ids, tk); A(h->o_topk_vals, tk); A(h->o_topk_probs, tk);
@@ -549,7 +569,7 @@ int stg_destroy(StgHandle h)
                      &h->dists, &h->st_hist, &h->st_bias_ids, &h->st_bias_vals, &h->st_uniforms, &h->st_mask, &h->st_logits,
                      &h->o_tokens, &h->o_probs, &h->o_flags, &h->o_topk_ids, &h->o_topk_vals, &h->o_topk_probs, &h->o_pairs, &h->ticks,
                      &h->sp_draft, &h->sp_uniforms, &h->sp_accepted, &h->sp_correction, &h->sp_aprobs, &h->sp_flags,
-                     &h->sp_rowstats, &h->xchg_local, &h->xchg_gather, &h->xchg_count_local, &h->xchg_count_gather};
+                     &h->sp_rowstats, &h->xchg_local, &h->xchg_gather};
     for (DevBuf *b : all) dev_free(*b);
     if (h->plan_host) cudaFreeHost(h->plan_host);
     for (auto &ev : h->plan_ev) if (ev) cudaEventDestroy(ev);

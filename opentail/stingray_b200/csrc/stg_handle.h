@@ -45,11 +45,12 @@ struct StgSampler_ {
     cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
     size_t plan_bytes_cap = 0;
     // exchange buffers of the vocabulary-sharded mode
-    stg::DevBuf xchg_local, xchg_gather, xchg_count_local, xchg_count_gather;
+    stg::DevBuf xchg_local, xchg_gather;  // per rank: [rows, stride] keys then [rows] counts
     void *nccl_lib = nullptr;
     void *nccl_comm = nullptr;
     int rank = 0, n_ranks = 1;
-    int shard_sel = 0, shard_rows = 0, shard_rows_used = 0;
+    int shard_sel = 0, shard_rows = 0, shard_rows_used = 0, shard_stride_used = 0;
+    size_t shard_block_bytes = 0;         // bytes one rank contributes to the exchange of the current step
 };
 
 namespace stg {

@@ -11,7 +11,7 @@ constexpr size_t kRowArenaBytes = 211968;  // layout in stg_rowdist.cuh (checked
 
 cudaError_t launch_sample_chunks(const SampleArgs &a, int grid, size_t smem, cudaStream_t stream);
 cudaError_t launch_sample_rows(const SampleArgs &a, int grid, cudaStream_t stream);
-cudaError_t launch_shard_finish(const SampleArgs &a, const void *gather, const int32_t *gcount, size_t smem,
+cudaError_t launch_shard_finish(const SampleArgs &a, const void *gather, size_t block_bytes, size_t smem,
                                 cudaStream_t stream);
 
 // speculative verification, second phase (stg_spec.cu)

@@ -1,0 +1,15 @@
+// The row kernel (full-vocabulary pipeline, one row per CTA) for f32 logits.
+#include "stg_kernels_impl.cuh"
+
+namespace stg {
+
+cudaError_t launch_rows_f32(const SampleArgs &a, int grid, cudaStream_t stream)
+{
+    void (*fn)(const SampleArgs) = k_sample_rows<false>;
+    cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRowArenaBytes);
+    if (e != cudaSuccess) return e;
+    fn<<<grid, kThreads, kRowArenaBytes, stream>>>(a);
+    return cudaGetLastError();
+}
+
+}  // namespace stg

@@ -10,6 +10,7 @@
 #include "stg_launch.h"
 
 using namespace stg;
+using stg::round_up;
 
 namespace {
 
@@ -70,20 +71,19 @@ int nccl_fail(StgHandle h, int code, const char *what)
 
 int ensure_exchange(StgHandle h, int n_ranks)
 {
+    // capacity of one rank's block: [max_rows, max_top_k + max_history] keys and [max_rows] counts
     const size_t R = (size_t)h->cfg.max_rows;
     const size_t sel = std::max<size_t>(1, (size_t)h->cfg.max_top_k + h->cfg.max_history);
-    const size_t local = R * sel * 8, gather = local * (size_t)n_ranks;
+    const size_t local = round_up(R * sel * 8 + R * 4, 16) + 16, gather = local * (size_t)n_ranks;
     int rc = STG_OK;
     if (h->xchg_local.bytes < local) {
-        dev_free(h->xchg_local); dev_free(h->xchg_count_local);
+        dev_free(h->xchg_local);
         rc = dev_alloc(h, h->xchg_local, local);
-        if (!rc) rc = dev_alloc(h, h->xchg_count_local, R * 4);
     }
     if (!rc && h->xchg_gather.bytes < gather) {
         // only the receive side grows with the number of ranks; this rank's own candidates stay
-        dev_free(h->xchg_gather); dev_free(h->xchg_count_gather);
+        dev_free(h->xchg_gather);
         rc = dev_alloc(h, h->xchg_gather, gather);
-        if (!rc) rc = dev_alloc(h, h->xchg_count_gather, R * 4 * (size_t)n_ranks);
     }
     if (rc) return rc;
     h->shard_sel = (int)sel;
@@ -114,6 +114,10 @@ int stg_spec_verify(StgHandle h, const StgSpecBatch *b, void *stream_)
     if (b->mode == 0 && L > 0 && any_sampled && !b->draft_logits)
         return fail(h, STG_ERR_INVALID_ARGUMENT, "draft_logits are required for the p/q accept rule");
     if (b->mem_flags & STG_MEM_HOST_LOGITS) return fail(h, STG_ERR_UNSUPPORTED, "stg_spec_verify takes device logits");
+    if (b->mem_flags & STG_MEM_HOST_DRAFT)
+        for (int64_t i = 0; i < (int64_t)S * L; i++)
+            if ((uint32_t)b->draft_tokens[i] >= (uint32_t)V)
+                return fail(h, STG_ERR_INVALID_ARGUMENT, "a draft token lies outside [0, vocab)");
     CK(cudaSetDevice(h->cfg.device));
 
     RowDist *tdist = (RowDist *)h->dists.p;
@@ -243,12 +247,20 @@ int stg_shard_allgather(StgHandle h, void *stream)
 {
     if (!h) return STG_ERR_INVALID_ARGUMENT;
     if (!h->nccl_comm) return fail(h, STG_ERR_NCCL, "stg_comm_init has not been called");
-    int rc = g_nccl.all_gather(h->xchg_local.p, h->xchg_gather.p, (size_t)h->shard_rows_used * h->shard_sel * 8, 1 /* ncclUint8 */,
-                               h->nccl_comm, (cudaStream_t)stream);
+    if (h->shard_block_bytes == 0) return fail(h, STG_ERR_INVALID_ARGUMENT, "stg_shard_select has not been called");
+    // ONE collective per step: every rank's keys and counts travel in the same block, and the block
+    // is as large as this step's selection counts need, not as the handle's capacities allow
+    int rc = g_nccl.all_gather(h->xchg_local.p, h->xchg_gather.p, h->shard_block_bytes, 1 /* ncclUint8 */, h->nccl_comm,
+                               (cudaStream_t)stream);
     if (rc != 0) return nccl_fail(h, rc, "ncclAllGather(candidates)");
-    rc = g_nccl.all_gather(h->xchg_count_local.p, h->xchg_count_gather.p, (size_t)h->shard_rows_used * 4, 1, h->nccl_comm,
-                           (cudaStream_t)stream);
-    if (rc != 0) return nccl_fail(h, rc, "ncclAllGather(counts)");
+    h->stats.kernel_launches++;
+    return STG_OK;
+}
+
+int stg_shard_exchange_bytes(StgHandle h, uint64_t *out_bytes)
+{
+    if (!h || !out_bytes) return STG_ERR_INVALID_ARGUMENT;
+    *out_bytes = (uint64_t)h->shard_block_bytes;
     return STG_OK;
 }
 
@@ -259,14 +271,16 @@ int stg_shard_gather_local(StgHandle h, const StgHandle *peers, int32_t n_ranks,
     h->n_ranks = n_ranks;
     int rc = ensure_exchange(h, n_ranks);
     if (rc) return rc;
-    h->shard_rows_used = peers[0] ? peers[0]->shard_rows_used : 0;
-    const size_t lb = (size_t)h->shard_rows_used * h->shard_sel * 8, cb = (size_t)h->shard_rows_used * 4;
+    if (!peers[0]) return fail(h, STG_ERR_INVALID_ARGUMENT, "peer handle is null");
+    h->shard_rows_used = peers[0]->shard_rows_used;
+    h->shard_stride_used = peers[0]->shard_stride_used;
+    h->shard_block_bytes = peers[0]->shard_block_bytes;
+    const size_t lb = h->shard_block_bytes;
     for (int r = 0; r < n_ranks; r++) {
         StgHandle p = peers[r];
-        if (!p || p->shard_sel != h->shard_sel || p->shard_rows_used != h->shard_rows_used || !p->xchg_local.p)
-            return fail(h, STG_ERR_INVALID_ARGUMENT, "peer handles must share the capacities of this one");
+        if (!p || p->shard_block_bytes != lb || p->shard_rows_used != h->shard_rows_used || !p->xchg_local.p)
+            return fail(h, STG_ERR_INVALID_ARGUMENT, "peer handles must have selected the same batch shape");
         CK(cudaMemcpyAsync((char *)h->xchg_gather.p + lb * r, p->xchg_local.p, lb, cudaMemcpyDeviceToDevice, stream));
-        CK(cudaMemcpyAsync((char *)h->xchg_count_gather.p + cb * r, p->xchg_count_local.p, cb, cudaMemcpyDeviceToDevice, stream));
     }
     return STG_OK;
 }

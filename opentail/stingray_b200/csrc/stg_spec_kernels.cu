@@ -79,6 +79,7 @@ struct SpecShared {
     EmulCtl em;
     Emul2Ctl em2;
     int accepted;
+    int bad_draft;
     int red_i[32];
 };
 
@@ -101,11 +102,18 @@ __global__ void __launch_bounds__(kThreads, 1) k_spec_finish(const __grid_consta
 
     if (tid == 0) {
         int acc = 0;
+        bool bad_draft = false;
         for (int i = 0; i < L; i++) {
             const int tok = a.draft_tokens[(int64_t)s * L + i];
             bool ok;
             float shown;
-            if (greedy) {
+            if ((unsigned)tok >= (unsigned)V) {
+                // a draft token outside the vocabulary (the reference's pDist[tokens[i]] throws,
+                // SpeculativeDecoder.cs:534): never read, rejected, and reported in the flags
+                ok = false;
+                shown = 0.f;
+                bad_draft = true;
+            } else if (greedy) {
                 // SpeculativeDecoder.Step, SpeculativeDecoder.cs:400-405
                 ok = (tok == td[i].tie_idx_max);
                 shown = ok ? 1.f : 0.f;
@@ -129,10 +137,11 @@ __global__ void __launch_bounds__(kThreads, 1) k_spec_finish(const __grid_consta
         if (a.accept_probs)
             for (int i = acc + 1; i < L; i++) a.accept_probs[(int64_t)s * L + i] = 0.f;
         sh.accepted = acc;
+        sh.bad_draft = bad_draft ? 1 : 0;
     }
     __syncthreads();
     const int acc = sh.accepted;
-    uint32_t fl = 0;
+    uint32_t fl = sh.bad_draft ? (1u << 9) : 0u;
     int corr;
     if (greedy) {
         corr = td[acc].tie_idx_max;

@@ -101,6 +101,7 @@ struct StaticDev {
     bool ready = false;
     u64 *partial = nullptr;
     unsigned int *ticket = nullptr;
+    int sm_count = 0;
 };
 static StaticDev g_static_dev[64];
 static std::mutex g_static_mu;
@@ -127,8 +128,11 @@ extern "C" int stg_argmax_rows_static(const void *logits, int32_t dtype, int32_t
             void *p = nullptr, *t = nullptr;
             if (cudaGetSymbolAddress(&p, g_static_partial) != cudaSuccess) return STG_ERR_CUDA;
             if (cudaGetSymbolAddress(&t, g_static_ticket) != cudaSuccess) return STG_ERR_CUDA;
+            int sms = 0;
+            if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) return STG_ERR_CUDA;
             g_static_dev[dev].partial = (u64 *)p;
             g_static_dev[dev].ticket = (unsigned int *)t;
+            g_static_dev[dev].sm_count = sms;
             g_static_dev[dev].ready = true;
         }
         sd = g_static_dev[dev];
@@ -136,7 +140,7 @@ extern "C" int stg_argmax_rows_static(const void *logits, int32_t dtype, int32_t
     // The counters are shared by every call and keep what the last call left; a call that was cut
     // short could leave them non-zero, so they are cleared on the stream before each launch.
     if (cudaMemsetAsync(sd.ticket, 0, sizeof(unsigned int) * (size_t)rows, stream) != cudaSuccess) return STG_ERR_CUDA;
-    int want = (4 * 148 + rows - 1) / rows;
+    int want = (4 * sd.sm_count + rows - 1) / rows;  // about four chunk CTAs per SM
     int max_s = (vocab + 16383) / 16384;
     int S = want < max_s ? want : max_s;
     if (S > kStaticMaxChunks) S = kStaticMaxChunks;

@@ -98,10 +98,12 @@ class BatchSampler:
     thread, like the reference's backend (``IThreadAffineBackend.cs:11-21``)."""
 
     def __init__(self, max_rows: int, max_vocab: int, max_history: int = 512, max_top_k: int = 256,
-                 max_bias: int = 64, max_spec_draft: int = 0, device: int = 0):
+                 max_bias: int = 64, max_spec_draft: int = 0, device: int = 0, host_logits: bool = False):
+        """``host_logits``: reserve the device staging for host-resident logits and masks at creation
+        (``STG_CFG_HOST_LOGITS``), so that no sampling call allocates."""
         self._lib = N.load()
         cfg = N.StgConfig(C.sizeof(N.StgConfig), device, max_rows, max_vocab, max_history, max_top_k,
-                          max_bias, max_spec_draft, 0)
+                          max_bias, max_spec_draft, N.CFG_HOST_LOGITS if host_logits else 0)
         h = C.c_void_p()
         rc = self._lib.stg_create(C.byref(cfg), C.byref(h))
         if rc != N.STG_OK:
@@ -364,6 +366,12 @@ class BatchSampler:
 
     def shard_allgather(self, stream=None):
         self._check(self._lib.stg_shard_allgather(self._h, self._stream(stream)))
+
+    def exchange_bytes(self) -> int:
+        """Bytes this rank sends in the all-gather of the step last selected."""
+        n = C.c_uint64(0)
+        self._check(self._lib.stg_shard_exchange_bytes(self._h, C.byref(n)))
+        return int(n.value)
 
     def shard_gather_local(self, peers: "Sequence[BatchSampler]", stream=None):
         arr = (C.c_void_p * len(peers))(*[p._h for p in peers])

@@ -41,6 +41,7 @@ class OrcTrace(C.Structure):
         ("prob", C.c_float),
         ("kept_sum", C.c_float),
         ("fallback", C.c_int32),
+        ("cut_margin", C.c_float),
     ]
 
 
@@ -67,6 +68,7 @@ TRACE_DTYPE = np.dtype(
         ("prob", "<f4"),
         ("kept_sum", "<f4"),
         ("fallback", "<i4"),
+        ("cut_margin", "<f4"),
     ]
 )
 
@@ -99,6 +101,11 @@ def lib() -> C.CDLL:
         _lib.orc_build_filtered_distribution.argtypes = [
             _f32p, C.c_int32, C.POINTER(OrcParams), _i32p, C.c_int32, _i32p, _f32p, C.c_int32,
             C.c_int, _f32p, _i32p,
+        ]
+        _lib.orc_build_filtered_distribution_ex.restype = None
+        _lib.orc_build_filtered_distribution_ex.argtypes = [
+            _f32p, C.c_int32, C.POINTER(OrcParams), _i32p, C.c_int32, _i32p, _f32p, C.c_int32,
+            C.c_int, _f32p, _i32p, _f32p,
         ]
         _lib.orc_sample_with_distribution.restype = C.c_int32
         _lib.orc_sample_with_distribution.argtypes = [
@@ -232,6 +239,27 @@ def build_filtered_distribution(logits, params: OrcParams, history=None, bias=No
                                           sum_mode, out.ctypes.data_as(C.POINTER(C.c_float)),
                                           C.byref(tie))
     return out, int(tie.value)
+
+
+def build_filtered_distribution_ex(logits, params: OrcParams, history=None, bias_ids=None, bias_vals=None,
+                                   sum_mode=0):
+    """BuildFilteredDistribution with the bias as parallel arrays; returns (probs, tie, cut_margin):
+    cut_margin is how close the sorted running sum of top-p came to top_p at the cut (inf: no top-p)."""
+    a, pa = _f32(logits)
+    h, ph = _i32(history)
+    hc = 0 if h is None else h.size
+    pbi = pbv = None
+    nb = 0
+    if bias_ids is not None and len(bias_ids):
+        bi, pbi = _i32(bias_ids)
+        bv, pbv = _f32(bias_vals)
+        nb = bi.size
+    out = np.zeros(a.size, np.float32)
+    tie = C.c_int32(0)
+    cm = C.c_float(0)
+    lib().orc_build_filtered_distribution_ex(pa, a.size, C.byref(params), ph, hc, pbi, pbv, nb, sum_mode,
+                                             out.ctypes.data_as(C.POINTER(C.c_float)), C.byref(tie), C.byref(cm))
+    return out, int(tie.value), float(cm.value)
 
 
 def sample_with_distribution(logits, params: OrcParams, u: float, history=None, sum_mode=0):

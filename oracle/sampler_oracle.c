@@ -61,6 +61,8 @@ typedef struct {
     float prob;            /* normalised probability of the returned token */
     float kept_sum;        /* fast path keptSum / full path final sequential CDF end value */
     int32_t fallback;      /* draw ran off the end of the CDF (rounding fallback taken) */
+    float cut_margin;      /* full path with top-p: distance of the sorted running sum from top_p at
+                              the cut, on the nearer side (0 when top-p did not run) */
 } OrcTrace;
 
 static const float NEG_INF = -INFINITY;
@@ -261,8 +263,9 @@ static int cmp_prob_desc(const void *a, const void *b)
 }
 
 /* ApplyTopP, Sampler.cs:516-551 */
-static void apply_top_p(float *probs, int32_t n, float top_p, int32_t *tie_at_cutoff)
+static void apply_top_p(float *probs, int32_t n, float top_p, int32_t *tie_at_cutoff, float *cut_margin)
 {
+    if (cut_margin) *cut_margin = INFINITY;
     int32_t m = 0;
     for (int32_t i = 0; i < n; i++)
         if (probs[i] > 0.f) m++;
@@ -275,9 +278,17 @@ static void apply_top_p(float *probs, int32_t n, float top_p, int32_t *tie_at_cu
     float cum = 0.f;
     int32_t cutoff = m;
     for (int32_t i = 0; i < m; i++) {
+        float before = cum;
         cum += ix[i].prob;
-        if (cum >= top_p) { cutoff = i + 1; break; }
+        if (cum >= top_p) {
+            cutoff = i + 1;
+            /* how close the running sum came to top_p on either side of the cut: a cut this close
+             * can move by one token when exp differs in its last bit */
+            if (cut_margin) *cut_margin = fminf(cum - top_p, top_p - before);
+            break;
+        }
     }
+    if (cut_margin && cutoff == m && cum < top_p) *cut_margin = top_p - cum;
     if (tie_at_cutoff)
         *tie_at_cutoff = (cutoff < m && ix[cutoff].prob == ix[cutoff - 1].prob) ? 1 : 0;
     for (int32_t i = cutoff; i < m; i++) probs[ix[i].idx] = 0.f;
@@ -327,8 +338,9 @@ ORC_API int32_t orc_sample_from_probs(const float *probs, int32_t n, double u, O
  * top-p -> normalise.  `probs` holds the logits on entry and the distribution on exit. */
 static void slow_pipeline(float *probs, int32_t n, const OrcParams *p, const int32_t *hist,
                           int32_t hcount, const int32_t *bias_ids, const float *bias_vals,
-                          int32_t nbias, int sum_mode, int32_t *tie_at_cutoff)
+                          int32_t nbias, int sum_mode, int32_t *tie_at_cutoff, float *cut_margin)
 {
+    if (cut_margin) *cut_margin = INFINITY;
     for (int32_t b = 0; b < nbias; b++)
         if ((uint32_t)bias_ids[b] < (uint32_t)n) probs[bias_ids[b]] += bias_vals[b];
     orc_apply_history_penalties(probs, n, p, hist, hcount);
@@ -343,7 +355,7 @@ static void slow_pipeline(float *probs, int32_t n, const OrcParams *p, const int
     }
     if (p->min_p > 0.f) apply_min_p(probs, n, p->min_p);
     if (tie_at_cutoff) *tie_at_cutoff = 0;
-    if (p->top_p < 1.0f && p->top_p > 0.f) apply_top_p(probs, n, p->top_p, tie_at_cutoff);
+    if (p->top_p < 1.0f && p->top_p > 0.f) apply_top_p(probs, n, p->top_p, tie_at_cutoff, cut_margin);
     normalize(probs, n, sum_mode);
 }
 
@@ -361,7 +373,25 @@ ORC_API void orc_build_filtered_distribution(const float *logits, int32_t n, con
         return;
     }
     memcpy(probs, logits, sizeof(float) * (size_t)n);
-    slow_pipeline(probs, n, p, hist, hcount, bias_ids, bias_vals, nbias, sum_mode, tie_at_cutoff);
+    slow_pipeline(probs, n, p, hist, hcount, bias_ids, bias_vals, nbias, sum_mode, tie_at_cutoff, NULL);
+}
+
+/* The same, also reporting how close the top-p running sum came to top_p at the cut
+ * (infinity when top-p is off): what a test needs to tell a last-bit exp difference from an error. */
+ORC_API void orc_build_filtered_distribution_ex(const float *logits, int32_t n, const OrcParams *p,
+                                                const int32_t *hist, int32_t hcount,
+                                                const int32_t *bias_ids, const float *bias_vals,
+                                                int32_t nbias, int sum_mode, float *probs,
+                                                int32_t *tie_at_cutoff, float *cut_margin)
+{
+    if (cut_margin) *cut_margin = INFINITY;
+    if (p->temperature <= 0.f) {
+        orc_build_filtered_distribution(logits, n, p, hist, hcount, bias_ids, bias_vals, nbias, sum_mode, probs,
+                                        tie_at_cutoff);
+        return;
+    }
+    memcpy(probs, logits, sizeof(float) * (size_t)n);
+    slow_pipeline(probs, n, p, hist, hcount, bias_ids, bias_vals, nbias, sum_mode, tie_at_cutoff, cut_margin);
 }
 
 /* SampleWithDistribution, Sampler.cs:172-187 */
@@ -529,8 +559,10 @@ ORC_API int32_t orc_sample(const float *logits, int32_t n, const OrcParams *p, c
 
     float *probs = (float *)malloc(sizeof(float) * (size_t)(n > 0 ? n : 1));
     memcpy(probs, logits, sizeof(float) * (size_t)n);
+    float cut_margin = INFINITY;
     slow_pipeline(probs, n, p, hist, hcount, bias_ids, bias_vals, nbias, sum_mode,
-                  &tr->tie_at_cutoff);
+                  &tr->tie_at_cutoff, &cut_margin);
+    tr->cut_margin = isinf(cut_margin) ? 0.f : cut_margin;
     tr->path = 3;
     int32_t nz = 0;
     for (int32_t i = 0; i < n; i++)

@@ -27,6 +27,7 @@ def test_static_argmax_matches_regular_entry_point_twice_in_a_row():
     import torch
     from opentail.stingray_b200 import BatchSampler
     from opentail.stingray_b200 import _native as N
+    from oracle import oracle as orc
 
     rng = np.random.default_rng(2024)
     bs = BatchSampler(max_rows=64, max_vocab=152064, max_history=1, max_top_k=1)
@@ -40,6 +41,9 @@ def test_static_argmax_matches_regular_entry_point_twice_in_a_row():
             assert np.array_equal(got_i, ref_i.cpu().numpy()), f"call {call}: indices differ"
             assert np.array_equal(got_v.view(np.uint32), ref_v.cpu().numpy().view(np.uint32)), f"call {call}: values differ"
             assert got_i[0] == 17
+            # and against the CPU restatement of Sampler.Greedy, row by row
+            want = np.array([orc.greedy(a[r]) for r in range(rows)])
+            assert np.array_equal(got_i, want), f"call {call}: indices differ from the oracle's"
         xb = torch.from_numpy(rng.normal(0, 3, (3, 70001)).astype(np.float32)).cuda().to(torch.bfloat16)
         ref_i, _ = bs.argmax_rows(xb)
         got_i, _ = _static_argmax(xb)           # odd width: unaligned rows take the scalar-load path
