@@ -72,7 +72,9 @@ enum {
     STG_ROW_TIE_AT_CUTOFF = 1u << 4, /* the top-p cut fell inside a group of equal probabilities */
     STG_ROW_CDF_FALLBACK = 1u << 5,  /* the draw ran past the end of the CDF (rounding fallback) */
     STG_ROW_FULLY_MASKED = 1u << 6,  /* no finite logit in the row */
-    STG_ROW_WIDE_NUCLEUS = 1u << 7   /* top-p candidates did not fit on chip; global-memory sort */
+    STG_ROW_WIDE_NUCLEUS = 1u << 7,  /* top-p candidates did not fit on chip; global-memory sort */
+    STG_ROW_READ_TWICE = 1u << 8     /* top-k path: the optimistic filter bound failed its check and the
+                                        row was streamed a second time with the exact selection */
 };
 
 /* ---- per-sequence flags written to StgSpecBatch.seq_flags (STG_ROW_CDF_FALLBACK applies too) --- */

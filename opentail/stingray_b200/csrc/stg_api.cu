@@ -10,6 +10,8 @@
 #include <string>
 #include <vector>
 
+#include "stg_emul2.cuh"
+#include "stg_flat.cuh"
 #include "stg_handle.h"
 #include "stg_launch.h"
 #include "stg_types.h"
@@ -54,23 +56,11 @@ namespace {
 // RepeatWindowStart, src/OpenTail.Stingray.Engine/Sampler.cs:364-365
 int repeat_window_start(int count, int last_n) { return (last_n <= 0 || last_n >= count) ? 0 : count - last_n; }
 
-struct Plan {
-    std::vector<RowPlan> rows;
-    std::vector<WorkItem> items;
-    std::vector<float> pow_tab;
-    int chunk_len = 0;
-    int cap = kSubTile + 1;
-    bool any_row_item = false;
-    int n_row_items = 0;
-    size_t smem = 0;
-    uint64_t n_greedy = 0, n_topk = 0, n_full = 0;
-    int max_topk_path_k = 0;  // largest top_k among the rows on the top-k path
-    int max_sel = 1;          // largest selection count of a chunked row
-};
 
 // Resolves every row's path exactly as Sampler.Sample dispatches (Sampler.cs:19-39) and lays out
 // the work items: whole-row items first (they run longest), then the chunk items row by row.
-int make_plan(StgHandle h, const StgSampleBatch *b, int mode, bool shard, int global_vocab, Plan &pl)
+int make_plan(StgHandle h, const StgSampleBatch *b, int mode, bool shard, int global_vocab, bool flat_ok, bool full_ok,
+              Plan &pl)
 {
     const int rows = b->rows, V = b->vocab;
     const int GV = global_vocab > 0 ? global_vocab : V;  // the vocabulary the reference's rules see
@@ -81,6 +71,7 @@ int make_plan(StgHandle h, const StgSampleBatch *b, int mode, bool shard, int gl
         const StgRowParams &p = b->params[r];
         RowPlan &rp = pl.rows[r];
         memset(&rp, 0, sizeof(rp));
+        rp.flat_full = -1;
         rp.temperature = p.temperature; rp.top_p = p.top_p; rp.min_p = p.min_p;
         rp.rep = p.repetition_penalty; rp.pres = p.presence_penalty; rp.freq = p.frequency_penalty;
         rp.top_k = p.top_k;
@@ -143,15 +134,25 @@ int make_plan(StgHandle h, const StgSampleBatch *b, int mode, bool shard, int gl
         else pl.any_row_item = true;
         if (rp.path == kPathTopK) pl.n_topk++; else if (rp.path == kPathFull) pl.n_full++; else pl.n_greedy++;
     }
+    pl.n_chunk_rows = n_chunk_rows;
+    // The flat step needs long, aligned rows and a candidate list (N + 4096 entries) that about 3 N
+    // expected survivors fit well inside.
+    pl.flat = flat_ok && n_chunk_rows > 0 && V >= kFlatPiece && 3 * (size_t)max_sel + 256 <= (size_t)max_sel + kFlatSlack;
+    if (pl.flat) {
+        size_t need = 0;
+        for (auto &rp : pl.rows)
+            if (rp.path == kPathTopK) need += (size_t)rp.sel + kFlatSlack;
+        if (need > h->cand_entries) pl.flat = false;
+    }
     // chunking: enough chunk items to balance the SMs, whole 4096-element sub-tiles per chunk
     int S = 1;
-    if (n_chunk_rows > 0) {
+    if (n_chunk_rows > 0 && !pl.flat) {
         int want = (2 * h->sm_count + n_chunk_rows - 1) / n_chunk_rows;  // about two items per SM
         int max_s = std::max(1, (V + 16383) / 16384);
         S = std::max(1, std::min({want, max_s, 64}));
         if (shard) S = std::min(S, 16);
     }
-    for (;;) {
+    for (; !pl.flat;) {
         pl.chunk_len = (int)round_up((size_t)((V + S - 1) / S), kSubTile);
         int n_chunks = (V + pl.chunk_len - 1) / pl.chunk_len;
         size_t need = 0;
@@ -164,6 +165,21 @@ int make_plan(StgHandle h, const StgSampleBatch *b, int mode, bool shard, int gl
     for (int r = 0; r < rows; r++) {
         RowPlan &rp = pl.rows[r];
         if (mode == 0 && (rp.path == kPathGreedy || rp.path == kPathTopK)) {
+            if (pl.flat) {
+                rp.n_chunks = 1;  // one finishing item per row
+                rp.cand_off = cand_off;
+                rp.slot = slot++;
+                if (rp.path == kPathTopK) {
+                    cand_off += rp.sel + kFlatSlack;
+                    // groups of the 4096-element sample: about 3 N survivors (at least 256) over the row
+                    const double t = std::max(3.0 * rp.sel, 256.0);
+                    const double m = t * kFlatSample / (double)V;
+                    int ng = 1;
+                    while (ng < 1024 && ng < m / 2.0) ng <<= 1;
+                    rp.flat_groups = ng;
+                }
+                continue;
+            }
             rp.n_chunks = S;
             rp.cand_off = cand_off;
             rp.slot = slot;
@@ -174,6 +190,16 @@ int make_plan(StgHandle h, const StgSampleBatch *b, int mode, bool shard, int gl
     for (int r = 0; r < rows; r++)
         if (pl.rows[r].n_chunks == 0) pl.items.push_back({r, -1});
     pl.n_row_items = (int)pl.items.size();
+    // The full-vocabulary rows join the flat step when every one of them can: no top-k on this path
+    // (it only arises together with a logit bias), a vocabulary the segment-parallel sum emulation
+    // covers, and room in the workspace.
+    pl.flat_full = full_ok && pl.n_row_items > 0 && pl.n_row_items <= h->full_cap && V <= kSub * kMaxSubTiles;
+    for (int i = 0; i < pl.n_row_items && pl.flat_full; i++) {
+        const RowPlan &rp = pl.rows[pl.items[i].row];
+        if (rp.top_k > 0 && rp.top_k < GV && rp.temperature > 0.f) pl.flat_full = false;
+    }
+    if (pl.flat_full)
+        for (int i = 0; i < pl.n_row_items; i++) pl.rows[pl.items[i].row].flat_full = i;
     for (int r = 0; r < rows; r++)
         for (int c = 0; c < pl.rows[r].n_chunks; c++) pl.items.push_back({r, c});
     // room for two 4096-element sub-tiles beyond the selection when shared memory allows it: fewer compactions
@@ -283,13 +309,36 @@ int run_batch(StgHandle h, const StgSampleBatch *b, const BatchExtra &x, void *s
     if (mode == 0 && !pairs_out && !b->tokens && !x.shard_mode) return fail(h, STG_ERR_INVALID_ARGUMENT, "tokens is required");
     if (x.shard_mode && (!h->xchg_local.p || b->rows > h->shard_rows)) return fail(h, STG_ERR_CAPACITY, "exchange buffers are missing or too small");
 
-    Plan pl;
-    rc = make_plan(h, b, mode, x.shard_mode != 0, x.global_vocab, pl);
-    if (rc) return rc;
-    if (pl.smem > h->smem_optin || kRowArenaBytes > h->smem_optin) return fail(h, STG_ERR_CAPACITY, "shared memory needed exceeds the device limit");
-    const RowPlan *d_rows; const WorkItem *d_items; const float *d_pow;
-    rc = upload_plan(h, pl, stream, &d_rows, &d_items, &d_pow);
-    if (rc) return rc;
+    const size_t esz0 = b->logits_dtype == STG_DTYPE_BF16 ? 2 : 4, need0 = b->logits_dtype == STG_DTYPE_BF16 ? 8 : 16;
+    const bool aligned = ((size_t)b->row_stride * esz0) % need0 == 0 &&
+                         ((b->mem_flags & STG_MEM_HOST_LOGITS) || ((uintptr_t)b->logits % need0) == 0);
+    const bool flat_ok = mode == 0 && x.shard_mode == 0 && aligned && !getenv("STG_NO_FLAT");
+    const bool full_ok = (mode == 0 || mode == 2) && x.shard_mode == 0 && aligned && !getenv("STG_NO_FLAT") && !getenv("STG_NO_FLAT_FULL");
+    // The plan depends on the batch description only (never on the logits): a decode loop that
+    // repeats a description byte for byte reuses the plan of the previous call as it is.
+    std::vector<unsigned char> &key = h->plan_key_scratch;
+    key.clear();
+    auto put = [&key](const void *p, size_t n) { const unsigned char *c = (const unsigned char *)p; key.insert(key.end(), c, c + n); };
+    const int32_t head[11] = {rows, V, b->logits_dtype, mode, x.shard_mode, x.global_vocab, (int32_t)flat_ok, (int32_t)full_ok,
+                              (int32_t)(b->mask != nullptr), (int32_t)(b->history_ids != nullptr), (int32_t)(b->bias_ids != nullptr && b->bias_values != nullptr)};
+    put(head, sizeof(head));
+    put(b->params, (size_t)rows * sizeof(StgRowParams));
+    if (b->history_offsets) put(b->history_offsets, (size_t)(rows + 1) * 4);
+    if (b->bias_offsets) put(b->bias_offsets, (size_t)(rows + 1) * 4);
+    if (b->row_uses_mask) put(b->row_uses_mask, (size_t)rows);
+    Plan &pl = h->plan;
+    if (!h->plan_valid || key != h->plan_key) {
+        h->plan_valid = false;
+        pl = Plan();
+        rc = make_plan(h, b, mode, x.shard_mode != 0, x.global_vocab, flat_ok, full_ok, pl);
+        if (rc) return rc;
+        if (pl.smem > h->smem_optin || kRowArenaBytes > h->smem_optin) return fail(h, STG_ERR_CAPACITY, "shared memory needed exceeds the device limit");
+        rc = upload_plan(h, pl, stream, &h->d_rows, &h->d_items, &h->d_pow);
+        if (rc) return rc;
+        h->plan_key = key;
+        h->plan_valid = true;
+    }
+    const RowPlan *d_rows = h->d_rows; const WorkItem *d_items = h->d_items; const float *d_pow = h->d_pow;
 
     SampleArgs a;
     memset(&a, 0, sizeof(a));
@@ -400,40 +449,75 @@ int run_batch(StgHandle h, const StgSampleBatch *b, const BatchExtra &x, void *s
         }
         return STG_OK;
     }
-    // two persistent kernels side by side: the row items (long, one SM each) go first on the
-    // caller's stream so that they take their SMs at once; the chunk items follow on a side stream
-    // with a grid that fits the SMs left over
+    // Row items are the full-vocabulary rows (and greedy rows with penalties), chunk items the rows
+    // of the top-k path and plain greedy rows.  In the flat form (stg_flat.cuh) ONE streaming kernel
+    // reads every row of both kinds from HBM; after it the per-row finish of the chunked rows runs on
+    // a side stream beside the phases of the full rows.  Rows the flat form does not take run in the
+    // two persistent kernels of the first design, again side by side.
     const int n_rows_items = pl.n_row_items, n_chunk_items = (int)pl.items.size() - pl.n_row_items;
     cudaError_t e = cudaSuccess;
     const bool both = n_rows_items > 0 && n_chunk_items > 0;
-    if (both) {
-        e = cudaEventRecord(h->ev_fork, stream);
-        if (e == cudaSuccess) e = cudaStreamWaitEvent(h->aux_stream, h->ev_fork, 0);
-    }
     int launches = 0;
     int row_grid = 0;
-    if (e == cudaSuccess && n_rows_items > 0) {
+    FlatRow *fr = (FlatRow *)h->flat_rows.p;
+    FullWs ws;
+    memset(&ws, 0, sizeof(ws));
+    ws.rows = (FullRow *)h->fw_rows.p; ws.e = (float *)h->fw_e.p; ws.e_stride = h->escratch_stride;
+    ws.ov_id = (int32_t *)h->fw_ov_id.p; ws.ov_adj = (float *)h->fw_ov_adj.p; ws.ew = (Emul2Work *)h->fw_ew.p;
+    ws.hist = (unsigned long long *)h->fw_hist.p; ws.bstart = (uint32_t *)h->fw_bstart.p;
+    ws.bin_exp = (unsigned char *)h->fw_binexp.p; ws.flag_bits = (uint32_t *)h->fw_flagbits.p;
+    ws.cursor = (uint32_t *)h->fw_cursor.p; ws.keys = (uint32_t *)h->fw_keys.p; ws.key_stride = h->key_stride;
+    const bool flat_chunks = pl.flat && n_chunk_items > 0, flat_full = pl.flat_full && n_rows_items > 0;
+    auto launch_rows_kernel = [&](bool redo_only) {
         SampleArgs r = a;
         r.n_items = n_rows_items;
         r.item_base = 0;
         r.work_counter = (uint32_t *)h->work_counter.p + 1;
         r.work_base = h->work_base_rows;
+        if (redo_only) { r.redo_flags = &ws.rows[0].redo; r.redo_stride = (int32_t)(sizeof(FullRow) / 4); }
         row_grid = std::min(n_rows_items, h->sm_count);
-        e = launch_sample_rows(r, row_grid, stream);
-        if (e == cudaSuccess) { h->work_base_rows += (uint32_t)n_rows_items + (uint32_t)row_grid; launches++; }
+        cudaError_t er = launch_sample_rows(r, row_grid, stream);
+        if (er == cudaSuccess) { h->work_base_rows += (uint32_t)n_rows_items + (uint32_t)row_grid; launches++; }
+        return er;
+    };
+    SampleArgs c = a;  // the chunked rows' view of the step
+    c.items = a.items + n_rows_items;
+    c.n_items = n_chunk_items;
+    if (flat_chunks || flat_full) {
+        if (flat_chunks) { e = launch_flat_prep(c, fr, stream); launches++; }
+        if (e == cudaSuccess && flat_full) { e = launch_full_prep(a, ws, stream); launches++; }
+        if (e == cudaSuccess) { e = launch_flat_stream(a, fr, ws, stream); launches++; }
     }
+    const bool fork = both || (flat_chunks && n_rows_items > 0);
+    if (e == cudaSuccess && fork) {
+        e = cudaEventRecord(h->ev_fork, stream);
+        if (e == cudaSuccess) e = cudaStreamWaitEvent(h->aux_stream, h->ev_fork, 0);
+    }
+    // the full rows (main stream) ...
+    if (e == cudaSuccess && n_rows_items > 0) {
+        if (flat_full) {
+            e = launch_full_rest(a, ws, a.items, n_rows_items, &launches, stream);
+            if (e == cudaSuccess) e = launch_rows_kernel(true);  // rows the flat form flagged; the others leave at once
+        } else {
+            e = launch_rows_kernel(false);
+        }
+    }
+    // ... beside the chunked rows (side stream when both kinds exist)
     if (e == cudaSuccess && n_chunk_items > 0) {
-        SampleArgs c = a;
-        c.items = a.items + n_rows_items;
-        c.n_items = n_chunk_items;
-        c.item_base = n_rows_items;
-        const int room = h->sm_count - row_grid >= 16 ? h->sm_count - row_grid : h->sm_count;
-        const int grid = std::min(n_chunk_items, room);
-        e = launch_sample_chunks(c, grid, pl.smem, both ? h->aux_stream : stream);
-        if (e == cudaSuccess) { h->work_base += (uint32_t)n_chunk_items + (uint32_t)grid; launches++; }
-        if (e == cudaSuccess && both) e = cudaEventRecord(h->ev_join, h->aux_stream);
+        cudaStream_t cs = fork ? h->aux_stream : stream;
+        if (flat_chunks) {
+            e = launch_flat_finish(c, fr, n_chunk_items, pl.smem, cs);
+            if (e == cudaSuccess) launches++;
+        } else {
+            c.item_base = n_rows_items;
+            const int room = h->sm_count - row_grid >= 16 ? h->sm_count - row_grid : h->sm_count;
+            const int grid = std::min(n_chunk_items, room);
+            e = launch_sample_chunks(c, grid, pl.smem, cs);
+            if (e == cudaSuccess) { h->work_base += (uint32_t)n_chunk_items + (uint32_t)grid; launches++; }
+        }
+        if (e == cudaSuccess && fork) e = cudaEventRecord(h->ev_join, h->aux_stream);
     }
-    if (e == cudaSuccess && both) e = cudaStreamWaitEvent(stream, h->ev_join, 0);
+    if (e == cudaSuccess && fork) e = cudaStreamWaitEvent(stream, h->ev_join, 0);
     if (e != cudaSuccess) {
         cudaMemsetAsync(h->work_counter.p, 0, 8, stream);
         cudaMemsetAsync(h->tickets.p, 0, h->tickets.bytes, stream);
@@ -493,7 +577,7 @@ int stg_create(const StgConfig *cfg, StgHandle *out)
     h->smem_optin = prop.sharedMemPerBlockOptin > 4096 ? prop.sharedMemPerBlockOptin - 4096 : 0;
     const size_t R = (size_t)cfg->max_rows, V = (size_t)cfg->max_vocab;
     const size_t sel_max = std::max<size_t>(1, (size_t)cfg->max_top_k + cfg->max_history);
-    h->cand_entries = R * std::max<size_t>(8 * sel_max, 64);
+    h->cand_entries = R * std::max<size_t>({8 * sel_max, sel_max + (size_t)kFlatSlack, (size_t)64});
     h->escratch_stride = (int64_t)round_up(V + 8, 64);
     h->key_stride = (int64_t)round_up(V + 8, 64);
     h->plan_bytes_cap = round_up(R * sizeof(RowPlan), 256) + round_up((R * 65) * sizeof(WorkItem), 256) +
@@ -504,6 +588,24 @@ int stg_create(const StgConfig *cfg, StgHandle *out)
     A(h->cand, h->cand_entries * 8);
     A(h->cand_count, R * 64 * 4);
     A(h->tickets, R * 4);
+    A(h->flat_rows, R * sizeof(FlatRow));
+    {
+        // full-vocabulary rows of the flat step (FullWs): per row the exp values and the candidate keys
+        // (4 bytes per token each), the histogram and its plan, the override list, the sub-tile summaries
+        h->full_cap = (int)std::min<size_t>(R, 1024);
+        const size_t F = (size_t)h->full_cap;
+        A(h->fw_rows, F * sizeof(FullRow));
+        A(h->fw_e, F * (size_t)h->escratch_stride * 4);
+        A(h->fw_keys, F * (size_t)h->key_stride * 4);
+        A(h->fw_ov_id, F * kMaxOverride * 4);
+        A(h->fw_ov_adj, F * kMaxOverride * 4);
+        A(h->fw_ew, F * sizeof(Emul2Work));
+        A(h->fw_hist, F * kHistBins * 8);
+        A(h->fw_bstart, F * kHistBins * 4);
+        A(h->fw_binexp, F * kHistBins);
+        A(h->fw_flagbits, F * (kHistBins / 32) * 4);
+        A(h->fw_cursor, F * kHistBins * 4);
+    }
     A(h->work_counter, 256);
     A(h->escratch, (size_t)h->sm_count * h->escratch_stride * 4);
     A(h->keyscratch, (size_t)h->sm_count * h->key_stride * 8);
@@ -565,7 +667,8 @@ int stg_destroy(StgHandle h)
     cudaSetDevice(h->cfg.device);
     cudaDeviceSynchronize();
     stg_comm_destroy(h);
-    DevBuf *all[] = {&h->plan_dev, &h->cand, &h->cand_count, &h->tickets, &h->work_counter, &h->escratch, &h->keyscratch, &h->listscratch,
+    DevBuf *all[] = {&h->plan_dev, &h->flat_rows, &h->fw_rows, &h->fw_e, &h->fw_keys, &h->fw_ov_id, &h->fw_ov_adj, &h->fw_ew, &h->fw_hist,
+                     &h->fw_bstart, &h->fw_binexp, &h->fw_flagbits, &h->fw_cursor, &h->cand, &h->cand_count, &h->tickets, &h->work_counter, &h->escratch, &h->keyscratch, &h->listscratch,
                      &h->dists, &h->st_hist, &h->st_bias_ids, &h->st_bias_vals, &h->st_uniforms, &h->st_mask, &h->st_logits,
                      &h->o_tokens, &h->o_probs, &h->o_flags, &h->o_topk_ids, &h->o_topk_vals, &h->o_topk_probs, &h->o_pairs, &h->ticks,
                      &h->sp_draft, &h->sp_uniforms, &h->sp_accepted, &h->sp_correction, &h->sp_aprobs, &h->sp_flags,

@@ -6,7 +6,7 @@ namespace stg {
 cudaError_t launch_chunks_f32(const SampleArgs &a, int grid, size_t smem, cudaStream_t stream)
 {
     void (*fn)(const SampleArgs) = a.vec == 4 ? k_sample_chunks<4, false> : k_sample_chunks<1, false>;
-    cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = ensure_dynamic_smem((const void *)fn, smem);
     if (e != cudaSuccess) return e;
     fn<<<grid, kThreads, smem, stream>>>(a);
     return cudaGetLastError();

@@ -264,6 +264,191 @@ __device__ __forceinline__ int replay_subtile(const float x[8], int base, int n,
     }
 }
 
+// Phase B on its own: exclusive fp64 prefix of the sub-tile sums in wk->sums[0..nsub) -> guessed
+// binade of the running sum at every sub-tile (wk->guess) and a crossing slot (wk->xslot) for the
+// sub-tiles in which the sum should pass into the next binade.  All kThreads threads call it.
+__device__ __forceinline__ void emul2_guess(Emul2Ctl *c, Emul2Work *wk, int nsub)
+{
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    {
+        double v = tid < nsub ? (double)wk->sums[tid] : 0.0;
+        double inc = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            double t = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+            if (lane >= o) inc += t;
+        }
+        if (lane == 31) c->wsum[warp] = inc;
+        __syncthreads();
+        if (warp == 0) {
+            double w = c->wsum[lane];
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                double t = __shfl_up_sync(0xFFFFFFFFu, w, o);
+                if (lane >= o) w += t;
+            }
+            c->wsum[lane] = w;
+        }
+        __syncthreads();
+        double excl = inc - v + (warp ? c->wsum[warp - 1] : 0.0);
+        if (tid < nsub) { wk->guess[tid] = (unsigned char)exp_of_double(excl); wk->xslot[tid] = 0; }
+        if (tid == 0) c->n_cross = 0;
+    }
+    __syncthreads();
+    // sub-tiles in which the sum should pass into the next binade get a CrossSlot
+    if (tid + 1 < nsub && (int)wk->guess[tid + 1] == (int)wk->guess[tid] + 1 && wk->sums[tid] > 0.f) {
+        const int slot = atomicAdd(&c->n_cross, 1);
+        if (slot < kMaxCross) wk->xslot[tid] = (unsigned char)(slot + 1);
+    }
+}
+
+// Phase D on its own: ONE WARP walks the sub-tiles of a sequence whose per-sub-tile sums, guessed
+// binades, composites and crossing slots are in `wk` (shared memory), with the exact running sum.
+// Leaves the final sum in c->s and the hit (or -1, or -2 with c->abort_at for a forbidden replay) in
+// c->hit.  Called by all 32 lanes of one warp; the caller synchronises the block afterwards.
+template <class Prov, bool POS_ONLY, bool FORCE>
+__device__ __forceinline__ void emul2_walk(Emul2Ctl *c, Emul2Work *wk, const Prov &pv, int n, int nsub, float target,
+                                           bool has_target, const unsigned char *replay_ok, unsigned long long *tk)
+{
+    const int lane = threadIdx.x & 31;
+    float s = 0.f;
+    int hit = -1;
+    int t = 0;
+    int abort_at = -1;
+    int n_iter = 0, n_replay = 0, n_fast = 0;
+    while (t < nsub && hit < 0) {
+        n_iter++;
+        const uint32_t sb = __float_as_uint(s);
+        const int ef = (int)(sb >> 23) & 255;
+        const int eb = ef ? ef : 1;
+        const int sint = (int)((sb & 0x7FFFFFu) | (ef ? 0x800000u : 0u));
+        if (ef == 255) break;  // inf / NaN: nothing changes any more
+        const long long tint = target_units(target, has_target, eb);
+        // lane l proposes sub-tile t + l
+        const int tt = t + lane;
+        int a0 = 0, a1 = 0;
+        bool valid = false;
+        if (tt < nsub) {
+            a0 = wk->comp[tt][0];
+            a1 = wk->comp[tt][1];
+            valid = (wk->guess[tt] == eb) || (a0 == 0 && a1 == 0 && wk->sums[tt] == 0.f);
+        }
+        int i0 = a0, i1 = a1;
+        if (__any_sync(0xFFFFFFFFu, a0 != a1)) {
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                int p0 = __shfl_up_sync(0xFFFFFFFFu, i0, o);
+                int p1 = __shfl_up_sync(0xFFFFFFFFu, i1, o);
+                if (lane >= o) { int r0, r1; comp(p0, p1, i0, i1, r0, r1); i0 = r0; i1 = r1; }
+            }
+        } else {
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                int p0 = __shfl_up_sync(0xFFFFFFFFu, i0, o);
+                if (lane >= o) i0 = sat_add(i0, p0);
+            }
+            i1 = i0;
+        }
+        const int S = sat_add(sint, (sint & 1) ? i1 : i0);  // sum after sub-tiles t .. t+lane
+        const bool bad = tt >= nsub || !valid || S >= (1 << 24) || (long long)S >= tint;
+        const unsigned badmask = __ballot_sync(0xFFFFFFFFu, bad);
+        const int ok = badmask ? __ffs(badmask) - 1 : 32;  // sub-tiles consumed whole
+        if (ok > 0) {
+            const int send = __shfl_sync(0xFFFFFFFFu, S, ok - 1);
+            s = ldexpf((float)send, eb - 150);
+            t += ok;
+        }
+        if (ok < 32 && t < nsub) {
+            if (wk->guess[t] != eb && !(wk->sums[t] == 0.f)) {
+                // the binade was guessed wrongly for this sub-tile (it follows a crossing closely):
+                // its composite under the actual binade needs no order, so recompute it and retry
+                float x[8];
+                pv.reload(t * kSub + lane * 8, n, x);
+                if (POS_ONLY) {
+#pragma unroll
+                    for (int j = 0; j < 8; j++) x[j] = x[j] > 0.f ? x[j] : 0.f;
+                }
+                int a0, a1;
+                subtile_composite<FORCE>(x, eb, a0, a1);
+                if (lane == 0) { wk->comp[t][0] = a0; wk->comp[t][1] = a1; wk->guess[t] = (unsigned char)eb; wk->xslot[t] = 0; }
+                __syncwarp();
+                continue;
+            }
+            if (FORCE && replay_ok != nullptr && !replay_ok[t]) { abort_at = t; break; }
+            float x[8];
+            pv.reload(t * kSub + lane * 8, n, x);
+            // prepared crossing: the lanes before the one in which the sum leaves the binade are
+            // taken by their composites, that lane adds its 8 elements for real, the lanes behind
+            // it are taken by their composites under the next binade
+            bool crossed = false;
+            const int xsl = wk->xslot[t];
+            if (xsl && eb < 253) {
+                const CrossSlot &cs = wk->xs[xsl - 1];
+                int i0 = cs.lo[lane][0], i1 = cs.lo[lane][1];
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    int p0 = __shfl_up_sync(0xFFFFFFFFu, i0, o);
+                    int p1 = __shfl_up_sync(0xFFFFFFFFu, i1, o);
+                    if (lane >= o) { int r0, r1; comp(p0, p1, i0, i1, r0, r1); i0 = r0; i1 = r1; }
+                }
+                const uint32_t sb1 = __float_as_uint(s);  // s has moved on since the top of the round
+                const int sint1 = (int)((sb1 & 0x7FFFFFu) | (((sb1 >> 23) & 255u) ? 0x800000u : 0u));
+                const int S1 = sat_add(sint1, (sint1 & 1) ? i1 : i0);  // sum after lanes 0 .. lane
+                const unsigned over = __ballot_sync(0xFFFFFFFFu, S1 >= (1 << 24));
+                const unsigned tgt = __ballot_sync(0xFFFFFFFFu, (long long)S1 >= tint);
+                const int L = over ? __ffs(over) - 1 : 32;
+                if (L < 32 && (tgt & ((1u << L) - 1u)) == 0u) {
+                    int sprev = __shfl_sync(0xFFFFFFFFu, S1, L > 0 ? L - 1 : 0);
+                    if (L == 0) sprev = sint1;
+                    float acc = ldexpf((float)sprev, eb - 150);
+                    int hit_l = -1;
+                    if (lane == L) {
+                        const int g0 = t * kSub + lane * 8;
+#pragma unroll
+                        for (int j = 0; j < 8; j++) {
+                            if (g0 + j < n && (!POS_ONLY || x[j] > 0.f) && hit_l < 0) {
+                                acc = __fadd_rn(acc, x[j]);
+                                if (has_target && acc >= target) hit_l = g0 + j;
+                            }
+                        }
+                    }
+                    acc = __shfl_sync(0xFFFFFFFFu, acc, L);
+                    hit_l = __shfl_sync(0xFFFFFFFFu, hit_l, L);
+                    const uint32_t ab = __float_as_uint(acc);
+                    const int ef2 = (int)(ab >> 23) & 255;
+                    if (hit_l >= 0) {
+                        s = acc; hit = hit_l; crossed = true;
+                    } else if (ef2 == eb + 1) {
+                        const int sint2 = (int)((ab & 0x7FFFFFu) | 0x800000u);
+                        const long long tint2 = target_units(target, has_target, ef2);
+                        int j0 = lane > L ? cs.hi[lane][0] : 0, j1 = lane > L ? cs.hi[lane][1] : 0;
+#pragma unroll
+                        for (int o = 1; o < 32; o <<= 1) {
+                            int p0 = __shfl_up_sync(0xFFFFFFFFu, j0, o);
+                            int p1 = __shfl_up_sync(0xFFFFFFFFu, j1, o);
+                            if (lane >= o) { int r0, r1; comp(p0, p1, j0, j1, r0, r1); j0 = r0; j1 = r1; }
+                        }
+                        const int S2 = sat_add(sint2, (sint2 & 1) ? j1 : j0);
+                        const bool fire2 = S2 >= (1 << 24) || (long long)S2 >= tint2;
+                        if (__ballot_sync(0xFFFFFFFFu, fire2) == 0u) {
+                            const int send = __shfl_sync(0xFFFFFFFFu, S2, 31);
+                            s = ldexpf((float)send, ef2 - 150);
+                            crossed = true;
+                            n_fast++;
+                        }
+                    }
+                }
+            }
+            if (!crossed) hit = replay_subtile<POS_ONLY>(x, t * kSub, n, target, has_target, s);
+            t += 1;
+            n_replay++;
+        }
+    }
+    if (lane == 0) { c->s = s; c->hit = abort_at >= 0 ? -2 : hit; c->abort_at = abort_at; }
+    tick(tk, 3);
+    if (tk && lane == 0) { tk[4] = (unsigned long long)n_iter; tk[5] = (unsigned long long)n_replay; tk[6] = (unsigned long long)n_fast; }
+}
+
 // Same contract as emul_scan (stg_emul.cuh), for n <= kSub * kMaxSubTiles.  `Prov::load` may have
 // side effects and is called exactly once per element; `Prov::reload` must be pure.
 // FORCE: the elements are only partially ordered (ordered between groups, arbitrary inside a
@@ -352,37 +537,7 @@ __device__ __noinline__ int emul_scan2(Emul2Ctl *c, Emul2Work *wk, const Prov &p
     }
     __syncthreads();
     tick(tk, 0);
-    // phase B: exclusive prefix of the sub-tile sums -> guessed binade per sub-tile
-    {
-        double v = tid < nsub ? (double)wk->sums[tid] : 0.0;
-        double inc = v;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            double t = __shfl_up_sync(0xFFFFFFFFu, inc, o);
-            if (lane >= o) inc += t;
-        }
-        if (lane == 31) c->wsum[warp] = inc;
-        __syncthreads();
-        if (warp == 0) {
-            double w = c->wsum[lane];
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                double t = __shfl_up_sync(0xFFFFFFFFu, w, o);
-                if (lane >= o) w += t;
-            }
-            c->wsum[lane] = w;
-        }
-        __syncthreads();
-        double excl = inc - v + (warp ? c->wsum[warp - 1] : 0.0);
-        if (tid < nsub) { wk->guess[tid] = (unsigned char)exp_of_double(excl); wk->xslot[tid] = 0; }
-        if (tid == 0) c->n_cross = 0;
-    }
-    __syncthreads();
-    // sub-tiles in which the sum should pass into the next binade get a CrossSlot
-    if (tid + 1 < nsub && (int)wk->guess[tid + 1] == (int)wk->guess[tid] + 1 && wk->sums[tid] > 0.f) {
-        const int slot = atomicAdd(&c->n_cross, 1);
-        if (slot < kMaxCross) wk->xslot[tid] = (unsigned char)(slot + 1);
-    }
+    emul2_guess(c, wk, nsub);
     __syncthreads();
     tick(tk, 1);
     // phase C: composite of every sub-tile under its guessed binade
@@ -480,144 +635,7 @@ __device__ __noinline__ int emul_scan2(Emul2Ctl *c, Emul2Work *wk, const Prov &p
     __syncthreads();
     tick(tk, 2);
     // phase D: one warp walks the sub-tiles with the exact sum
-    if (warp == 0) {
-        float s = 0.f;
-        int hit = -1;
-        int t = 0;
-        int abort_at = -1;
-        int n_iter = 0, n_replay = 0, n_fast = 0;
-        while (t < nsub && hit < 0) {
-            n_iter++;
-            const uint32_t sb = __float_as_uint(s);
-            const int ef = (int)(sb >> 23) & 255;
-            const int eb = ef ? ef : 1;
-            const int sint = (int)((sb & 0x7FFFFFu) | (ef ? 0x800000u : 0u));
-            if (ef == 255) break;  // inf / NaN: nothing changes any more
-            const long long tint = target_units(target, has_target, eb);
-            // lane l proposes sub-tile t + l
-            const int tt = t + lane;
-            int a0 = 0, a1 = 0;
-            bool valid = false;
-            if (tt < nsub) {
-                a0 = wk->comp[tt][0];
-                a1 = wk->comp[tt][1];
-                valid = (wk->guess[tt] == eb) || (a0 == 0 && a1 == 0 && wk->sums[tt] == 0.f);
-            }
-            int i0 = a0, i1 = a1;
-            if (__any_sync(0xFFFFFFFFu, a0 != a1)) {
-#pragma unroll
-                for (int o = 1; o < 32; o <<= 1) {
-                    int p0 = __shfl_up_sync(0xFFFFFFFFu, i0, o);
-                    int p1 = __shfl_up_sync(0xFFFFFFFFu, i1, o);
-                    if (lane >= o) { int r0, r1; comp(p0, p1, i0, i1, r0, r1); i0 = r0; i1 = r1; }
-                }
-            } else {
-#pragma unroll
-                for (int o = 1; o < 32; o <<= 1) {
-                    int p0 = __shfl_up_sync(0xFFFFFFFFu, i0, o);
-                    if (lane >= o) i0 = sat_add(i0, p0);
-                }
-                i1 = i0;
-            }
-            const int S = sat_add(sint, (sint & 1) ? i1 : i0);  // sum after sub-tiles t .. t+lane
-            const bool bad = tt >= nsub || !valid || S >= (1 << 24) || (long long)S >= tint;
-            const unsigned badmask = __ballot_sync(0xFFFFFFFFu, bad);
-            const int ok = badmask ? __ffs(badmask) - 1 : 32;  // sub-tiles consumed whole
-            if (ok > 0) {
-                const int send = __shfl_sync(0xFFFFFFFFu, S, ok - 1);
-                s = ldexpf((float)send, eb - 150);
-                t += ok;
-            }
-            if (ok < 32 && t < nsub) {
-                if (wk->guess[t] != eb && !(wk->sums[t] == 0.f)) {
-                    // the binade was guessed wrongly for this sub-tile (it follows a crossing closely):
-                    // its composite under the actual binade needs no order, so recompute it and retry
-                    float x[8];
-                    pv.reload(t * kSub + lane * 8, n, x);
-                    if (POS_ONLY) {
-#pragma unroll
-                        for (int j = 0; j < 8; j++) x[j] = x[j] > 0.f ? x[j] : 0.f;
-                    }
-                    int a0, a1;
-                    subtile_composite<FORCE>(x, eb, a0, a1);
-                    if (lane == 0) { wk->comp[t][0] = a0; wk->comp[t][1] = a1; wk->guess[t] = (unsigned char)eb; wk->xslot[t] = 0; }
-                    __syncwarp();
-                    continue;
-                }
-                if (FORCE && replay_ok != nullptr && !replay_ok[t]) { abort_at = t; break; }
-                float x[8];
-                pv.reload(t * kSub + lane * 8, n, x);
-                // prepared crossing: the lanes before the one in which the sum leaves the binade are
-                // taken by their composites, that lane adds its 8 elements for real, the lanes behind
-                // it are taken by their composites under the next binade
-                bool crossed = false;
-                const int xsl = wk->xslot[t];
-                if (xsl && eb < 253) {
-                    const CrossSlot &cs = wk->xs[xsl - 1];
-                    int i0 = cs.lo[lane][0], i1 = cs.lo[lane][1];
-#pragma unroll
-                    for (int o = 1; o < 32; o <<= 1) {
-                        int p0 = __shfl_up_sync(0xFFFFFFFFu, i0, o);
-                        int p1 = __shfl_up_sync(0xFFFFFFFFu, i1, o);
-                        if (lane >= o) { int r0, r1; comp(p0, p1, i0, i1, r0, r1); i0 = r0; i1 = r1; }
-                    }
-                    const uint32_t sb1 = __float_as_uint(s);  // s has moved on since the top of the round
-                    const int sint1 = (int)((sb1 & 0x7FFFFFu) | (((sb1 >> 23) & 255u) ? 0x800000u : 0u));
-                    const int S1 = sat_add(sint1, (sint1 & 1) ? i1 : i0);  // sum after lanes 0 .. lane
-                    const unsigned over = __ballot_sync(0xFFFFFFFFu, S1 >= (1 << 24));
-                    const unsigned tgt = __ballot_sync(0xFFFFFFFFu, (long long)S1 >= tint);
-                    const int L = over ? __ffs(over) - 1 : 32;
-                    if (L < 32 && (tgt & ((1u << L) - 1u)) == 0u) {
-                        int sprev = __shfl_sync(0xFFFFFFFFu, S1, L > 0 ? L - 1 : 0);
-                        if (L == 0) sprev = sint1;
-                        float acc = ldexpf((float)sprev, eb - 150);
-                        int hit_l = -1;
-                        if (lane == L) {
-                            const int g0 = t * kSub + lane * 8;
-#pragma unroll
-                            for (int j = 0; j < 8; j++) {
-                                if (g0 + j < n && (!POS_ONLY || x[j] > 0.f) && hit_l < 0) {
-                                    acc = __fadd_rn(acc, x[j]);
-                                    if (has_target && acc >= target) hit_l = g0 + j;
-                                }
-                            }
-                        }
-                        acc = __shfl_sync(0xFFFFFFFFu, acc, L);
-                        hit_l = __shfl_sync(0xFFFFFFFFu, hit_l, L);
-                        const uint32_t ab = __float_as_uint(acc);
-                        const int ef2 = (int)(ab >> 23) & 255;
-                        if (hit_l >= 0) {
-                            s = acc; hit = hit_l; crossed = true;
-                        } else if (ef2 == eb + 1) {
-                            const int sint2 = (int)((ab & 0x7FFFFFu) | 0x800000u);
-                            const long long tint2 = target_units(target, has_target, ef2);
-                            int j0 = lane > L ? cs.hi[lane][0] : 0, j1 = lane > L ? cs.hi[lane][1] : 0;
-#pragma unroll
-                            for (int o = 1; o < 32; o <<= 1) {
-                                int p0 = __shfl_up_sync(0xFFFFFFFFu, j0, o);
-                                int p1 = __shfl_up_sync(0xFFFFFFFFu, j1, o);
-                                if (lane >= o) { int r0, r1; comp(p0, p1, j0, j1, r0, r1); j0 = r0; j1 = r1; }
-                            }
-                            const int S2 = sat_add(sint2, (sint2 & 1) ? j1 : j0);
-                            const bool fire2 = S2 >= (1 << 24) || (long long)S2 >= tint2;
-                            if (__ballot_sync(0xFFFFFFFFu, fire2) == 0u) {
-                                const int send = __shfl_sync(0xFFFFFFFFu, S2, 31);
-                                s = ldexpf((float)send, ef2 - 150);
-                                crossed = true;
-                                n_fast++;
-                            }
-                        }
-                    }
-                }
-                if (!crossed) hit = replay_subtile<POS_ONLY>(x, t * kSub, n, target, has_target, s);
-                t += 1;
-                n_replay++;
-            }
-        }
-        if (lane == 0) { c->s = s; c->hit = abort_at >= 0 ? -2 : hit; c->abort_at = abort_at; }
-        tick(tk, 3);
-        if (tk && lane == 0) { tk[4] = (unsigned long long)n_iter; tk[5] = (unsigned long long)n_replay; tk[6] = (unsigned long long)n_fast; }
-    }
+    if (warp == 0) emul2_walk<Prov, POS_ONLY, FORCE>(c, wk, pv, n, nsub, target, has_target, replay_ok, tk);
     __syncthreads();
     if (sum_out) *sum_out = c->s;
     const int h = c->hit;

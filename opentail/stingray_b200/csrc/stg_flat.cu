@@ -1,0 +1,414 @@
+// Kernels of the flat form of a sampling step (see stg_flat.cuh): prep, the HBM streaming pass, and
+// the per-row finish of the top-k path.
+#include <cuda_runtime.h>
+#include <math_constants.h>
+#include <stdint.h>
+
+#include "stg_flat.cuh"
+#include "stg_launch.h"
+#include "stg_select.cuh"
+#include "stg_types.h"
+
+namespace stg {
+
+// ---- k_flat_prep --------------------------------------------------------------------------------------
+// One 1024-thread CTA per row.  Top-k rows: the filter bound.  Thread t takes elements 4t .. 4t+3 of
+// the row's first 4096 (masked) logits and keeps their maximum; the 1024 maxima are cut into
+// `flat_groups` equal groups of consecutive threads, and the bound is the smallest of the groups'
+// maxima: at least flat_groups elements of the sample lie at or above it, about twice as many on
+// average, and the planner picks flat_groups so that about 3 N elements of the whole row should.
+template <bool BF16>
+__global__ void __launch_bounds__(kThreads) k_flat_prep(const __grid_constant__ SampleArgs a, FlatRow *fr)
+{
+    __shared__ uint32_t red[32];
+    const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const RowPlan rp = a.plans[row];
+    if (rp.n_chunks == 0) return;  // not a row of the flat step
+    if (rp.path != kPathTopK) {
+        if (tid == 0) { fr[row].key = 0ull; fr[row].tau = 0.f; fr[row].cnt = 0; fr[row].cap = 0; }
+        return;
+    }
+    const int esz = BF16 ? 2 : 4;
+    const void *rowp = (const char *)a.logits + (int64_t)row * a.row_stride * esz;
+    const uint32_t *mrow = (rp.use_mask && a.mask) ? a.mask + (int64_t)row * a.mask_stride : nullptr;
+    float v[4];
+    int idx[4];
+    load_items<4, BF16, false>(rowp, mrow, 0, 0, min(a.vocab, kFlatSample), v, idx);  // out of range reads -inf
+    uint32_t m = ord32(fmaxf(fmaxf(v[0], v[1]), fmaxf(v[2], v[3])));
+    const int ng = rp.flat_groups;          // power of two, 1 .. 1024
+    const int w = kThreads / ng;            // threads per group
+    // maximum over the thread's group
+    for (int o = 1; o < min(w, 32); o <<= 1) m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+    if (w > 32) {
+        if (lane == 0) red[warp] = m;
+        __syncthreads();
+        const int wpg = w / 32;             // warps per group
+        const int g0 = (warp / wpg) * wpg;
+        m = 0u;
+        for (int k = 0; k < wpg; k++) m = max(m, red[g0 + k]);
+        __syncthreads();
+    }
+    // minimum over all groups (every thread holds its group's maximum)
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = min(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+    if (lane == 0) red[warp] = m;
+    __syncthreads();
+    if (warp == 0) {
+        m = red[lane];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = min(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+        if (lane == 0) { fr[row].key = 0ull; fr[row].tau = unord32(m); fr[row].cnt = 0; fr[row].cap = rp.sel + kFlatSlack; }
+    }
+}
+
+// ---- k_flat_stream ------------------------------------------------------------------------------------
+// Four masked elements of a 16-byte aligned row starting at element i (a multiple of 4); elements at
+// or beyond `end` read as -infinity.
+template <bool BF16>
+__device__ __forceinline__ void flat_load4(const void *rowp, const uint32_t *mrow, int i, int end, float v[4])
+{
+    if (i + 3 < end) {
+        load_vec4<BF16, true>(rowp, i, v);
+    } else {
+#pragma unroll
+        for (int e = 0; e < 4; e++) v[e] = (i + e < end) ? load_one<BF16>(rowp, i + e) : -CUDART_INF_F;
+    }
+    if (mrow != nullptr && i < end) {
+        const uint32_t bits = __ldg(mrow + (i >> 5)) >> (i & 31);
+#pragma unroll
+        for (int e = 0; e < 4; e++)
+            if (!((bits >> e) & 1u)) v[e] = -CUDART_INF_F;
+    }
+}
+
+// One CTA of 256 threads per 16384-element piece of a row (grid.x pieces, grid.y rows).  Sub-step q
+// (0..15) of a piece covers 1024 consecutive elements, thread t its elements 4t .. 4t+3; a thread
+// keeps the loads of the next four sub-steps in flight while it works on the current four.
+template <bool BF16>
+__global__ void __launch_bounds__(kFlatThreads) k_flat_stream(const __grid_constant__ SampleArgs a, FlatRow *fr, const FullWs ws)
+{
+    __shared__ unsigned long long red[kFlatThreads / 32];
+    const int row = blockIdx.y, tid = threadIdx.x, lane = tid & 31;
+    const RowPlan *rpp = a.plans + row;
+    const int fi = __ldg(&rpp->flat_full);
+    if (__ldg(&rpp->n_chunks) == 0 && fi < 0) return;  // not a row of the flat step
+    const int begin = blockIdx.x * kFlatPiece;
+    const int end = min(a.vocab, begin + kFlatPiece);
+    if (begin >= end) return;
+    const int path = __ldg(&rpp->path);
+    const int esz = BF16 ? 2 : 4;
+    const void *rowp = (const char *)a.logits + (int64_t)row * a.row_stride * esz;
+    const uint32_t *mrow = (__ldg(&rpp->use_mask) && a.mask) ? a.mask + (int64_t)row * a.mask_stride : nullptr;
+    const int i0 = begin + tid * 4;
+
+    float cur[4][4], nxt[4][4];
+#pragma unroll
+    for (int u = 0; u < 4; u++) flat_load4<BF16>(rowp, mrow, i0 + u * 1024, end, cur[u]);
+
+    if (fi >= 0) {
+        // a full-vocabulary row (or greedy with penalties): x = overrides(masked logit) * 1/T goes to
+        // the row's scratch, and the running (max, lowest index) key of x to the row's state
+        __shared__ int s_id[kMaxOverride];
+        __shared__ float s_adj[kMaxOverride];
+        __shared__ unsigned s_bits[kFlatPiece / 32];
+        FullRow *fw = ws.rows + fi;
+        const float temperature = __ldg(&rpp->temperature);
+        const bool greedy = !(temperature > 0.f);
+        const bool scale = !greedy && temperature != 1.0f;
+        const float inv_t = scale ? __fdiv_rn(1.0f, temperature) : 1.0f;
+        const int ov_lo = fw->ov_piece[blockIdx.x], ov_n = fw->ov_piece[blockIdx.x + 1] - ov_lo;
+        if (ov_n > 0) {
+            for (int t = tid; t < kFlatPiece / 32; t += kFlatThreads) s_bits[t] = 0u;
+            __syncthreads();
+            const int32_t *gid = ws.ov_id + (size_t)fi * kMaxOverride + ov_lo;
+            const float *gadj = ws.ov_adj + (size_t)fi * kMaxOverride + ov_lo;
+            for (int t = tid; t < ov_n; t += kFlatThreads) {
+                const int id = __ldg(gid + t);
+                s_id[t] = id;
+                s_adj[t] = __ldg(gadj + t);
+                atomicOr(&s_bits[(id - begin) >> 5], 1u << ((id - begin) & 31));
+            }
+            __syncthreads();
+        }
+        float *e = ws.e + (size_t)fi * ws.e_stride;
+        float best = -CUDART_INF_F, rbest = -CUDART_INF_F;
+        int best_i = -1, rbest_i = -1;
+        const bool want_raw = a.mode == 2;
+#pragma unroll
+        for (int s = 0; s < 4; s++) {
+            if (s + 1 < 4) {
+#pragma unroll
+                for (int u = 0; u < 4; u++) flat_load4<BF16>(rowp, mrow, i0 + ((s + 1) * 4 + u) * 1024, end, nxt[u]);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const int i = i0 + (s * 4 + u) * 1024;
+                if (i < end) {
+                    if (want_raw) {
+#pragma unroll
+                        for (int k = 0; k < 4; k++)
+                            if (cur[u][k] > rbest) { rbest = cur[u][k]; rbest_i = i + k; }
+                    }
+                    if (ov_n > 0) {
+                        const int rel = i - begin;
+                        const unsigned nib = (s_bits[rel >> 5] >> (rel & 31)) & 0xFu;
+                        if (nib) {
+#pragma unroll
+                            for (int k = 0; k < 4; k++) {
+                                if ((nib >> k) & 1u) {
+                                    int lo = 0, hi = ov_n - 1;  // the id is in the list: find it
+                                    while (lo < hi) {
+                                        const int mid = (lo + hi) >> 1;
+                                        if (s_id[mid] < i + k) lo = mid + 1; else hi = mid;
+                                    }
+                                    cur[u][k] = s_adj[lo];
+                                }
+                            }
+                        }
+                    }
+                    if (scale) {
+#pragma unroll
+                        for (int k = 0; k < 4; k++) cur[u][k] = __fmul_rn(cur[u][k], inv_t);
+                    }
+#pragma unroll
+                    for (int k = 0; k < 4; k++)
+                        if (i + k < end && cur[u][k] > best) { best = cur[u][k]; best_i = i + k; }
+                    if (!greedy) {
+                        if (i + 3 < end) {
+                            __stcg((float4 *)(e + i), make_float4(cur[u][0], cur[u][1], cur[u][2], cur[u][3]));
+                        } else {
+#pragma unroll
+                            for (int k = 0; k < 4; k++)
+                                if (i + k < end) __stcg(e + i + k, cur[u][k]);
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; u++)
+#pragma unroll
+                for (int k = 0; k < 4; k++) cur[u][k] = nxt[u][k];
+        }
+        unsigned long long k = best_i >= 0 ? make_key(best, best_i) : 0ull;
+        unsigned long long rk = rbest_i >= 0 ? make_key(rbest, rbest_i) : 0ull;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const unsigned long long t = __shfl_xor_sync(0xFFFFFFFFu, k, o);
+            k = t > k ? t : k;
+            const unsigned long long rt = __shfl_xor_sync(0xFFFFFFFFu, rk, o);
+            rk = rt > rk ? rt : rk;
+        }
+        __shared__ unsigned long long rred[kFlatThreads / 32];
+        if (lane == 0) { red[tid >> 5] = k; rred[tid >> 5] = rk; }
+        __syncthreads();
+        if (tid == 0) {
+            for (int w = 1; w < kFlatThreads / 32; w++) { k = red[w] > k ? red[w] : k; rk = rred[w] > rk ? rred[w] : rk; }
+            if (k != 0ull) atomicMax(&fw->maxkey, k);
+            if (want_raw && rk != 0ull) atomicMax(&fw->rawkey, rk);
+        }
+        return;
+    }
+
+    if (path == kPathGreedy) {
+        float best = -CUDART_INF_F;
+        int best_i = -1;
+#pragma unroll
+        for (int s = 0; s < 4; s++) {
+            if (s + 1 < 4) {
+#pragma unroll
+                for (int u = 0; u < 4; u++) flat_load4<BF16>(rowp, mrow, i0 + ((s + 1) * 4 + u) * 1024, end, nxt[u]);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; u++)
+#pragma unroll
+                for (int e = 0; e < 4; e++)
+                    if (cur[u][e] > best) { best = cur[u][e]; best_i = i0 + (s * 4 + u) * 1024 + e; }
+#pragma unroll
+            for (int u = 0; u < 4; u++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) cur[u][e] = nxt[u][e];
+        }
+        // a thread visits ascending indices, so it holds its lowest index of the value; the key
+        // order (value, then lower index) settles ties between threads, pieces and CTAs
+        unsigned long long k = best_i >= 0 ? make_key(best, best_i) : 0ull;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const unsigned long long t = __shfl_xor_sync(0xFFFFFFFFu, k, o);
+            k = t > k ? t : k;
+        }
+        if (lane == 0) red[tid >> 5] = k;
+        __syncthreads();
+        if (tid == 0) {
+            for (int w = 1; w < kFlatThreads / 32; w++) k = red[w] > k ? red[w] : k;
+            if (k != 0ull) atomicMax(&fr[row].key, k);
+        }
+        return;
+    }
+
+    // top-k path: every element above the row's bound becomes a candidate.  The CTA collects its
+    // candidates in shared memory (one shared-memory atomicAdd per warp and step) and hands them to
+    // the row's list with a single global atomicAdd at the end; should a piece hold more than the
+    // staging area takes, the excess goes to the list directly.
+    __shared__ unsigned long long stage[kFlatStage];
+    __shared__ int stage_cnt, list_first;
+    if (tid == 0) stage_cnt = 0;
+    __syncthreads();
+    const float tau = fr[row].tau;
+    const int cap = fr[row].cap;
+    unsigned long long *cand = a.cand + __ldg(&rpp->cand_off);
+    int *cnt_p = &fr[row].cnt;
+#pragma unroll
+    for (int s = 0; s < 4; s++) {
+        if (s + 1 < 4) {
+#pragma unroll
+            for (int u = 0; u < 4; u++) flat_load4<BF16>(rowp, mrow, i0 + ((s + 1) * 4 + u) * 1024, end, nxt[u]);
+        }
+        unsigned pass = 0u;
+#pragma unroll
+        for (int u = 0; u < 4; u++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) pass |= (cur[u][e] > tau) ? (1u << (u * 4 + e)) : 0u;
+        if (__any_sync(0xFFFFFFFFu, pass != 0u)) {
+            const int n = __popc(pass);
+            int incl = n;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int t = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+                if (lane >= o) incl += t;
+            }
+            int first = 0;
+            if (lane == 31) first = atomicAdd(&stage_cnt, incl);
+            first = __shfl_sync(0xFFFFFFFFu, first, 31);
+            int slot = first + incl - n;
+#pragma unroll
+            for (int u = 0; u < 4; u++)
+#pragma unroll
+                for (int e = 0; e < 4; e++)
+                    if ((pass >> (u * 4 + e)) & 1u) {
+                        const unsigned long long key = make_key(cur[u][e], i0 + (s * 4 + u) * 1024 + e);
+                        if (slot < kFlatStage) {
+                            stage[slot] = key;
+                        } else {
+                            const int g = atomicAdd(cnt_p, 1);
+                            if (g < cap) cand[g] = key;
+                        }
+                        slot++;
+                    }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; u++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) cur[u][e] = nxt[u][e];
+    }
+    __syncthreads();
+    const int staged = min(stage_cnt, kFlatStage);
+    if (staged > 0) {
+        if (tid == 0) list_first = atomicAdd(cnt_p, staged);
+        __syncthreads();
+        const int g0 = list_first;
+        for (int t = tid; t < staged; t += kFlatThreads)
+            if (g0 + t < cap) cand[g0 + t] = stage[t];
+    }
+}
+
+// ---- k_flat_finish ------------------------------------------------------------------------------------
+struct FlatShared {
+    FinishOut fout;
+    int ok;
+};
+
+// One 1024-thread CTA per row of the flat step (a.items lists them).
+template <bool BF16>
+__global__ void __launch_bounds__(kThreads, 1) k_flat_finish(const __grid_constant__ SampleArgs a, FlatRow *fr)
+{
+    extern __shared__ __align__(16) unsigned char arena[];
+    __shared__ SelCtl ctl;
+    __shared__ FlatShared fs;
+    const int row = a.items[blockIdx.x].row;
+    const RowPlan rp = a.plans[row];
+    const int esz = BF16 ? 2 : 4;
+    const void *rowp = (const char *)a.logits + (int64_t)row * a.row_stride * esz;
+    if (rp.path == kPathGreedy) {
+        if (threadIdx.x == 0) {
+            const unsigned long long key = fr[row].key;
+            int tok = 0;
+            float val;
+            uint32_t fl = kPathGreedy;
+            if (key != 0ull) {
+                tok = key_idx(key);
+                val = key_val(key);
+            } else {
+                val = load_one<BF16>(rowp, 0);  // Greedy of a row without a finite value: token 0
+                fl |= (1u << 6);
+            }
+            if (a.pairs_out) {
+                ((int32_t *)a.pairs_out)[2 * row] = tok;
+                ((float *)a.pairs_out)[2 * row + 1] = val;
+            }
+            if (a.tokens) a.tokens[row] = tok;
+            if (a.token_probs) a.token_probs[row] = 1.0f;
+            if (a.row_flags) a.row_flags[row] = fl;
+        }
+        return;
+    }
+    const uint32_t *mrow = (rp.use_mask && a.mask) ? a.mask + (int64_t)row * a.mask_stride : nullptr;
+    Sel s;
+    s.c = &ctl;
+    s.buf[0] = (u64 *)arena;
+    s.buf[1] = s.buf[0] + a.cap;
+    s.cap = a.cap;
+    s.n = rp.sel;
+    s.idx_off = 0;
+    sel_reset(s);
+    if (threadIdx.x == 0) {
+        const FlatRow f = fr[row];
+        fs.ok = (f.cnt >= rp.sel && f.cnt <= f.cap && f.tau > -CUDART_INF_F) ? f.cnt : -1;
+    }
+    __syncthreads();
+    const int cnt = fs.ok;
+    if (cnt >= 0) {
+        // the list holds exactly the logits above the bound, N or more of them: a superset of the N best
+        // (when no penalty can promote a logit the finish works on the whole list, see finish_topk_select)
+        sel_append_keys(s, a.cand + rp.cand_off, cnt, !(rp.top_k <= kFastFinishK && penalties_only_demote(rp)));
+    } else {
+        // the bound was off (or dropped candidates): the exact, self-correcting selection over the row
+        sel_stream<4, BF16>(s, rowp, mrow, 0, a.vocab);
+    }
+    const int32_t *hist = a.hist_ids ? a.hist_ids + rp.hist_off : nullptr;
+    const float *ptab = (a.pow_tab && rp.pow_off >= 0) ? a.pow_tab + rp.pow_off : nullptr;
+    const float u = a.uniforms ? __ldg(a.uniforms + row) : 0.5f;
+    const int64_t o = (int64_t)row * a.topk_stride;
+    finish_topk(s, rp, hist, ptab, u, &fs.fout, a.topk_ids ? a.topk_ids + o : nullptr,
+                a.topk_logits ? a.topk_logits + o : nullptr, a.topk_probs ? a.topk_probs + o : nullptr);
+    if (threadIdx.x == 0) {
+        a.tokens[row] = fs.fout.token;
+        if (a.token_probs) a.token_probs[row] = fs.fout.prob;
+        if (a.row_flags) a.row_flags[row] = fs.fout.flags | (cnt < 0 ? kFlagFlatRedo : 0u);
+    }
+}
+
+cudaError_t launch_flat_prep(const SampleArgs &a, FlatRow *fr, cudaStream_t stream)
+{
+    if (a.dtype == 1) k_flat_prep<true><<<a.rows, kThreads, 0, stream>>>(a, fr);
+    else k_flat_prep<false><<<a.rows, kThreads, 0, stream>>>(a, fr);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_flat_stream(const SampleArgs &a, FlatRow *fr, const FullWs &ws, cudaStream_t stream)
+{
+    const dim3 grid((unsigned)((a.vocab + kFlatPiece - 1) / kFlatPiece), (unsigned)a.rows);
+    if (a.dtype == 1) k_flat_stream<true><<<grid, kFlatThreads, 0, stream>>>(a, fr, ws);
+    else k_flat_stream<false><<<grid, kFlatThreads, 0, stream>>>(a, fr, ws);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_flat_finish(const SampleArgs &a, FlatRow *fr, int n_rows, size_t smem, cudaStream_t stream)
+{
+    void (*fn)(const SampleArgs, FlatRow *) = a.dtype == 1 ? k_flat_finish<true> : k_flat_finish<false>;
+    cudaError_t e = ensure_dynamic_smem((const void *)fn, smem);
+    if (e != cudaSuccess) return e;
+    fn<<<n_rows, kThreads, smem, stream>>>(a, fr);
+    return cudaGetLastError();
+}
+
+}  // namespace stg

@@ -1,0 +1,110 @@
+// The flat form of a sampling step: instead of a few fat persistent CTAs that each own a row (or a
+// large piece of one) from the first load to the last draw, the step is a short sequence of kernels
+//
+//   k_flat_prep    one CTA per row   what a row needs before it can be streamed: the filter bound of
+//                                    a top-k row (guessed from its first 4096 logits), zeroed
+//                                    counters
+//   k_flat_stream  one small CTA per 16384-element piece of a row, every row of the batch in one
+//                  grid: the only kernel that reads the logits from HBM.  Greedy rows keep a running
+//                  arg-max key (64-bit atomicMax), top-k rows append every logit above the row's
+//                  bound to the row's candidate list (one atomicAdd per warp and step)
+//   k_flat_finish  one CTA per row   candidates only: the exact top-N selection, penalties, softmax
+//                                    over k, min-p, top-p and the draw of SampleTopK
+//                                    (src/OpenTail.Stingray.Engine/Sampler.cs:216-357)
+//
+// so that the HBM pass runs at copy speed on all SMs whatever the mix of rows - thousands of
+// 256-thread CTAs that the hardware scheduler balances, 16 independent 16-byte loads per thread in
+// flight - and everything serial touches a few hundred candidates per row.
+//
+// The bound of a top-k row is optimistic, and checked: k_flat_finish accepts the candidate list only
+// when it holds between N = top_k + history length and its capacity entries - they are then exactly
+// the logits above the bound, hence a superset of the N best.  Otherwise (the first 4096 logits were
+// not representative: ties, masks, sorted rows) the finishing CTA streams the row again itself with
+// the exact selection of stg_select.cuh.  Nothing waits on another CTA anywhere.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "stg_types.h"
+
+namespace stg {
+
+constexpr int kFlatThreads = 256;                  // threads of a k_flat_stream CTA
+constexpr int kFlatPiece = 16384;                  // elements of a row one such CTA reads
+constexpr int kFlatSample = 4096;                  // leading elements of a row the bound is guessed from
+constexpr int kFlatSlack = 4096;                   // candidate capacity of a top-k row beyond N
+constexpr int kFlatStage = 1024;                   // candidates a k_flat_stream CTA collects in shared memory
+
+// per-row state of the flat step (device memory, 32 bytes)
+struct FlatRow {
+    unsigned long long key;  // greedy: running (value, lowest index) arg-max key; 0: nothing finite yet
+    float tau;               // top-k: every logit > tau is a candidate
+    int32_t cnt;             // top-k: candidates appended (may exceed the capacity: the excess was dropped)
+    int32_t cap;             // top-k: capacity of the row's candidate list
+    int32_t pad[3];
+};
+static_assert(sizeof(FlatRow) == 32, "FlatRow layout");
+
+// ---- full-vocabulary rows in the flat step -------------------------------------------------------------
+// The same idea carried through the full-vocabulary pipeline (stg_rowdist.cuh has it as ONE CTA per
+// row): every pass over the V elements of a row is a flat kernel of small CTAs over 16384-element
+// pieces, every strictly serial part (the walks of the exact sequential sums, the top-p cut) a
+// one-CTA-per-row kernel that touches per-sub-tile summaries or candidates only.  Between them the
+// row lives in device memory (the 126 MB L2 holds the exp values of some 200 rows of 151,936):
+//
+//   prep     history / bias overrides of the row -> a sorted (token, adjusted logit) list
+//   stream   HBM read: mask, overrides, 1/T -> x (stored), running max key
+//   exp      e = exp(x - max) (stored over x), sub-tile sums, exp-value histogram
+//   scan     fp64 prefix of the sub-tile sums -> guessed binade per sub-tile
+//   comp     composite increment of every sub-tile under its guess
+//   walk     exact softmax sum; min-p threshold; top-p plan (bound, bin starts, flagged bins)
+//   scatter  candidates above the bound into bin order (or fp64 partial sums without top-p)
+//   cut      dirty-bin sorts and the emulated sorted-order sum -> top-p threshold; normalise
+//   sums, scan, comp, draw   the same three steps over the final probabilities, then the walk that
+//            finds the token the uniform lands on
+//
+// A row the flat step cannot finish (its nucleus bound proved too tight) is flagged and redone by the
+// self-contained row kernel afterwards.
+constexpr int kFullMaxPieces = 16;  // 262144 / kFlatPiece
+
+struct FullRow {
+    unsigned long long maxkey;          // (max, lowest index) key of the adjusted, scaled logits
+    unsigned long long rawkey;          // descriptor mode: arg-max key of the masked raw logits
+    RowDist dist;
+    float sum;                          // exact sequential softmax sum
+    int32_t n_ov;                       // entries of the override list
+    int32_t ov_piece[kFullMaxPieces + 1];  // first override entry of every piece
+    int32_t c_lo, bound;                // top-p plan: lowest candidate bin, candidates the histogram counted
+    int32_t surv;                       // survivors of the filters before top-p (counted by scatter)
+    int32_t redo;                       // 1: redo the row with the self-contained row kernel
+    uint32_t flags;                     // STG_ROW_* bits gathered on the way
+    int32_t pad;
+    double part[kFullMaxPieces];        // rows without top-p: per-piece fp64 sums of the probabilities
+};
+
+struct Emul2Work;
+// device workspace of the full-vocabulary rows of a flat step, indexed by RowPlan::flat_full
+struct FullWs {
+    FullRow *rows;
+    float *e;                  // [n, e_stride]: x, then exp values
+    int64_t e_stride;
+    int32_t *ov_id;            // [n, kMaxOverride] sorted token ids
+    float *ov_adj;             // [n, kMaxOverride] their adjusted (unscaled) logits
+    Emul2Work *ew;             // [n] sub-tile sums, guesses, composites, crossing slots
+    unsigned long long *hist;  // [n, kHistBins] count << 40 | mass
+    uint32_t *bstart;          // [n, kHistBins]
+    unsigned char *bin_exp;    // [n, kHistBins]
+    uint32_t *flag_bits;       // [n, kHistBins / 32]
+    uint32_t *cursor;          // [n, kHistBins]
+    uint32_t *keys;            // [n, key_stride] candidate probabilities in bin order
+    int64_t key_stride;
+};
+
+cudaError_t launch_flat_prep(const SampleArgs &a, FlatRow *fr, cudaStream_t stream);
+cudaError_t launch_flat_stream(const SampleArgs &a, FlatRow *fr, const FullWs &ws, cudaStream_t stream);
+cudaError_t launch_full_prep(const SampleArgs &a, const FullWs &ws, cudaStream_t stream);
+cudaError_t launch_full_rest(const SampleArgs &a, const FullWs &ws, const WorkItem *full_items, int n_full, int *launches,
+                             cudaStream_t stream);
+cudaError_t launch_flat_finish(const SampleArgs &a, FlatRow *fr, int n_rows, size_t smem, cudaStream_t stream);
+
+}  // namespace stg

@@ -1,0 +1,819 @@
+// Full-vocabulary rows of the flat step (see stg_flat.cuh): the per-row and per-piece kernels behind
+// the HBM pass.  The arithmetic is that of stg_rowdist.cuh, whose device functions are reused; what
+// differs is where the work runs - every pass over V as small CTAs over pieces of all rows at once,
+// every serial part as one CTA per row over summaries or candidates.
+#include <cuda_runtime.h>
+#include <limits.h>
+#include <math_constants.h>
+#include <stdint.h>
+
+#include "stg_flat.cuh"
+#include "stg_launch.h"
+#include "stg_rowdist.cuh"
+
+namespace stg {
+
+constexpr int kFullThreads = 256;              // threads of a per-piece kernel: 8 warps, one sub-tile each at a time
+constexpr int kPieceSubTiles = kFlatPiece / kSub;  // 64 sub-tiles of 256 elements per piece
+
+__device__ __forceinline__ bool row_wants_topp(const RowPlan &rp) { return rp.top_p < 1.0f && rp.top_p > 0.f; }
+
+// ---- prep: the override list ---------------------------------------------------------------------------
+// One 1024-thread CTA per row of the batch; rows outside the full flat pipeline leave at once.
+// ApplyHistoryPenalties after the logit bias (Sampler.cs:50-56, :367-419) through build_overrides,
+// then the distinct tokens sorted by id with their adjusted logits, and where every piece starts
+// in that list.  Also clears the row's histogram and bin cursors.
+template <bool BF16>
+__global__ void __launch_bounds__(kThreads, 1) k_full_prep(const __grid_constant__ SampleArgs a, const FullWs ws)
+{
+    extern __shared__ __align__(16) unsigned char arena[];
+    __shared__ int n_ent;
+    const int row = blockIdx.x, tid = threadIdx.x;
+    const RowPlan rp = a.plans[row];
+    const int fi = rp.flat_full;
+    if (fi < 0) return;
+    FullRow *fr = ws.rows + fi;
+    const int n = a.vocab;
+    const bool greedy = rp.temperature <= 0.f;
+    const bool with_bias = !greedy && rp.bias_len > 0;
+    const bool with_hist = rp.has_penalty && rp.hist_len > 0;
+    if (tid == 0) {
+        fr->maxkey = 0ull; fr->rawkey = 0ull; fr->sum = 0.f; fr->surv = 0; fr->redo = 0; fr->flags = 0u;
+        fr->c_lo = 0; fr->bound = 0; fr->n_ov = 0;
+        for (int p = 0; p <= kFullMaxPieces; p++) fr->ov_piece[p] = 0;
+    }
+    if (row_wants_topp(rp) && !greedy) {
+        unsigned long long *hist = ws.hist + (size_t)fi * kHistBins;
+        uint32_t *cursor = ws.cursor + (size_t)fi * kHistBins;
+        for (int b = tid; b < kHistBins; b += kThreads) { hist[b] = 0ull; cursor[b] = 0u; }
+    }
+    if (!(with_hist || with_bias)) return;
+    const int esz = BF16 ? 2 : 4;
+    const void *rowp = (const char *)a.logits + (int64_t)row * a.row_stride * esz;
+    const uint32_t *mrow = (rp.use_mask && a.mask) ? a.mask + (int64_t)row * a.mask_stride : nullptr;
+    const int entries = (with_hist ? rp.hist_len : 0) + (with_bias ? rp.bias_len : 0);
+    int slots = 64;
+    while (slots < 2 * entries) slots <<= 1;
+    OvTable table;
+    build_overrides<BF16>(a, rp, rowp, mrow, n, with_hist, with_bias, table, arena, slots);
+    const int table_bytes = (slots * 24 + 8192 + 1023) & ~1023;
+    int *cid = (int *)(arena + table_bytes);
+    float *cadj = (float *)(cid + kMaxOverride);
+    int *sid = (int *)(cadj + kMaxOverride);
+    float *sadj = (float *)(sid + kMaxOverride);
+    if (tid == 0) n_ent = 0;
+    __syncthreads();
+    for (int h = tid; h < slots; h += kThreads) {
+        const int id = table.key[h];
+        if (id >= 0) {
+            const int k = atomicAdd(&n_ent, 1);
+            if (k < kMaxOverride) { cid[k] = id; cadj[k] = table.adj[h]; }
+        }
+    }
+    __syncthreads();
+    const int cnt = min(n_ent, kMaxOverride);
+    for (int t = tid; t < cnt; t += kThreads) {
+        const int id = cid[t];
+        int rank = 0;
+        for (int j = 0; j < cnt; j++) rank += (cid[j] < id) ? 1 : 0;  // ids are distinct
+        sid[rank] = id;
+        sadj[rank] = cadj[t];
+    }
+    __syncthreads();
+    int32_t *gid = ws.ov_id + (size_t)fi * kMaxOverride;
+    float *gadj = ws.ov_adj + (size_t)fi * kMaxOverride;
+    for (int t = tid; t < cnt; t += kThreads) { gid[t] = sid[t]; gadj[t] = sadj[t]; }
+    for (int p = tid; p <= kFullMaxPieces; p += kThreads) {
+        const long long first = (long long)p * kFlatPiece;  // first token id of piece p
+        int lo = 0, hi = cnt;
+        while (lo < hi) {
+            const int mid = (lo + hi) >> 1;
+            if ((long long)sid[mid] < first) lo = mid + 1; else hi = mid;
+        }
+        fr->ov_piece[p] = lo;
+    }
+    if (tid == 0) fr->n_ov = cnt;
+}
+
+// ---- exp: e = exp(x - max), sub-tile sums, histogram ----------------------------------------------------
+// grid (pieces, full rows), 256 threads: warp w takes sub-tiles w, w + 8, ... of the piece, lane l the
+// 8 consecutive elements 8l .. 8l+7 of a sub-tile (the element order the sequential-sum emulation
+// is defined on, stg_emul2.cuh).
+__global__ void __launch_bounds__(kFullThreads) k_full_exp(const __grid_constant__ SampleArgs a, const FullWs ws,
+                                                           const WorkItem *full_items)
+{
+    __shared__ unsigned hcnt[kHistBins];
+    __shared__ unsigned hmass[kHistBins];
+    const int fi = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int row = full_items[fi].row;
+    const RowPlan *rpp = a.plans + row;
+    if (!(__ldg(&rpp->temperature) > 0.f)) return;  // greedy with penalties: the stream pass found the token
+    const int n = a.vocab;
+    const int begin = blockIdx.x * kFlatPiece;
+    if (begin >= n) return;
+    const FullRow *fr = ws.rows + fi;
+    const float top_p = __ldg(&rpp->top_p);
+    const bool want_hist = top_p < 1.0f && top_p > 0.f;
+    const unsigned long long mk = fr->maxkey;
+    const bool uniform = mk == 0ull;  // nothing finite: Softmax's 1/V case (Sampler.cs:452-458)
+    const float mx = uniform ? -CUDART_INF_F : key_val(mk);
+    const float up = __fdiv_rn(1.0f, (float)n);
+    float *e = ws.e + (size_t)fi * ws.e_stride;
+    Emul2Work *ew = ws.ew + fi;
+    if (want_hist) {
+        for (int b = tid; b < kHistBins; b += kFullThreads) { hcnt[b] = 0u; hmass[b] = 0u; }
+        __syncthreads();
+    }
+    for (int st = warp; st < kPieceSubTiles; st += kFullThreads / 32) {
+        const int base = begin + st * kSub + lane * 8;
+        if (begin + st * kSub >= n) break;
+        float x[8];
+        if (base + 8 <= n) {
+            const float4 q0 = __ldcg((const float4 *)(e + base)), q1 = __ldcg((const float4 *)(e + base + 4));
+            x[0] = q0.x; x[1] = q0.y; x[2] = q0.z; x[3] = q0.w; x[4] = q1.x; x[5] = q1.y; x[6] = q1.z; x[7] = q1.w;
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; j++) x[j] = base + j < n ? __ldcg(e + base + j) : -CUDART_INF_F;
+        }
+        float acc = 0.f;
+        int low = 0;
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            float v = 0.f;
+            if (base + j < n) v = uniform ? up : expf(__fsub_rn(x[j], mx));
+            x[j] = v;
+            acc += v > 0.f ? v : 0.f;
+            if (want_hist && v > 0.f) {
+                const uint32_t eb = __float_as_uint(v);
+                const unsigned bin = bin_of(eb);
+                if (bin == 0u) low++;
+                else { atomicAdd(&hcnt[bin], 1u); atomicAdd(&hmass[bin], ((eb & 0x7FFFFFu) | 0x800000u) >> 12); }
+            }
+        }
+        if (want_hist) {
+            low = __reduce_add_sync(0xFFFFFFFFu, low);
+            if (low && lane == 0) { atomicAdd(&hcnt[0], (unsigned)low); atomicAdd(&hmass[0], (unsigned)low * 0xFFFu); }
+        }
+        if (base < n) store8(e, base, n, x);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
+        if (lane == 0) ew->sums[(begin >> 8) + st] = acc;
+    }
+    if (want_hist) {
+        __syncthreads();
+        unsigned long long *hist = ws.hist + (size_t)fi * kHistBins;
+        for (int b = tid; b < kHistBins; b += kFullThreads) {
+            const unsigned c = hcnt[b];
+            if (c) atomicAdd(&hist[b], ((unsigned long long)c << 40) | (unsigned long long)hmass[b]);
+        }
+    }
+}
+
+// ---- sums of the final probabilities (the draw's phase A) ------------------------------------------------
+__global__ void __launch_bounds__(kFullThreads) k_full_psums(const __grid_constant__ SampleArgs a, const FullWs ws,
+                                                             const WorkItem *full_items)
+{
+    const int fi = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int row = full_items[fi].row;
+    const RowPlan *rpp = a.plans + row;
+    if (!(__ldg(&rpp->temperature) > 0.f)) return;
+    const int n = a.vocab;
+    const int begin = blockIdx.x * kFlatPiece;
+    if (begin >= n) return;
+    const FullRow *fr = ws.rows + fi;
+    if (fr->redo) return;
+    const ProvFinal pf{ws.e + (size_t)fi * ws.e_stride, fr->dist, nullptr};
+    Emul2Work *ew = ws.ew + fi;
+    for (int st = warp; st < kPieceSubTiles; st += kFullThreads / 32) {
+        const int base = begin + st * kSub + lane * 8;
+        if (begin + st * kSub >= n) break;
+        float x[8];
+        pf.reload(base, n, x);
+        float acc = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; j++) acc += x[j] > 0.f ? x[j] : 0.f;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
+        if (lane == 0) ew->sums[(begin >> 8) + st] = acc;
+    }
+}
+
+// ---- scan: guessed binade of the running sum at every sub-tile (phase B) -------------------------------
+__global__ void __launch_bounds__(kThreads) k_full_scan(const __grid_constant__ SampleArgs a, const FullWs ws,
+                                                        const WorkItem *full_items)
+{
+    __shared__ Emul2Ctl ctl;
+    const int fi = blockIdx.x;
+    const int row = full_items[fi].row;
+    if (!(a.plans[row].temperature > 0.f) || ws.rows[fi].redo) return;
+    const int nsub = (a.vocab + kSub - 1) / kSub;
+    emul2_guess(&ctl, ws.ew + fi, nsub);
+}
+
+// ---- comp: composite increment of every sub-tile under its guessed binade (phase C) --------------------
+template <bool FINAL>
+__global__ void __launch_bounds__(kFullThreads) k_full_comp(const __grid_constant__ SampleArgs a, const FullWs ws,
+                                                            const WorkItem *full_items)
+{
+    const int fi = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int row = full_items[fi].row;
+    const RowPlan *rpp = a.plans + row;
+    if (!(__ldg(&rpp->temperature) > 0.f)) return;
+    const int n = a.vocab;
+    const int begin = blockIdx.x * kFlatPiece;
+    if (begin >= n) return;
+    const FullRow *fr = ws.rows + fi;
+    if (fr->redo) return;
+    const float *e = ws.e + (size_t)fi * ws.e_stride;
+    const ProvFinal pf{e, fr->dist, nullptr};
+    Emul2Work *ew = ws.ew + fi;
+    for (int st = warp; st < kPieceSubTiles; st += kFullThreads / 32) {
+        const int t = (begin >> 8) + st;
+        const int base = t * kSub + lane * 8;
+        if (t * kSub >= n) break;
+        int a0 = 0, a1 = 0;
+        if (!(ew->sums[t] == 0.f)) {
+            float x[8];
+            if (FINAL) {
+                pf.reload(base, n, x);
+            } else {
+                SrcScratch sc{e, 1.f, false};
+                if (base < n) sc.get8(base, n, x);
+#pragma unroll
+                for (int j = 0; j < 8; j++)
+                    if (base + j >= n) x[j] = 0.f;
+            }
+            const int g = ew->guess[t];
+            subtile_composite<false>(x, g, a0, a1);
+            const int xsl = ew->xslot[t];
+            if (xsl) {
+                CrossSlot &cs = ew->xs[xsl - 1];
+                int l0, l1, h0, h1;
+                lane_composite(x, g, l0, l1);
+                lane_composite(x, g + 1, h0, h1);
+                cs.lo[lane][0] = l0; cs.lo[lane][1] = l1;
+                cs.hi[lane][0] = h0; cs.hi[lane][1] = h1;
+            }
+        }
+        if (lane == 0) { ew->comp[t][0] = a0; ew->comp[t][1] = a1; }
+    }
+}
+
+// copies a row's sub-tile summaries from device memory into the shared-memory work area of the walk
+__device__ __forceinline__ void load_work(Emul2Work *dst, const Emul2Work *src)
+{
+    const uint4 *s = (const uint4 *)src;
+    uint4 *d = (uint4 *)dst;
+    for (int i = threadIdx.x; i < (int)(sizeof(Emul2Work) / 16); i += kThreads) d[i] = __ldcg(s + i);
+    __syncthreads();
+}
+static_assert(sizeof(Emul2Work) % 16 == 0, "Emul2Work is copied in 16-byte words");
+
+// exp values of a row as the walk replays them (ProvExp's reload without its load side)
+struct ProvE {
+    const float *scratch;
+    __device__ __forceinline__ void load(int base, int n, float x[8]) const { reload(base, n, x); }
+    __device__ __forceinline__ void reload(int base, int n, float x[8]) const
+    {
+        if (base >= n) {
+#pragma unroll
+            for (int j = 0; j < 8; j++) x[j] = 0.f;
+            return;
+        }
+        SrcScratch s{scratch, 1.f, false};
+        s.get8(base, n, x);
+#pragma unroll
+        for (int j = 0; j < 8; j++)
+            if (base + j >= n) x[j] = 0.f;
+    }
+};
+
+// ---- walk: exact softmax sum, min-p, top-p plan ----------------------------------------------------------
+// One 1024-thread CTA per full row.  The top-p plan is steps (1)-(3) of topp_cut (stg_rowdist.cuh):
+// the bins that bound the nucleus, where every bin starts in the bin-ordered candidate list, the
+// binade the sorted running sum is in at every bin, and the bins that must be in exact order.
+__global__ void __launch_bounds__(kThreads, 1) k_full_walk(const __grid_constant__ SampleArgs a, const FullWs ws,
+                                                           const WorkItem *full_items)
+{
+    extern __shared__ __align__(16) unsigned char arena[];
+    __shared__ RowCtl rc;
+    const int fi = blockIdx.x, tid = threadIdx.x;
+    const int row = full_items[fi].row;
+    const RowPlan rp = a.plans[row];
+    FullRow *fr = ws.rows + fi;
+    const int n = a.vocab;
+    const unsigned long long mk = fr->maxkey;
+    if (!(rp.temperature > 0.f)) {
+        // GreedyWithHistoryPenalties (Sampler.cs:421-437): the arg-max of the adjusted logits
+        if (tid == 0) {
+            const int tok = mk ? key_idx(mk) : 0;
+            if (a.mode == 2) {
+                RowDist d;
+                memset(&d, 0, sizeof(d));
+                d.flags = kDistOneHot;
+                d.tie_idx_max = tok;
+                d.argmax = tok;
+                d.inv_t = 1.f; d.inv1 = 1.f; d.inv2 = 1.f; d.inv3 = 1.f;
+                a.dists[row] = d;
+            } else {
+                if (a.tokens) a.tokens[row] = tok;
+                if (a.token_probs) a.token_probs[row] = 1.f;
+                if (a.row_flags) a.row_flags[row] = (uint32_t)rp.path | (mk ? 0u : (1u << 6));
+            }
+        }
+        return;
+    }
+    unsigned *hcount = (unsigned *)(arena + kOffCount);
+    unsigned *hmass = (unsigned *)(arena + kOffMass);
+    unsigned *bstart = (unsigned *)(arena + kOffBinOff);
+    Emul2Work *wk2 = (Emul2Work *)(arena + kOffEmul);
+    unsigned char *bin_exp = arena + kOffBinExp;
+    const float *e = ws.e + (size_t)fi * ws.e_stride;
+    const bool want_topp = row_wants_topp(rp);
+    const bool uniform = mk == 0ull;
+    const float inv_t = rp.temperature != 1.0f ? __fdiv_rn(1.0f, rp.temperature) : 1.0f;
+    RowDist d;
+    d.flags = 0;
+    d.inv_t = inv_t;
+    d.tie_idx_max = INT_MAX;
+    d.kth = 0.f; d.inv2 = 1.f; d.minp_thr = 0.f; d.tstar = 0.f; d.inv3 = 1.f; d.inv1 = 1.f;
+    d.uniform_p = 0.f; d.sum_end = 0.f; d.argmax = 0;
+    float sum = 0.f;
+    if (uniform) {
+        d.flags |= kDistUniform;
+        d.max_x = -CUDART_INF_F;
+        d.uniform_p = __fdiv_rn(1.0f, (float)n);
+    } else {
+        d.max_x = key_val(mk);
+        load_work(wk2, ws.ew + fi);
+        const int nsub = (n + kSub - 1) / kSub;
+        if (tid < 32) {
+            const ProvE pe{e};
+            emul2_walk<ProvE, false, false>(&rc.em2, wk2, pe, n, nsub, 0.f, false, nullptr, nullptr);
+        }
+        __syncthreads();
+        sum = rc.em2.s;
+        if (sum > 0.f && sum != 1.0f) { d.flags |= kDistScale1; d.inv1 = __fdiv_rn(1.0f, sum); }
+    }
+    if (rp.min_p > 0.f) {
+        // ApplyMinP (Sampler.cs:493-503): the largest probability belongs to exp value 1 (or 1/V)
+        const float emax = uniform ? d.uniform_p : 1.0f;
+        const float pmax = (d.flags & kDistScale1) ? __fmul_rn(emax, d.inv1) : emax;
+        d.minp_thr = __fmul_rn(rp.min_p, pmax);
+        d.flags |= kDistMinP;
+    }
+    if (want_topp) {
+        // histogram of the exp values as the exp pass left it
+        const unsigned long long *hist = ws.hist + (size_t)fi * kHistBins;
+        if (uniform) {
+            for (int b = tid; b < kHistBins; b += kThreads) { hcount[b] = 0u; hmass[b] = 0u; }
+            __syncthreads();
+            if (tid == 0) {
+                const unsigned bin = bin_of(__float_as_uint(d.uniform_p));
+                hcount[bin] = (unsigned)n;
+                hmass[bin] = (unsigned)min((unsigned long long)n * ((((unsigned long long)__float_as_uint(d.uniform_p) & 0x7FFFFFu) | 0x800000u) >> 12), 0xFFFFFFFFull);
+            }
+        } else {
+            for (int b = tid; b < kHistBins; b += kThreads) {
+                const unsigned long long v = __ldcg(hist + b);
+                hcount[b] = (unsigned)(v >> 40);
+                hmass[b] = (unsigned)(v & 0xFFFFFFFFull);
+            }
+        }
+        __syncthreads();
+        const double scale_p = (d.flags & kDistScale1) ? (double)d.inv1 : 1.0;
+        if (tid == 0) rc.c_lo = 0;
+        __syncthreads();
+        {
+            // (1) bound the nucleus: bins from the top until the estimated mass clears top_p
+            double lm[4], tm = 0.0, tc = 0.0;
+            unsigned lc[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int b = kBins - 1 - (tid * 4 + j);
+                lc[j] = hcount[b];
+                lm[j] = lc[j] ? bin_mass(hmass, b) : 0.0;
+                tm += lm[j];
+                tc += (double)lc[j];
+            }
+            double am = scan4_double(tm, &rc) - tm;
+            double ac = scan4_double(tc, &rc) - tc;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int b = kBins - 1 - (tid * 4 + j);
+                am += lm[j];
+                ac += (double)lc[j];
+                if (lc[j]) {
+                    const double need = (double)rp.top_p * (1.0 + 1.0 / 65536.0) + 16.0 * sqrt(ac) * 2.98e-8 + 1e-7;
+                    if (am * scale_p >= need) atomicMax(&rc.c_lo, b > 0 ? b - 1 : 0);
+                }
+            }
+            __syncthreads();
+        }
+        const int c_lo = rc.c_lo;
+        {
+            // (2) start of every candidate bin in the bin-ordered list (largest bin first)
+            unsigned loc[4], tot = 0;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int b = kBins - 1 - (tid * 4 + j);
+                loc[j] = b >= c_lo ? hcount[b] : 0u;
+                tot += loc[j];
+            }
+            const double incl = scan4_double((double)tot, &rc);
+            unsigned run = (unsigned)(incl - (double)tot);
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int b = kBins - 1 - (tid * 4 + j);
+                bstart[b] = run;
+                run += loc[j];
+            }
+            if (tid == kThreads - 1) rc.bound = (int)run;
+            __syncthreads();
+        }
+        for (int t = tid; t < kBins / 32; t += kThreads) rc.flag_bits[t] = 0u;
+        __syncthreads();
+        {
+            // (3) the binade the sorted running sum is in at every bin; bins in which it may change
+            // binade or meet top_p, and the head of the list, must be in exact order
+            double loc[4], tot = 0.0;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int b = kBins - 1 - (tid * 4 + j);
+                loc[j] = (b >= c_lo && hcount[b]) ? bin_mass(hmass, b) * scale_p : 0.0;
+                tot += loc[j];
+            }
+            double before = scan4_double(tot, &rc) - tot;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int b = kBins - 1 - (tid * 4 + j);
+                const double lo = before * (1.0 - 1.0 / 32768.0), hi = (before + loc[j]) * (1.0 + 1.0 / 2048.0);
+                const int e_lo = exp_of_double(lo);
+                bin_exp[b] = (unsigned char)e_lo;
+                if (b >= c_lo && hcount[b]) {
+                    const bool crosses = e_lo != exp_of_double(hi);
+                    const bool cut = lo <= (double)rp.top_p && hi >= (double)rp.top_p;
+                    const bool head = bstart[b] < 2048u;
+                    if (crosses || cut || head) atomicOr(&rc.flag_bits[b >> 5], 1u << (b & 31));
+                }
+                before += loc[j];
+            }
+            __syncthreads();
+        }
+        // the plan, for the scatter pass and the cut
+        uint32_t *g_bstart = ws.bstart + (size_t)fi * kHistBins;
+        unsigned char *g_binexp = ws.bin_exp + (size_t)fi * kHistBins;
+        uint32_t *g_flags = ws.flag_bits + (size_t)fi * (kHistBins / 32);
+        for (int b = tid; b < kHistBins; b += kThreads) { g_bstart[b] = bstart[b]; g_binexp[b] = bin_exp[b]; }
+        for (int t = tid; t < kHistBins / 32; t += kThreads) g_flags[t] = rc.flag_bits[t];
+        if (tid == 0) { fr->c_lo = c_lo; fr->bound = rc.bound; }
+    }
+    if (tid == 0) { fr->dist = d; fr->sum = sum; }
+}
+
+// ---- scatter: candidates into bin order, survivors counted ---------------------------------------------
+// Step (4) of topp_cut over a piece.  Rows without top-p only need the fp64 sum of their
+// probabilities for Normalize (Sampler.cs:553-562).
+__global__ void __launch_bounds__(kFullThreads) k_full_scatter(const __grid_constant__ SampleArgs a, const FullWs ws,
+                                                               const WorkItem *full_items)
+{
+    __shared__ double red_d[kFullThreads / 32];
+    __shared__ int red_i[kFullThreads / 32];
+    const int fi = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int row = full_items[fi].row;
+    const RowPlan *rpp = a.plans + row;
+    if (!(__ldg(&rpp->temperature) > 0.f)) return;
+    const int n = a.vocab;
+    const int begin = blockIdx.x * kFlatPiece;
+    if (begin >= n) return;
+    FullRow *fr = ws.rows + fi;
+    const RowDist d = fr->dist;
+    const float top_p = __ldg(&rpp->top_p);
+    const bool want_topp = top_p < 1.0f && top_p > 0.f;
+    const float *e = ws.e + (size_t)fi * ws.e_stride;
+    const int end = min(n, begin + kFlatPiece);
+    if (!want_topp) {
+        double part = 0.0;
+        for (int base = begin + tid * 8; base < end; base += kFullThreads * 8) {
+            float x[8];
+            SrcScratch sc{e, 1.f, false};
+            sc.get8(base, n, x);
+#pragma unroll
+            for (int j = 0; j < 8; j++)
+                if (base + j < n) part += (double)eval_p2(x[j], d);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xFFFFFFFFu, part, o);
+        if (lane == 0) red_d[warp] = part;
+        __syncthreads();
+        if (tid == 0) {
+            double t = 0.0;
+            for (int w = 0; w < kFullThreads / 32; w++) t += red_d[w];
+            fr->part[blockIdx.x] = t;
+        }
+        return;
+    }
+    const int c_lo = fr->c_lo;
+    const uint32_t lo_bits = bin_floor_bits(c_lo);
+    const int cap = (int)ws.key_stride;
+    const uint32_t *bstart = ws.bstart + (size_t)fi * kHistBins;
+    const unsigned char *bin_exp = ws.bin_exp + (size_t)fi * kHistBins;
+    uint32_t *flag_bits = ws.flag_bits + (size_t)fi * (kHistBins / 32);
+    uint32_t *cursor = ws.cursor + (size_t)fi * kHistBins;
+    uint32_t *keys = ws.keys + (size_t)fi * ws.key_stride;
+    int my_surv = 0;
+    for (int base = begin + tid * 8; base < end; base += kFullThreads * 8) {
+        float x[8];
+        SrcScratch sc{e, 1.f, false};
+        sc.get8(base, n, x);
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            if (base + j >= n) continue;
+            const float ev = x[j];
+            const float p = eval_p2(ev, d);
+            if (p > 0.f) {
+                my_surv++;
+                const uint32_t ebits = __float_as_uint(ev);
+                if (ebits >= lo_bits) {
+                    const unsigned bin = bin_of(ebits);
+                    const unsigned pos = __ldg(bstart + bin) + atomicAdd(&cursor[bin], 1u);
+                    const uint32_t pbits = __float_as_uint(p);
+                    if (pos < (unsigned)cap) keys[pos] = pbits;
+                    // a key whose addition would be an exact tie (the parity of the running sum then
+                    // decides the rounding, so the order inside its bin matters) flags its bin
+                    const int k = (int)__ldg(bin_exp + bin) - (int)((pbits >> 23) & 255u);
+                    if (k >= 1 && k <= 24) {
+                        const uint32_t m = (pbits & 0x7FFFFFu) | 0x800000u;
+                        if ((m & ((1u << k) - 1u)) == (1u << (k - 1))) atomicOr(&flag_bits[bin >> 5], 1u << (bin & 31));
+                    }
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) my_surv += __shfl_xor_sync(0xFFFFFFFFu, my_surv, o);
+    if (lane == 0) red_i[warp] = my_surv;
+    __syncthreads();
+    if (tid == 0) {
+        int t = 0;
+        for (int w = 0; w < kFullThreads / 32; w++) t += red_i[w];
+        if (t) atomicAdd(&fr->surv, t);
+    }
+}
+
+// ---- cut: the top-p threshold from the bin-ordered candidates; Normalize ---------------------------------
+// Steps (5) onwards of topp_cut for a row whose candidates the scatter pass left in device memory.
+__global__ void __launch_bounds__(kThreads, 1) k_full_cut(const __grid_constant__ SampleArgs a, const FullWs ws,
+                                                          const WorkItem *full_items)
+{
+    extern __shared__ __align__(16) unsigned char arena[];
+    __shared__ RowCtl rc_s;
+    __shared__ uint32_t sh_flags;
+    RowCtl *rc = &rc_s;
+    const int fi = blockIdx.x, tid = threadIdx.x;
+    const int row = full_items[fi].row;
+    const RowPlan rp = a.plans[row];
+    if (!(rp.temperature > 0.f)) return;
+    FullRow *fr = ws.rows + fi;
+    const int n = a.vocab;
+    RowDist d = fr->dist;
+    const float *scratch = ws.e + (size_t)fi * ws.e_stride;
+    const bool want_topp = row_wants_topp(rp);
+    double sum3 = 0.0;
+    if (tid == 0) sh_flags = 0u;
+    __syncthreads();
+    if (!want_topp) {
+        const int pieces = (n + kFlatPiece - 1) / kFlatPiece;
+        for (int p = 0; p < pieces; p++) sum3 += fr->part[p];  // fixed order: deterministic
+    } else {
+        uint32_t *skeys = (uint32_t *)(arena + kOffKeys);
+        unsigned *hcount = (unsigned *)(arena + kOffCount);
+        unsigned *bstart = (unsigned *)(arena + kOffBinOff);
+        Emul2Work *wk2 = (Emul2Work *)(arena + kOffEmul);
+        unsigned char *replay_ok = arena + kOffReplayOk;
+        const bool uniform = (d.flags & kDistUniform) != 0;
+        const int c_lo = fr->c_lo;
+        const int bound = fr->bound;
+        const int my_surv = fr->surv;
+        const uint32_t *g_cursor = ws.cursor + (size_t)fi * kHistBins;
+        const uint32_t *g_bstart = ws.bstart + (size_t)fi * kHistBins;
+        const uint32_t *g_flags = ws.flag_bits + (size_t)fi * (kHistBins / 32);
+        uint32_t *gkeys = ws.keys + (size_t)fi * ws.key_stride;
+        if (tid == 0) { rc->c_lo = c_lo; rc->give_up = 0; rc->n_dirty = 0; rc->bound = bound; }
+        // from here on the histogram describes the list: the filters before top-p drop the smallest
+        // values only, so the bins that lost elements are the last ones of the list and it stays dense
+        int mine = 0;
+        for (int b = tid; b < kHistBins; b += kThreads) {
+            const unsigned have = b >= c_lo ? __ldcg(g_cursor + b) : 0u;
+            hcount[b] = have;
+            bstart[b] = __ldcg(g_bstart + b);
+            mine += (int)have;
+        }
+        for (int t = tid; t < kHistBins / 32; t += kThreads) { rc->flag_bits[t] = __ldcg(g_flags + t); rc->sorted_bits[t] = 0u; }
+        uint32_t *keys = skeys;
+        int cap = kSortCap;
+        if (bound > kSortCap) { keys = gkeys; cap = (int)ws.key_stride; if (tid == 0) sh_flags |= (1u << 7); }
+        const int nc = min(block_sum_int(mine, rc->red_i), cap);
+        __syncthreads();
+        if (keys == skeys) {
+            for (int t = tid; t < nc; t += kThreads) skeys[t] = __ldcg(gkeys + t);
+            __syncthreads();
+        }
+        if (nc > 0) {
+            // (5) a sub-tile of the emulated sum is replayed whole, so every bin that shares a
+            // sub-tile with a flagged bin has to be sorted with it
+            for (int t = tid; t < kMaxSubTiles; t += kThreads) replay_ok[t] = 0;
+            __syncthreads();
+            for (int b = c_lo + tid; b < kBins; b += kThreads) {
+                const unsigned cnt = hcount[b];
+                if (cnt && ((rc->flag_bits[b >> 5] >> (b & 31)) & 1u)) {
+                    const int t0 = (int)bstart[b] >> 8, t1 = (int)(bstart[b] + cnt - 1) >> 8;
+                    for (int t = t0; t <= t1 && t < kMaxSubTiles; t++) replay_ok[t] = 1;
+                }
+            }
+            __syncthreads();
+            for (int b = c_lo + tid; b < kBins; b += kThreads) {
+                const unsigned cnt = hcount[b];
+                if (cnt >= 2u) {
+                    const int t0 = (int)bstart[b] >> 8, t1 = (int)(bstart[b] + cnt - 1) >> 8;
+                    bool need = false;
+                    for (int t = t0; t <= t1 && t < kMaxSubTiles; t++) need |= replay_ok[t] != 0;
+                    if (need) {
+                        const int slot = atomicAdd(&rc->n_dirty, 1);
+                        if (slot < kMaxDirty) rc->dirty[slot] = (unsigned short)b; else rc->give_up = 1;
+                    }
+                }
+            }
+            __syncthreads();
+            int hit = -1;
+            float cum = 0.f;
+            bool sorted_all = uniform;  // all keys equal: any order is sorted
+            for (int pass = 0; pass < 64; pass++) {
+                if (!sorted_all && (rc->give_up || pass == 63)) {
+                    const int p2 = pow2_ceil(max(nc, 2));
+                    for (int t = nc + tid; t < p2; t += kThreads) keys[t] = 0u;
+                    __syncthreads();
+                    bitonic_sort_desc_t<uint32_t>(keys, p2);
+                    sorted_all = true;
+                } else if (!sorted_all && rc->n_dirty > 0) {
+                    sort_dirty_bins(rc, keys, bstart, hcount, (uint32_t *)wk2, (int *)wk2 + kDirtyRound);
+                    __syncthreads();
+                    if (rc->give_up) continue;
+                    for (int i = tid; i < min(rc->n_dirty, kMaxDirty); i += kThreads)
+                        atomicOr(&rc->sorted_bits[rc->dirty[i] >> 5], 1u << (rc->dirty[i] & 31));
+                    __syncthreads();
+                    if (tid == 0) rc->n_dirty = 0;
+                }
+                __syncthreads();
+                if (!sorted_all) {
+                    for (int t = tid; t < kMaxSubTiles; t += kThreads) replay_ok[t] = 1;
+                    __syncthreads();
+                    for (int b = c_lo + tid; b < kBins; b += kThreads) {
+                        const unsigned cnt = hcount[b];
+                        if (cnt >= 2u && !((rc->sorted_bits[b >> 5] >> (b & 31)) & 1u)) {
+                            const int t0 = (int)bstart[b] >> 8, t1 = (int)(bstart[b] + cnt - 1) >> 8;
+                            for (int t = t0; t <= t1 && t < kMaxSubTiles; t++) replay_ok[t] = 0;
+                        }
+                    }
+                    __syncthreads();
+                }
+                ProvKeys pk{keys, keys != skeys};
+                if (nc <= kSub * kMaxSubTiles) {
+                    hit = emul_scan2<ProvKeys, false, true, 4>(&rc->em2, wk2, pk, nc, rp.top_p, true, &cum,
+                                                            sorted_all ? nullptr : replay_ok, nullptr,
+                                                            keys != skeys ? arena + kOffKeys : nullptr, kSortCap * 4);
+                } else {
+                    if (!sorted_all) { if (tid == 0) rc->give_up = 1; __syncthreads(); continue; }
+                    hit = emul_scan<ProvKeys, false>(&rc->em, pk, nc, rp.top_p, true, &cum);
+                }
+                if (hit != -2) break;
+                const int t_abort = rc->em2.abort_at;
+                for (int b = c_lo + tid; b < kBins; b += kThreads) {
+                    const unsigned cnt = hcount[b];
+                    if (cnt >= 2u && !((rc->sorted_bits[b >> 5] >> (b & 31)) & 1u)) {
+                        const int t0 = (int)bstart[b] >> 8, t1 = (int)(bstart[b] + cnt - 1) >> 8;
+                        if (t0 <= t_abort && t_abort <= t1) {
+                            const int slot = atomicAdd(&rc->n_dirty, 1);
+                            if (slot < kMaxDirty) rc->dirty[slot] = (unsigned short)b; else rc->give_up = 1;
+                        }
+                    }
+                }
+                __syncthreads();
+            }
+            if (hit < 0 && nc < my_surv) {
+                // the bound was too tight (the sum never reached top_p although survivors remain
+                // below it): the self-contained row kernel redoes the row
+                if (tid == 0) fr->redo = 1;
+                return;
+            }
+            const int last = hit >= 0 ? hit : nc - 1;
+            const float tstar = hit >= 0 ? __uint_as_float(keys[last]) : 0.f;
+            int keep = 0, all = 0;
+            double part = 0.0;
+            for (int t = tid; t < nc; t += kThreads) {
+                const uint32_t kb = keys[t];
+                if (kb == __float_as_uint(tstar)) { all++; keep += (t <= last) ? 1 : 0; }
+                if (t <= last) part += (double)__uint_as_float(kb);
+            }
+            keep = block_sum_int(keep, rc->red_i);
+            all = block_sum_int(all, rc->red_i);
+            sum3 = block_sum_double(part, rc->red_d);
+            d.flags |= kDistTopP;
+            d.tstar = tstar;
+            d.tie_idx_max = INT_MAX;
+            if (keep < all) {
+                if (tid == 0) sh_flags |= (1u << 4);
+                d.tie_idx_max = find_kth_match(rc, scratch, n, d, tstar, keep);
+            }
+        }
+    }
+    // Normalize (Sampler.cs:553-562)
+    const float s3 = (float)sum3;
+    if (s3 > 0.f && s3 != 1.0f) { d.flags |= kDistScale3; d.inv3 = __fdiv_rn(1.0f, s3); }
+    __syncthreads();
+    if (tid == 0) {
+        fr->dist = d;
+        fr->flags |= sh_flags;
+        if (a.mode == 2) {
+            const unsigned long long rk = fr->rawkey;
+            d.argmax = rk ? key_idx(rk) : 0;
+            a.dists[row] = d;
+        }
+    }
+}
+
+// ---- draw: SampleFromDistribution (Sampler.cs:564-576) ----------------------------------------------------
+__global__ void __launch_bounds__(kThreads, 1) k_full_draw(const __grid_constant__ SampleArgs a, const FullWs ws,
+                                                           const WorkItem *full_items)
+{
+    extern __shared__ __align__(16) unsigned char arena[];
+    __shared__ Emul2Ctl ctl;
+    const int fi = blockIdx.x, tid = threadIdx.x;
+    const int row = full_items[fi].row;
+    const RowPlan rp = a.plans[row];
+    if (!(rp.temperature > 0.f)) return;
+    const FullRow *fr = ws.rows + fi;
+    if (fr->redo) return;
+    const int n = a.vocab;
+    Emul2Work *wk2 = (Emul2Work *)arena;
+    load_work(wk2, ws.ew + fi);
+    const float *e = ws.e + (size_t)fi * ws.e_stride;
+    const RowDist d = fr->dist;
+    const float u = a.uniforms ? __ldg(a.uniforms + row) : 0.5f;
+    const int nsub = (n + kSub - 1) / kSub;
+    if (tid < 32) {
+        const ProvFinal pf{e, d, nullptr};
+        emul2_walk<ProvFinal, false, false>(&ctl, wk2, pf, n, nsub, u, true, nullptr, nullptr);
+    }
+    __syncthreads();
+    if (tid == 0) {
+        uint32_t fl = kPathFull | fr->flags;
+        if (d.flags & kDistUniform) fl |= (1u << 6);
+        int tok = ctl.hit;
+        if (tok < 0) { tok = n - 1; fl |= (1u << 5); }
+        a.tokens[row] = tok;
+        if (a.token_probs) a.token_probs[row] = eval_p3(__ldcg(e + tok), tok, d);
+        if (a.row_flags) a.row_flags[row] = fl;
+    }
+}
+
+// ---- launchers ---------------------------------------------------------------------------------------------
+static dim3 piece_grid(const SampleArgs &a, int n_full) { return dim3((unsigned)((a.vocab + kFlatPiece - 1) / kFlatPiece), (unsigned)n_full); }
+
+cudaError_t launch_full_prep(const SampleArgs &a, const FullWs &ws, cudaStream_t stream)
+{
+    const size_t smem = (size_t)kMaxOvSlots * 24 + 8192 + 1024 + (size_t)kMaxOverride * 16;
+    void (*fn)(const SampleArgs, const FullWs) = a.dtype == 1 ? k_full_prep<true> : k_full_prep<false>;
+    cudaError_t e = ensure_dynamic_smem((const void *)fn, smem);
+    if (e != cudaSuccess) return e;
+    fn<<<a.rows, kThreads, smem, stream>>>(a, ws);
+    return cudaGetLastError();
+}
+
+// everything behind the HBM pass for the `n_full` full rows listed in `full_rows` (device array)
+cudaError_t launch_full_rest(const SampleArgs &a, const FullWs &ws, const WorkItem *full_items, int n_full, int *launches,
+                             cudaStream_t stream)
+{
+    const dim3 pg = piece_grid(a, n_full);
+    cudaError_t e = ensure_dynamic_smem((const void *)k_full_walk, kRowArenaBytes);
+    if (e == cudaSuccess) e = ensure_dynamic_smem((const void *)k_full_cut, kRowArenaBytes);
+    if (e == cudaSuccess) e = ensure_dynamic_smem((const void *)k_full_draw, sizeof(Emul2Work));
+    if (e != cudaSuccess) return e;
+    k_full_exp<<<pg, kFullThreads, 0, stream>>>(a, ws, full_items);
+    k_full_scan<<<n_full, kThreads, 0, stream>>>(a, ws, full_items);
+    k_full_comp<false><<<pg, kFullThreads, 0, stream>>>(a, ws, full_items);
+    k_full_walk<<<n_full, kThreads, kRowArenaBytes, stream>>>(a, ws, full_items);
+    k_full_scatter<<<pg, kFullThreads, 0, stream>>>(a, ws, full_items);
+    k_full_cut<<<n_full, kThreads, kRowArenaBytes, stream>>>(a, ws, full_items);
+    *launches += 6;
+    if (a.mode == 0) {
+        k_full_psums<<<pg, kFullThreads, 0, stream>>>(a, ws, full_items);
+        k_full_scan<<<n_full, kThreads, 0, stream>>>(a, ws, full_items);
+        k_full_comp<true><<<pg, kFullThreads, 0, stream>>>(a, ws, full_items);
+        k_full_draw<<<n_full, kThreads, sizeof(Emul2Work), stream>>>(a, ws, full_items);
+        *launches += 4;
+    }
+    return cudaGetLastError();
+}
+
+}  // namespace stg

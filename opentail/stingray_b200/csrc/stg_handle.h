@@ -17,6 +17,24 @@ struct DevBuf {
     size_t bytes = 0;
 };
 
+// The host plan of one sampling step (built by make_plan in stg_api.cu).
+struct Plan {
+    std::vector<RowPlan> rows;
+    std::vector<WorkItem> items;
+    std::vector<float> pow_tab;
+    int chunk_len = 0;
+    int cap = kSubTile + 1;
+    bool any_row_item = false;
+    int n_row_items = 0;
+    size_t smem = 0;
+    uint64_t n_greedy = 0, n_topk = 0, n_full = 0;
+    int max_topk_path_k = 0;  // largest top_k among the rows on the top-k path
+    int max_sel = 1;          // largest selection count of a chunked row
+    bool flat = false;        // the chunked rows run as the flat step (stg_flat.cuh)
+    bool flat_full = false;   // ... and so do the full-vocabulary rows
+    int n_chunk_rows = 0;
+};
+
 }  // namespace stg
 
 struct StgSampler_ {
@@ -32,6 +50,16 @@ struct StgSampler_ {
     cudaEvent_t plan_ev[4]{};
     int plan_slot = 0;
     std::vector<unsigned char> plan_cache;  // bytes of the plan last uploaded
+    stg::Plan plan;                          // the plan of the last step ...
+    std::vector<unsigned char> plan_key, plan_key_scratch;  // ... and the batch description it was built for
+    bool plan_valid = false;
+    const stg::RowPlan *d_rows = nullptr;    // where that plan lives on the device
+    const stg::WorkItem *d_items = nullptr;
+    const float *d_pow = nullptr;
+    stg::DevBuf flat_rows;               // FlatRow per row (stg_flat.cuh)
+    // full-vocabulary rows of the flat step: FullWs arrays for up to full_cap rows
+    stg::DevBuf fw_rows, fw_e, fw_ov_id, fw_ov_adj, fw_ew, fw_hist, fw_bstart, fw_binexp, fw_flagbits, fw_cursor, fw_keys;
+    int full_cap = 0;
     stg::DevBuf cand, cand_count, tickets, work_counter, escratch, keyscratch, listscratch, dists;
     stg::DevBuf st_hist, st_bias_ids, st_bias_vals, st_uniforms, st_mask, st_logits;
     stg::DevBuf o_tokens, o_probs, o_flags, o_topk_ids, o_topk_vals, o_topk_probs, o_pairs;

@@ -65,7 +65,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_shard_finish(const __grid_const
 cudaError_t launch_shard_finish(const SampleArgs &a, const void *gather, size_t block_bytes, size_t smem,
                                 cudaStream_t stream)
 {
-    cudaError_t e = cudaFuncSetAttribute(k_shard_finish, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = ensure_dynamic_smem((const void *)k_shard_finish, smem);
     if (e != cudaSuccess) return e;
     k_shard_finish<<<a.rows, kThreads, smem, stream>>>(a, (const unsigned char *)gather, block_bytes);
     return cudaGetLastError();

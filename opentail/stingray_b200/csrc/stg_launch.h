@@ -2,9 +2,30 @@
 #pragma once
 #include <cuda_runtime.h>
 
+#include <map>
+#include <mutex>
+#include <utility>
+
 #include "stg_types.h"
 
 namespace stg {
+
+// Raises a kernel's dynamic shared-memory limit to `bytes` unless an earlier launch on this device
+// already did: the attribute call costs microseconds that a per-step launch path should not pay.
+inline cudaError_t ensure_dynamic_smem(const void *fn, size_t bytes)
+{
+    static std::mutex mu;
+    static std::map<std::pair<const void *, int>, size_t> done;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    std::lock_guard<std::mutex> lock(mu);
+    size_t &cur = done[{fn, dev}];
+    if (bytes <= cur) return cudaSuccess;
+    e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e == cudaSuccess) cur = bytes;
+    return e;
+}
 
 // shared memory a row-type work item needs: sort keys + exp-value histogram
 constexpr size_t kRowArenaBytes = 211968;  // layout in stg_rowdist.cuh (checked there)

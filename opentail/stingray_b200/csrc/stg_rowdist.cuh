@@ -1384,6 +1384,8 @@ static __device__ void run_row(const SampleArgs &a, int row, int item, SelCtl *s
     if (tid == 0) sh_rp = a.plans[row];
     __syncthreads();
     const RowPlan &rp = sh_rp;
+    // second chance of the flat step: only the rows it flagged are run
+    if (a.redo_flags != nullptr && (rp.flat_full < 0 || a.redo_flags[(size_t)rp.flat_full * a.redo_stride] == 0)) return;
     const int n = a.vocab;
     const int esz = BF16 ? 2 : 4;
     const void *rowp = (const char *)a.logits + (int64_t)row * a.row_stride * esz;

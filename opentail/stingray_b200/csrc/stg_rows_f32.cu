@@ -6,7 +6,7 @@ namespace stg {
 cudaError_t launch_rows_f32(const SampleArgs &a, int grid, cudaStream_t stream)
 {
     void (*fn)(const SampleArgs) = k_sample_rows<false>;
-    cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRowArenaBytes);
+    cudaError_t e = ensure_dynamic_smem((const void *)fn, kRowArenaBytes);
     if (e != cudaSuccess) return e;
     fn<<<grid, kThreads, kRowArenaBytes, stream>>>(a);
     return cudaGetLastError();

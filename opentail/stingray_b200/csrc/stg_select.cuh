@@ -501,7 +501,7 @@ static __device__ void sel_stream(Sel &s, const void *rowp, const uint32_t *mrow
 }
 
 // Appends `count` keys from global memory (another chunk's survivors).
-static __device__ void sel_append_keys(Sel &s, const u64 *keys, int count)
+static __device__ void sel_append_keys(Sel &s, const u64 *keys, int count, bool reduce = true)
 {
     SelCtl *c = s.c;
     for (int base = 0; base < count; base += kSubTile) {
@@ -516,8 +516,8 @@ static __device__ void sel_append_keys(Sel &s, const u64 *keys, int count)
         if (threadIdx.x == 0) c->cnt = cnt + m;
         __syncthreads();
     }
-    if (c->cnt > 2 * s.n) sel_raise(s);
-    if (c->cnt > 2 * s.n) sel_compact(s);
+    if (reduce && c->cnt > 2 * s.n) sel_raise(s);
+    if (reduce && c->cnt > 2 * s.n) sel_compact(s);
 }
 
 // ---- block-wide bitonic sort, descending, of `p2` (power of two) 64-bit keys in shared memory --
@@ -663,13 +663,23 @@ static __device__ void finish_topk_draw(Sel &s, const RowPlan &rp, float uniform
 // the k best of those by a second radix select, and a rank sort of just these k in the stable
 // order of Sampler.cs:289-294 (penalised value descending, raw order among equals).  Leaves vals /
 // ids of the first k at the start of the buffer that is not active.
+static __device__ __forceinline__ bool penalties_only_demote(const RowPlan &rp)
+{
+    return !rp.has_penalty || (rp.rep >= 1.0f && rp.pres >= 0.f && rp.freq >= 0.f);
+}
+
 static __device__ void finish_topk_select(Sel &s, const RowPlan &rp, const int32_t *hist, const float *pow_tab)
 {
     SelCtl *c = s.c;
     const int tid = threadIdx.x;
     const int k = rp.top_k;
     const int keep = rp.has_penalty ? rp.sel : k;
-    if (c->cnt > keep) {
+    // The reference penalises the `sel` best raw logits and takes the k best penalised ones.  When
+    // no penalty can raise a logit (repetition >= 1, presence and frequency >= 0) any superset of
+    // those `sel` gives the same k candidates in the same order: a logit outside the raw top-`sel`
+    // has at least k unpenalised logits above it and penalties only move others further down.  So
+    // the exact raw selection is skipped then, and it runs only when a penalty may promote.
+    if (!penalties_only_demote(rp) && c->cnt > keep) {
         if (c->cnt <= 512) {
             // few candidates: rank them directly (fewer barriers than the radix passes)
             const int m = c->cnt;
@@ -698,14 +708,14 @@ static __device__ void finish_topk_select(Sel &s, const RowPlan &rp, const int32
     float *vals = (float *)bb;
     int *ids = (int *)(vals + k);
     const int ke = min(k, cnt);
-    if (!rp.has_penalty) {
-        for (int t = tid; t < k; t += kThreads) {
-            if (t >= cnt) { vals[t] = -CUDART_INF_F; ids[t] = -1; continue; }
+    if (!rp.has_penalty && cnt <= 256) {
+        for (int t = tid; t < k; t += kThreads)
+            if (t >= ke) { vals[t] = -CUDART_INF_F; ids[t] = -1; }
+        for (int t = tid; t < cnt; t += kThreads) {
             const u64 key = a[t];
             int rank = 0;
             for (int j = 0; j < cnt; j++) rank += (a[j] > key) ? 1 : 0;
-            vals[rank] = key_val(key);
-            ids[rank] = key_idx(key);
+            if (rank < ke) { vals[rank] = key_val(key); ids[rank] = key_idx(key); }
         }
         __syncthreads();
         return;
@@ -718,7 +728,7 @@ static __device__ void finish_topk_select(Sel &s, const RowPlan &rp, const int32
     while (hslots < 2 * rp.hist_len) hslots <<= 1;
     int *hkey = (int *)(SK + k);
     int *hall = hkey + hslots, *hwin = hall + hslots;
-    const bool use_hash = (char *)(hwin + hslots) <= (char *)(s.buf[c->cur ^ 1] + s.cap);
+    const bool use_hash = rp.has_penalty && (char *)(hwin + hslots) <= (char *)(s.buf[c->cur ^ 1] + s.cap);
     if (use_hash) {
         for (int t = tid; t < hslots; t += kThreads) { hkey[t] = -1; hall[t] = 0; hwin[t] = 0; }
         __syncthreads();
@@ -740,7 +750,9 @@ static __device__ void finish_topk_select(Sel &s, const RowPlan &rp, const int32
         float v = key_val(a[t]);
         const int id = key_idx(a[t]);
         int occ_all = 0, occ_w = 0;
-        if (use_hash) {
+        if (!rp.has_penalty) {
+            // no penalties: the candidates compete with their raw values
+        } else if (use_hash) {
             int h = (int)(((unsigned)id * 2654435761u) >> 7) & (hslots - 1);
             for (;;) {
                 const int kx = hkey[h];

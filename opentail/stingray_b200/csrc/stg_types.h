@@ -14,6 +14,8 @@ constexpr int kSortCap = 32768;         // top-p candidate keys sorted in shared
 constexpr int kHistBins = 4096;         // probability histogram bins (exponent + 4 mantissa bits)
 constexpr int kMaxOverride = 2048;      // history + bias entries per row on the full-vocabulary path
 
+constexpr uint32_t kFlagFlatRedo = 1u << 8;  // row flag: the optimistic bound failed, the row was read twice
+
 enum Path : int32_t {
     kPathGreedy = 0,        // Sampler.Greedy
     kPathGreedyPen = 1,     // GreedyWithHistoryPenalties
@@ -32,6 +34,8 @@ struct RowPlan {
     int32_t n_chunks;   // chunk work items of this row (0 for row-type rows)
     int32_t cand_off;   // first entry of this row's candidate scratch (entries of 8 bytes)
     int32_t use_mask, has_penalty, pow_off, slot;
+    int32_t flat_groups; // flat step, top-k rows: groups of the sample whose maxima bound the filter (power of two)
+    int32_t flat_full;   // flat step: index of a full-vocabulary row in the step's FullWs, -1 otherwise
 };
 
 struct WorkItem {
@@ -106,6 +110,8 @@ struct SampleArgs {
     int32_t vocab_offset;            // vocabulary-sharded mode: global id of local column 0
     int32_t shard_mode;              // 0 off, 1 select only (write candidates), 2 finish from gather
     int32_t n_ranks;
+    const int32_t *redo_flags;       // row kernel as the flat step's second chance: only rows whose flag
+    int32_t redo_stride;             // redo_flags[flat_full * redo_stride] is set are run; null: every row item
 };
 
 #ifdef __CUDACC__
