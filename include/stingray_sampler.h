@@ -261,6 +261,33 @@ STG_API int stg_sample_rows(StgHandle handle, const StgSampleBatch *batch, void 
 STG_API int stg_build_distribution(StgHandle handle, const StgSampleBatch *batch, float *probs,
                                    void *stream);
 
+/* Sampler.SampleWithDistribution (Sampler.cs:172-187), called once per draft token by the speculative
+ * decoder (src/OpenTail.Stingray.Engine/SpeculativeDecoder.cs:509-513): builds the post-filter
+ * distribution of every row with the full-vocabulary pipeline whatever top_k is (the top-k fast path
+ * of Sampler.Sample rounds differently and is never taken here), stores it in `probs` [rows, vocab]
+ * (device memory, or NULL when only the tokens are wanted) and draws the row's token from it with
+ * uniforms[r].  temperature <= 0 rows return the greedy arg-max and a one-hot row. */
+STG_API int stg_sample_with_distribution(StgHandle handle, const StgSampleBatch *batch, float *probs,
+                                         void *stream);
+
+/* Sampler.SampleFromProbs (Sampler.cs:195-199, :564-576) on caller-held distributions: for each row
+ * the first token whose sequential fp32 running sum reaches (float)uniforms[r], the last token when
+ * rounding leaves the sum short (STG_ROW_CDF_FALLBACK).  probs: device [rows, row_stride] fp32;
+ * uniforms and tokens follow mem_flags (STG_MEM_HOST_UNIFORMS, STG_MEM_HOST_OUTPUTS); row_flags may
+ * be NULL. */
+STG_API int stg_sample_from_probs(StgHandle handle, const float *probs, int32_t rows, int32_t vocab,
+                                  int64_t row_stride, const float *uniforms, int32_t *tokens,
+                                  uint32_t *row_flags, uint32_t mem_flags, void *stream);
+
+/* Sampler.ResampleResidual (Sampler.cs:587-618) on caller-held distributions p and q (device
+ * [rows, row_stride] fp32 each): a token drawn in proportion to max(p - q, 0) with uniforms[2r];
+ * an empty residual falls back to a draw from p with the same uniform (STG_SEQ_EMPTY_RESIDUAL); the
+ * rounding fallback is the last token with a positive residual (STG_ROW_CDF_FALLBACK), and only if
+ * there is none a draw from p with uniforms[2r + 1].  uniforms is [rows, 2]. */
+STG_API int stg_resample_residual(StgHandle handle, const float *p, const float *q, int32_t rows,
+                                  int32_t vocab, int64_t row_stride, const float *uniforms,
+                                  int32_t *tokens, uint32_t *row_flags, uint32_t mem_flags, void *stream);
+
 /* Speculative accept / reject with residual resampling for a batch of sequences: the loop of
  * SpeculativeDecoder.StepSampled (SpeculativeDecoder.cs:529-559) with Sampler.ResampleResidual
  * (Sampler.cs:587-618) and the bonus draw.  temperature <= 0 rows use the greedy accept of

@@ -21,6 +21,7 @@ SEQ_EMPTY_RESIDUAL, SEQ_BAD_DRAFT = 1 << 8, 1 << 9
 EXPORTS = [
     "stg_abi_version", "stg_create", "stg_destroy", "stg_last_error", "stg_get_stats", "stg_debug_phase_ticks",
     "stg_argmax_rows", "stg_argmax_rows_static", "stg_sample_rows", "stg_build_distribution", "stg_spec_verify",
+    "stg_sample_with_distribution", "stg_sample_from_probs", "stg_resample_residual",
     "stg_mtp_accept", "stg_and_masks", "stg_comm_unique_id", "stg_comm_init", "stg_comm_destroy",
     "stg_shard_select", "stg_shard_allgather", "stg_shard_exchange_bytes", "stg_shard_finish", "stg_shard_gather_local",
 ]
@@ -98,6 +99,9 @@ def load() -> C.CDLL:
     lib.stg_sample_rows.argtypes = [vp, C.POINTER(StgSampleBatch), vp]
     lib.stg_build_distribution.argtypes = [vp, C.POINTER(StgSampleBatch), vp, vp]
     lib.stg_spec_verify.argtypes = [vp, C.POINTER(StgSpecBatch), vp]
+    lib.stg_sample_with_distribution.argtypes = [vp, C.POINTER(StgSampleBatch), vp, vp]
+    lib.stg_sample_from_probs.argtypes = [vp, vp, i32, i32, i64, vp, vp, vp, C.c_uint32, vp]
+    lib.stg_resample_residual.argtypes = [vp, vp, vp, i32, i32, i64, vp, vp, vp, C.c_uint32, vp]
     lib.stg_mtp_accept.argtypes = [vp, vp, i32, i32, i32, i64, vp, f32, vp, vp, vp, vp]
     lib.stg_and_masks.argtypes = [vp, vp, i32, i32, i32, i64, vp, i64, vp, vp]
     lib.stg_comm_unique_id.argtypes = [vp]

@@ -306,7 +306,7 @@ int run_batch(StgHandle h, const StgSampleBatch *b, const BatchExtra &x, void *s
     CK(cudaSetDevice(h->cfg.device));
     const uint32_t mf = b->mem_flags;
     const int rows = b->rows, V = b->vocab;
-    if (mode == 0 && !pairs_out && !b->tokens && !x.shard_mode) return fail(h, STG_ERR_INVALID_ARGUMENT, "tokens is required");
+    if ((mode == 0 || mode == 3) && !pairs_out && !b->tokens && !x.shard_mode) return fail(h, STG_ERR_INVALID_ARGUMENT, "tokens is required");
     if (x.shard_mode && (!h->xchg_local.p || b->rows > h->shard_rows)) return fail(h, STG_ERR_CAPACITY, "exchange buffers are missing or too small");
 
     const size_t esz0 = b->logits_dtype == STG_DTYPE_BF16 ? 2 : 4, need0 = b->logits_dtype == STG_DTYPE_BF16 ? 8 : 16;
@@ -401,6 +401,7 @@ int run_batch(StgHandle h, const StgSampleBatch *b, const BatchExtra &x, void *s
         }
         if (a.tokens == nullptr) a.tokens = (int32_t *)h->o_tokens.p;
     }
+    if (mode == 3) a.dist_out = dist_out;  // sample and materialise: device memory, may be null
     a.plans = d_rows; a.items = d_items; a.pow_tab = d_pow;
     a.cand = (unsigned long long *)h->cand.p;
     a.cand_count = (int32_t *)h->cand_count.p;
@@ -532,7 +533,7 @@ int run_batch(StgHandle h, const StgSampleBatch *b, const BatchExtra &x, void *s
     h->stats.rows_greedy += pl.n_greedy; h->stats.rows_topk_path += pl.n_topk; h->stats.rows_full_path += pl.n_full;
 
     if (host_out) {
-        if (mode == 0 && b->tokens) CK(cudaMemcpyAsync(b->tokens, a.tokens, (size_t)rows * 4, cudaMemcpyDeviceToHost, stream));
+        if ((mode == 0 || mode == 3) && b->tokens) CK(cudaMemcpyAsync(b->tokens, a.tokens, (size_t)rows * 4, cudaMemcpyDeviceToHost, stream));
         if (b->token_probs) CK(cudaMemcpyAsync(b->token_probs, a.token_probs, (size_t)rows * 4, cudaMemcpyDeviceToHost, stream));
         if (b->row_flags) CK(cudaMemcpyAsync(b->row_flags, a.row_flags, (size_t)rows * 4, cudaMemcpyDeviceToHost, stream));
         if (b->topk_ids) CK(cudaMemcpyAsync(b->topk_ids, a.topk_ids, (size_t)rows * ts * 4, cudaMemcpyDeviceToHost, stream));
@@ -613,7 +614,7 @@ int stg_create(const StgConfig *cfg, StgHandle *out)
     A(h->st_hist, R * std::max<size_t>(cfg->max_history, 1) * 4);
     A(h->st_bias_ids, R * std::max<size_t>(cfg->max_bias, 1) * 4);
     A(h->st_bias_vals, R * std::max<size_t>(cfg->max_bias, 1) * 4);
-    A(h->st_uniforms, R * 4);
+    A(h->st_uniforms, R * 8);
     if (cfg->flags & STG_CFG_HOST_LOGITS) {
         A(h->st_mask, R * ((V + 31) / 32) * 4);
         A(h->st_logits, R * V * 4);
@@ -716,6 +717,14 @@ int stg_get_stats(StgHandle h, StgStats *out)
 int stg_sample_rows(StgHandle h, const StgSampleBatch *b, void *stream)
 {
     BatchExtra x;
+    return run_batch(h, b, x, stream);
+}
+
+int stg_sample_with_distribution(StgHandle h, const StgSampleBatch *b, float *probs, void *stream)
+{
+    BatchExtra x;
+    x.mode = 3;
+    x.dist_out = probs;
     return run_batch(h, b, x, stream);
 }
 

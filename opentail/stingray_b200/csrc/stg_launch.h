@@ -51,6 +51,10 @@ struct SpecArgs {
     int32_t n_seq, n_draft, vocab, dtype, mode, vec;
 };
 cudaError_t launch_spec_finish(const SpecArgs &a, cudaStream_t stream);
+cudaError_t launch_probs_draw(const float *probs, int rows, int vocab, int64_t row_stride, const float *uniforms,
+                              int32_t *tokens, uint32_t *flags, cudaStream_t stream);
+cudaError_t launch_residual_draw(const float *p, const float *q, int rows, int vocab, int64_t row_stride,
+                                 const float *uniforms2, int32_t *tokens, uint32_t *flags, cudaStream_t stream);
 cudaError_t launch_mtp_accept(const void *logits, int dtype, int rows, int vocab, int64_t row_stride, int vec,
                               const int32_t *draft, float p_min, int32_t *accept, int32_t *argmax, float *prob,
                               cudaStream_t stream);

@@ -1445,7 +1445,7 @@ static __device__ void run_row(const SampleArgs &a, int row, int item, SelCtl *s
             __syncthreads();
             return;
         }
-        if (a.mode == 1 && a.dist_out) {
+        if ((a.mode == 1 || a.mode == 3) && a.dist_out) {
             float *o = a.dist_out + (int64_t)row * n;
             for (int i = tid; i < n; i += kThreads) o[i] = (i == tok) ? 1.f : 0.f;
         }
@@ -1478,13 +1478,17 @@ static __device__ void run_row(const SampleArgs &a, int row, int item, SelCtl *s
     }
 
     // draw: SampleFromDistribution (Sampler.cs:564-576)
-    float *dout = (a.mode == 1 && a.dist_out) ? a.dist_out + (int64_t)row * n : nullptr;
+    float *dout = ((a.mode == 1 || a.mode == 3) && a.dist_out) ? a.dist_out + (int64_t)row * n : nullptr;
     ProvFinal pf{scratch, rc.dist, dout};
-    if (a.mode == 1) {
+    if (a.mode == 1 || (a.mode == 3 && dout != nullptr)) {
         for (int base = tid * 8; base < n; base += kThreads * 8) { float x[8]; pf.load(base, n, x); }
-        if (tid == 0 && a.row_flags) a.row_flags[row] = kPathFull | sh_flags;
+        if (a.mode == 1) {
+            if (tid == 0 && a.row_flags) a.row_flags[row] = kPathFull | sh_flags;
+            __syncthreads();
+            return;
+        }
+        pf.dist_out = nullptr;  // mode 3 goes on to the draw
         __syncthreads();
-        return;
     }
     const float u = a.uniforms ? __ldg(a.uniforms + row) : 0.5f;
     float cum = 0.f;

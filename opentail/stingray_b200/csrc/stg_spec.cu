@@ -191,6 +191,57 @@ int stg_mtp_accept(StgHandle h, const void *logits, int32_t dtype, int32_t rows,
     return STG_OK;
 }
 
+}  // extern "C"
+
+namespace {
+
+// shared by the two draws on caller-held distributions: stages uniforms, launches, returns tokens
+int draw_rows(StgHandle h, const float *p, const float *q, int32_t rows, int32_t vocab, int64_t row_stride,
+              const float *uniforms, int per_row, int32_t *tokens, uint32_t *row_flags, uint32_t mem_flags, void *stream_)
+{
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (!h) return STG_ERR_INVALID_ARGUMENT;
+    if (!p || (per_row == 2 && !q) || !uniforms || !tokens || rows < 0 || vocab <= 0 || row_stride < vocab)
+        return fail(h, STG_ERR_INVALID_ARGUMENT, "bad arguments to a draw on caller-held distributions");
+    if (rows > h->cfg.max_rows) return fail(h, STG_ERR_CAPACITY, "rows exceed max_rows");
+    if (rows == 0) return STG_OK;
+    CK(cudaSetDevice(h->cfg.device));
+    const void *u;
+    int rc = stage_in(h, uniforms, (size_t)rows * per_row * 4, mem_flags & STG_MEM_HOST_UNIFORMS, h->st_uniforms, stream, &u);
+    if (rc) return rc;
+    const bool host_out = mem_flags & STG_MEM_HOST_OUTPUTS;
+    int32_t *d_tok = host_out ? (int32_t *)h->o_tokens.p : tokens;
+    uint32_t *d_fl = row_flags ? (host_out ? (uint32_t *)h->o_flags.p : row_flags) : nullptr;
+    cudaError_t e = per_row == 2 ? launch_residual_draw(p, q, rows, vocab, row_stride, (const float *)u, d_tok, d_fl, stream)
+                                 : launch_probs_draw(p, rows, vocab, row_stride, (const float *)u, d_tok, d_fl, stream);
+    if (e != cudaSuccess) return cuda_fail(h, e, "draw kernel launch");
+    h->stats.kernel_launches++;
+    if (host_out) {
+        CK(cudaMemcpyAsync(tokens, d_tok, (size_t)rows * 4, cudaMemcpyDeviceToHost, stream));
+        if (row_flags) CK(cudaMemcpyAsync(row_flags, d_fl, (size_t)rows * 4, cudaMemcpyDeviceToHost, stream));
+        CK(cudaStreamSynchronize(stream));
+    }
+    return STG_OK;
+}
+
+}  // namespace
+
+extern "C" int stg_sample_from_probs(StgHandle h, const float *probs, int32_t rows, int32_t vocab, int64_t row_stride,
+                                     const float *uniforms, int32_t *tokens, uint32_t *row_flags, uint32_t mem_flags,
+                                     void *stream)
+{
+    return draw_rows(h, probs, nullptr, rows, vocab, row_stride, uniforms, 1, tokens, row_flags, mem_flags, stream);
+}
+
+extern "C" int stg_resample_residual(StgHandle h, const float *p, const float *q, int32_t rows, int32_t vocab,
+                                     int64_t row_stride, const float *uniforms, int32_t *tokens, uint32_t *row_flags,
+                                     uint32_t mem_flags, void *stream)
+{
+    return draw_rows(h, p, q, rows, vocab, row_stride, uniforms, 2, tokens, row_flags, mem_flags, stream);
+}
+
+extern "C" {
+
 // ---- vocabulary-sharded mode ---------------------------------------------------------------------
 
 int stg_comm_unique_id(void *out_id128)

@@ -212,6 +212,116 @@ cudaError_t launch_spec_finish(const SpecArgs &a, cudaStream_t stream)
     return cudaGetLastError();
 }
 
+// ---- draws on caller-held distributions -------------------------------------------------------------
+struct ProvPlain {  // a probability row as it is
+    const float *p;
+    __device__ __forceinline__ void load(int base, int n, float x[8]) const
+    {
+#pragma unroll
+        for (int j = 0; j < 8; j++) x[j] = (base + j < n) ? __ldg(p + base + j) : 0.f;
+    }
+    __device__ __forceinline__ void reload(int base, int n, float x[8]) const { load(base, n, x); }
+};
+struct ProvPlainResidual {  // positive part of p - q
+    const float *p, *q;
+    __device__ __forceinline__ void load(int base, int n, float x[8]) const
+    {
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const float r = (base + j < n) ? __fsub_rn(__ldg(p + base + j), __ldg(q + base + j)) : 0.f;
+            x[j] = r > 0.f ? r : 0.f;
+        }
+    }
+    __device__ __forceinline__ void reload(int base, int n, float x[8]) const { load(base, n, x); }
+};
+
+// SampleFromDistribution (Sampler.cs:564-576), one CTA per row
+__device__ __forceinline__ int draw_from_probs(SpecShared &sh, Emul2Work *wk2, const float *row, int n, float u, uint32_t &fl)
+{
+    if (!(u > 0.f)) return 0;  // r <= cum holds at the first token whatever its probability
+    ProvPlain pp{row};
+    float cum;
+    int tok = emul_any<ProvPlain, false>(&sh.em, &sh.em2, wk2, pp, n, u, true, &cum);
+    if (tok < 0) { tok = n - 1; fl |= (1u << 5); }
+    return tok;
+}
+
+__global__ void __launch_bounds__(kThreads, 1) k_probs_draw(const float *probs, int vocab, int64_t row_stride,
+                                                            const float *uniforms, int32_t *tokens, uint32_t *flags)
+{
+    __shared__ SpecShared sh;
+    extern __shared__ __align__(16) unsigned char spec_dyn[];
+    const int row = blockIdx.x;
+    uint32_t fl = 0u;
+    const int tok = draw_from_probs(sh, (Emul2Work *)spec_dyn, probs + (int64_t)row * row_stride, vocab, __ldg(uniforms + row), fl);
+    if (threadIdx.x == 0) {
+        tokens[row] = tok;
+        if (flags) flags[row] = fl;
+    }
+}
+
+// ResampleResidual (Sampler.cs:587-618), one CTA per row
+__global__ void __launch_bounds__(kThreads, 1) k_residual_draw(const float *p, const float *q, int vocab, int64_t row_stride,
+                                                               const float *uniforms2, int32_t *tokens, uint32_t *flags)
+{
+    __shared__ SpecShared sh;
+    extern __shared__ __align__(16) unsigned char spec_dyn[];
+    Emul2Work *wk2 = (Emul2Work *)spec_dyn;
+    const int row = blockIdx.x, tid = threadIdx.x;
+    const float *pr = p + (int64_t)row * row_stride, *qr = q + (int64_t)row * row_stride;
+    const float u0 = __ldg(uniforms2 + 2 * row), u1 = __ldg(uniforms2 + 2 * row + 1);
+    ProvPlainResidual rr{pr, qr};
+    uint32_t fl = 0u;
+    int tok;
+    float sum, cum;
+    emul_any<ProvPlainResidual, true>(&sh.em, &sh.em2, wk2, rr, vocab, 0.f, false, &sum);
+    if (sum <= 0.f || isnan(sum)) {
+        fl |= (1u << 8);  // empty residual: a draw from p
+        tok = draw_from_probs(sh, wk2, pr, vocab, u0, fl);
+    } else {
+        const float target = __fmul_rn(u0, sum);
+        tok = emul_any<ProvPlainResidual, true>(&sh.em, &sh.em2, wk2, rr, vocab, target, true, &cum);
+        if (tok < 0) {
+            // rounding fallback: the last token with a positive residual
+            int lastp = -1;
+            for (int base = tid * 8; base < vocab; base += kThreads * 8) {
+                float x[8];
+                rr.load(base, vocab, x);
+#pragma unroll
+                for (int j = 0; j < 8; j++)
+                    if (base + j < vocab && x[j] > 0.f) lastp = base + j;
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) lastp = max(lastp, __shfl_xor_sync(0xFFFFFFFFu, lastp, o));
+            __syncthreads();
+            if ((tid & 31) == 0) sh.red_i[tid >> 5] = lastp;
+            __syncthreads();
+            lastp = -1;
+            for (int w = 0; w < 32; w++) lastp = max(lastp, sh.red_i[w]);
+            fl |= (1u << 5);
+            tok = lastp >= 0 ? lastp : draw_from_probs(sh, wk2, pr, vocab, u1, fl);
+        }
+    }
+    if (tid == 0) {
+        tokens[row] = tok;
+        if (flags) flags[row] = fl;
+    }
+}
+
+cudaError_t launch_probs_draw(const float *probs, int rows, int vocab, int64_t row_stride, const float *uniforms,
+                              int32_t *tokens, uint32_t *flags, cudaStream_t stream)
+{
+    k_probs_draw<<<rows, kThreads, sizeof(Emul2Work), stream>>>(probs, vocab, row_stride, uniforms, tokens, flags);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_residual_draw(const float *p, const float *q, int rows, int vocab, int64_t row_stride,
+                                 const float *uniforms2, int32_t *tokens, uint32_t *flags, cudaStream_t stream)
+{
+    k_residual_draw<<<rows, kThreads, sizeof(Emul2Work), stream>>>(p, q, vocab, row_stride, uniforms2, tokens, flags);
+    return cudaGetLastError();
+}
+
 // MtpDecoder.AcceptDraft + SoftmaxProbAt, src/OpenTail.Stingray.Engine/MtpDecoder.cs:562-596
 template <bool BF16>
 __global__ void __launch_bounds__(kThreads) k_mtp_accept(const void *logits, int vocab, int64_t row_stride, int vec,

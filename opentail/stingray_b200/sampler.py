@@ -275,6 +275,56 @@ class BatchSampler:
                                                      self._stream(stream)))
         return probs
 
+    def sample_with_distribution(self, logits, params, *, history_ids=None, history_offsets=None, mask=None,
+                                 uniforms=None, want_probs=True, stream=None):
+        """``Sampler.SampleWithDistribution`` for every row (``stg_sample_with_distribution``): the
+        full-vocabulary pipeline whatever ``TopK`` is.  ``logits`` is a CUDA tensor; returns
+        (tokens, probs ``[rows, vocab]`` or None), both on the device."""
+        b, keep = self._batch(logits, params, history_ids, history_offsets, mask, None, None, uniforms)
+        tokens = self._alloc((b.rows,), np.int32, False)
+        b.tokens = _ptr(tokens)
+        probs = self._alloc((b.rows, b.vocab), np.float32, False) if want_probs else None
+        self._check(self._lib.stg_sample_with_distribution(self._h, C.byref(b), _ptr(probs), self._stream(stream)))
+        return tokens, probs
+
+    def sample_from_probs(self, probs, uniforms, stream=None):
+        """``Sampler.SampleFromProbs`` per row of a CUDA ``[rows, vocab]`` float32 tensor."""
+        import torch
+
+        rows, vocab = probs.shape
+        assert probs.is_cuda and probs.dtype == torch.float32 and probs.stride(1) == 1
+        flags = 0
+        if not _is_torch(uniforms):
+            uniforms = np.ascontiguousarray(uniforms, dtype=np.float32)
+            flags |= N.MEM_HOST_UNIFORMS
+        tokens = self._alloc((rows,), np.int32, False)
+        rf = self._alloc((rows,), np.uint32, False)
+        self._check(self._lib.stg_sample_from_probs(self._h, probs.data_ptr(), rows, vocab, probs.stride(0) if rows > 1 else vocab,
+                                                    _ptr(uniforms), _ptr(tokens), _ptr(rf), flags, self._stream(stream)))
+        return tokens, rf
+
+    def resample_residual(self, p, q, uniforms, stream=None):
+        """``Sampler.ResampleResidual`` per row; ``p`` and ``q`` CUDA ``[rows, vocab]`` float32 tensors of
+        equal shape, ``uniforms`` ``[rows, 2]``."""
+        import torch
+
+        if tuple(p.shape) != tuple(q.shape):
+            # ResampleResidual, Sampler.cs:590-592
+            raise ValueError(f"p and q must have equal length ({p.shape[-1]} vs {q.shape[-1]}).")
+        rows, vocab = p.shape
+        assert p.is_cuda and q.is_cuda and p.dtype == torch.float32 and q.dtype == torch.float32
+        assert p.stride(1) == 1 and q.stride() == p.stride()
+        flags = 0
+        if not _is_torch(uniforms):
+            uniforms = np.ascontiguousarray(uniforms, dtype=np.float32).reshape(rows, 2)
+            flags |= N.MEM_HOST_UNIFORMS
+        tokens = self._alloc((rows,), np.int32, False)
+        rf = self._alloc((rows,), np.uint32, False)
+        self._check(self._lib.stg_resample_residual(self._h, p.data_ptr(), q.data_ptr(), rows, vocab,
+                                                    p.stride(0) if rows > 1 else vocab, _ptr(uniforms), _ptr(tokens),
+                                                    _ptr(rf), flags, self._stream(stream)))
+        return tokens, rf
+
     def spec_verify(self, target_logits, draft_logits, draft_tokens, params, uniforms, *, mode=0,
                     p_min=1.0, want_probs=False, stream=None):
         """``SpeculativeDecoder.StepSampled``'s accept loop for ``n_seq`` sequences
@@ -486,6 +536,56 @@ class Sampler:
             vals = np.array(list(p.LogitBias.values()), dtype=np.float32)
             kw["bias"] = (ids, vals, np.array([0, ids.size], dtype=np.int32))
         probs[...] = _single(a.shape[1]).build_distribution(a, [p], **kw)[0]
+
+
+    @staticmethod
+    def SampleWithDistribution(logits, p: SamplingParams, probs: np.ndarray, rng: Optional[Random] = None) -> int:
+        """``Sampler.SampleWithDistribution`` (``Sampler.cs:172-187``): fills ``probs`` and returns the
+        drawn token; one ``NextDouble()`` is consumed unless ``Temperature <= 0``."""
+        import torch
+
+        a = np.ascontiguousarray(logits, dtype=np.float32).reshape(1, -1)
+        if probs.shape[-1] != a.shape[1]:
+            raise ValueError(f"probs length ({probs.shape[-1]}) must equal logits length ({a.shape[1]}).")
+        kw = {}
+        if p.PreviousTokens is not None and len(p.PreviousTokens) > 0:
+            ids, off = _csr(p.PreviousTokens)
+            kw["history_ids"], kw["history_offsets"] = torch.from_numpy(ids).cuda(), off
+        if p.Temperature > 0:
+            rng = rng or _default_rng
+            kw["uniforms"] = torch.tensor([np.float32(rng.NextDouble())], dtype=torch.float32, device="cuda")
+        tok, pr = _single(a.shape[1]).sample_with_distribution(torch.from_numpy(a).cuda(), [p], **kw)
+        probs[...] = pr[0].cpu().numpy()
+        return int(tok[0].item())
+
+    @staticmethod
+    def SampleFromProbs(probs, rng: Random) -> int:
+        """``Sampler.SampleFromProbs`` (``Sampler.cs:195-199``)."""
+        import torch
+
+        if rng is None:
+            raise ValueError("rng must not be None")  # ArgumentNullException.ThrowIfNull(rng)
+        a = np.ascontiguousarray(probs, dtype=np.float32).reshape(1, -1)
+        u = np.array([np.float32(rng.NextDouble())], dtype=np.float32)
+        tok, _ = _single(a.shape[1]).sample_from_probs(torch.from_numpy(a).cuda(), u)
+        return int(tok[0].item())
+
+    @staticmethod
+    def ResampleResidual(p, q, rng: Random) -> int:
+        """``Sampler.ResampleResidual`` (``Sampler.cs:587-618``).  One ``NextDouble()`` is consumed, as in
+        the reference; its last-resort second draw (no positive residual although their sum was
+        positive) cannot occur, and a fixed 0.5 stands in for it."""
+        import torch
+
+        if rng is None:
+            raise ValueError("rng must not be None")
+        pa = np.ascontiguousarray(p, dtype=np.float32).reshape(1, -1)
+        qa = np.ascontiguousarray(q, dtype=np.float32).reshape(1, -1)
+        if pa.shape != qa.shape:
+            raise ValueError(f"p and q must have equal length ({pa.shape[1]} vs {qa.shape[1]}).")
+        u = np.array([[np.float32(rng.NextDouble()), 0.5]], dtype=np.float32)
+        tok, _ = _single(pa.shape[1]).resample_residual(torch.from_numpy(pa).cuda(), torch.from_numpy(qa).cuda(), u)
+        return int(tok[0].item())
 
 
 _default_rng = Random()
