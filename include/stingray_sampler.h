@@ -34,7 +34,7 @@ extern "C" {
 #define STG_API __attribute__((visibility("default")))
 #endif
 
-#define STG_ABI_VERSION 1
+#define STG_ABI_VERSION 2
 
 /* ---- status codes --------------------------------------------------------------------------- */
 enum {
@@ -69,12 +69,18 @@ enum {
 enum {
     STG_ROW_PATH_MASK = 0x7u,        /* 0 greedy, 1 greedy with penalties, 2 top-k path,
                                         3 full-vocabulary path, 4 top-k path found no finite logit */
+    STG_ROW_NEAR_BOUNDARY = 1u << 3, /* the draw lies within 1e-6 (of the kept mass) of the step of the running
+                                        sum below or above the sampled token: another exp or summation
+                                        order could have returned the neighbouring token */
     STG_ROW_TIE_AT_CUTOFF = 1u << 4, /* the top-p cut fell inside a group of equal probabilities */
     STG_ROW_CDF_FALLBACK = 1u << 5,  /* the draw ran past the end of the CDF (rounding fallback) */
     STG_ROW_FULLY_MASKED = 1u << 6,  /* no finite logit in the row */
     STG_ROW_WIDE_NUCLEUS = 1u << 7,  /* top-p candidates did not fit on chip; global-memory sort */
-    STG_ROW_READ_TWICE = 1u << 8     /* top-k path: the optimistic filter bound failed its check and the
-                                        row was streamed a second time with the exact selection */
+    STG_ROW_READ_TWICE = 1u << 8,    /* an optimistic bound failed its check and the row was processed a second
+                                        time: the filter bound of a top-k row, or the nucleus bound of a
+                                        full-vocabulary row */
+    STG_ROW_NEAR_CUT = 1u << 10      /* full-vocabulary path: the sorted running sum of top-p passes top_p within
+                                        1e-6, so a last-bit difference in exp could move the cut by a token */
 };
 
 /* ---- per-sequence flags written to StgSpecBatch.seq_flags (STG_ROW_CDF_FALLBACK applies too) --- */
@@ -201,6 +207,15 @@ typedef struct StgStats {
     uint64_t sequences_verified;
     uint64_t kernel_launches;
     uint64_t plan_uploads;
+    /* events counted on the device where a row's flags are written (stg_get_stats waits for the work
+     * enqueued so far to read them) */
+    uint64_t boundary_draws;     /* rows flagged STG_ROW_NEAR_BOUNDARY */
+    uint64_t tie_rows;           /* STG_ROW_TIE_AT_CUTOFF */
+    uint64_t cdf_fallbacks;      /* STG_ROW_CDF_FALLBACK */
+    uint64_t wide_nucleus_rows;  /* STG_ROW_WIDE_NUCLEUS */
+    uint64_t reread_rows;        /* STG_ROW_READ_TWICE */
+    uint64_t near_cut_rows;      /* STG_ROW_NEAR_CUT */
+    uint64_t fully_masked_rows;  /* STG_ROW_FULLY_MASKED on a sampled row */
 } StgStats;
 
 /* ---- lifetime ---------------------------------------------------------------------------------- */
@@ -222,6 +237,12 @@ STG_API int stg_get_stats(StgHandle handle, StgStats *out);
  * in the environment; blocks.  The reference's counterpart is its env-gated Stopwatch buckets
  * (src/OpenTail.Stingray.Engine/DecodeProfileTimers.cs:17-67). */
 STG_API int stg_debug_phase_ticks(StgHandle handle, uint64_t *out, int32_t max_items, int32_t *n_items);
+
+/* Diagnostic: device time (microseconds) between the kernels of the last sampling step on the caller's
+ * stream, measured with CUDA events, and their names (max_items strings of name_len bytes).  Only
+ * recorded when the handle was created with STG_KERNEL_TIMES=1 in the environment; blocks. */
+STG_API int stg_debug_kernel_times(StgHandle handle, float *out_us, char *names, int32_t name_len,
+                                   int32_t max_items, int32_t *n_items);
 
 /* ---- the hot path ------------------------------------------------------------------------------- */
 

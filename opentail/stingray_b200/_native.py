@@ -20,6 +20,7 @@ SEQ_EMPTY_RESIDUAL, SEQ_BAD_DRAFT = 1 << 8, 1 << 9
 
 EXPORTS = [
     "stg_abi_version", "stg_create", "stg_destroy", "stg_last_error", "stg_get_stats", "stg_debug_phase_ticks",
+    "stg_debug_kernel_times",
     "stg_argmax_rows", "stg_argmax_rows_static", "stg_sample_rows", "stg_build_distribution", "stg_spec_verify",
     "stg_sample_with_distribution", "stg_sample_from_probs", "stg_resample_residual",
     "stg_mtp_accept", "stg_and_masks", "stg_comm_unique_id", "stg_comm_init", "stg_comm_destroy",
@@ -70,7 +71,8 @@ class StgSpecBatch(C.Structure):
 class StgStats(C.Structure):
     _fields_ = [(n, C.c_uint64) for n in (
         "calls", "rows_sampled", "rows_greedy", "rows_topk_path", "rows_full_path",
-        "sequences_verified", "kernel_launches", "plan_uploads")]
+        "sequences_verified", "kernel_launches", "plan_uploads", "boundary_draws", "tie_rows", "cdf_fallbacks",
+        "wide_nucleus_rows", "reread_rows", "near_cut_rows", "fully_masked_rows")]
 
 
 _lib = None
@@ -94,6 +96,7 @@ def load() -> C.CDLL:
     lib.stg_last_error.argtypes = [vp, C.c_char_p, C.c_size_t]
     lib.stg_get_stats.argtypes = [vp, C.POINTER(StgStats)]
     lib.stg_debug_phase_ticks.argtypes = [vp, vp, i32, C.POINTER(C.c_int32)]
+    lib.stg_debug_kernel_times.argtypes = [vp, vp, vp, i32, i32, C.POINTER(C.c_int32)]
     lib.stg_argmax_rows.argtypes = [vp, vp, i32, i32, i32, i64, vp, vp]
     lib.stg_argmax_rows_static.argtypes = [vp, i32, i32, i32, i64, vp, vp]
     lib.stg_sample_rows.argtypes = [vp, C.POINTER(StgSampleBatch), vp]

@@ -137,7 +137,7 @@ int make_plan(StgHandle h, const StgSampleBatch *b, int mode, bool shard, int gl
     pl.n_chunk_rows = n_chunk_rows;
     // The flat step needs long, aligned rows and a candidate list (N + 4096 entries) that about 3 N
     // expected survivors fit well inside.
-    pl.flat = flat_ok && n_chunk_rows > 0 && V >= kFlatPiece && 3 * (size_t)max_sel + 256 <= (size_t)max_sel + kFlatSlack;
+    pl.flat = flat_ok && n_chunk_rows > 0 && V >= 4 * kFlatSample && 3 * (size_t)max_sel + 256 <= (size_t)max_sel + kFlatSlack;
     if (pl.flat) {
         size_t need = 0;
         for (auto &rp : pl.rows)
@@ -172,10 +172,24 @@ int make_plan(StgHandle h, const StgSampleBatch *b, int mode, bool shard, int gl
                 if (rp.path == kPathTopK) {
                     cand_off += rp.sel + kFlatSlack;
                     // groups of the 4096-element sample: about 3 N survivors (at least 256) over the row
-                    const double t = std::max(3.0 * rp.sel, 256.0);
-                    const double m = t * kFlatSample / (double)V;
-                    int ng = 1;
-                    while (ng < 1024 && ng < m / 2.0) ng <<= 1;
+                    // The bound is the smallest of ng group maxima of the sample, above which about
+                    // ng * H(ng) of the sample's elements lie (H the harmonic number), so about
+                    // E(ng) = ng * H(ng) * V / sample of the row's.  Wanted: E between 2.5 N (at least
+                    // 400: small group counts scatter widely) and 0.6 of the list's capacity; the
+                    // smallest power of two that gets there, else the one that comes closest.
+                    const double lo = std::max(2.5 * rp.sel, 400.0), hi = 0.6 * (rp.sel + (double)kFlatSlack);
+                    const double per = (double)V / std::min<double>(kFlatSample, V);
+                    int ng = 8, best_ng = 8;
+                    double best_fit = -1.0, hn = 0.0;
+                    for (int i = 1; i <= 8; i++) hn += 1.0 / i;
+                    for (int g = 8; g <= 1024; g *= 2) {
+                        const double ex = g * hn * per;
+                        const double fit = std::min(ex / lo, hi / ex);
+                        if (fit > best_fit) { best_fit = fit; best_ng = g; }
+                        if (ex >= lo && ex <= hi) { best_ng = g; break; }
+                        for (int i = g + 1; i <= 2 * g; i++) hn += 1.0 / i;
+                    }
+                    ng = best_ng;
                     rp.flat_groups = ng;
                 }
                 continue;
@@ -407,6 +421,7 @@ int run_batch(StgHandle h, const StgSampleBatch *b, const BatchExtra &x, void *s
     a.cand_count = (int32_t *)h->cand_count.p;
     a.tickets = (uint32_t *)h->tickets.p;
     a.work_counter = (uint32_t *)h->work_counter.p;
+    a.counters = (unsigned long long *)h->work_counter.p + 16;  // bytes 128..191 of the same small buffer
     a.phase_ticks = (unsigned long long *)h->ticks.p;
     h->ticks_items = (int)pl.items.size();
     a.escratch = (float *)h->escratch.p;
@@ -484,10 +499,11 @@ int run_batch(StgHandle h, const StgSampleBatch *b, const BatchExtra &x, void *s
     SampleArgs c = a;  // the chunked rows' view of the step
     c.items = a.items + n_rows_items;
     c.n_items = n_chunk_items;
+    h->kt.begin(stream);
     if (flat_chunks || flat_full) {
-        if (flat_chunks) { e = launch_flat_prep(c, fr, stream); launches++; }
-        if (e == cudaSuccess && flat_full) { e = launch_full_prep(a, ws, stream); launches++; }
-        if (e == cudaSuccess) { e = launch_flat_stream(a, fr, ws, stream); launches++; }
+        if (flat_chunks) { e = launch_flat_prep(c, fr, stream); launches++; h->kt.mark("flat_prep", stream); }
+        if (e == cudaSuccess && flat_full) { e = launch_full_prep(a, ws, stream); launches++; h->kt.mark("full_prep", stream); }
+        if (e == cudaSuccess) { e = launch_flat_stream(a, fr, ws, stream); launches++; h->kt.mark("flat_stream", stream); }
     }
     const bool fork = both || (flat_chunks && n_rows_items > 0);
     if (e == cudaSuccess && fork) {
@@ -497,10 +513,12 @@ int run_batch(StgHandle h, const StgSampleBatch *b, const BatchExtra &x, void *s
     // the full rows (main stream) ...
     if (e == cudaSuccess && n_rows_items > 0) {
         if (flat_full) {
-            e = launch_full_rest(a, ws, a.items, n_rows_items, &launches, stream);
+            e = launch_full_rest(a, ws, a.items, n_rows_items, &launches, &h->kt, stream);
             if (e == cudaSuccess) e = launch_rows_kernel(true);  // rows the flat form flagged; the others leave at once
+            h->kt.mark("rows_redo", stream);
         } else {
             e = launch_rows_kernel(false);
+            h->kt.mark("rows_kernel", stream);
         }
     }
     // ... beside the chunked rows (side stream when both kinds exist)
@@ -519,6 +537,7 @@ int run_batch(StgHandle h, const StgSampleBatch *b, const BatchExtra &x, void *s
         if (e == cudaSuccess && fork) e = cudaEventRecord(h->ev_join, h->aux_stream);
     }
     if (e == cudaSuccess && fork) e = cudaStreamWaitEvent(stream, h->ev_join, 0);
+    h->kt.mark("join_side_stream", stream);
     if (e != cudaSuccess) {
         cudaMemsetAsync(h->work_counter.p, 0, 8, stream);
         cudaMemsetAsync(h->tickets.p, 0, h->tickets.bytes, stream);
@@ -626,6 +645,10 @@ int stg_create(const StgConfig *cfg, StgHandle *out)
     const size_t tk = R * std::max<size_t>(cfg->max_top_k, 1) * 4;
     A(h->o_topk_ids, tk); A(h->o_topk_vals, tk); A(h->o_topk_probs, tk);
     if (getenv("STG_PHASE_TICKS") && getenv("STG_PHASE_TICKS")[0] == '1') A(h->ticks, R * 65 * 32 * 8);
+    if (getenv("STG_KERNEL_TIMES") && getenv("STG_KERNEL_TIMES")[0] == '1') {
+        h->kt.on = true;
+        for (int i = 0; i <= KernelTimer::kMax; i++) cudaEventCreate(&h->kt.ev[i]);
+    }
     if (cfg->max_spec_draft > 0) {
         const size_t L = (size_t)cfg->max_spec_draft;
         A(h->sp_draft, R * L * 4); A(h->sp_uniforms, R * (L + 2) * 8);
@@ -707,9 +730,37 @@ int stg_debug_phase_ticks(StgHandle h, uint64_t *out, int32_t max_items, int32_t
     return STG_OK;
 }
 
+int stg_debug_kernel_times(StgHandle h, float *out_us, char *names, int32_t name_len, int32_t max_items, int32_t *n_items)
+{
+    if (!h || !out_us || !n_items) return STG_ERR_INVALID_ARGUMENT;
+    if (!h->kt.on) return fail(h, STG_ERR_UNSUPPORTED, "create the handle with STG_KERNEL_TIMES=1 in the environment");
+    CK(cudaSetDevice(h->cfg.device));
+    CK(cudaDeviceSynchronize());
+    const int n = std::min<int>(max_items, h->kt.n);
+    for (int i = 0; i < n; i++) {
+        float ms = 0.f;
+        CK(cudaEventElapsedTime(&ms, h->kt.ev[i], h->kt.ev[i + 1]));
+        out_us[i] = ms * 1000.f;
+        if (names && name_len > 0) {
+            strncpy(names + (size_t)i * name_len, h->kt.name[i] ? h->kt.name[i] : "", (size_t)name_len - 1);
+            names[(size_t)i * name_len + name_len - 1] = 0;
+        }
+    }
+    *n_items = n;
+    return STG_OK;
+}
+
 int stg_get_stats(StgHandle h, StgStats *out)
 {
     if (!h || !out) return STG_ERR_INVALID_ARGUMENT;
+    // the event counters live on the device (the kernels bump them where they write a row's flags):
+    // this call waits for the work enqueued so far
+    unsigned long long ctr[kCtrCount] = {0};
+    CK(cudaSetDevice(h->cfg.device));
+    CK(cudaMemcpy(ctr, (unsigned long long *)h->work_counter.p + 16, sizeof(ctr), cudaMemcpyDeviceToHost));
+    h->stats.boundary_draws = ctr[kCtrBoundary]; h->stats.tie_rows = ctr[kCtrTie]; h->stats.cdf_fallbacks = ctr[kCtrFallback];
+    h->stats.wide_nucleus_rows = ctr[kCtrWide]; h->stats.reread_rows = ctr[kCtrReread]; h->stats.near_cut_rows = ctr[kCtrNearCut];
+    h->stats.fully_masked_rows = ctr[kCtrMasked];
     *out = h->stats;
     return STG_OK;
 }

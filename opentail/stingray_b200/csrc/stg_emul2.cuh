@@ -88,6 +88,8 @@ struct Emul2Ctl {
     float s;
     int hit;
     int abort_at;                   // sub-tile that needed a replay the caller had forbidden, or -1
+    float hit_before;               // running sum just before the element that met the target (with `s` just
+                                    // after it: how close the target lies to a step of the running sum)
 };
 
 // increment of x (>= 0) in units of 1/scale, for an even (d0) and an odd (d1) running sum
@@ -188,7 +190,7 @@ __device__ __forceinline__ void subtile_composite(const float x[8], int eb, int 
 // `s` is the exact running sum before the sub-tile; returns the hit index or -1.
 template <bool POS_ONLY>
 __device__ __forceinline__ int replay_subtile(const float x[8], int base, int n, float target, bool has_target,
-                                              float &s)
+                                              float &s, float &before)
 {
     const int lane = threadIdx.x & 31;
     const int g0 = base + lane * 8;
@@ -246,11 +248,13 @@ __device__ __forceinline__ int replay_subtile(const float x[8], int base, int n,
         int sprev = __shfl_sync(0xFFFFFFFFu, S, L > 0 ? L - 1 : 0);
         if (L == 0) sprev = sint;
         float acc = ldexpf((float)sprev, eb - 150);
+        float prev = acc;
         int hit = -1;
         if (lane == L) {
 #pragma unroll
             for (int j = 0; j < 8; j++) {
                 if (g0 + j < n && (!POS_ONLY || x[j] > 0.f) && hit < 0) {
+                    prev = acc;
                     acc = __fadd_rn(acc, x[j]);
                     if (has_target && acc >= target) hit = g0 + j;
                 }
@@ -258,7 +262,7 @@ __device__ __forceinline__ int replay_subtile(const float x[8], int base, int n,
         }
         s = __shfl_sync(0xFFFFFFFFu, acc, L);
         hit = __shfl_sync(0xFFFFFFFFu, hit, L);
-        if (hit >= 0) return hit;
+        if (hit >= 0) { before = __shfl_sync(0xFFFFFFFFu, prev, L); return hit; }
         start_lane = L + 1;
         if (start_lane >= 32) return -1;
     }
@@ -311,7 +315,7 @@ __device__ __forceinline__ void emul2_walk(Emul2Ctl *c, Emul2Work *wk, const Pro
                                            bool has_target, const unsigned char *replay_ok, unsigned long long *tk)
 {
     const int lane = threadIdx.x & 31;
-    float s = 0.f;
+    float s = 0.f, before = 0.f;
     int hit = -1;
     int t = 0;
     int abort_at = -1;
@@ -439,12 +443,12 @@ __device__ __forceinline__ void emul2_walk(Emul2Ctl *c, Emul2Work *wk, const Pro
                     }
                 }
             }
-            if (!crossed) hit = replay_subtile<POS_ONLY>(x, t * kSub, n, target, has_target, s);
+            if (!crossed) hit = replay_subtile<POS_ONLY>(x, t * kSub, n, target, has_target, s, before);
             t += 1;
             n_replay++;
         }
     }
-    if (lane == 0) { c->s = s; c->hit = abort_at >= 0 ? -2 : hit; c->abort_at = abort_at; }
+    if (lane == 0) { c->s = s; c->hit = abort_at >= 0 ? -2 : hit; c->abort_at = abort_at; c->hit_before = before; }
     tick(tk, 3);
     if (tk && lane == 0) { tk[4] = (unsigned long long)n_iter; tk[5] = (unsigned long long)n_replay; tk[6] = (unsigned long long)n_fast; }
 }

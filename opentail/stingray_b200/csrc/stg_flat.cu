@@ -135,8 +135,8 @@ __global__ void __launch_bounds__(kFlatThreads) k_flat_stream(const __grid_const
         int best_i = -1, rbest_i = -1;
         const bool want_raw = a.mode == 2;
 #pragma unroll
-        for (int s = 0; s < 4; s++) {
-            if (s + 1 < 4) {
+        for (int s = 0; s < kFlatSteps; s++) {
+            if (s + 1 < kFlatSteps) {
 #pragma unroll
                 for (int u = 0; u < 4; u++) flat_load4<BF16>(rowp, mrow, i0 + ((s + 1) * 4 + u) * 1024, end, nxt[u]);
             }
@@ -213,8 +213,8 @@ __global__ void __launch_bounds__(kFlatThreads) k_flat_stream(const __grid_const
         float best = -CUDART_INF_F;
         int best_i = -1;
 #pragma unroll
-        for (int s = 0; s < 4; s++) {
-            if (s + 1 < 4) {
+        for (int s = 0; s < kFlatSteps; s++) {
+            if (s + 1 < kFlatSteps) {
 #pragma unroll
                 for (int u = 0; u < 4; u++) flat_load4<BF16>(rowp, mrow, i0 + ((s + 1) * 4 + u) * 1024, end, nxt[u]);
             }
@@ -258,8 +258,8 @@ __global__ void __launch_bounds__(kFlatThreads) k_flat_stream(const __grid_const
     unsigned long long *cand = a.cand + __ldg(&rpp->cand_off);
     int *cnt_p = &fr[row].cnt;
 #pragma unroll
-    for (int s = 0; s < 4; s++) {
-        if (s + 1 < 4) {
+    for (int s = 0; s < kFlatSteps; s++) {
+        if (s + 1 < kFlatSteps) {
 #pragma unroll
             for (int u = 0; u < 4; u++) flat_load4<BF16>(rowp, mrow, i0 + ((s + 1) * 4 + u) * 1024, end, nxt[u]);
         }
@@ -383,7 +383,9 @@ __global__ void __launch_bounds__(kThreads, 1) k_flat_finish(const __grid_consta
     if (threadIdx.x == 0) {
         a.tokens[row] = fs.fout.token;
         if (a.token_probs) a.token_probs[row] = fs.fout.prob;
-        if (a.row_flags) a.row_flags[row] = fs.fout.flags | (cnt < 0 ? kFlagFlatRedo : 0u);
+        const uint32_t fl = fs.fout.flags | (cnt < 0 ? kFlagFlatRedo : 0u);
+        if (a.row_flags) a.row_flags[row] = fl;
+        count_row_flags(a.counters, fl);
     }
 }
 

@@ -31,6 +31,7 @@ namespace stg {
 
 constexpr int kFlatThreads = 256;                  // threads of a k_flat_stream CTA
 constexpr int kFlatPiece = 16384;                  // elements of a row one such CTA reads
+constexpr int kFlatSteps = kFlatPiece / 4096;      // steps of 4 sub-steps of 1024 elements each
 constexpr int kFlatSample = 4096;                  // leading elements of a row the bound is guessed from
 constexpr int kFlatSlack = 4096;                   // candidate capacity of a top-k row beyond N
 constexpr int kFlatStage = 1024;                   // candidates a k_flat_stream CTA collects in shared memory
@@ -47,8 +48,8 @@ static_assert(sizeof(FlatRow) == 32, "FlatRow layout");
 
 // ---- full-vocabulary rows in the flat step -------------------------------------------------------------
 // The same idea carried through the full-vocabulary pipeline (stg_rowdist.cuh has it as ONE CTA per
-// row): every pass over the V elements of a row is a flat kernel of small CTAs over 16384-element
-// pieces, every strictly serial part (the walks of the exact sequential sums, the top-p cut) a
+// row): every pass over the V elements of a row is a flat kernel of small CTAs over pieces of the
+// row, every strictly serial part (the walks of the exact sequential sums, the top-p cut) a
 // one-CTA-per-row kernel that touches per-sub-tile summaries or candidates only.  Between them the
 // row lives in device memory (the 126 MB L2 holds the exp values of some 200 rows of 151,936):
 //
@@ -66,6 +67,7 @@ static_assert(sizeof(FlatRow) == 32, "FlatRow layout");
 // A row the flat step cannot finish (its nucleus bound proved too tight) is flagged and redone by the
 // self-contained row kernel afterwards.
 constexpr int kFullMaxPieces = 16;  // 262144 / kFlatPiece
+constexpr int kFullMaxParts = 32;   // per-piece partial sums of the phase kernels (8192-element pieces)
 
 struct FullRow {
     unsigned long long maxkey;          // (max, lowest index) key of the adjusted, scaled logits
@@ -79,7 +81,7 @@ struct FullRow {
     int32_t redo;                       // 1: redo the row with the self-contained row kernel
     uint32_t flags;                     // STG_ROW_* bits gathered on the way
     int32_t pad;
-    double part[kFullMaxPieces];        // rows without top-p: per-piece fp64 sums of the probabilities
+    double part[kFullMaxParts];         // rows without top-p: per-piece fp64 sums of the probabilities
 };
 
 struct Emul2Work;
@@ -103,8 +105,9 @@ struct FullWs {
 cudaError_t launch_flat_prep(const SampleArgs &a, FlatRow *fr, cudaStream_t stream);
 cudaError_t launch_flat_stream(const SampleArgs &a, FlatRow *fr, const FullWs &ws, cudaStream_t stream);
 cudaError_t launch_full_prep(const SampleArgs &a, const FullWs &ws, cudaStream_t stream);
+struct KernelTimer;
 cudaError_t launch_full_rest(const SampleArgs &a, const FullWs &ws, const WorkItem *full_items, int n_full, int *launches,
-                             cudaStream_t stream);
+                             KernelTimer *kt, cudaStream_t stream);
 cudaError_t launch_flat_finish(const SampleArgs &a, FlatRow *fr, int n_rows, size_t smem, cudaStream_t stream);
 
 }  // namespace stg

@@ -14,7 +14,9 @@
 namespace stg {
 
 constexpr int kFullThreads = 256;              // threads of a per-piece kernel: 8 warps, one sub-tile each at a time
-constexpr int kPieceSubTiles = kFlatPiece / kSub;  // 64 sub-tiles of 256 elements per piece
+constexpr int kPhasePiece = 8192;                  // elements of a row one CTA of a per-piece phase kernel covers
+constexpr int kPieceSubTiles = kPhasePiece / kSub;  // 32 sub-tiles of 256 elements: 4 per warp, two in flight at a time
+static_assert(kSub * kMaxSubTiles / kPhasePiece <= kFullMaxParts, "FullRow::part has one entry per phase piece");
 
 __device__ __forceinline__ bool row_wants_topp(const RowPlan &rp) { return rp.top_p < 1.0f && rp.top_p > 0.f; }
 
@@ -109,7 +111,7 @@ __global__ void __launch_bounds__(kFullThreads) k_full_exp(const __grid_constant
     const RowPlan *rpp = a.plans + row;
     if (!(__ldg(&rpp->temperature) > 0.f)) return;  // greedy with penalties: the stream pass found the token
     const int n = a.vocab;
-    const int begin = blockIdx.x * kFlatPiece;
+    const int begin = blockIdx.x * kPhasePiece;
     if (begin >= n) return;
     const FullRow *fr = ws.rows + fi;
     const float top_p = __ldg(&rpp->top_p);
@@ -124,40 +126,51 @@ __global__ void __launch_bounds__(kFullThreads) k_full_exp(const __grid_constant
         for (int b = tid; b < kHistBins; b += kFullThreads) { hcnt[b] = 0u; hmass[b] = 0u; }
         __syncthreads();
     }
-    for (int st = warp; st < kPieceSubTiles; st += kFullThreads / 32) {
-        const int base = begin + st * kSub + lane * 8;
-        if (begin + st * kSub >= n) break;
-        float x[8];
-        if (base + 8 <= n) {
-            const float4 q0 = __ldcg((const float4 *)(e + base)), q1 = __ldcg((const float4 *)(e + base + 4));
-            x[0] = q0.x; x[1] = q0.y; x[2] = q0.z; x[3] = q0.w; x[4] = q1.x; x[5] = q1.y; x[6] = q1.z; x[7] = q1.w;
-        } else {
+    constexpr int W = kFullThreads / 32;
+    for (int st0 = warp; st0 < kPieceSubTiles; st0 += 2 * W) {
+        float x[2][8];
 #pragma unroll
-            for (int j = 0; j < 8; j++) x[j] = base + j < n ? __ldcg(e + base + j) : -CUDART_INF_F;
-        }
-        float acc = 0.f;
-        int low = 0;
+        for (int h = 0; h < 2; h++) {
+            const int st = st0 + h * W;
+            const int base = begin + st * kSub + lane * 8;
+            if (st < kPieceSubTiles && base + 8 <= n) {
+                const float4 q0 = __ldcg((const float4 *)(e + base)), q1 = __ldcg((const float4 *)(e + base + 4));
+                x[h][0] = q0.x; x[h][1] = q0.y; x[h][2] = q0.z; x[h][3] = q0.w;
+                x[h][4] = q1.x; x[h][5] = q1.y; x[h][6] = q1.z; x[h][7] = q1.w;
+            } else {
 #pragma unroll
-        for (int j = 0; j < 8; j++) {
-            float v = 0.f;
-            if (base + j < n) v = uniform ? up : expf(__fsub_rn(x[j], mx));
-            x[j] = v;
-            acc += v > 0.f ? v : 0.f;
-            if (want_hist && v > 0.f) {
-                const uint32_t eb = __float_as_uint(v);
-                const unsigned bin = bin_of(eb);
-                if (bin == 0u) low++;
-                else { atomicAdd(&hcnt[bin], 1u); atomicAdd(&hmass[bin], ((eb & 0x7FFFFFu) | 0x800000u) >> 12); }
+                for (int j = 0; j < 8; j++) x[h][j] = (st < kPieceSubTiles && base + j < n) ? __ldcg(e + base + j) : -CUDART_INF_F;
             }
         }
-        if (want_hist) {
-            low = __reduce_add_sync(0xFFFFFFFFu, low);
-            if (low && lane == 0) { atomicAdd(&hcnt[0], (unsigned)low); atomicAdd(&hmass[0], (unsigned)low * 0xFFFu); }
-        }
-        if (base < n) store8(e, base, n, x);
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
-        if (lane == 0) ew->sums[(begin >> 8) + st] = acc;
+        for (int h = 0; h < 2; h++) {
+            const int st = st0 + h * W;
+            const int base = begin + st * kSub + lane * 8;
+            if (st >= kPieceSubTiles || begin + st * kSub >= n) continue;  // the same for the whole warp
+            float acc = 0.f;
+            int low = 0;
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                float v = 0.f;
+                if (base + j < n) v = uniform ? up : expf(__fsub_rn(x[h][j], mx));
+                x[h][j] = v;
+                acc += v > 0.f ? v : 0.f;
+                if (want_hist && v > 0.f) {
+                    const uint32_t eb = __float_as_uint(v);
+                    const unsigned bin = bin_of(eb);
+                    if (bin == 0u) low++;
+                    else { atomicAdd(&hcnt[bin], 1u); atomicAdd(&hmass[bin], ((eb & 0x7FFFFFu) | 0x800000u) >> 12); }
+                }
+            }
+            if (want_hist) {
+                low = __reduce_add_sync(0xFFFFFFFFu, low);
+                if (low && lane == 0) { atomicAdd(&hcnt[0], (unsigned)low); atomicAdd(&hmass[0], (unsigned)low * 0xFFFu); }
+            }
+            if (base < n) store8(e, base, n, x[h]);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
+            if (lane == 0) ew->sums[(begin >> 8) + st] = acc;
+        }
     }
     if (want_hist) {
         __syncthreads();
@@ -178,23 +191,31 @@ __global__ void __launch_bounds__(kFullThreads) k_full_psums(const __grid_consta
     const RowPlan *rpp = a.plans + row;
     if (!(__ldg(&rpp->temperature) > 0.f)) return;
     const int n = a.vocab;
-    const int begin = blockIdx.x * kFlatPiece;
+    const int begin = blockIdx.x * kPhasePiece;
     if (begin >= n) return;
     const FullRow *fr = ws.rows + fi;
     if (fr->redo) return;
     const ProvFinal pf{ws.e + (size_t)fi * ws.e_stride, fr->dist, nullptr};
     Emul2Work *ew = ws.ew + fi;
-    for (int st = warp; st < kPieceSubTiles; st += kFullThreads / 32) {
-        const int base = begin + st * kSub + lane * 8;
-        if (begin + st * kSub >= n) break;
-        float x[8];
-        pf.reload(base, n, x);
-        float acc = 0.f;
+    constexpr int W = kFullThreads / 32;
+    for (int st0 = warp; st0 < kPieceSubTiles; st0 += 2 * W) {
+        float x[2][8];
 #pragma unroll
-        for (int j = 0; j < 8; j++) acc += x[j] > 0.f ? x[j] : 0.f;
+        for (int h = 0; h < 2; h++) {
+            const int st = st0 + h * W;
+            pf.reload(st < kPieceSubTiles ? begin + st * kSub + lane * 8 : n, n, x[h]);
+        }
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
-        if (lane == 0) ew->sums[(begin >> 8) + st] = acc;
+        for (int h = 0; h < 2; h++) {
+            const int st = st0 + h * W;
+            if (st >= kPieceSubTiles || begin + st * kSub >= n) continue;
+            float acc = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; j++) acc += x[h][j] > 0.f ? x[h][j] : 0.f;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
+            if (lane == 0) ew->sums[(begin >> 8) + st] = acc;
+        }
     }
 }
 
@@ -220,42 +241,55 @@ __global__ void __launch_bounds__(kFullThreads) k_full_comp(const __grid_constan
     const RowPlan *rpp = a.plans + row;
     if (!(__ldg(&rpp->temperature) > 0.f)) return;
     const int n = a.vocab;
-    const int begin = blockIdx.x * kFlatPiece;
+    const int begin = blockIdx.x * kPhasePiece;
     if (begin >= n) return;
     const FullRow *fr = ws.rows + fi;
     if (fr->redo) return;
     const float *e = ws.e + (size_t)fi * ws.e_stride;
     const ProvFinal pf{e, fr->dist, nullptr};
     Emul2Work *ew = ws.ew + fi;
-    for (int st = warp; st < kPieceSubTiles; st += kFullThreads / 32) {
-        const int t = (begin >> 8) + st;
-        const int base = t * kSub + lane * 8;
-        if (t * kSub >= n) break;
-        int a0 = 0, a1 = 0;
-        if (!(ew->sums[t] == 0.f)) {
-            float x[8];
+    constexpr int W = kFullThreads / 32;
+    for (int st0 = warp; st0 < kPieceSubTiles; st0 += 2 * W) {
+        float x[2][8];
+        bool live[2];
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int st = st0 + h * W;
+            const int t = (begin >> 8) + st;
+            live[h] = st < kPieceSubTiles && t * kSub < n && !(ew->sums[t] == 0.f);  // nothing to add: composite 0
+            const int base = t * kSub + lane * 8;
+            if (!live[h]) continue;
             if (FINAL) {
-                pf.reload(base, n, x);
+                pf.reload(base, n, x[h]);
             } else {
                 SrcScratch sc{e, 1.f, false};
-                if (base < n) sc.get8(base, n, x);
+                if (base < n) sc.get8(base, n, x[h]);
 #pragma unroll
                 for (int j = 0; j < 8; j++)
-                    if (base + j >= n) x[j] = 0.f;
-            }
-            const int g = ew->guess[t];
-            subtile_composite<false>(x, g, a0, a1);
-            const int xsl = ew->xslot[t];
-            if (xsl) {
-                CrossSlot &cs = ew->xs[xsl - 1];
-                int l0, l1, h0, h1;
-                lane_composite(x, g, l0, l1);
-                lane_composite(x, g + 1, h0, h1);
-                cs.lo[lane][0] = l0; cs.lo[lane][1] = l1;
-                cs.hi[lane][0] = h0; cs.hi[lane][1] = h1;
+                    if (base + j >= n) x[h][j] = 0.f;
             }
         }
-        if (lane == 0) { ew->comp[t][0] = a0; ew->comp[t][1] = a1; }
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int st = st0 + h * W;
+            const int t = (begin >> 8) + st;
+            if (st >= kPieceSubTiles || t * kSub >= n) continue;
+            int a0 = 0, a1 = 0;
+            if (live[h]) {
+                const int g = ew->guess[t];
+                subtile_composite<false>(x[h], g, a0, a1);
+                const int xsl = ew->xslot[t];
+                if (xsl) {
+                    CrossSlot &cs = ew->xs[xsl - 1];
+                    int l0, l1, h0, h1;
+                    lane_composite(x[h], g, l0, l1);
+                    lane_composite(x[h], g + 1, h0, h1);
+                    cs.lo[lane][0] = l0; cs.lo[lane][1] = l1;
+                    cs.hi[lane][0] = h0; cs.hi[lane][1] = h1;
+                }
+            }
+            if (lane == 0) { ew->comp[t][0] = a0; ew->comp[t][1] = a1; }
+        }
     }
 }
 
@@ -288,6 +322,87 @@ struct ProvE {
     }
 };
 
+// ---- a shared-memory cache of the sub-tiles a walk will replay ------------------------------------------
+// The walk (emul2_walk) consumes most sub-tiles by their composites and touches elements only where
+// the running sum changes binade, where a guess was off by one sub-tile, or where the target is met.
+// Those places are known in advance from the fp64 prefix of the sub-tile sums: the sub-tiles with a
+// crossing slot and their neighbours, the first sub-tiles (the sum climbs through many binades
+// there), and the sub-tile in which the prefix reaches the target.  All warps copy them into shared
+// memory before the one walking warp starts, so that its replays do not wait on L2.
+constexpr int kXcEntries = 64;
+struct XCache {
+    int of[kMaxSubTiles];      // 0: not cached, else 1 + entry
+    int tile[kXcEntries];
+    int n;
+    int hit_tile;
+    double wsum[32];
+};
+
+template <class P>
+struct ProvCached {
+    P base;
+    const float *xc;
+    const int *of;
+    __device__ __forceinline__ void load(int b, int n, float x[8]) const { reload(b, n, x); }
+    __device__ __forceinline__ void reload(int b, int n, float x[8]) const
+    {
+        const int idx = of[b >> 8];
+        if (idx > 0) {
+            const float4 *q = (const float4 *)(xc + (size_t)(idx - 1) * kSub + (b & (kSub - 1)));
+            const float4 q0 = q[0], q1 = q[1];
+            x[0] = q0.x; x[1] = q0.y; x[2] = q0.z; x[3] = q0.w; x[4] = q1.x; x[5] = q1.y; x[6] = q1.z; x[7] = q1.w;
+        } else {
+            base.reload(b, n, x);
+        }
+    }
+};
+
+// Fills the cache for the sequence behind `pv` (n elements, nsub sub-tiles, summaries in wk).  With
+// has_target the sub-tile in which the fp64 prefix of the sums reaches `target` is cached too.
+// All kThreads threads call it.
+template <class P>
+__device__ void build_xcache(XCache *xc, float *xdata, const Emul2Work *wk, const P &pv, int n, int nsub, float target,
+                             bool has_target)
+{
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (int t = tid; t < kMaxSubTiles; t += kThreads) xc->of[t] = 0;
+    if (tid == 0) { xc->n = 0; xc->hit_tile = INT_MAX; }
+    __syncthreads();
+    if (has_target) {
+        double v = tid < nsub ? (double)wk->sums[tid] : 0.0, inc = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const double t = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+            if (lane >= o) inc += t;
+        }
+        if (lane == 31) xc->wsum[warp] = inc;
+        __syncthreads();
+        double before = 0.0;
+        for (int w = 0; w < warp; w++) before += xc->wsum[w];
+        if (tid < nsub && before + inc >= (double)target * (1.0 - 1e-5)) atomicMin(&xc->hit_tile, tid);
+        __syncthreads();
+    }
+    auto mark = [&](int t) {
+        if (t >= 0 && t < nsub && atomicCAS(&xc->of[t], 0, -1) == 0) {
+            const int e = atomicAdd(&xc->n, 1);
+            if (e < kXcEntries) { xc->tile[e] = t; xc->of[t] = e + 1; } else { xc->of[t] = 0; }
+        }
+    };
+    if (tid < 4) mark(tid);
+    if (tid < nsub && wk->xslot[tid]) { mark(tid - 1); mark(tid); mark(tid + 1); mark(tid + 2); }
+    if (has_target && tid == 0 && xc->hit_tile != INT_MAX) { mark(xc->hit_tile - 1); mark(xc->hit_tile); mark(xc->hit_tile + 1); }
+    __syncthreads();
+    const int ne = min(xc->n, kXcEntries);
+    for (int e = warp; e < ne; e += kThreads / 32) {
+        float x[8];
+        pv.reload(xc->tile[e] * kSub + lane * 8, n, x);
+        float4 *q = (float4 *)(xdata + (size_t)e * kSub + lane * 8);
+        q[0] = make_float4(x[0], x[1], x[2], x[3]);
+        q[1] = make_float4(x[4], x[5], x[6], x[7]);
+    }
+    __syncthreads();
+}
+
 // ---- walk: exact softmax sum, min-p, top-p plan ----------------------------------------------------------
 // One 1024-thread CTA per full row.  The top-p plan is steps (1)-(3) of topp_cut (stg_rowdist.cuh):
 // the bins that bound the nucleus, where every bin starts in the bin-ordered candidate list, the
@@ -297,12 +412,15 @@ __global__ void __launch_bounds__(kThreads, 1) k_full_walk(const __grid_constant
 {
     extern __shared__ __align__(16) unsigned char arena[];
     __shared__ RowCtl rc;
+    __shared__ XCache xcache;
     const int fi = blockIdx.x, tid = threadIdx.x;
     const int row = full_items[fi].row;
     const RowPlan rp = a.plans[row];
     FullRow *fr = ws.rows + fi;
     const int n = a.vocab;
     const unsigned long long mk = fr->maxkey;
+    unsigned long long *tk = a.phase_ticks ? a.phase_ticks + (int64_t)fi * 32 : nullptr;
+    tick(tk, 0);
     if (!(rp.temperature > 0.f)) {
         // GreedyWithHistoryPenalties (Sampler.cs:421-437): the arg-max of the adjusted logits
         if (tid == 0) {
@@ -346,12 +464,18 @@ __global__ void __launch_bounds__(kThreads, 1) k_full_walk(const __grid_constant
     } else {
         d.max_x = key_val(mk);
         load_work(wk2, ws.ew + fi);
+        tick(tk, 1);
         const int nsub = (n + kSub - 1) / kSub;
+        const ProvE pe{e};
+        float *xdata = (float *)(arena + kOffKeys);  // the key region is free in this kernel
+        build_xcache(&xcache, xdata, wk2, pe, n, nsub, 0.f, false);
+        tick(tk, 2);
         if (tid < 32) {
-            const ProvE pe{e};
-            emul2_walk<ProvE, false, false>(&rc.em2, wk2, pe, n, nsub, 0.f, false, nullptr, nullptr);
+            const ProvCached<ProvE> pc{pe, xdata, xcache.of};
+            emul2_walk<ProvCached<ProvE>, false, false>(&rc.em2, wk2, pc, n, nsub, 0.f, false, nullptr, tk ? tk + 24 : nullptr);
         }
         __syncthreads();
+        tick(tk, 3);
         sum = rc.em2.s;
         if (sum > 0.f && sum != 1.0f) { d.flags |= kDistScale1; d.inv1 = __fdiv_rn(1.0f, sum); }
     }
@@ -468,6 +592,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_full_walk(const __grid_constant
         for (int t = tid; t < kHistBins / 32; t += kThreads) g_flags[t] = rc.flag_bits[t];
         if (tid == 0) { fr->c_lo = c_lo; fr->bound = rc.bound; }
     }
+    tick(tk, 4);
     if (tid == 0) { fr->dist = d; fr->sum = sum; }
 }
 
@@ -484,14 +609,14 @@ __global__ void __launch_bounds__(kFullThreads) k_full_scatter(const __grid_cons
     const RowPlan *rpp = a.plans + row;
     if (!(__ldg(&rpp->temperature) > 0.f)) return;
     const int n = a.vocab;
-    const int begin = blockIdx.x * kFlatPiece;
+    const int begin = blockIdx.x * kPhasePiece;
     if (begin >= n) return;
     FullRow *fr = ws.rows + fi;
     const RowDist d = fr->dist;
     const float top_p = __ldg(&rpp->top_p);
     const bool want_topp = top_p < 1.0f && top_p > 0.f;
     const float *e = ws.e + (size_t)fi * ws.e_stride;
-    const int end = min(n, begin + kFlatPiece);
+    const int end = min(n, begin + kPhasePiece);
     if (!want_topp) {
         double part = 0.0;
         for (int base = begin + tid * 8; base < end; base += kFullThreads * 8) {
@@ -580,10 +705,12 @@ __global__ void __launch_bounds__(kThreads, 1) k_full_cut(const __grid_constant_
     const float *scratch = ws.e + (size_t)fi * ws.e_stride;
     const bool want_topp = row_wants_topp(rp);
     double sum3 = 0.0;
+    unsigned long long *tk = a.phase_ticks ? a.phase_ticks + (int64_t)fi * 32 : nullptr;
+    tick(tk, 8);
     if (tid == 0) sh_flags = 0u;
     __syncthreads();
     if (!want_topp) {
-        const int pieces = (n + kFlatPiece - 1) / kFlatPiece;
+        const int pieces = (n + kPhasePiece - 1) / kPhasePiece;
         for (int p = 0; p < pieces; p++) sum3 += fr->part[p];  // fixed order: deterministic
     } else {
         uint32_t *skeys = (uint32_t *)(arena + kOffKeys);
@@ -619,6 +746,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_full_cut(const __grid_constant_
             for (int t = tid; t < nc; t += kThreads) skeys[t] = __ldcg(gkeys + t);
             __syncthreads();
         }
+        tick(tk, 9);
+        if (tk && tid == 0) { tk[20] = (unsigned long long)nc; tk[21] = 0; }
         if (nc > 0) {
             // (5) a sub-tile of the emulated sum is replayed whole, so every bin that shares a
             // sub-tile with a flagged bin has to be sorted with it
@@ -648,7 +777,10 @@ __global__ void __launch_bounds__(kThreads, 1) k_full_cut(const __grid_constant_
             int hit = -1;
             float cum = 0.f;
             bool sorted_all = uniform;  // all keys equal: any order is sorted
+            tick(tk, 10);
+            if (tk && tid == 0) tk[22] = (unsigned long long)rc->n_dirty;
             for (int pass = 0; pass < 64; pass++) {
+                if (tk && tid == 0) tk[21] = (unsigned long long)(pass + 1);
                 if (!sorted_all && (rc->give_up || pass == 63)) {
                     const int p2 = pow2_ceil(max(nc, 2));
                     for (int t = nc + tid; t < p2; t += kThreads) keys[t] = 0u;
@@ -665,6 +797,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_full_cut(const __grid_constant_
                     if (tid == 0) rc->n_dirty = 0;
                 }
                 __syncthreads();
+                if (pass == 0) tick(tk, 11);
                 if (!sorted_all) {
                     for (int t = tid; t < kMaxSubTiles; t += kThreads) replay_ok[t] = 1;
                     __syncthreads();
@@ -680,7 +813,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_full_cut(const __grid_constant_
                 ProvKeys pk{keys, keys != skeys};
                 if (nc <= kSub * kMaxSubTiles) {
                     hit = emul_scan2<ProvKeys, false, true, 4>(&rc->em2, wk2, pk, nc, rp.top_p, true, &cum,
-                                                            sorted_all ? nullptr : replay_ok, nullptr,
+                                                            sorted_all ? nullptr : replay_ok, tk ? tk + 24 : nullptr,
                                                             keys != skeys ? arena + kOffKeys : nullptr, kSortCap * 4);
                 } else {
                     if (!sorted_all) { if (tid == 0) rc->give_up = 1; __syncthreads(); continue; }
@@ -700,6 +833,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_full_cut(const __grid_constant_
                 }
                 __syncthreads();
             }
+            tick(tk, 12);
             if (hit < 0 && nc < my_surv) {
                 // the bound was too tight (the sum never reached top_p although survivors remain
                 // below it): the self-contained row kernel redoes the row
@@ -708,6 +842,9 @@ __global__ void __launch_bounds__(kThreads, 1) k_full_cut(const __grid_constant_
             }
             const int last = hit >= 0 ? hit : nc - 1;
             const float tstar = hit >= 0 ? __uint_as_float(keys[last]) : 0.f;
+            if (hit >= 0 && nc <= kSub * kMaxSubTiles && tid == 0 &&
+                (cum - rp.top_p <= kNearTol || rp.top_p - rc->em2.hit_before <= kNearTol))
+                sh_flags |= kFlagNearCut;  // a last-bit difference in exp could move the cut by a token
             int keep = 0, all = 0;
             double part = 0.0;
             for (int t = tid; t < nc; t += kThreads) {
@@ -731,6 +868,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_full_cut(const __grid_constant_
     const float s3 = (float)sum3;
     if (s3 > 0.f && s3 != 1.0f) { d.flags |= kDistScale3; d.inv3 = __fdiv_rn(1.0f, s3); }
     __syncthreads();
+    tick(tk, 13);
     if (tid == 0) {
         fr->dist = d;
         fr->flags |= sh_flags;
@@ -748,6 +886,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_full_draw(const __grid_constant
 {
     extern __shared__ __align__(16) unsigned char arena[];
     __shared__ Emul2Ctl ctl;
+    __shared__ XCache xcache;
     const int fi = blockIdx.x, tid = threadIdx.x;
     const int row = full_items[fi].row;
     const RowPlan rp = a.plans[row];
@@ -756,29 +895,41 @@ __global__ void __launch_bounds__(kThreads, 1) k_full_draw(const __grid_constant
     if (fr->redo) return;
     const int n = a.vocab;
     Emul2Work *wk2 = (Emul2Work *)arena;
+    float *xdata = (float *)(arena + sizeof(Emul2Work));
+    unsigned long long *tk = a.phase_ticks ? a.phase_ticks + (int64_t)fi * 32 : nullptr;
+    tick(tk, 16);
     load_work(wk2, ws.ew + fi);
+    tick(tk, 17);
     const float *e = ws.e + (size_t)fi * ws.e_stride;
     const RowDist d = fr->dist;
     const float u = a.uniforms ? __ldg(a.uniforms + row) : 0.5f;
     const int nsub = (n + kSub - 1) / kSub;
+    const ProvFinal pf{e, d, nullptr};
+    build_xcache(&xcache, xdata, wk2, pf, n, nsub, u, true);
+    tick(tk, 18);
     if (tid < 32) {
-        const ProvFinal pf{e, d, nullptr};
-        emul2_walk<ProvFinal, false, false>(&ctl, wk2, pf, n, nsub, u, true, nullptr, nullptr);
+        const ProvCached<ProvFinal> pc{pf, xdata, xcache.of};
+        emul2_walk<ProvCached<ProvFinal>, false, false>(&ctl, wk2, pc, n, nsub, u, true, nullptr, nullptr);
     }
     __syncthreads();
+    tick(tk, 19);
     if (tid == 0) {
         uint32_t fl = kPathFull | fr->flags;
         if (d.flags & kDistUniform) fl |= (1u << 6);
         int tok = ctl.hit;
         if (tok < 0) { tok = n - 1; fl |= (1u << 5); }
+        else if (u > 0.f && (u - ctl.hit_before <= kNearTol || ctl.s - u <= kNearTol)) fl |= kFlagNearBoundary;
         a.tokens[row] = tok;
         if (a.token_probs) a.token_probs[row] = eval_p3(__ldcg(e + tok), tok, d);
         if (a.row_flags) a.row_flags[row] = fl;
+        count_row_flags(a.counters, fl);
     }
 }
 
+constexpr size_t kDrawSmem = sizeof(Emul2Work) + (size_t)kXcEntries * kSub * 4;
+
 // ---- launchers ---------------------------------------------------------------------------------------------
-static dim3 piece_grid(const SampleArgs &a, int n_full) { return dim3((unsigned)((a.vocab + kFlatPiece - 1) / kFlatPiece), (unsigned)n_full); }
+static dim3 piece_grid(const SampleArgs &a, int n_full) { return dim3((unsigned)((a.vocab + kPhasePiece - 1) / kPhasePiece), (unsigned)n_full); }
 
 cudaError_t launch_full_prep(const SampleArgs &a, const FullWs &ws, cudaStream_t stream)
 {
@@ -792,25 +943,35 @@ cudaError_t launch_full_prep(const SampleArgs &a, const FullWs &ws, cudaStream_t
 
 // everything behind the HBM pass for the `n_full` full rows listed in `full_rows` (device array)
 cudaError_t launch_full_rest(const SampleArgs &a, const FullWs &ws, const WorkItem *full_items, int n_full, int *launches,
-                             cudaStream_t stream)
+                             KernelTimer *kt, cudaStream_t stream)
 {
     const dim3 pg = piece_grid(a, n_full);
     cudaError_t e = ensure_dynamic_smem((const void *)k_full_walk, kRowArenaBytes);
     if (e == cudaSuccess) e = ensure_dynamic_smem((const void *)k_full_cut, kRowArenaBytes);
-    if (e == cudaSuccess) e = ensure_dynamic_smem((const void *)k_full_draw, sizeof(Emul2Work));
+    if (e == cudaSuccess) e = ensure_dynamic_smem((const void *)k_full_draw, kDrawSmem);
     if (e != cudaSuccess) return e;
     k_full_exp<<<pg, kFullThreads, 0, stream>>>(a, ws, full_items);
+    kt->mark("full_exp", stream);
     k_full_scan<<<n_full, kThreads, 0, stream>>>(a, ws, full_items);
+    kt->mark("full_scan", stream);
     k_full_comp<false><<<pg, kFullThreads, 0, stream>>>(a, ws, full_items);
+    kt->mark("full_comp", stream);
     k_full_walk<<<n_full, kThreads, kRowArenaBytes, stream>>>(a, ws, full_items);
+    kt->mark("full_walk", stream);
     k_full_scatter<<<pg, kFullThreads, 0, stream>>>(a, ws, full_items);
+    kt->mark("full_scatter", stream);
     k_full_cut<<<n_full, kThreads, kRowArenaBytes, stream>>>(a, ws, full_items);
+    kt->mark("full_cut", stream);
     *launches += 6;
     if (a.mode == 0) {
         k_full_psums<<<pg, kFullThreads, 0, stream>>>(a, ws, full_items);
+        kt->mark("full_psums", stream);
         k_full_scan<<<n_full, kThreads, 0, stream>>>(a, ws, full_items);
+        kt->mark("full_scan2", stream);
         k_full_comp<true><<<pg, kFullThreads, 0, stream>>>(a, ws, full_items);
-        k_full_draw<<<n_full, kThreads, sizeof(Emul2Work), stream>>>(a, ws, full_items);
+        kt->mark("full_comp2", stream);
+        k_full_draw<<<n_full, kThreads, kDrawSmem, stream>>>(a, ws, full_items);
+        kt->mark("full_draw", stream);
         *launches += 4;
     }
     return cudaGetLastError();

@@ -8,6 +8,7 @@
 #include <vector>
 
 #include "../../../include/stingray_sampler.h"
+#include "stg_launch.h"
 #include "stg_types.h"
 
 namespace stg {
@@ -64,6 +65,7 @@ struct StgSampler_ {
     stg::DevBuf st_hist, st_bias_ids, st_bias_vals, st_uniforms, st_mask, st_logits;
     stg::DevBuf o_tokens, o_probs, o_flags, o_topk_ids, o_topk_vals, o_topk_probs, o_pairs;
     stg::DevBuf ticks;                   // diagnostic phase stamps (STG_PHASE_TICKS=1)
+    stg::KernelTimer kt;                 // diagnostic events between kernels (STG_KERNEL_TIMES=1)
     int ticks_items = 0;
     stg::DevBuf sp_draft, sp_uniforms, sp_accepted, sp_correction, sp_aprobs, sp_flags, sp_rowstats;
     int64_t escratch_stride = 0, key_stride = 0;

@@ -59,6 +59,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_shard_finish(const __grid_const
         a.tokens[row] = ish.fout.token;
         if (a.token_probs) a.token_probs[row] = ish.fout.prob;
         if (a.row_flags) a.row_flags[row] = ish.fout.flags;
+        count_row_flags(a.counters, ish.fout.flags);
     }
 }
 

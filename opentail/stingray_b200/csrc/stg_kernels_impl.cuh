@@ -203,6 +203,7 @@ __device__ void run_chunk(const SampleArgs &a, int row, int chunk, int item, Sel
         a.tokens[row] = ish->fout.token;
         if (a.token_probs) a.token_probs[row] = ish->fout.prob;
         if (a.row_flags) a.row_flags[row] = ish->fout.flags;
+        count_row_flags(a.counters, ish->fout.flags);
     }
     tick(tk, 3);
     __syncthreads();

@@ -27,6 +27,23 @@ inline cudaError_t ensure_dynamic_smem(const void *fn, size_t bytes)
     return e;
 }
 
+// Diagnostic: CUDA events recorded between the kernels of a step (STG_KERNEL_TIMES=1), read back by
+// stg_debug_kernel_times.  mark(name) stamps the end of the kernel(s) launched since the last mark.
+struct KernelTimer {
+    static constexpr int kMax = 32;
+    cudaEvent_t ev[kMax + 1] = {};
+    const char *name[kMax] = {};
+    int n = 0;
+    bool on = false;
+    void begin(cudaStream_t s) { n = 0; if (on) cudaEventRecord(ev[0], s); }
+    void mark(const char *what, cudaStream_t s)
+    {
+        if (!on || n >= kMax) return;
+        name[n] = what;
+        cudaEventRecord(ev[++n], s);
+    }
+};
+
 // shared memory a row-type work item needs: sort keys + exp-value histogram
 constexpr size_t kRowArenaBytes = 211968;  // layout in stg_rowdist.cuh (checked there)
 

@@ -1226,6 +1226,9 @@ static __device__ __noinline__ double topp_cut(RowCtl *rc, const RowPlan &rp, in
             // so its last key is not its smallest: the threshold is simply zero.
             const int last = hit >= 0 ? hit : nc - 1;
             const float tstar = hit >= 0 ? __uint_as_float(keys[last]) : 0.f;
+            if (hit >= 0 && nc <= kSub * kMaxSubTiles && tid == 0 &&
+                (cum - rp.top_p <= kNearTol || rp.top_p - rc->em2.hit_before <= kNearTol))
+                *flags_out |= kFlagNearCut;  // a last-bit difference in exp could move the cut by a token
             // ties at the cut: the kept ones are a prefix (by token id) of the equal probabilities
             int keep = 0, all = 0;
             double part = 0.0;
@@ -1508,13 +1511,15 @@ static __device__ void run_row(const SampleArgs &a, int row, int item, SelCtl *s
         hit = emul_any<ProvFinal, false>(&rc.em, &rc.em2, wk2, pf, n, u, true, &cum, tk ? tk + 20 : nullptr);
     }
     if (tid == 0) {
-        uint32_t fl = kPathFull | sh_flags;
+        uint32_t fl = kPathFull | sh_flags | (a.redo_flags ? kFlagFlatRedo : 0u);  // redone after the flat step gave up
         if (rc.dist.flags & kDistUniform) fl |= (1u << 6);
         int tok = hit;
         if (hit < 0) { tok = n - 1; fl |= (1u << 5); }
+        else if (n <= kSub * kMaxSubTiles && u > 0.f && (u - rc.em2.hit_before <= kNearTol || cum - u <= kNearTol)) fl |= kFlagNearBoundary;
         a.tokens[row] = tok;
         if (a.token_probs) a.token_probs[row] = eval_p3(__ldcg(scratch + tok), tok, rc.dist);
         if (a.row_flags) a.row_flags[row] = fl;
+        count_row_flags(a.counters, fl);
     }
     tick(tk, 10);
     __syncthreads();

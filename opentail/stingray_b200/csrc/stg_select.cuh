@@ -1039,8 +1039,14 @@ static __device__ void finish_topk_draw(Sel &s, const RowPlan &rp, float uniform
         float pr = probs[0];
         uint32_t fl = kPathTopK | (1u << 5);
         for (int t = 0; t < count; t++) {
+            const float prev = cacc;
             cacc = __fadd_rn(cacc, probs[t]);
-            if (r <= cacc && ids[t] >= 0) { tok = ids[t]; pr = probs[t]; fl = kPathTopK; break; }
+            if (r <= cacc && ids[t] >= 0) {
+                tok = ids[t]; pr = probs[t]; fl = kPathTopK;
+                // the draw within 1e-6 (of the kept mass) of the step below or above the token
+                if (r - prev <= kNearTol * kept || cacc - r <= kNearTol * kept) fl |= kFlagNearBoundary;
+                break;
+            }
         }
         out_sh->token = tok;
         out_sh->prob = kept > 0.f ? pr / kept : 0.f;

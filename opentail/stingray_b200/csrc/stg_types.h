@@ -14,7 +14,13 @@ constexpr int kSortCap = 32768;         // top-p candidate keys sorted in shared
 constexpr int kHistBins = 4096;         // probability histogram bins (exponent + 4 mantissa bits)
 constexpr int kMaxOverride = 2048;      // history + bias entries per row on the full-vocabulary path
 
-constexpr uint32_t kFlagFlatRedo = 1u << 8;  // row flag: the optimistic bound failed, the row was read twice
+constexpr uint32_t kFlagFlatRedo = 1u << 8;       // row flag: an optimistic bound failed, the row was processed twice
+constexpr uint32_t kFlagNearBoundary = 1u << 3;   // row flag: the draw lies within kNearTol of a CDF step at the token
+constexpr uint32_t kFlagNearCut = 1u << 10;       // row flag: the top-p running sum passes top_p within kNearTol
+constexpr float kNearTol = 1e-6f;
+
+// device event counters of a handle (read by stg_get_stats)
+enum { kCtrBoundary = 0, kCtrTie, kCtrFallback, kCtrWide, kCtrReread, kCtrNearCut, kCtrMasked, kCtrCount = 8 };
 
 enum Path : int32_t {
     kPathGreedy = 0,        // Sampler.Greedy
@@ -110,11 +116,25 @@ struct SampleArgs {
     int32_t vocab_offset;            // vocabulary-sharded mode: global id of local column 0
     int32_t shard_mode;              // 0 off, 1 select only (write candidates), 2 finish from gather
     int32_t n_ranks;
+    unsigned long long *counters;    // kCtr* event counters, never null
     const int32_t *redo_flags;       // row kernel as the flat step's second chance: only rows whose flag
     int32_t redo_stride;             // redo_flags[flat_full * redo_stride] is set are run; null: every row item
 };
 
 #ifdef __CUDACC__
+// counts the reportable events of a finished row (called by the one thread that writes its flags)
+__device__ __forceinline__ void count_row_flags(unsigned long long *ctr, uint32_t fl)
+{
+    if (ctr == nullptr || (fl & ~7u) == 0u) return;
+    if (fl & kFlagNearBoundary) atomicAdd(ctr + kCtrBoundary, 1ull);
+    if (fl & (1u << 4)) atomicAdd(ctr + kCtrTie, 1ull);
+    if (fl & (1u << 5)) atomicAdd(ctr + kCtrFallback, 1ull);
+    if (fl & (1u << 6)) atomicAdd(ctr + kCtrMasked, 1ull);
+    if (fl & (1u << 7)) atomicAdd(ctr + kCtrWide, 1ull);
+    if (fl & kFlagFlatRedo) atomicAdd(ctr + kCtrReread, 1ull);
+    if (fl & kFlagNearCut) atomicAdd(ctr + kCtrNearCut, 1ull);
+}
+
 // diagnostic time stamp (nanoseconds) of phase k of the current work item; a no-op when disabled
 __device__ __forceinline__ void tick(unsigned long long *t, int k)
 {

@@ -26,7 +26,7 @@ def test_header_symbols_are_exported():
     assert declared == set(N.EXPORTS)
     for name in declared:
         assert hasattr(lib, name), f"{name} is declared but not exported"
-    assert lib.stg_abi_version() == 1
+    assert lib.stg_abi_version() == 2
 
 
 def test_struct_layouts_match_the_header():
@@ -34,7 +34,7 @@ def test_struct_layouts_match_the_header():
     assert C.sizeof(N.StgRowParams) == 32
     assert C.sizeof(N.StgConfig) == 36
     assert C.sizeof(N.StgSampleBatch) == 168
-    assert C.sizeof(N.StgStats) == 64
+    assert C.sizeof(N.StgStats) == 120
     from opentail.stingray_b200.sampler import PARAMS_DTYPE
 
     assert PARAMS_DTYPE.itemsize == C.sizeof(N.StgRowParams)
