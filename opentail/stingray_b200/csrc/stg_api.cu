@@ -421,7 +421,8 @@ int run_batch(StgHandle h, const StgSampleBatch *b, const BatchExtra &x, void *s
     a.cand_count = (int32_t *)h->cand_count.p;
     a.tickets = (uint32_t *)h->tickets.p;
     a.work_counter = (uint32_t *)h->work_counter.p;
-    a.counters = (unsigned long long *)h->work_counter.p + 16;  // bytes 128..191 of the same small buffer
+    a.counters = (unsigned long long *)h->work_counter.p + 16;
+    a.debug_bits = getenv("STG_DEBUG_BITS") ? atoi(getenv("STG_DEBUG_BITS")) : 0;  // bytes 128..191 of the same small buffer
     a.phase_ticks = (unsigned long long *)h->ticks.p;
     h->ticks_items = (int)pl.items.size();
     a.escratch = (float *)h->escratch.p;

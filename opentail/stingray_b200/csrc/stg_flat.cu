@@ -246,9 +246,9 @@ __global__ void __launch_bounds__(kFlatThreads) k_flat_stream(const __grid_const
     }
 
     // top-k path: every element above the row's bound becomes a candidate.  The CTA collects its
-    // candidates in shared memory (one shared-memory atomicAdd per warp and step) and hands them to
-    // the row's list with a single global atomicAdd at the end; should a piece hold more than the
-    // staging area takes, the excess goes to the list directly.
+    // candidates in shared memory and hands them to the row's list with a single global atomicAdd at
+    // the end; should a piece hold more than the staging area takes, the excess goes to the list
+    // directly.
     __shared__ unsigned long long stage[kFlatStage];
     __shared__ int stage_cnt, list_first;
     if (tid == 0) stage_cnt = 0;
@@ -257,6 +257,10 @@ __global__ void __launch_bounds__(kFlatThreads) k_flat_stream(const __grid_const
     const int cap = fr[row].cap;
     unsigned long long *cand = a.cand + __ldg(&rpp->cand_off);
     int *cnt_p = &fr[row].cnt;
+    // The sweep itself only notes which of the thread's 64 elements pass (one bit each): keeping the
+    // key construction and the appends out of the loop keeps it as tight as the arg-max loop.  The
+    // few that pass (a fraction of a percent) are read again afterwards, from L2.
+    unsigned long long passed = 0ull;
 #pragma unroll
     for (int s = 0; s < kFlatSteps; s++) {
         if (s + 1 < kFlatSteps) {
@@ -267,38 +271,26 @@ __global__ void __launch_bounds__(kFlatThreads) k_flat_stream(const __grid_const
 #pragma unroll
         for (int u = 0; u < 4; u++)
 #pragma unroll
-            for (int e = 0; e < 4; e++) pass |= (cur[u][e] > tau) ? (1u << (u * 4 + e)) : 0u;
-        if (__any_sync(0xFFFFFFFFu, pass != 0u)) {
-            const int n = __popc(pass);
-            int incl = n;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const int t = __shfl_up_sync(0xFFFFFFFFu, incl, o);
-                if (lane >= o) incl += t;
-            }
-            int first = 0;
-            if (lane == 31) first = atomicAdd(&stage_cnt, incl);
-            first = __shfl_sync(0xFFFFFFFFu, first, 31);
-            int slot = first + incl - n;
-#pragma unroll
-            for (int u = 0; u < 4; u++)
-#pragma unroll
-                for (int e = 0; e < 4; e++)
-                    if ((pass >> (u * 4 + e)) & 1u) {
-                        const unsigned long long key = make_key(cur[u][e], i0 + (s * 4 + u) * 1024 + e);
-                        if (slot < kFlatStage) {
-                            stage[slot] = key;
-                        } else {
-                            const int g = atomicAdd(cnt_p, 1);
-                            if (g < cap) cand[g] = key;
-                        }
-                        slot++;
-                    }
-        }
+            for (int e = 0; e < 4; e++) pass |= (cur[u][e] > tau) ? (1u << (u * 4 + e)) : 0u;  // out of range and masked read -inf
+        passed |= (unsigned long long)pass << (16 * s);
 #pragma unroll
         for (int u = 0; u < 4; u++)
 #pragma unroll
             for (int e = 0; e < 4; e++) cur[u][e] = nxt[u][e];
+    }
+    static_assert(kFlatSteps * 16 <= 64, "one bit per element of a thread");
+    while (passed != 0ull) {
+        const int b = __ffsll((long long)passed) - 1;
+        passed &= passed - 1ull;
+        const int idx = i0 + (b >> 2) * 1024 + (b & 3);  // bit 16 s + 4 u + e: sub-step 4 s + u, element e
+        const unsigned long long key = make_key(load_one<BF16>(rowp, idx), idx);
+        const int slot = atomicAdd(&stage_cnt, 1);
+        if (slot < kFlatStage) {
+            stage[slot] = key;
+        } else {
+            const int g = atomicAdd(cnt_p, 1);
+            if (g < cap) cand[g] = key;
+        }
     }
     __syncthreads();
     const int staged = min(stage_cnt, kFlatStage);
