@@ -62,7 +62,10 @@ enum {
     STG_MEM_HOST_BIAS = 1u << 3,     /* bias_ids, bias_values */
     STG_MEM_HOST_UNIFORMS = 1u << 4,
     STG_MEM_HOST_OUTPUTS = 1u << 5,  /* every output array; makes the call blocking */
-    STG_MEM_HOST_DRAFT = 1u << 6     /* stg_spec_verify: draft_tokens */
+    STG_MEM_HOST_DRAFT = 1u << 6,    /* stg_spec_verify: draft_tokens */
+    STG_MEM_HISTORY_RING = 1u << 7   /* StgSampleBatch: row r's PreviousTokens are the handle's device-resident
+                                        history of slot r (stg_history_*); history_ids / history_offsets
+                                        are ignored */
 };
 
 /* ---- per-row flags written to StgSampleBatch.row_flags -------------------------------------- */
@@ -115,6 +118,8 @@ typedef struct StgConfig {
     int32_t max_bias;     /* logit-bias entries per row */
     int32_t max_spec_draft; /* draft length of stg_spec_verify (0 = entry point unused) */
     uint32_t flags;       /* STG_CFG_* */
+    int32_t max_cached_masks; /* entries of the device-resident bitmask cache (stg_mask_cache_*), each
+                                 (max_vocab + 31) / 32 words; 0 = no cache */
 } StgConfig;
 
 /* SamplingParams of the reference (src/OpenTail.Stingray.Engine/Sampler.cs:648-686), the fields
@@ -165,6 +170,10 @@ typedef struct StgSampleBatch {
     int32_t topk_stride;            /* >= the largest top_k of any row on the top-k path when a topk_*
                                        output is given (STG_ERR_INVALID_ARGUMENT otherwise) */
     uint32_t mem_flags;             /* STG_MEM_HOST_* */
+    float logit_softcap;            /* != 0: every logit is read as tanh(x / cap) * cap, the final-logit
+                                       soft cap the reference applies in place before it samples
+                                       (llm_softcap_inplace, src/OpenTail.Stingray.Cuda/CudaTextKernels.cs:374-383;
+                                       SimdKernels.SoftcapInPlace on the CPU); 0: logits as given */
 } StgSampleBatch;
 
 /* One speculative verification step over `n_seq` sequences with `n_draft` draft tokens each
@@ -196,6 +205,8 @@ typedef struct StgSpecBatch {
     float *accept_probs;            /* out [n_seq, n_draft] or NULL: the ratio a (mode 0) or p(x) */
     uint32_t *seq_flags;            /* out [n_seq] or NULL: STG_ROW_CDF_FALLBACK etc. */
     uint32_t mem_flags;             /* STG_MEM_HOST_LOGITS | _DRAFT | _UNIFORMS | _OUTPUTS */
+    float target_softcap;           /* soft caps of the two models' logits, as StgSampleBatch.logit_softcap */
+    float draft_softcap;
 } StgSpecBatch;
 
 typedef struct StgStats {
@@ -335,6 +346,59 @@ STG_API int stg_mtp_accept(StgHandle handle, const void *logits, int32_t logits_
 STG_API int stg_and_masks(StgHandle handle, const uint32_t *masks, int32_t n_masks, int32_t rows,
                           int32_t vocab, int64_t mask_row_stride, uint32_t *out,
                           int64_t out_row_stride, uint8_t *out_uses_mask, void *stream);
+
+/* ---- bitmask cache ---------------------------------------------------------------------------------
+ * The reference's schema and tool-argument constraints rebuild a row's allowed-token set with a walk
+ * over the whole vocabulary on every step (JsonSchemaGrammarMasker.Filter,
+ * src/OpenTail.Stingray.Core/Grammar/JsonSchemaGrammarMasker.cs:67-95), although the set depends
+ * only on the constraint and its automaton state.  The cache keeps such sets on the device as
+ * bitmasks under a caller-chosen 64-bit key (for instance constraint id << 32 | state id; 0 is
+ * reserved for "no constraint in this slot"), so that a state seen before costs no walk and no
+ * host-to-device copy, and composes the masks of each row of a step with word operations. */
+enum { STG_MASK_AND = 0, STG_MASK_OR = 1 };
+
+/* Stores the (vocab + 31) / 32 words at `words` (host memory; bit convention of StgSampleBatch.mask)
+ * under `key`, replacing an entry of that key or, when the cache is full, the entry least recently
+ * put or composed.  The copy is enqueued on `stream`; compositions that should see it, or that still
+ * read the entry it replaces, must be ordered with it by the caller (use one stream). */
+STG_API int stg_mask_cache_put(StgHandle handle, uint64_t key, const uint32_t *words, int32_t vocab,
+                               void *stream);
+/* 1 when `key` is cached, else 0 (never an error code; a null handle answers 0). */
+STG_API int stg_mask_cache_contains(StgHandle handle, uint64_t key);
+/* Writes out[row] = the composition of the cached masks keys[row * keys_per_row + 0 .. keys_per_row)
+ * (host array; key 0 = empty slot), ready to be passed as StgSampleBatch.mask.  STG_MASK_AND is
+ * AndTokenConstraint.Filter (AndTokenConstraint.cs:44-86) exactly as stg_and_masks states it;
+ * STG_MASK_OR allows a token when any inner that allows something allows it (alternatives of a
+ * grammar; the engaged branch of CompositeToolArgumentConstraint.cs:43-48 is the one-key case).  A
+ * row without usable inners comes out all ones with out_uses_mask[row] = 0.  keys_per_row <= 32; a
+ * key that is not cached is STG_ERR_INVALID_ARGUMENT, and nothing is written. */
+STG_API int stg_mask_compose(StgHandle handle, const uint64_t *keys, int32_t keys_per_row, int32_t rows,
+                             int32_t vocab, int32_t op, uint32_t *out, int64_t out_row_stride,
+                             uint8_t *out_uses_mask, void *stream);
+
+/* ---- device-resident token histories -------------------------------------------------------------
+ * The reference keeps each sequence's PreviousTokens on the host and hands the sampler a fresh list
+ * every step (ContinuousBatchingEngine.cs:650, :1280).  Here the handle owns max_rows histories of up
+ * to max_history tokens in device memory; a step samples against them with STG_MEM_HISTORY_RING in
+ * StgSampleBatch.mem_flags (batch row r = slot r) and appends its own output with
+ * stg_history_append, so a decode loop moves no history bytes between host and device.  A full
+ * history drops its oldest token on append; from then on the slot serves only rows that cannot
+ * tell: no penalty set, or a repetition penalty alone whose repeat_last_n window (1 .. max_history)
+ * lies inside what is kept (Sampler.cs:364-375: the repetition penalty sees the trailing window,
+ * presence and frequency penalties the whole history).  Any other row is refused with
+ * STG_ERR_CAPACITY.  The host keeps the
+ * lengths (they shape the step's plan), so nothing here reads the device back. */
+/* Empties the histories of slots [first_slot, first_slot + n_slots). */
+STG_API int stg_history_reset(StgHandle handle, int32_t first_slot, int32_t n_slots, void *stream);
+/* Replaces slot's history by tokens[0 .. n) (host memory, oldest first; n <= max_history). */
+STG_API int stg_history_load(StgHandle handle, int32_t slot, const int32_t *tokens, int32_t n, void *stream);
+/* Appends tokens[r] (device int32 [rows], typically StgSampleBatch.tokens of the step just enqueued
+ * on the same stream) to slot r for every r < rows whose active[r] != 0 (host uint8 [rows], or NULL:
+ * every row). */
+STG_API int stg_history_append(StgHandle handle, const int32_t *tokens, int32_t rows, const uint8_t *active,
+                               void *stream);
+/* Tokens slot holds now, or a negative STG_ERR_* code. */
+STG_API int stg_history_length(StgHandle handle, int32_t slot);
 
 /* ---- vocabulary-sharded mode (no counterpart in the reference, which is single-device:
  *      src/OpenTail.Stingray.Cli/RunCommand.cs:100) ------------------------------------------------

@@ -15,6 +15,8 @@ ERR_NAMES = {
 DTYPE_F32, DTYPE_BF16 = 0, 1
 MEM_HOST_LOGITS, MEM_HOST_HISTORY, MEM_HOST_MASK, MEM_HOST_BIAS = 1, 2, 4, 8
 MEM_HOST_UNIFORMS, MEM_HOST_OUTPUTS, MEM_HOST_DRAFT = 16, 32, 64
+MEM_HISTORY_RING = 128
+MASK_AND, MASK_OR = 0, 1
 CFG_HOST_LOGITS = 1
 SEQ_EMPTY_RESIDUAL, SEQ_BAD_DRAFT = 1 << 8, 1 << 9
 
@@ -25,6 +27,8 @@ EXPORTS = [
     "stg_sample_with_distribution", "stg_sample_from_probs", "stg_resample_residual",
     "stg_mtp_accept", "stg_and_masks", "stg_comm_unique_id", "stg_comm_init", "stg_comm_destroy",
     "stg_shard_select", "stg_shard_allgather", "stg_shard_exchange_bytes", "stg_shard_finish", "stg_shard_gather_local",
+    "stg_mask_cache_put", "stg_mask_cache_contains", "stg_mask_compose",
+    "stg_history_reset", "stg_history_load", "stg_history_append", "stg_history_length",
 ]
 
 
@@ -33,6 +37,7 @@ class StgConfig(C.Structure):
         ("struct_size", C.c_int32), ("device", C.c_int32), ("max_rows", C.c_int32),
         ("max_vocab", C.c_int32), ("max_history", C.c_int32), ("max_top_k", C.c_int32),
         ("max_bias", C.c_int32), ("max_spec_draft", C.c_int32), ("flags", C.c_uint32),
+        ("max_cached_masks", C.c_int32),
     ]
 
 
@@ -54,6 +59,7 @@ class StgSampleBatch(C.Structure):
         ("uniforms", C.c_void_p), ("tokens", C.c_void_p), ("token_probs", C.c_void_p),
         ("row_flags", C.c_void_p), ("topk_ids", C.c_void_p), ("topk_logits", C.c_void_p),
         ("topk_probs", C.c_void_p), ("topk_stride", C.c_int32), ("mem_flags", C.c_uint32),
+        ("logit_softcap", C.c_float),
     ]
 
 
@@ -65,6 +71,7 @@ class StgSpecBatch(C.Structure):
         ("params", C.c_void_p), ("uniforms", C.c_void_p), ("p_min", C.c_float),
         ("accepted", C.c_void_p), ("correction", C.c_void_p), ("accept_probs", C.c_void_p),
         ("seq_flags", C.c_void_p), ("mem_flags", C.c_uint32),
+        ("target_softcap", C.c_float), ("draft_softcap", C.c_float),
     ]
 
 
@@ -107,6 +114,13 @@ def load() -> C.CDLL:
     lib.stg_resample_residual.argtypes = [vp, vp, vp, i32, i32, i64, vp, vp, vp, C.c_uint32, vp]
     lib.stg_mtp_accept.argtypes = [vp, vp, i32, i32, i32, i64, vp, f32, vp, vp, vp, vp]
     lib.stg_and_masks.argtypes = [vp, vp, i32, i32, i32, i64, vp, i64, vp, vp]
+    lib.stg_mask_cache_put.argtypes = [vp, C.c_uint64, vp, i32, vp]
+    lib.stg_mask_cache_contains.argtypes = [vp, C.c_uint64]
+    lib.stg_mask_compose.argtypes = [vp, vp, i32, i32, i32, i32, vp, i64, vp, vp]
+    lib.stg_history_reset.argtypes = [vp, i32, i32, vp]
+    lib.stg_history_load.argtypes = [vp, i32, vp, i32, vp]
+    lib.stg_history_append.argtypes = [vp, vp, i32, vp, vp]
+    lib.stg_history_length.argtypes = [vp, i32]
     lib.stg_comm_unique_id.argtypes = [vp]
     lib.stg_comm_init.argtypes = [vp, vp, i32, i32]
     lib.stg_comm_destroy.argtypes = [vp]

@@ -76,7 +76,14 @@ int make_plan(StgHandle h, const StgSampleBatch *b, int mode, bool shard, int gl
         rp.rep = p.repetition_penalty; rp.pres = p.presence_penalty; rp.freq = p.frequency_penalty;
         rp.top_k = p.top_k;
         int hoff = 0, hlen = 0, boff = 0, blen = 0;
-        if (b->history_offsets && b->history_ids) {
+        if (b->mem_flags & STG_MEM_HISTORY_RING) {
+            hoff = r * std::max(h->cfg.max_history, 1);
+            hlen = h->ring_len[r];
+            const bool pen = p.repetition_penalty != 1.0f || p.presence_penalty != 0.f || p.frequency_penalty != 0.f;
+            if (h->ring_dropped[r] && pen &&
+                (p.presence_penalty != 0.f || p.frequency_penalty != 0.f || p.repeat_last_n <= 0 || p.repeat_last_n > hlen))
+                return fail(h, STG_ERR_CAPACITY, "the device-resident history has dropped tokens this row's penalties would count");
+        } else if (b->history_offsets && b->history_ids) {
             hoff = b->history_offsets[r];
             hlen = b->history_offsets[r + 1] - hoff;
         }
@@ -287,6 +294,8 @@ int check_batch(StgHandle h, const StgSampleBatch *b, bool no_logits)
 {
     if (!h) return STG_ERR_INVALID_ARGUMENT;
     if (!b || b->struct_size != (int32_t)sizeof(StgSampleBatch)) return fail(h, STG_ERR_INVALID_ARGUMENT, "bad StgSampleBatch");
+    if (!(b->logit_softcap >= 0.f) || b->logit_softcap > 3.0e38f)
+        return fail(h, STG_ERR_INVALID_ARGUMENT, "logit_softcap must be 0 (off) or a finite positive cap");
     if (b->rows < 0 || b->vocab <= 0) return fail(h, STG_ERR_INVALID_ARGUMENT, "rows must be >= 0 and vocab > 0");
     if (b->rows > h->cfg.max_rows) return fail(h, STG_ERR_CAPACITY, "rows exceed max_rows");
     if (b->vocab > h->cfg.max_vocab) return fail(h, STG_ERR_CAPACITY, "vocab exceeds max_vocab");
@@ -334,10 +343,14 @@ int run_batch(StgHandle h, const StgSampleBatch *b, const BatchExtra &x, void *s
     key.clear();
     auto put = [&key](const void *p, size_t n) { const unsigned char *c = (const unsigned char *)p; key.insert(key.end(), c, c + n); };
     const int32_t head[11] = {rows, V, b->logits_dtype, mode, x.shard_mode, x.global_vocab, (int32_t)flat_ok, (int32_t)full_ok,
-                              (int32_t)(b->mask != nullptr), (int32_t)(b->history_ids != nullptr), (int32_t)(b->bias_ids != nullptr && b->bias_values != nullptr)};
+                              (int32_t)(b->mask != nullptr), (b->mem_flags & STG_MEM_HISTORY_RING) ? 2 : (int32_t)(b->history_ids != nullptr), (int32_t)(b->bias_ids != nullptr && b->bias_values != nullptr)};
     put(head, sizeof(head));
     put(b->params, (size_t)rows * sizeof(StgRowParams));
-    if (b->history_offsets) put(b->history_offsets, (size_t)(rows + 1) * 4);
+    const bool ring = (b->mem_flags & STG_MEM_HISTORY_RING) != 0;
+    if (ring) {
+        put(h->ring_len.data(), (size_t)rows * 4);
+        put(h->ring_dropped.data(), (size_t)rows);
+    } else if (b->history_offsets) put(b->history_offsets, (size_t)(rows + 1) * 4);
     if (b->bias_offsets) put(b->bias_offsets, (size_t)(rows + 1) * 4);
     if (b->row_uses_mask) put(b->row_uses_mask, (size_t)rows);
     Plan &pl = h->plan;
@@ -364,9 +377,13 @@ int run_batch(StgHandle h, const StgSampleBatch *b, const BatchExtra &x, void *s
         if (rc) return rc;
     }
     a.logits = p;
-    const int hist_total = (b->history_offsets && b->history_ids) ? b->history_offsets[rows] : 0;
-    rc = stage_in(h, b->history_ids, (size_t)hist_total * 4, mf & STG_MEM_HOST_HISTORY, h->st_hist, stream, &p);
-    if (rc) return rc;
+    if (ring) {
+        p = h->ring_ids.p;
+    } else {
+        const int hist_total = (b->history_offsets && b->history_ids) ? b->history_offsets[rows] : 0;
+        rc = stage_in(h, b->history_ids, (size_t)hist_total * 4, mf & STG_MEM_HOST_HISTORY, h->st_hist, stream, &p);
+        if (rc) return rc;
+    }
     a.hist_ids = (const int32_t *)p;
     const int bias_total = (b->bias_offsets && b->bias_ids) ? b->bias_offsets[rows] : 0;
     rc = stage_in(h, b->bias_ids, (size_t)bias_total * 4, mf & STG_MEM_HOST_BIAS, h->st_bias_ids, stream, &p);
@@ -421,8 +438,8 @@ int run_batch(StgHandle h, const StgSampleBatch *b, const BatchExtra &x, void *s
     a.cand_count = (int32_t *)h->cand_count.p;
     a.tickets = (uint32_t *)h->tickets.p;
     a.work_counter = (uint32_t *)h->work_counter.p;
-    a.counters = (unsigned long long *)h->work_counter.p + 16;
-    a.debug_bits = getenv("STG_DEBUG_BITS") ? atoi(getenv("STG_DEBUG_BITS")) : 0;  // bytes 128..191 of the same small buffer
+    a.counters = (unsigned long long *)h->work_counter.p + 16;  // bytes 128..191 of the same small buffer
+    a.softcap = b->logit_softcap;
     a.phase_ticks = (unsigned long long *)h->ticks.p;
     h->ticks_items = (int)pl.items.size();
     a.escratch = (float *)h->escratch.p;
@@ -577,7 +594,8 @@ int stg_create(const StgConfig *cfg, StgHandle *out)
     if (!cfg || !out || cfg->struct_size != (int32_t)sizeof(StgConfig))
         return fail(nullptr, STG_ERR_INVALID_ARGUMENT, "bad StgConfig");
     *out = nullptr;
-    if (cfg->max_rows <= 0 || cfg->max_vocab <= 0 || cfg->max_history < 0 || cfg->max_top_k < 0 || cfg->max_bias < 0)
+    if (cfg->max_rows <= 0 || cfg->max_vocab <= 0 || cfg->max_history < 0 || cfg->max_top_k < 0 || cfg->max_bias < 0 ||
+        cfg->max_cached_masks < 0)
         return fail(nullptr, STG_ERR_INVALID_ARGUMENT, "capacities must be positive");
     if ((int64_t)cfg->max_top_k + cfg->max_history > kMaxSel)
         return fail(nullptr, STG_ERR_CAPACITY, "max_top_k + max_history must not exceed 8192");
@@ -632,6 +650,17 @@ int stg_create(const StgConfig *cfg, StgHandle *out)
     A(h->keyscratch, (size_t)h->sm_count * h->key_stride * 8);
     A(h->listscratch, (size_t)h->sm_count * (h->key_stride + 512) * 8);  // + 2 sub-tiles: padded reads
     A(h->st_hist, R * std::max<size_t>(cfg->max_history, 1) * 4);
+    A(h->ring_ids, R * std::max<size_t>(cfg->max_history, 1) * 4);
+    A(h->ring_len_dev, R * 4);
+    h->ring_len.assign(R, 0);
+    h->ring_dropped.assign(R, 0);
+    if (cfg->max_cached_masks > 0) {
+        h->mc_stride = (int64_t)round_up(((size_t)V + 31) / 32, 4);  // rows start on 16-byte boundaries
+        A(h->mc_words, (size_t)cfg->max_cached_masks * h->mc_stride * 4);
+        A(h->mc_slots, R * 32 * 4);
+        h->mc_key.assign(cfg->max_cached_masks, 0);
+        h->mc_used.assign(cfg->max_cached_masks, 0);
+    }
     A(h->st_bias_ids, R * std::max<size_t>(cfg->max_bias, 1) * 4);
     A(h->st_bias_vals, R * std::max<size_t>(cfg->max_bias, 1) * 4);
     A(h->st_uniforms, R * 8);
@@ -675,6 +704,7 @@ int stg_create(const StgConfig *cfg, StgHandle *out)
     if (rc == STG_OK) {
         e = cudaMemset(h->work_counter.p, 0, 256);
         if (e == cudaSuccess) e = cudaMemset(h->tickets.p, 0, h->tickets.bytes);
+        if (e == cudaSuccess) e = cudaMemset(h->ring_len_dev.p, 0, h->ring_len_dev.bytes);
         if (e != cudaSuccess) rc = cuda_fail(nullptr, e, "cudaMemset");
     }
     if (rc != STG_OK) {
@@ -696,6 +726,7 @@ int stg_destroy(StgHandle h)
                      &h->fw_bstart, &h->fw_binexp, &h->fw_flagbits, &h->fw_cursor, &h->cand, &h->cand_count, &h->tickets, &h->work_counter, &h->escratch, &h->keyscratch, &h->listscratch,
                      &h->dists, &h->st_hist, &h->st_bias_ids, &h->st_bias_vals, &h->st_uniforms, &h->st_mask, &h->st_logits,
                      &h->o_tokens, &h->o_probs, &h->o_flags, &h->o_topk_ids, &h->o_topk_vals, &h->o_topk_probs, &h->o_pairs, &h->ticks,
+                     &h->ring_ids, &h->ring_len_dev, &h->mc_words, &h->mc_slots,
                      &h->sp_draft, &h->sp_uniforms, &h->sp_accepted, &h->sp_correction, &h->sp_aprobs, &h->sp_flags,
                      &h->sp_rowstats, &h->xchg_local, &h->xchg_gather};
     for (DevBuf *b : all) dev_free(*b);

@@ -29,7 +29,7 @@ __global__ void __launch_bounds__(kThreads) k_flat_prep(const __grid_constant__ 
         return;
     }
     const int esz = BF16 ? 2 : 4;
-    const void *rowp = (const char *)a.logits + (int64_t)row * a.row_stride * esz;
+    const LogitRow rowp{(const char *)a.logits + (int64_t)row * a.row_stride * esz, a.softcap};
     const uint32_t *mrow = (rp.use_mask && a.mask) ? a.mask + (int64_t)row * a.mask_stride : nullptr;
     float v[4];
     int idx[4];
@@ -65,7 +65,7 @@ __global__ void __launch_bounds__(kThreads) k_flat_prep(const __grid_constant__ 
 // Four masked elements of a 16-byte aligned row starting at element i (a multiple of 4); elements at
 // or beyond `end` read as -infinity.
 template <bool BF16>
-__device__ __forceinline__ void flat_load4(const void *rowp, const uint32_t *mrow, int i, int end, float v[4])
+__device__ __forceinline__ void flat_load4(const LogitRow rowp, const uint32_t *mrow, int i, int end, float v[4])
 {
     if (i + 3 < end) {
         load_vec4<BF16, true>(rowp, i, v);
@@ -97,7 +97,7 @@ __global__ void __launch_bounds__(kFlatThreads) k_flat_stream(const __grid_const
     if (begin >= end) return;
     const int path = __ldg(&rpp->path);
     const int esz = BF16 ? 2 : 4;
-    const void *rowp = (const char *)a.logits + (int64_t)row * a.row_stride * esz;
+    const LogitRow rowp{(const char *)a.logits + (int64_t)row * a.row_stride * esz, a.softcap};
     const uint32_t *mrow = (__ldg(&rpp->use_mask) && a.mask) ? a.mask + (int64_t)row * a.mask_stride : nullptr;
     const int i0 = begin + tid * 4;
 
@@ -319,7 +319,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_flat_finish(const __grid_consta
     const int row = a.items[blockIdx.x].row;
     const RowPlan rp = a.plans[row];
     const int esz = BF16 ? 2 : 4;
-    const void *rowp = (const char *)a.logits + (int64_t)row * a.row_stride * esz;
+    const LogitRow rowp{(const char *)a.logits + (int64_t)row * a.row_stride * esz, a.softcap};
     if (rp.path == kPathGreedy) {
         if (threadIdx.x == 0) {
             const unsigned long long key = fr[row].key;

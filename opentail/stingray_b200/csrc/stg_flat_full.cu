@@ -51,7 +51,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_full_prep(const __grid_constant
     }
     if (!(with_hist || with_bias)) return;
     const int esz = BF16 ? 2 : 4;
-    const void *rowp = (const char *)a.logits + (int64_t)row * a.row_stride * esz;
+    const LogitRow rowp{(const char *)a.logits + (int64_t)row * a.row_stride * esz, a.softcap};
     const uint32_t *mrow = (rp.use_mask && a.mask) ? a.mask + (int64_t)row * a.mask_stride : nullptr;
     const int entries = (with_hist ? rp.hist_len : 0) + (with_bias ? rp.bias_len : 0);
     int slots = 64;

@@ -5,6 +5,7 @@
 
 #include <algorithm>
 #include <string>
+#include <unordered_map>
 #include <vector>
 
 #include "../../../include/stingray_sampler.h"
@@ -81,6 +82,17 @@ struct StgSampler_ {
     int rank = 0, n_ranks = 1;
     int shard_sel = 0, shard_rows = 0, shard_rows_used = 0, shard_stride_used = 0;
     size_t shard_block_bytes = 0;         // bytes one rank contributes to the exchange of the current step
+    // device-resident histories (stg_history.cu): slot r at ring_ids + r * max(max_history, 1)
+    stg::DevBuf ring_ids, ring_len_dev;
+    std::vector<int32_t> ring_len;        // host mirror of the lengths
+    std::vector<uint8_t> ring_dropped;    // the slot has dropped its oldest token at least once
+    // bitmask cache (stg_mask.cu)
+    stg::DevBuf mc_words, mc_slots;       // [max_cached_masks, mc_stride] words; slot indices of one composition
+    int64_t mc_stride = 0;
+    std::vector<uint64_t> mc_key, mc_used;  // per entry: key (0 = free) and the tick of its last use
+    uint64_t mc_tick = 0;
+    std::unordered_map<uint64_t, int> mc_index;  // key -> entry
+    std::vector<int32_t> mc_slot_scratch;
 };
 
 namespace stg {

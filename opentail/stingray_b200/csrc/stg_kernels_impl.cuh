@@ -55,7 +55,7 @@ __device__ __forceinline__ u64 block_max_key(u64 k, u64 *scratch /* 32 entries *
 
 // Arg-max of elements [begin, end) as a key (0 when no element is > -infinity).
 template <int VEC, bool BF16>
-__device__ u64 greedy_stream(const void *rowp, const uint32_t *mrow, int begin, int end, int idx_off,
+__device__ u64 greedy_stream(const LogitRow rowp, const uint32_t *mrow, int begin, int end, int idx_off,
                              u64 *scratch)
 {
     constexpr int U = 4;
@@ -76,7 +76,7 @@ __device__ u64 greedy_stream(const void *rowp, const uint32_t *mrow, int begin, 
     return block_max_key(k, scratch);
 }
 
-__device__ __forceinline__ void write_greedy(const SampleArgs &a, int row, u64 key, const void *rowp)
+__device__ __forceinline__ void write_greedy(const SampleArgs &a, int row, u64 key, const LogitRow rowp)
 {
     if (threadIdx.x != 0) return;
     int tok = 0;
@@ -106,7 +106,7 @@ __device__ void run_chunk(const SampleArgs &a, int row, int chunk, int item, Sel
     tick(tk, 0);
     const RowPlan rp = a.plans[row];
     const int esz = BF16 ? 2 : 4;
-    const void *rowp = (const char *)a.logits + (int64_t)row * a.row_stride * esz;
+    const LogitRow rowp{(const char *)a.logits + (int64_t)row * a.row_stride * esz, a.softcap};
     const uint32_t *mrow = (rp.use_mask && a.mask) ? a.mask + (int64_t)row * a.mask_stride : nullptr;
     const int begin = chunk * a.chunk_len;
     const int end = min(a.vocab, begin + a.chunk_len);

@@ -65,6 +65,7 @@ struct SpecArgs {
     float *accept_probs;
     uint32_t *seq_flags;
     float p_min;
+    float target_cap, draft_cap;  // soft caps of the two models' logits, 0: none
     int32_t n_seq, n_draft, vocab, dtype, mode, vec;
 };
 cudaError_t launch_spec_finish(const SpecArgs &a, cudaStream_t stream);

@@ -141,7 +141,7 @@ struct OvView {
 // ---- sources of the row's adjusted, temperature-scaled logits ---------------------------------
 template <bool BF16>
 struct SrcLogits {
-    const void *rowp;
+    LogitRow rowp;
     const uint32_t *mrow;
     int aligned;
     float inv_t;
@@ -183,7 +183,7 @@ struct SrcLogits {
     __device__ __forceinline__ bool stage_ok() const { return aligned != 0; }
     __device__ __forceinline__ const char *stage_src(int base) const
     {
-        return (const char *)rowp + (size_t)base * (BF16 ? 2 : 4);
+        return (const char *)rowp.p + (size_t)base * (BF16 ? 2 : 4);
     }
     __device__ __forceinline__ void decode(int base, const float4 *q, float x[8]) const
     {
@@ -194,6 +194,10 @@ struct SrcLogits {
         } else {
             x[0] = q[0].x; x[1] = q[0].y; x[2] = q[0].z; x[3] = q[0].w;
             x[4] = q[1].x; x[5] = q[1].y; x[6] = q[1].z; x[7] = q[1].w;
+        }
+        if (rowp.cap != 0.f) {
+#pragma unroll
+            for (int j = 0; j < 8; j++) x[j] = soft_cap(x[j], rowp.cap);
         }
         if (mrow) {
             uint32_t bits = __ldg(mrow + (base >> 5)) >> (base & 31);
@@ -631,7 +635,7 @@ static __device__ int find_kth_match(RowCtl *rc, const float *scratch, int n, co
 // window, and the presence/frequency penalty over the whole history.  Requires
 // 2 * (history + bias entries) <= slots <= kMaxOvSlots.
 template <bool BF16>
-static __device__ void build_overrides(const SampleArgs &a, const RowPlan &rp, const void *rowp,
+static __device__ void build_overrides(const SampleArgs &a, const RowPlan &rp, const LogitRow rowp,
                                        const uint32_t *mrow, int n, bool with_hist, bool with_bias, OvTable &ov,
                                        unsigned char *arena, int slots)
 {
@@ -878,7 +882,7 @@ static __device__ __noinline__ void topk_cut(RowCtl *rc, SelCtl *sctl, const Row
         s.n = rp.top_k;
         s.idx_off = 0;
         sel_reset(s);
-        sel_stream<4, false>(s, scratch, nullptr, 0, n);
+        sel_stream<4, false>(s, LogitRow{scratch, 0.f}, nullptr, 0, n);
         if (sctl->cnt > s.n) sel_compact(s);  // exactly the best k: their minimum is the k-th largest
         const u64 *b = s.buf[sctl->cur];
         u64 inv_min = 0ull;
@@ -1391,7 +1395,7 @@ static __device__ void run_row(const SampleArgs &a, int row, int item, SelCtl *s
     if (a.redo_flags != nullptr && (rp.flat_full < 0 || a.redo_flags[(size_t)rp.flat_full * a.redo_stride] == 0)) return;
     const int n = a.vocab;
     const int esz = BF16 ? 2 : 4;
-    const void *rowp = (const char *)a.logits + (int64_t)row * a.row_stride * esz;
+    const LogitRow rowp{(const char *)a.logits + (int64_t)row * a.row_stride * esz, a.softcap};
     const uint32_t *mrow = (rp.use_mask && a.mask) ? a.mask + (int64_t)row * a.mask_stride : nullptr;
     float *scratch = a.escratch + (int64_t)blockIdx.x * a.escratch_stride;
     uint32_t *gkeys = (uint32_t *)(a.keyscratch + (int64_t)blockIdx.x * a.key_stride);

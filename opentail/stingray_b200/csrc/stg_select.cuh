@@ -38,26 +38,43 @@ static __device__ __forceinline__ int key_idx(u64 k) { return (int)(0xFFFFFFFFu 
 static __device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
 static __device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
 
+// A row of logits as the kernels read it.  cap != 0: the final-logit soft cap
+// x <- tanh(x / cap) * cap (llm_softcap_inplace, src/OpenTail.Stingray.Cuda/CudaTextKernels.cs:374-383,
+// which the reference runs as a pass of its own over the logits before sampling) is applied to every
+// element as it is loaded, with that kernel's own operations in its order, so the row is never
+// rewritten in device memory.
+struct LogitRow {
+    const void *p;
+    float cap;
+};
+static __device__ __forceinline__ float soft_cap(float x, float cap) { return __fmul_rn(tanhf(__fdiv_rn(x, cap)), cap); }
+
 template <bool BF16, bool STREAM>
-static __device__ __forceinline__ void load_vec4(const void *rowp, int i, float v[4])
+static __device__ __forceinline__ void load_vec4(const LogitRow rowp, int i, float v[4])
 {
     if (BF16) {
-        const uint2 *p = (const uint2 *)((const uint16_t *)rowp + i);
+        const uint2 *p = (const uint2 *)((const uint16_t *)rowp.p + i);
         uint2 t = STREAM ? __ldcs(p) : __ldg(p);
         v[0] = bf16_lo(t.x); v[1] = bf16_hi(t.x); v[2] = bf16_lo(t.y); v[3] = bf16_hi(t.y);
     } else {
-        const float4 *p = (const float4 *)((const float *)rowp + i);
+        const float4 *p = (const float4 *)((const float *)rowp.p + i);
         float4 t = STREAM ? __ldcs(p) : __ldg(p);
         v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
     }
+    if (rowp.cap != 0.f) {
+#pragma unroll
+        for (int e = 0; e < 4; e++) v[e] = soft_cap(v[e], rowp.cap);
+    }
 }
 template <bool BF16>
-static __device__ __forceinline__ float load_one(const void *rowp, int i)
+static __device__ __forceinline__ float load_one(const LogitRow rowp, int i)
 {
-    if (BF16) return __uint_as_float((uint32_t)__ldg((const uint16_t *)rowp + i) << 16);
-    return __ldg((const float *)rowp + i);
+    float x;
+    if (BF16) x = __uint_as_float((uint32_t)__ldg((const uint16_t *)rowp.p + i) << 16);
+    else x = __ldg((const float *)rowp.p + i);
+    return rowp.cap != 0.f ? soft_cap(x, rowp.cap) : x;
 }
-static __device__ __forceinline__ float load_one_dyn(const void *rowp, int dtype, int i)
+static __device__ __forceinline__ float load_one_dyn(const LogitRow rowp, int dtype, int i)
 {
     return dtype ? load_one<true>(rowp, i) : load_one<false>(rowp, i);
 }
@@ -71,7 +88,7 @@ static __device__ __forceinline__ bool mask_bit(const uint32_t *mrow, int i)
 // VEC == 4: elements base + (u*1024 + tid)*4 + e (one 128-bit / 64-bit load);
 // VEC == 1: elements base + (u*4 + e)*1024 + tid (scalar loads, any alignment).
 template <int VEC, bool BF16, bool STREAM>
-static __device__ __forceinline__ void load_items(const void *rowp, const uint32_t *mrow, int base, int u,
+static __device__ __forceinline__ void load_items(const LogitRow rowp, const uint32_t *mrow, int base, int u,
                                            int end, float v[4], int idx[4])
 {
     const int tid = threadIdx.x;
@@ -371,7 +388,7 @@ static __device__ __forceinline__ int item_index(int base, int u, int e)
 }
 
 template <int VEC, bool BF16>
-static __device__ __forceinline__ void sel_load_iter(const void *rowp, const uint32_t *mrow, int base, int end,
+static __device__ __forceinline__ void sel_load_iter(const LogitRow rowp, const uint32_t *mrow, int base, int end,
                                                      float v[4][4])
 {
     int idx[4];
@@ -432,7 +449,7 @@ static __device__ __forceinline__ void sel_process_iter(Sel &s, const float v[4]
 // current one is filtered (two iterations, 128 KB, in flight per CTA).  On return the buffer
 // holds a superset of the best N keys of the range, at most 2N of them.
 template <int VEC, bool BF16>
-static __device__ void sel_stream_pass(Sel &s, const void *rowp, const uint32_t *mrow, int begin, int end,
+static __device__ void sel_stream_pass(Sel &s, const LogitRow rowp, const uint32_t *mrow, int begin, int end,
                                        bool optimistic)
 {
     SelCtl *c = s.c;
@@ -478,7 +495,7 @@ static __device__ void sel_stream_pass(Sel &s, const void *rowp, const uint32_t 
 }
 
 template <int VEC, bool BF16>
-static __device__ void sel_stream(Sel &s, const void *rowp, const uint32_t *mrow, int begin, int end)
+static __device__ void sel_stream(Sel &s, const LogitRow rowp, const uint32_t *mrow, int begin, int end)
 {
     SelCtl *c = s.c;
     // With a bound guessed from the first sub-tile the buffer rarely fills and tau is rarely raised

@@ -135,6 +135,7 @@ int stg_spec_verify(StgHandle h, const StgSpecBatch *b, void *stream_)
         sb.struct_size = sizeof(sb);
         sb.rows = S * per; sb.vocab = V; sb.logits_dtype = b->logits_dtype; sb.logits = logits; sb.row_stride = V;
         sb.params = params.data();
+        sb.logit_softcap = which == 0 ? b->target_softcap : b->draft_softcap;
         BatchExtra x;
         x.mode = 2;
         x.dists_out = which == 0 ? tdist : ddist;
@@ -158,6 +159,7 @@ int stg_spec_verify(StgHandle h, const StgSpecBatch *b, void *stream_)
     a.accept_probs = b->accept_probs ? (host_out ? (float *)h->sp_aprobs.p : b->accept_probs) : nullptr;
     a.seq_flags = b->seq_flags ? (host_out ? (uint32_t *)h->sp_flags.p : b->seq_flags) : nullptr;
     a.p_min = b->p_min;
+    a.target_cap = b->target_softcap; a.draft_cap = b->draft_softcap;
     a.n_seq = S; a.n_draft = L; a.vocab = V; a.dtype = b->logits_dtype; a.mode = b->mode;
     a.vec = rows_aligned2(b->target_logits, V, b->logits_dtype) &&
             (!b->draft_logits || rows_aligned2(b->draft_logits, V, b->logits_dtype)) ? 4 : 1;

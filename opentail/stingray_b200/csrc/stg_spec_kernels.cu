@@ -16,7 +16,7 @@
 namespace stg {
 
 template <bool BF16>
-__device__ __forceinline__ float eval_point(const void *rowp, int i, const RowDist &d)
+__device__ __forceinline__ float eval_point(const LogitRow rowp, int i, const RowDist &d)
 {
     if (d.flags & kDistOneHot) return i == d.tie_idx_max ? 1.f : 0.f;
     float e;
@@ -118,9 +118,9 @@ __global__ void __launch_bounds__(kThreads, 1) k_spec_finish(const __grid_consta
                 ok = (tok == td[i].tie_idx_max);
                 shown = ok ? 1.f : 0.f;
             } else {
-                const float px = eval_point<BF16>(trows + (int64_t)i * V * esz, tok, td[i]);
+                const float px = eval_point<BF16>(LogitRow{trows + (int64_t)i * V * esz, a.target_cap}, tok, td[i]);
                 if (a.mode == 0) {
-                    const float qx = eval_point<BF16>(drows + (int64_t)i * V * esz, tok, dd[i]);
+                    const float qx = eval_point<BF16>(LogitRow{drows + (int64_t)i * V * esz, a.draft_cap}, tok, dd[i]);
                     const float r = qx > 0.f ? fminf(1.f, __fdiv_rn(px, qx)) : (px > 0.f ? 1.f : 0.f);
                     ok = u[i] < (double)r;
                     shown = r;
@@ -147,7 +147,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_spec_finish(const __grid_consta
         corr = td[acc].tie_idx_max;
     } else {
         const bool al = a.vec == 4;
-        const void *prow = trows + (int64_t)acc * V * esz;
+        const LogitRow prow{trows + (int64_t)acc * V * esz, a.target_cap};
         ProvRow<BF16> pp{SrcLogits<BF16>{prow, nullptr, al, td[acc].inv_t, td[acc].inv_t != 1.0f}, td[acc]};
         const float u0 = __double2float_rn(u[L]);
         const float u1 = __double2float_rn(u[L + 1]);
@@ -158,7 +158,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_spec_finish(const __grid_consta
             corr = emul_any<ProvRow<BF16>, false>(&sh.em, &sh.em2, wk2, pp, V, u0, true, &cum);
             if (corr < 0) { corr = V - 1; fl |= (1u << 5); }
         } else {
-            const void *qrow = drows + (int64_t)acc * V * esz;
+            const LogitRow qrow{drows + (int64_t)acc * V * esz, a.draft_cap};
             ProvRow<BF16> qq{SrcLogits<BF16>{qrow, nullptr, al, dd[acc].inv_t, dd[acc].inv_t != 1.0f}, dd[acc]};
             ProvResidual<BF16> rr{pp, qq};
             float sum;
@@ -332,7 +332,7 @@ __global__ void __launch_bounds__(kThreads) k_mtp_accept(const void *logits, int
     __shared__ double red_d[32];
     const int row = blockIdx.x, tid = threadIdx.x;
     const int esz = BF16 ? 2 : 4;
-    const void *rowp = (const char *)logits + (int64_t)row * row_stride * esz;
+    const LogitRow rowp{(const char *)logits + (int64_t)row * row_stride * esz, 0.f};
     SrcLogits<BF16> raw{rowp, nullptr, vec == 4, 1.f, false};
     const u64 mk = pass_max(raw, vocab, red_k);
     const int am = mk ? key_idx(mk) : 0;

@@ -42,7 +42,7 @@ __global__ void __launch_bounds__(kThreads) k_argmax_static(const void *logits, 
     __shared__ int last;
     const int row = blockIdx.y, chunk = blockIdx.x;
     const int esz = BF16 ? 2 : 4;
-    const void *rowp = (const char *)logits + (int64_t)row * row_stride * esz;
+    const LogitRow rowp{(const char *)logits + (int64_t)row * row_stride * esz, 0.f};
     const int begin = chunk * chunk_len, end = min(vocab, begin + chunk_len);
     constexpr int U = 4;
     float best = -CUDART_INF_F;

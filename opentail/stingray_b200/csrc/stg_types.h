@@ -117,7 +117,7 @@ struct SampleArgs {
     int32_t shard_mode;              // 0 off, 1 select only (write candidates), 2 finish from gather
     int32_t n_ranks;
     unsigned long long *counters;    // kCtr* event counters, never null
-    int32_t debug_bits;              // experiments (STG_DEBUG_BITS), 0 in normal use
+    float softcap;                   // != 0: every logit is read as tanh(x / softcap) * softcap
     const int32_t *redo_flags;       // row kernel as the flat step's second chance: only rows whose flag
     int32_t redo_stride;             // redo_flags[flat_full * redo_stride] is set are run; null: every row item
 };

@@ -98,12 +98,14 @@ class BatchSampler:
     thread, like the reference's backend (``IThreadAffineBackend.cs:11-21``)."""
 
     def __init__(self, max_rows: int, max_vocab: int, max_history: int = 512, max_top_k: int = 256,
-                 max_bias: int = 64, max_spec_draft: int = 0, device: int = 0, host_logits: bool = False):
+                 max_bias: int = 64, max_spec_draft: int = 0, device: int = 0, host_logits: bool = False,
+                 max_cached_masks: int = 0):
         """``host_logits``: reserve the device staging for host-resident logits and masks at creation
-        (``STG_CFG_HOST_LOGITS``), so that no sampling call allocates."""
+        (``STG_CFG_HOST_LOGITS``), so that no sampling call allocates.  ``max_cached_masks``: entries
+        of the device-resident bitmask cache (``mask_cache_put`` / ``mask_compose``)."""
         self._lib = N.load()
         cfg = N.StgConfig(C.sizeof(N.StgConfig), device, max_rows, max_vocab, max_history, max_top_k,
-                          max_bias, max_spec_draft, N.CFG_HOST_LOGITS if host_logits else 0)
+                          max_bias, max_spec_draft, N.CFG_HOST_LOGITS if host_logits else 0, max_cached_masks)
         h = C.c_void_p()
         rc = self._lib.stg_create(C.byref(cfg), C.byref(h))
         if rc != N.STG_OK:
@@ -155,7 +157,7 @@ class BatchSampler:
         return torch.empty(shape, dtype=td, device=f"cuda:{self.device}")
 
     def _batch(self, logits, params, history_ids, history_offsets, mask, row_uses_mask, bias,
-               uniforms):
+               uniforms, softcap: float = 0.0, history_ring: bool = False):
         """Builds the StgSampleBatch; returns it with the objects that must stay alive."""
         keep = []
         rows, vocab = logits.shape
@@ -180,7 +182,10 @@ class BatchSampler:
         b.struct_size = C.sizeof(N.StgSampleBatch)
         b.rows, b.vocab, b.logits_dtype = rows, vocab, dtype
         b.logits, b.row_stride, b.params = _ptr(logits), stride, pa.ctypes.data
-        if history_ids is not None:
+        if history_ring:
+            assert history_ids is None, "history_ring uses the handle's own histories"
+            flags |= N.MEM_HISTORY_RING
+        elif history_ids is not None:
             ho = np.ascontiguousarray(history_offsets, dtype=np.int32)
             if not _is_torch(history_ids):
                 history_ids = np.ascontiguousarray(history_ids, dtype=np.int32)
@@ -216,6 +221,7 @@ class BatchSampler:
             keep.append(uniforms)
             b.uniforms = _ptr(uniforms)
         b.mem_flags = flags
+        b.logit_softcap = softcap
         return b, keep
 
     # -- entry points ------------------------------------------------------------------------------
@@ -235,13 +241,17 @@ class BatchSampler:
 
     def sample_rows(self, logits, params, *, history_ids=None, history_offsets=None, mask=None,
                     row_uses_mask=None, bias=None, uniforms=None, want_probs=False,
-                    want_flags=False, want_topk=0, host_outputs: Optional[bool] = None, stream=None):
+                    want_flags=False, want_topk=0, host_outputs: Optional[bool] = None, softcap: float = 0.0,
+                    history_ring: bool = False, stream=None):
         """One sampling step (``stg_sample_rows``).  ``logits`` is a CUDA tensor (fp32/bf16) or a
         NumPy array (float32, or uint16 bf16 bit patterns); ``params`` a list of SamplingParams or
         a PARAMS_DTYPE array; histories/bias are CSR; ``uniforms`` one float per row.  Returns a
-        dict with ``tokens`` and the optional outputs, on the device unless ``host_outputs``."""
+        dict with ``tokens`` and the optional outputs, on the device unless ``host_outputs``.
+        ``softcap`` != 0 reads every logit as ``tanh(x / softcap) * softcap`` (the final-logit soft
+        cap, ``CudaTextKernels.cs:374-383``) without rewriting the logits.  ``history_ring``: row r's
+        PreviousTokens are the handle's device-resident history of slot r (``history_append``)."""
         b, keep = self._batch(logits, params, history_ids, history_offsets, mask, row_uses_mask,
-                              bias, uniforms)
+                              bias, uniforms, softcap, history_ring)
         host = (not _is_torch(logits)) if host_outputs is None else host_outputs
         rows = b.rows
         out = {"tokens": self._alloc((rows,), np.int32, host)}
@@ -264,9 +274,10 @@ class BatchSampler:
         return out
 
     def build_distribution(self, logits, params, *, history_ids=None, history_offsets=None,
-                           mask=None, bias=None, host_outputs: Optional[bool] = None, stream=None):
+                           mask=None, bias=None, host_outputs: Optional[bool] = None, softcap: float = 0.0,
+                           stream=None):
         """``Sampler.BuildFilteredDistribution`` for every row: returns ``[rows, vocab]`` float32."""
-        b, keep = self._batch(logits, params, history_ids, history_offsets, mask, None, bias, None)
+        b, keep = self._batch(logits, params, history_ids, history_offsets, mask, None, bias, None, softcap)
         host = (not _is_torch(logits)) if host_outputs is None else host_outputs
         probs = self._alloc((b.rows, b.vocab), np.float32, host)
         if host:
@@ -276,11 +287,11 @@ class BatchSampler:
         return probs
 
     def sample_with_distribution(self, logits, params, *, history_ids=None, history_offsets=None, mask=None,
-                                 uniforms=None, want_probs=True, stream=None):
+                                 uniforms=None, want_probs=True, softcap: float = 0.0, stream=None):
         """``Sampler.SampleWithDistribution`` for every row (``stg_sample_with_distribution``): the
         full-vocabulary pipeline whatever ``TopK`` is.  ``logits`` is a CUDA tensor; returns
         (tokens, probs ``[rows, vocab]`` or None), both on the device."""
-        b, keep = self._batch(logits, params, history_ids, history_offsets, mask, None, None, uniforms)
+        b, keep = self._batch(logits, params, history_ids, history_offsets, mask, None, None, uniforms, softcap)
         tokens = self._alloc((b.rows,), np.int32, False)
         b.tokens = _ptr(tokens)
         probs = self._alloc((b.rows, b.vocab), np.float32, False) if want_probs else None
@@ -326,7 +337,8 @@ class BatchSampler:
         return tokens, rf
 
     def spec_verify(self, target_logits, draft_logits, draft_tokens, params, uniforms, *, mode=0,
-                    p_min=1.0, want_probs=False, stream=None):
+                    p_min=1.0, want_probs=False, target_softcap: float = 0.0, draft_softcap: float = 0.0,
+                    stream=None):
         """``SpeculativeDecoder.StepSampled``'s accept loop for ``n_seq`` sequences
         (``stg_spec_verify``).  target ``[n_seq, L + 1, V]``, draft ``[n_seq, L, V]`` CUDA tensors,
         draft_tokens ``[n_seq, L]`` int32, uniforms ``[n_seq, L + 2]`` float64 (host or device)."""
@@ -356,6 +368,7 @@ class BatchSampler:
         b.draft_logits = draft_logits.data_ptr() if draft_logits is not None else None
         b.draft_tokens, b.params, b.uniforms = _ptr(draft_tokens), pa.ctypes.data, _ptr(uniforms)
         b.p_min = p_min
+        b.target_softcap, b.draft_softcap = target_softcap, draft_softcap
         b.accepted, b.correction = accepted.data_ptr(), correction.data_ptr()
         b.accept_probs, b.seq_flags, b.mem_flags = aprobs.data_ptr(), sflags.data_ptr(), flags
         self._check(self._lib.stg_spec_verify(self._h, C.byref(b), self._stream(stream)))
@@ -393,6 +406,67 @@ class BatchSampler:
                                             C.c_int64(words), C.c_void_p(out.data_ptr()), C.c_int64(words),
                                             C.c_void_p(uses.data_ptr()), self._stream(stream)))
         return out, uses
+
+    # -- bitmask cache ---------------------------------------------------------------------------------
+    def mask_cache_put(self, key: int, words, vocab: int, stream=None):
+        """Stores a host bitmask (uint32 words) under ``key`` (``stg_mask_cache_put``)."""
+        w = np.ascontiguousarray(words, dtype=np.uint32)
+        assert w.size >= (vocab + 31) // 32
+        self._check(self._lib.stg_mask_cache_put(self._h, C.c_uint64(key), w.ctypes.data, vocab, self._stream(stream)))
+
+    def mask_cache_contains(self, key: int) -> bool:
+        return bool(self._lib.stg_mask_cache_contains(self._h, C.c_uint64(key)))
+
+    def mask_cache_get_or_put(self, key: int, vocab: int, allowed_tokens, stream=None) -> bool:
+        """The use the cache is made for: ``allowed_tokens()`` - the walk over the vocabulary that
+        ``JsonSchemaGrammarMasker.Filter`` (``JsonSchemaGrammarMasker.cs:67-95``) repeats every step -
+        is called only when the (constraint, state) ``key`` has not been seen; it returns the ids of
+        the allowed tokens.  Returns True when the walk ran."""
+        if self.mask_cache_contains(key):
+            return False
+        words = np.zeros((vocab + 31) // 32, dtype=np.uint32)
+        ids = np.asarray(allowed_tokens(), dtype=np.int64)
+        np.bitwise_or.at(words, ids >> 5, (np.uint32(1) << (ids & 31).astype(np.uint32)))
+        self.mask_cache_put(key, words, vocab, stream)
+        return True
+
+    def mask_compose(self, keys, vocab: int, op: str = "and", stream=None):
+        """``stg_mask_compose``: ``keys`` is ``[rows, keys_per_row]`` (0 = empty slot); returns the
+        device mask ``[rows, words]`` (int32 view of the words) and the per-row uses-mask bytes."""
+        import torch
+
+        k = np.ascontiguousarray(keys, dtype=np.uint64)
+        rows, per = k.shape
+        words = (vocab + 31) // 32
+        dev = f"cuda:{self.device}"
+        out = torch.empty((rows, words), dtype=torch.int32, device=dev)
+        uses = torch.empty(rows, dtype=torch.uint8, device=dev)
+        self._check(self._lib.stg_mask_compose(self._h, k.ctypes.data, per, rows, vocab,
+                                               {"and": N.MASK_AND, "or": N.MASK_OR}[op], C.c_void_p(out.data_ptr()),
+                                               C.c_int64(words), C.c_void_p(uses.data_ptr()), self._stream(stream)))
+        return out, uses
+
+    # -- device-resident histories ---------------------------------------------------------------------
+    def history_reset(self, first_slot: int = 0, n_slots: Optional[int] = None, stream=None):
+        n = self.max_rows - first_slot if n_slots is None else n_slots
+        self._check(self._lib.stg_history_reset(self._h, first_slot, n, self._stream(stream)))
+
+    def history_load(self, slot: int, tokens, stream=None):
+        t = np.ascontiguousarray(tokens, dtype=np.int32)
+        self._check(self._lib.stg_history_load(self._h, slot, t.ctypes.data, t.size, self._stream(stream)))
+
+    def history_append(self, tokens, active=None, stream=None):
+        """Appends ``tokens[r]`` (device int32 tensor, e.g. the ``tokens`` a step returned) to slot r."""
+        assert _is_torch(tokens) and tokens.is_cuda
+        act = None if active is None else np.ascontiguousarray(active, dtype=np.uint8)
+        self._check(self._lib.stg_history_append(self._h, tokens.data_ptr(), tokens.numel(),
+                                                 None if act is None else act.ctypes.data, self._stream(stream)))
+
+    def history_length(self, slot: int) -> int:
+        n = self._lib.stg_history_length(self._h, slot)
+        if n < 0:
+            raise StingrayError(-n, self._error(self._h))
+        return n
 
     # -- vocabulary-sharded mode ---------------------------------------------------------------------
     @staticmethod

@@ -90,6 +90,8 @@ def lib() -> C.CDLL:
         _lib = C.CDLL(build())
         _f32p = C.POINTER(C.c_float)
         _i32p = C.POINTER(C.c_int32)
+        _lib.orc_softcap_inplace.restype = None
+        _lib.orc_softcap_inplace.argtypes = [_f32p, C.c_int64, C.c_float]
         _lib.orc_greedy.restype = C.c_int32
         _lib.orc_greedy.argtypes = [_f32p, C.c_int32]
         _lib.orc_sample.restype = C.c_int32
@@ -171,6 +173,13 @@ class SampleResult:
     cand_vals: np.ndarray | None = None
     cand_probs: np.ndarray | None = None
     probs: np.ndarray | None = None
+
+
+def softcap(logits, cap: float) -> np.ndarray:
+    """A soft-capped copy of ``logits`` (any shape): tanh(x / cap) * cap in float32."""
+    a = np.array(logits, dtype=np.float32, order="C", copy=True)
+    lib().orc_softcap_inplace(a.ctypes.data_as(C.POINTER(C.c_float)), a.size, cap)
+    return a
 
 
 def greedy(logits) -> int:

@@ -69,6 +69,17 @@ static const float NEG_INF = -INFINITY;
 
 /* ---- TensorPrimitives stand-ins ------------------------------------------------------- */
 
+/* Final-logit soft cap, applied in place to the logits before they are sampled
+ * (CudaForwardPass.cs:2434): x[i] = tanh(x[i] / cap) * cap, the scalar statement of the GPU kernel
+ * llm_softcap_inplace (CudaTextKernels.cs:374-383).  The reference's CPU route
+ * (SimdKernels.SoftcapInPlace, src/OpenTail.Stingray.Cpu/SimdKernels.cs:7133) evaluates the same
+ * function with a vectorised exp approximation; neither is pinned to the last bit by a reference
+ * test, so comparisons against this function carry a tolerance. */
+ORC_API void orc_softcap_inplace(float *x, int64_t n, float cap)
+{
+    for (int64_t i = 0; i < n; i++) x[i] = tanhf(x[i] / cap) * cap;
+}
+
 /* Sampler.Greedy, Sampler.cs:442-446 = TensorPrimitives.IndexOfMax: the highest value, the
  * lowest index on ties; pinned by CudaTextKernels.cs:396-402 and CudaGpuArgmaxParityTests.cs
  * :31-38 (strict '>' left-to-right scan).  Empty span -> 0. */

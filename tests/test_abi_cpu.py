@@ -32,8 +32,8 @@ def test_header_symbols_are_exported():
 def test_struct_layouts_match_the_header():
     _, N = _lib()
     assert C.sizeof(N.StgRowParams) == 32
-    assert C.sizeof(N.StgConfig) == 36
-    assert C.sizeof(N.StgSampleBatch) == 168
+    assert C.sizeof(N.StgConfig) == 40
+    assert C.sizeof(N.StgSampleBatch) == 176
     assert C.sizeof(N.StgStats) == 120
     from opentail.stingray_b200.sampler import PARAMS_DTYPE
 
@@ -44,9 +44,9 @@ def test_create_rejects_bad_config_without_a_device():
     lib, N = _lib()
     h = C.c_void_p()
     assert lib.stg_create(None, C.byref(h)) == 1
-    cfg = N.StgConfig(C.sizeof(N.StgConfig), 0, 0, 1000, 0, 0, 0, 0, 0)
+    cfg = N.StgConfig(C.sizeof(N.StgConfig), 0, 0, 1000, 0, 0, 0, 0, 0, 0)
     assert lib.stg_create(C.byref(cfg), C.byref(h)) == 1  # max_rows must be positive
-    cfg = N.StgConfig(C.sizeof(N.StgConfig), 0, 4, 1000, 8000, 4000, 0, 0, 0)
+    cfg = N.StgConfig(C.sizeof(N.StgConfig), 0, 4, 1000, 8000, 4000, 0, 0, 0, 0)
     assert lib.stg_create(C.byref(cfg), C.byref(h)) == 3  # top_k + history beyond 8192
     buf = C.create_string_buffer(256)
     lib.stg_last_error(None, buf, 256)
@@ -60,7 +60,7 @@ def test_no_cpu_fallback_without_a_device():
         pytest.skip("a CUDA device is present")
     lib, N = _lib()
     h = C.c_void_p()
-    cfg = N.StgConfig(C.sizeof(N.StgConfig), 0, 4, 1000, 16, 16, 0, 0, 0)
+    cfg = N.StgConfig(C.sizeof(N.StgConfig), 0, 4, 1000, 16, 16, 0, 0, 0, 0)
     assert lib.stg_create(C.byref(cfg), C.byref(h)) == 7  # STG_ERR_NO_DEVICE
     from opentail.stingray_b200 import BatchSampler, StingrayError
 
