@@ -142,7 +142,7 @@ int make_plan(StgHandle h, const StgSampleBatch *b, int mode, bool shard, int gl
         if (rp.path == kPathTopK) pl.n_topk++; else if (rp.path == kPathFull) pl.n_full++; else pl.n_greedy++;
     }
     pl.n_chunk_rows = n_chunk_rows;
-    // The flat step needs long, aligned rows and a candidate list (N + 4096 entries) that about 3 N
+    // The flat step needs long, aligned rows and a candidate list (N + kFlatSlack entries) that about 3 N
     // expected survivors fit well inside.
     pl.flat = flat_ok && n_chunk_rows > 0 && V >= 4 * kFlatSample && 3 * (size_t)max_sel + 256 <= (size_t)max_sel + kFlatSlack;
     if (pl.flat) {
@@ -545,6 +545,7 @@ int run_batch(StgHandle h, const StgSampleBatch *b, const BatchExtra &x, void *s
         if (flat_chunks) {
             e = launch_flat_finish(c, fr, n_chunk_items, pl.smem, cs);
             if (e == cudaSuccess) launches++;
+            if (!fork) h->kt.mark("flat_finish", cs);
         } else {
             c.item_base = n_rows_items;
             const int room = h->sm_count - row_grid >= 16 ? h->sm_count - row_grid : h->sm_count;
@@ -692,7 +693,7 @@ int stg_create(const StgConfig *cfg, StgHandle *out)
     if (rc == STG_OK) {
         int lo = 0, hi = 0;
         cudaDeviceGetStreamPriorityRange(&lo, &hi);
-        e = cudaStreamCreateWithPriority(&h->aux_stream, cudaStreamNonBlocking, hi);
+        e = cudaStreamCreateWithPriority(&h->aux_stream, cudaStreamNonBlocking, lo);
         if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->ev_fork, cudaEventDisableTiming);
         if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->ev_join, cudaEventDisableTiming);
         if (e != cudaSuccess) rc = cuda_fail(nullptr, e, "side stream");

@@ -17,7 +17,7 @@ namespace stg {
 // `flat_groups` equal groups of consecutive threads, and the bound is the smallest of the groups'
 // maxima: at least flat_groups elements of the sample lie at or above it, about twice as many on
 // average, and the planner picks flat_groups so that about 3 N elements of the whole row should.
-template <bool BF16>
+template <bool BF16, bool CAP>
 __global__ void __launch_bounds__(kThreads) k_flat_prep(const __grid_constant__ SampleArgs a, FlatRow *fr)
 {
     __shared__ uint32_t red[32];
@@ -29,7 +29,7 @@ __global__ void __launch_bounds__(kThreads) k_flat_prep(const __grid_constant__ 
         return;
     }
     const int esz = BF16 ? 2 : 4;
-    const LogitRow rowp{(const char *)a.logits + (int64_t)row * a.row_stride * esz, a.softcap};
+    const LogitRow rowp{(const char *)a.logits + (int64_t)row * a.row_stride * esz, CAP ? a.softcap : 0.f};
     const uint32_t *mrow = (rp.use_mask && a.mask) ? a.mask + (int64_t)row * a.mask_stride : nullptr;
     float v[4];
     int idx[4];
@@ -83,8 +83,9 @@ __device__ __forceinline__ void flat_load4(const LogitRow rowp, const uint32_t *
 
 // One CTA of 256 threads per 16384-element piece of a row (grid.x pieces, grid.y rows).  Sub-step q
 // (0..15) of a piece covers 1024 consecutive elements, thread t its elements 4t .. 4t+3; a thread
-// keeps the loads of the next four sub-steps in flight while it works on the current four.
-template <bool BF16>
+// keeps the loads of the next four sub-steps in flight while it works on the current four.  CAP: the
+// batch has a soft cap (a build of its own, so that the common case carries no trace of it).
+template <bool BF16, bool CAP>
 __global__ void __launch_bounds__(kFlatThreads) k_flat_stream(const __grid_constant__ SampleArgs a, FlatRow *fr, const FullWs ws)
 {
     __shared__ unsigned long long red[kFlatThreads / 32];
@@ -97,7 +98,7 @@ __global__ void __launch_bounds__(kFlatThreads) k_flat_stream(const __grid_const
     if (begin >= end) return;
     const int path = __ldg(&rpp->path);
     const int esz = BF16 ? 2 : 4;
-    const LogitRow rowp{(const char *)a.logits + (int64_t)row * a.row_stride * esz, a.softcap};
+    const LogitRow rowp{(const char *)a.logits + (int64_t)row * a.row_stride * esz, CAP ? a.softcap : 0.f};
     const uint32_t *mrow = (__ldg(&rpp->use_mask) && a.mask) ? a.mask + (int64_t)row * a.mask_stride : nullptr;
     const int i0 = begin + tid * 4;
 
@@ -309,14 +310,11 @@ struct FlatShared {
     int ok;
 };
 
-// One 1024-thread CTA per row of the flat step (a.items lists them).
+// One row of the flat step by a 1024-thread CTA: any top_k, any penalties, and the second chance of
+// a row whose candidate list failed its check.
 template <bool BF16>
-__global__ void __launch_bounds__(kThreads, 1) k_flat_finish(const __grid_constant__ SampleArgs a, FlatRow *fr)
+__device__ void flat_finish_row(const SampleArgs &a, FlatRow *fr, int row, unsigned char *arena, SelCtl &ctl, FlatShared &fs)
 {
-    extern __shared__ __align__(16) unsigned char arena[];
-    __shared__ SelCtl ctl;
-    __shared__ FlatShared fs;
-    const int row = a.items[blockIdx.x].row;
     const RowPlan rp = a.plans[row];
     const int esz = BF16 ? 2 : 4;
     const LogitRow rowp{(const char *)a.logits + (int64_t)row * a.row_stride * esz, a.softcap};
@@ -340,10 +338,13 @@ __global__ void __launch_bounds__(kThreads, 1) k_flat_finish(const __grid_consta
             if (a.tokens) a.tokens[row] = tok;
             if (a.token_probs) a.token_probs[row] = 1.0f;
             if (a.row_flags) a.row_flags[row] = fl;
+            count_row_flags(a.counters, fl);
         }
         return;
     }
     const uint32_t *mrow = (rp.use_mask && a.mask) ? a.mask + (int64_t)row * a.mask_stride : nullptr;
+    unsigned long long *tk = a.phase_ticks ? a.phase_ticks + (int64_t)(a.item_base + blockIdx.x) * 32 : nullptr;
+    tick(tk, 0);
     Sel s;
     s.c = &ctl;
     s.buf[0] = (u64 *)arena;
@@ -363,15 +364,35 @@ __global__ void __launch_bounds__(kThreads, 1) k_flat_finish(const __grid_consta
         // (when no penalty can promote a logit the finish works on the whole list, see finish_topk_select)
         sel_append_keys(s, a.cand + rp.cand_off, cnt, !(rp.top_k <= kFastFinishK && penalties_only_demote(rp)));
     } else {
-        // the bound was off (or dropped candidates): the exact, self-correcting selection over the row
-        sel_stream<4, BF16>(s, rowp, mrow, 0, a.vocab);
+        // the bound was off (or dropped candidates): the row is read again by this CTA, with a generous
+        // bound first (about 8 N survivors, capacity permitting) and the exact selection behind it
+        const int over = (int)max(5ll, min(16ll, (long long)s.cap / max(s.n, 1)));
+        const FlatRow f = fr[row];
+        bool preset = false;
+        float bound = 0.f;
+        if (f.tau > -CUDART_INF_F && f.cnt > f.cap && f.cap > rp.sel && f.cap <= s.cap) {
+            // too many passed the first bound: the list kept f.cap of them, some subset.  The N-th best of a
+            // subset is no higher than the N-th best of the row, so everything at or above it is a superset of
+            // the row's best N - and a far smaller one than before
+            sel_append_keys(s, a.cand + rp.cand_off, f.cap, false);
+            sel_raise(s);
+            const uint32_t o = ord32(ctl.tau);
+            bound = unord32(o > 0u ? o - 1u : 0u);  // the next value below: the strict test then keeps ties with the bound
+            preset = true;
+            __syncthreads();
+            sel_reset(s);
+        }
+        sel_stream_generous<4, BF16>(s, rowp, mrow, 0, a.vocab, over, preset, bound);
     }
+    tick(tk, 1);
+    if (tk && threadIdx.x == 0) { tk[8] = (unsigned long long)(long long)cnt; tk[9] = (unsigned long long)fr[row].cnt; tk[10] = (unsigned long long)fr[row].cap; }
     const int32_t *hist = a.hist_ids ? a.hist_ids + rp.hist_off : nullptr;
     const float *ptab = (a.pow_tab && rp.pow_off >= 0) ? a.pow_tab + rp.pow_off : nullptr;
     const float u = a.uniforms ? __ldg(a.uniforms + row) : 0.5f;
     const int64_t o = (int64_t)row * a.topk_stride;
     finish_topk(s, rp, hist, ptab, u, &fs.fout, a.topk_ids ? a.topk_ids + o : nullptr,
                 a.topk_logits ? a.topk_logits + o : nullptr, a.topk_probs ? a.topk_probs + o : nullptr);
+    tick(tk, 3);
     if (threadIdx.x == 0) {
         a.tokens[row] = fs.fout.token;
         if (a.token_probs) a.token_probs[row] = fs.fout.prob;
@@ -381,18 +402,30 @@ __global__ void __launch_bounds__(kThreads, 1) k_flat_finish(const __grid_consta
     }
 }
 
+// One CTA per row of a.items.
+template <bool BF16>
+__global__ void __launch_bounds__(kThreads, 1) k_flat_finish(const __grid_constant__ SampleArgs a, FlatRow *fr)
+{
+    extern __shared__ __align__(16) unsigned char arena[];
+    __shared__ SelCtl ctl;
+    __shared__ FlatShared fs;
+    flat_finish_row<BF16>(a, fr, a.items[blockIdx.x].row, arena, ctl, fs);
+}
+
 cudaError_t launch_flat_prep(const SampleArgs &a, FlatRow *fr, cudaStream_t stream)
 {
-    if (a.dtype == 1) k_flat_prep<true><<<a.rows, kThreads, 0, stream>>>(a, fr);
-    else k_flat_prep<false><<<a.rows, kThreads, 0, stream>>>(a, fr);
+    const bool cap = a.softcap != 0.f;
+    if (a.dtype == 1) { if (cap) k_flat_prep<true, true><<<a.rows, kThreads, 0, stream>>>(a, fr); else k_flat_prep<true, false><<<a.rows, kThreads, 0, stream>>>(a, fr); }
+    else { if (cap) k_flat_prep<false, true><<<a.rows, kThreads, 0, stream>>>(a, fr); else k_flat_prep<false, false><<<a.rows, kThreads, 0, stream>>>(a, fr); }
     return cudaGetLastError();
 }
 
 cudaError_t launch_flat_stream(const SampleArgs &a, FlatRow *fr, const FullWs &ws, cudaStream_t stream)
 {
     const dim3 grid((unsigned)((a.vocab + kFlatPiece - 1) / kFlatPiece), (unsigned)a.rows);
-    if (a.dtype == 1) k_flat_stream<true><<<grid, kFlatThreads, 0, stream>>>(a, fr, ws);
-    else k_flat_stream<false><<<grid, kFlatThreads, 0, stream>>>(a, fr, ws);
+    const bool cap = a.softcap != 0.f;
+    if (a.dtype == 1) { if (cap) k_flat_stream<true, true><<<grid, kFlatThreads, 0, stream>>>(a, fr, ws); else k_flat_stream<true, false><<<grid, kFlatThreads, 0, stream>>>(a, fr, ws); }
+    else { if (cap) k_flat_stream<false, true><<<grid, kFlatThreads, 0, stream>>>(a, fr, ws); else k_flat_stream<false, false><<<grid, kFlatThreads, 0, stream>>>(a, fr, ws); }
     return cudaGetLastError();
 }
 

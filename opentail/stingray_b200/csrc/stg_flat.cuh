@@ -33,7 +33,7 @@ constexpr int kFlatThreads = 256;                  // threads of a k_flat_stream
 constexpr int kFlatPiece = 16384;                  // elements of a row one such CTA reads
 constexpr int kFlatSteps = kFlatPiece / 4096;      // steps of 4 sub-steps of 1024 elements each
 constexpr int kFlatSample = 4096;                  // leading elements of a row the bound is guessed from
-constexpr int kFlatSlack = 4096;                   // candidate capacity of a top-k row beyond N
+constexpr int kFlatSlack = 8192;                   // candidate capacity of a top-k row beyond N (the bound scatters: up to ~3x the expected count was seen)
 constexpr int kFlatStage = 1024;                   // candidates a k_flat_stream CTA collects in shared memory
 
 // per-row state of the flat step (device memory, 32 bytes)

@@ -72,7 +72,7 @@ struct StgSampler_ {
     int64_t escratch_stride = 0, key_stride = 0;
     size_t cand_entries = 0;
     uint32_t work_base = 0, work_base_rows = 0;
-    cudaStream_t aux_stream = nullptr;   // the row kernel runs here, beside the chunk kernel
+    cudaStream_t aux_stream = nullptr;   // lowest priority: the chunked rows' finish runs here, beside the full rows' phases
     cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
     size_t plan_bytes_cap = 0;
     // exchange buffers of the vocabulary-sharded mode

@@ -517,6 +517,85 @@ static __device__ void sel_stream(Sel &s, const LogitRow rowp, const uint32_t *m
     if (c->cnt > 2 * s.n) sel_compact(s);
 }
 
+// A whole row by one CTA when time matters more than certainty (the second chance of a row of the
+// flat step, stg_flat.cu): the bound is set from the first sub-tile as in sel_stream_pass, but
+// generously - about `over` / 2 times N elements of the row should pass - and the rest of the row is
+// filtered against it without any block-wide step: a thread that finds an element above the bound
+// appends it by itself.  The outcome is checked like every optimistic bound here (N or more
+// survivors, none dropped for lack of room); on failure the exact, self-correcting sel_stream runs.
+// `preset`: the caller knows a bound below which no element of the best N lies (tau_preset); the
+// sample is skipped and the whole range filtered against it.
+template <int VEC, bool BF16>
+static __device__ void sel_stream_generous(Sel &s, const LogitRow rowp, const uint32_t *mrow, int begin, int end, int over,
+                                           bool preset, float tau_preset)
+{
+    SelCtl *c = s.c;
+    constexpr int STEP = kThreads * 16;
+    int first_end = min(end, begin + kSubTile);
+    bool ok = preset || end - begin >= 4 * kSubTile;
+    if (preset) {
+        if (threadIdx.x == 0) c->tau = tau_preset;
+        __syncthreads();
+        first_end = begin;
+    } else if (ok) {
+        float v[4];
+        int idx[4];
+        load_items<VEC, BF16, true>(rowp, mrow, begin, 0, first_end, v, idx);
+        sel_append_exact(s, v, idx, first_end);
+        ok = c->cnt > s.n;
+        if (ok) {
+            const int n_saved = s.n;
+            const long long m = ((long long)over * s.n * kSubTile) / (2ll * (long long)(end - begin));
+            s.n = (int)max(32ll, min((long long)s.n, m));
+            sel_raise(s);
+            s.n = n_saved;
+        }
+    }
+    if (ok) {
+        const float tau = c->tau;
+        u64 *b = s.buf[c->cur];
+        float va[4][4], vb[4][4];
+        int base = first_end;
+        auto filter = [&](const float (&v)[4][4], int at) {
+#pragma unroll
+            for (int u = 0; u < 4; u++)
+#pragma unroll
+                for (int e = 0; e < 4; e++)
+                    if (v[u][e] > tau) {  // out of range and masked elements read -inf
+                        const int slot = atomicAdd(&c->cnt, 1);
+                        if (slot < s.cap) b[slot] = make_key(v[u][e], item_index<VEC>(at, u, e) + s.idx_off);
+                    }
+        };
+        if (base < end) {
+            sel_load_iter<VEC, BF16>(rowp, mrow, base, end, va);
+            for (;;) {
+                int nb = base + STEP;
+                bool more = nb < end;
+                if (more) sel_load_iter<VEC, BF16>(rowp, mrow, nb, end, vb);
+                filter(va, base);
+                if (!more) break;
+                base = nb;
+                nb = base + STEP;
+                more = nb < end;
+                if (more) sel_load_iter<VEC, BF16>(rowp, mrow, nb, end, va);
+                filter(vb, base);
+                if (!more) break;
+                base = nb;
+            }
+        }
+        __syncthreads();
+        ok = c->cnt >= s.n && c->cnt <= s.cap;
+        __syncthreads();
+    }
+    if (!ok) {
+        sel_reset(s);
+        sel_stream<VEC, BF16>(s, rowp, mrow, begin, end);
+        return;
+    }
+    if (c->cnt > 2 * s.n) sel_raise(s);
+    if (c->cnt > 2 * s.n) sel_compact(s);
+}
+
 // Appends `count` keys from global memory (another chunk's survivors).
 static __device__ void sel_append_keys(Sel &s, const u64 *keys, int count, bool reduce = true)
 {
@@ -639,6 +718,7 @@ static __device__ void select_thr32(SelCtl *c, const uint32_t *P, int cnt, int w
                         c->want = (int)(want - acc);
                         if (pass == 0) {
                             c->stop = 1;  // np is the exact threshold value
+                            c->cut = (int)h[j];  // entries equal to it
                         } else if (h[j] == want - acc) {
                             c->stop = 2;  // the whole bucket is taken: no ties to resolve
                             c->thr = (u64)np << sh;
@@ -658,7 +738,10 @@ static __device__ void select_thr32(SelCtl *c, const uint32_t *P, int cnt, int w
         *need = lo ? 0 : 0x7FFFFFFF;           // lo == 0: every entry, also those equal to 0
     } else {
         *thr = (uint32_t)c->prefix;
-        *need = c->want;
+        // all the entries equal to the threshold are wanted: nothing to rank, they are taken like the ones above
+        const uint32_t at = (uint32_t)c->prefix;
+        if (c->want >= c->cut && at != 0u) { *thr = at - 1u; *need = 0; }
+        else *need = c->want;
     }
     __syncthreads();
 }
