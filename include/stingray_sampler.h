@@ -17,6 +17,12 @@
  * thread, src/OpenTail.Stingray.Engine/ContinuousBatchingEngine.cs:495-500); distinct handles are
  * independent.  Work is enqueued on the caller's stream; a call blocks only when it has to hand
  * results back in host memory (STG_MEM_HOST_OUTPUTS) or is documented as blocking.
+ *
+ * Streams: the workspace belongs to the handle, so the sampling calls of one handle run one after
+ * the other on the device.  On a single stream that is the stream's own order; a call on a different
+ * stream than the previous one is put behind everything enqueued on the previous stream so far (an
+ * event, no host wait), which must therefore still exist.  Inputs and outputs follow the usual
+ * rule: they must be ready on, and are ready after, the stream of the call that uses them.
  */
 #ifndef STINGRAY_SAMPLER_H
 #define STINGRAY_SAMPLER_H

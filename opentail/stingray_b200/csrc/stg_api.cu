@@ -327,6 +327,15 @@ int run_batch(StgHandle h, const StgSampleBatch *b, const BatchExtra &x, void *s
     if (rc) return rc;
     if (b->rows == 0) return STG_OK;
     CK(cudaSetDevice(h->cfg.device));
+    // The workspace, the plan and the work counters belong to the handle, so consecutive calls must
+    // not overlap on the device.  On one stream they cannot; when the stream changes, this call is
+    // put behind everything enqueued so far on the previous one.
+    if (h->last_stream_valid && stream != h->last_stream) {
+        CK(cudaEventRecord(h->ev_order, h->last_stream));
+        CK(cudaStreamWaitEvent(stream, h->ev_order, 0));
+    }
+    h->last_stream = stream;
+    h->last_stream_valid = true;
     const uint32_t mf = b->mem_flags;
     const int rows = b->rows, V = b->vocab;
     if ((mode == 0 || mode == 3) && !pairs_out && !b->tokens && !x.shard_mode) return fail(h, STG_ERR_INVALID_ARGUMENT, "tokens is required");
@@ -696,6 +705,7 @@ int stg_create(const StgConfig *cfg, StgHandle *out)
         e = cudaStreamCreateWithPriority(&h->aux_stream, cudaStreamNonBlocking, lo);
         if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->ev_fork, cudaEventDisableTiming);
         if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->ev_join, cudaEventDisableTiming);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->ev_order, cudaEventDisableTiming);
         if (e != cudaSuccess) rc = cuda_fail(nullptr, e, "side stream");
     }
     for (int i = 0; i < 4 && rc == STG_OK; i++) {
@@ -735,6 +745,7 @@ int stg_destroy(StgHandle h)
     for (auto &ev : h->plan_ev) if (ev) cudaEventDestroy(ev);
     if (h->ev_fork) cudaEventDestroy(h->ev_fork);
     if (h->ev_join) cudaEventDestroy(h->ev_join);
+    if (h->ev_order) cudaEventDestroy(h->ev_order);
     if (h->aux_stream) cudaStreamDestroy(h->aux_stream);
     delete h;
     return STG_OK;

@@ -143,7 +143,7 @@ class BatchSampler:
     @staticmethod
     def _stream(stream) -> Optional[int]:
         if stream is not None:
-            return stream
+            return getattr(stream, "cuda_stream", stream)  # a torch.cuda.Stream or a raw handle
         import torch
 
         return torch.cuda.current_stream().cuda_stream

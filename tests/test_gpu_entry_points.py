@@ -123,3 +123,29 @@ def test_resample_residual_reference_literals_and_oracle(bs):
     for r in range(rows):
         want, used, tr = orc.resample_residual(P[r], Q[r], float(u[r, 0]), float(u[r, 1]))
         assert tok[r] == want or tr.margin <= parity.BOUNDARY, f"row {r}: {tok[r]} != {want}"
+
+
+def test_calls_alternating_between_streams_are_ordered(bs):
+    """Two streams driving one handle in turn: every call must see the workspace as the previous call
+    left it, so the results equal those of the same calls on a single stream."""
+    import torch
+    from opentail.stingray_b200 import workloads as W
+
+    ws = [W.config2(rows=48, seed=40 + i) for i in range(4)]
+    devs = [parity.to_device(w) for w in ws]
+    torch.cuda.synchronize()
+
+    def run(streams):
+        outs = []
+        for i in range(8):
+            w, d = ws[i % 4], devs[i % 4]
+            st = streams[i % len(streams)]
+            outs.append(bs.sample_rows(d["logits"], w.params, uniforms=d["uniforms"], history_ids=d["history_ids"],
+                                       history_offsets=w.history_offsets, want_probs=True, stream=st))
+        torch.cuda.synchronize()
+        return [(o["tokens"].cpu().numpy(), o["probs"].cpu().numpy()) for o in outs]
+
+    one = run([torch.cuda.Stream()])
+    two = run([torch.cuda.Stream(), torch.cuda.Stream()])
+    for (t1, p1), (t2, p2) in zip(one, two):
+        assert np.array_equal(t1, t2) and np.array_equal(p1, p2)
