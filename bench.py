@@ -314,6 +314,60 @@ def sampling_leg(w, steps=6, warmup=3, device=0, bs=None, params=None, use_histo
                    else "L2 flushed between steps")}
 
 
+def kernel_times_leg(w, steps=8, warmup=4, device=0):
+    """Device time of every kernel of a sampling step, measured live: a handle created with the
+    library's event timer on (STG_KERNEL_TIMES=1 at stg_create) records a CUDA event on the launching
+    stream after each kernel of a step, and stg_debug_kernel_times returns the intervals.  The steps
+    run back to back on rotating input copies exactly as in the timed region, so the numbers are
+    warm-pipeline times (unlike a profiler's serialised, cache-flushed launches); the extra event
+    records cost a few microseconds per step, which is why this leg is not the headline."""
+    import torch
+    from opentail.stingray_b200 import BatchSampler
+    from opentail.stingray_b200 import _native as N
+
+    hist_max = int(np.diff(w.history_offsets).max()) if w.history_offsets is not None else 0
+    os.environ["STG_KERNEL_TIMES"] = "1"
+    try:
+        bs = BatchSampler(max_rows=w.rows, max_vocab=w.vocab, max_history=max(hist_max, 1),
+                          max_top_k=max(int(w.params["top_k"].max()), 1), device=device)
+    finally:
+        del os.environ["STG_KERNEL_TIMES"]
+    lib = N.load()
+    n_copies = copies_for(w.logits.nbytes)
+    devs = [to_device(w) for _ in range(n_copies)]
+    acc, names = None, None
+    for i in range(warmup + steps):
+        d = devs[i % n_copies]
+        kw = dict(uniforms=d["uniforms"])
+        if w.history_ids is not None:
+            kw.update(history_ids=d["history_ids"], history_offsets=w.history_offsets)
+        if w.mask is not None:
+            kw.update(mask=d["mask"])
+        bs.sample_rows(d["logits"], w.params, **kw)
+        us = np.zeros(32, np.float32)
+        nm = ctypes.create_string_buffer(32 * 24)
+        k = ctypes.c_int32(0)
+        if lib.stg_debug_kernel_times(bs._h, us.ctypes.data, nm, 24, 32, ctypes.byref(k)) != 0:
+            break
+        if i >= warmup:
+            acc = us[:k.value].copy() if acc is None else acc + us[:k.value]
+            names = [nm.raw[j * 24:(j + 1) * 24].split(b"\0")[0].decode() for j in range(k.value)]
+    bs.close()
+    del devs
+    torch.cuda.empty_cache()
+    if acc is None:
+        return {"unavailable": "the event timer returned nothing"}
+    acc = acc / steps
+    peak, _ = measured_peak()
+    out = {"us": {n: round(float(t), 2) for n, t in zip(names, acc)}, "sum_us": round(float(acc.sum()), 1)}
+    if "flat_stream" in out["us"]:
+        # the one kernel that reads the logits from HBM: algorithmic bytes of the step over its own time
+        gbs = w.algorithmic_bytes() / (out["us"]["flat_stream"] * 1e-6) / 1e9
+        out["flat_stream_gbs"] = round(gbs, 1)
+        out["flat_stream_frac"] = round(gbs / peak, 4)
+    return out
+
+
 def spec_leg(steps=4, warmup=3, device=0):
     """Config 4: one speculative verification step, 32 sequences x (9 target + 8 draft) rows."""
     import torch
@@ -726,6 +780,7 @@ def main():
             legs["c2_all_top_k_50"] = sampling_leg(w, device=local, params=topk, use_history=False)
             legs["c2_all_top_k_50_history_512"] = sampling_leg(w, device=local, params=topk_pen)
             legs["c2_vary_plan"] = vary_plan_leg(w, device=local)
+            legs["c2_kernel_times"] = kernel_times_leg(w, device=local)
             legs["reference_gpu_argmax"] = reference_gpu_argmax_leg(w, device=local)
             del flush
             torch.cuda.empty_cache()
@@ -740,7 +795,7 @@ def main():
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_kind": peak_kind, "frac_of_8TBs": achieved / 8000.0,
                          "algorithmic_bytes_per_launch": alg_bytes, "launch_ms": launch_ms_mean,
-                         "traffic": ncu_traffic(f"k_sample_{args.config}")},
+                         "traffic": ncu_traffic(f"sample_step_{args.config}")},
             "e2e": {"value": total_rows / (e2e_ms / 1000.0), "unit": "rows/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": 4 * w.rows, "ms_per_step": e2e_ms,
                     "h2d_gbs_per_rank": h2d / (e2e_ms / 1000.0) / 1e9},

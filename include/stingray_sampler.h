@@ -255,6 +255,13 @@ STG_API int stg_get_stats(StgHandle handle, StgStats *out);
  * (src/OpenTail.Stingray.Engine/DecodeProfileTimers.cs:17-67). */
 STG_API int stg_debug_phase_ticks(StgHandle handle, uint64_t *out, int32_t max_items, int32_t *n_items);
 
+/* Checked handles: a handle created while the environment variable STG_CHECKED=1 is set puts 256
+ * guard bytes of a fixed pattern behind every device buffer it owns.  This call waits for the device
+ * and reads them back: n_guarded = buffers checked (0 for an unchecked handle), first_bad = index of
+ * the first buffer whose guard was overwritten, or -1.  The stand-in for a memory checker where none
+ * can be run. */
+STG_API int stg_debug_check_guards(StgHandle handle, int32_t *n_guarded, int32_t *first_bad);
+
 /* Diagnostic: device time (microseconds) between the kernels of the last sampling step on the caller's
  * stream, measured with CUDA events, and their names (max_items strings of name_len bytes).  Only
  * recorded when the handle was created with STG_KERNEL_TIMES=1 in the environment; blocks. */

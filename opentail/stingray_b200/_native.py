@@ -22,7 +22,7 @@ SEQ_EMPTY_RESIDUAL, SEQ_BAD_DRAFT = 1 << 8, 1 << 9
 
 EXPORTS = [
     "stg_abi_version", "stg_create", "stg_destroy", "stg_last_error", "stg_get_stats", "stg_debug_phase_ticks",
-    "stg_debug_kernel_times",
+    "stg_debug_kernel_times", "stg_debug_check_guards",
     "stg_argmax_rows", "stg_argmax_rows_static", "stg_sample_rows", "stg_build_distribution", "stg_spec_verify",
     "stg_sample_with_distribution", "stg_sample_from_probs", "stg_resample_residual",
     "stg_mtp_accept", "stg_and_masks", "stg_comm_unique_id", "stg_comm_init", "stg_comm_destroy",
@@ -103,6 +103,7 @@ def load() -> C.CDLL:
     lib.stg_last_error.argtypes = [vp, C.c_char_p, C.c_size_t]
     lib.stg_get_stats.argtypes = [vp, C.POINTER(StgStats)]
     lib.stg_debug_phase_ticks.argtypes = [vp, vp, i32, C.POINTER(C.c_int32)]
+    lib.stg_debug_check_guards.argtypes = [vp, C.POINTER(C.c_int32), C.POINTER(C.c_int32)]
     lib.stg_debug_kernel_times.argtypes = [vp, vp, vp, i32, i32, C.POINTER(C.c_int32)]
     lib.stg_argmax_rows.argtypes = [vp, vp, i32, i32, i32, i64, vp, vp]
     lib.stg_argmax_rows_static.argtypes = [vp, i32, i32, i32, i64, vp, vp]

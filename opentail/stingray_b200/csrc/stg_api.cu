@@ -36,9 +36,16 @@ int cuda_fail(StgHandle h, cudaError_t e, const char *what)
 int dev_alloc(StgHandle h, DevBuf &b, size_t bytes)
 {
     bytes = std::max<size_t>(bytes, 256);
-    cudaError_t e = cudaMalloc(&b.p, bytes);
+    const bool guard = h != nullptr && h->checked;
+    if (guard) bytes = round_up(bytes, 256);
+    cudaError_t e = cudaMalloc(&b.p, bytes + (guard ? kGuardBytes : 0));
     if (e != cudaSuccess) return cuda_fail(h, e, "cudaMalloc");
     b.bytes = bytes;
+    b.guarded = guard;
+    if (guard) {
+        e = cudaMemset((char *)b.p + bytes, kGuardByte, kGuardBytes);
+        if (e != cudaSuccess) return cuda_fail(h, e, "cudaMemset");
+    }
     return STG_OK;
 }
 
@@ -47,6 +54,7 @@ void dev_free(DevBuf &b)
     if (b.p) cudaFree(b.p);
     b.p = nullptr;
     b.bytes = 0;
+    b.guarded = false;
 }
 
 }  // namespace stg
@@ -592,6 +600,17 @@ int run_batch(StgHandle h, const StgSampleBatch *b, const BatchExtra &x, void *s
     return STG_OK;
 }
 
+// every device buffer a handle owns
+std::vector<DevBuf *> all_buffers(StgHandle h)
+{
+    return {&h->plan_dev, &h->flat_rows, &h->fw_rows, &h->fw_e, &h->fw_keys, &h->fw_ov_id, &h->fw_ov_adj, &h->fw_ew, &h->fw_hist,
+            &h->fw_bstart, &h->fw_binexp, &h->fw_flagbits, &h->fw_cursor, &h->cand, &h->cand_count, &h->tickets, &h->work_counter,
+            &h->escratch, &h->keyscratch, &h->listscratch, &h->dists, &h->st_hist, &h->st_bias_ids, &h->st_bias_vals, &h->st_uniforms,
+            &h->st_mask, &h->st_logits, &h->o_tokens, &h->o_probs, &h->o_flags, &h->o_topk_ids, &h->o_topk_vals, &h->o_topk_probs,
+            &h->o_pairs, &h->ticks, &h->ring_ids, &h->ring_len_dev, &h->mc_words, &h->mc_slots, &h->sp_draft, &h->sp_uniforms,
+            &h->sp_accepted, &h->sp_correction, &h->sp_aprobs, &h->sp_flags, &h->sp_rowstats, &h->xchg_local, &h->xchg_gather};
+}
+
 }  // namespace stg
 
 extern "C" {
@@ -622,6 +641,7 @@ int stg_create(const StgConfig *cfg, StgHandle *out)
 
     h = new StgSampler_();
     h->cfg = *cfg;
+    h->checked = getenv("STG_CHECKED") != nullptr && getenv("STG_CHECKED")[0] == '1';
     h->sm_count = prop.multiProcessorCount;
     h->smem_optin = prop.sharedMemPerBlockOptin > 4096 ? prop.sharedMemPerBlockOptin - 4096 : 0;
     const size_t R = (size_t)cfg->max_rows, V = (size_t)cfg->max_vocab;
@@ -733,14 +753,7 @@ int stg_destroy(StgHandle h)
     cudaSetDevice(h->cfg.device);
     cudaDeviceSynchronize();
     stg_comm_destroy(h);
-    DevBuf *all[] = {&h->plan_dev, &h->flat_rows, &h->fw_rows, &h->fw_e, &h->fw_keys, &h->fw_ov_id, &h->fw_ov_adj, &h->fw_ew, &h->fw_hist,
-                     &h->fw_bstart, &h->fw_binexp, &h->fw_flagbits, &h->fw_cursor, &h->cand, &h->cand_count, &h->tickets, &h->work_counter, &h->escratch, &h->keyscratch, &h->listscratch,
-                     &h->dists, &h->st_hist, &h->st_bias_ids, &h->st_bias_vals, &h->st_uniforms, &h->st_mask, &h->st_logits,
-                     &h->o_tokens, &h->o_probs, &h->o_flags, &h->o_topk_ids, &h->o_topk_vals, &h->o_topk_probs, &h->o_pairs, &h->ticks,
-                     &h->ring_ids, &h->ring_len_dev, &h->mc_words, &h->mc_slots,
-                     &h->sp_draft, &h->sp_uniforms, &h->sp_accepted, &h->sp_correction, &h->sp_aprobs, &h->sp_flags,
-                     &h->sp_rowstats, &h->xchg_local, &h->xchg_gather};
-    for (DevBuf *b : all) dev_free(*b);
+    for (DevBuf *b : all_buffers(h)) dev_free(*b);
     if (h->plan_host) cudaFreeHost(h->plan_host);
     for (auto &ev : h->plan_ev) if (ev) cudaEventDestroy(ev);
     if (h->ev_fork) cudaEventDestroy(h->ev_fork);
@@ -748,6 +761,27 @@ int stg_destroy(StgHandle h)
     if (h->ev_order) cudaEventDestroy(h->ev_order);
     if (h->aux_stream) cudaStreamDestroy(h->aux_stream);
     delete h;
+    return STG_OK;
+}
+
+int stg_debug_check_guards(StgHandle h, int32_t *n_guarded, int32_t *first_bad)
+{
+    if (!h || !n_guarded || !first_bad) return STG_ERR_INVALID_ARGUMENT;
+    *n_guarded = 0;
+    *first_bad = -1;
+    CK(cudaSetDevice(h->cfg.device));
+    CK(cudaDeviceSynchronize());
+    std::vector<unsigned char> tail(kGuardBytes);
+    int index = 0;
+    for (DevBuf *b : all_buffers(h)) {
+        if (b->p && b->guarded) {
+            CK(cudaMemcpy(tail.data(), (char *)b->p + b->bytes, kGuardBytes, cudaMemcpyDeviceToHost));
+            ++*n_guarded;
+            for (unsigned char c : tail)
+                if (c != kGuardByte && *first_bad < 0) *first_bad = index;
+        }
+        index++;
+    }
     return STG_OK;
 }
 

@@ -17,7 +17,10 @@ namespace stg {
 struct DevBuf {
     void *p = nullptr;
     size_t bytes = 0;
+    bool guarded = false;  // checked build of the handle: kGuardBytes of a fixed pattern follow the buffer
 };
+constexpr size_t kGuardBytes = 256;
+constexpr int kGuardByte = 0xC5;
 
 // The host plan of one sampling step (built by make_plan in stg_api.cu).
 struct Plan {
@@ -45,6 +48,7 @@ struct StgSampler_ {
     size_t smem_optin = 0;
     std::string err;
     StgStats stats{};
+    bool checked = false;                // STG_CHECKED=1 at creation: guard words behind every device buffer
 
     // workspace (allocated once at creation)
     stg::DevBuf plan_dev;                // RowPlan[], WorkItem[], pow table
