@@ -519,7 +519,7 @@ int run_batch(StgHandle h, const StgSampleBatch *b, const BatchExtra &x, void *s
     ws.bin_exp = (unsigned char *)h->fw_binexp.p; ws.flag_bits = (uint32_t *)h->fw_flagbits.p;
     ws.cursor = (uint32_t *)h->fw_cursor.p; ws.keys = (uint32_t *)h->fw_keys.p; ws.key_stride = h->key_stride;
     const bool flat_chunks = pl.flat && n_chunk_items > 0, flat_full = pl.flat_full && n_rows_items > 0;
-    auto launch_rows_kernel = [&](bool redo_only) {
+    auto launch_rows_kernel = [&](bool redo_only, cudaStream_t on) {
         SampleArgs r = a;
         r.n_items = n_rows_items;
         r.item_base = 0;
@@ -527,7 +527,7 @@ int run_batch(StgHandle h, const StgSampleBatch *b, const BatchExtra &x, void *s
         r.work_base = h->work_base_rows;
         if (redo_only) { r.redo_flags = &ws.rows[0].redo; r.redo_stride = (int32_t)(sizeof(FullRow) / 4); }
         row_grid = std::min(n_rows_items, h->sm_count);
-        cudaError_t er = launch_sample_rows(r, row_grid, stream);
+        cudaError_t er = launch_sample_rows(r, row_grid, on);
         if (er == cudaSuccess) { h->work_base_rows += (uint32_t)n_rows_items + (uint32_t)row_grid; launches++; }
         return er;
     };
@@ -540,24 +540,15 @@ int run_batch(StgHandle h, const StgSampleBatch *b, const BatchExtra &x, void *s
         if (e == cudaSuccess && flat_full) { e = launch_full_prep(a, ws, stream); launches++; h->kt.mark("full_prep", stream); }
         if (e == cudaSuccess) { e = launch_flat_stream(a, fr, ws, stream); launches++; h->kt.mark("flat_stream", stream); }
     }
-    const bool fork = both || (flat_chunks && n_rows_items > 0);
+    const bool flat_rows = flat_full && n_rows_items > 0;
+    const bool fork = both || flat_rows;  // the redo pass of the flat full rows runs on the side stream too
     if (e == cudaSuccess && fork) {
         e = cudaEventRecord(h->ev_fork, stream);
         if (e == cudaSuccess) e = cudaStreamWaitEvent(h->aux_stream, h->ev_fork, 0);
     }
-    // the full rows (main stream) ...
-    if (e == cudaSuccess && n_rows_items > 0) {
-        if (flat_full) {
-            e = launch_full_rest(a, ws, a.items, n_rows_items, &launches, &h->kt, stream);
-            if (e == cudaSuccess) e = launch_rows_kernel(true);  // rows the flat form flagged; the others leave at once
-            h->kt.mark("rows_redo", stream);
-        } else {
-            e = launch_rows_kernel(false);
-            h->kt.mark("rows_kernel", stream);
-        }
-    }
-    // ... beside the chunked rows (side stream when both kinds exist)
-    if (e == cudaSuccess && n_chunk_items > 0) {
+    // the chunked rows: on the side stream when the step also has full rows
+    auto launch_chunked = [&]() {
+        if (e != cudaSuccess || n_chunk_items == 0) return;
         cudaStream_t cs = fork ? h->aux_stream : stream;
         if (flat_chunks) {
             e = launch_flat_finish(c, fr, n_chunk_items, pl.smem, cs);
@@ -570,8 +561,25 @@ int run_batch(StgHandle h, const StgSampleBatch *b, const BatchExtra &x, void *s
             e = launch_sample_chunks(c, grid, pl.smem, cs);
             if (e == cudaSuccess) { h->work_base += (uint32_t)n_chunk_items + (uint32_t)grid; launches++; }
         }
-        if (e == cudaSuccess && fork) e = cudaEventRecord(h->ev_join, h->aux_stream);
+    };
+    if (flat_rows) {
+        // Main stream: the phases of the full rows.  Side stream: the finish of the chunked rows, and
+        // behind it - once the cut kernel has said which rows the flat form gave up - the row kernel
+        // for exactly those (every other CTA of it leaves at once), beside the draw's two kernels.
+        launch_chunked();
+        if (e == cudaSuccess) e = launch_full_rest(a, ws, a.items, n_rows_items, &launches, &h->kt, stream, 0);
+        if (e == cudaSuccess) e = cudaEventRecord(h->ev_cut, stream);
+        if (e == cudaSuccess) e = cudaStreamWaitEvent(h->aux_stream, h->ev_cut, 0);
+        if (e == cudaSuccess) e = launch_rows_kernel(true, h->aux_stream);
+        if (e == cudaSuccess) e = launch_full_rest(a, ws, a.items, n_rows_items, &launches, &h->kt, stream, 1);
+    } else {
+        if (e == cudaSuccess && n_rows_items > 0) {
+            e = launch_rows_kernel(false, stream);
+            h->kt.mark("rows_kernel", stream);
+        }
+        launch_chunked();
     }
+    if (e == cudaSuccess && fork) e = cudaEventRecord(h->ev_join, h->aux_stream);
     if (e == cudaSuccess && fork) e = cudaStreamWaitEvent(stream, h->ev_join, 0);
     h->kt.mark("join_side_stream", stream);
     if (e != cudaSuccess) {
@@ -726,6 +734,7 @@ int stg_create(const StgConfig *cfg, StgHandle *out)
         if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->ev_fork, cudaEventDisableTiming);
         if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->ev_join, cudaEventDisableTiming);
         if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->ev_order, cudaEventDisableTiming);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->ev_cut, cudaEventDisableTiming);
         if (e != cudaSuccess) rc = cuda_fail(nullptr, e, "side stream");
     }
     for (int i = 0; i < 4 && rc == STG_OK; i++) {
@@ -759,6 +768,7 @@ int stg_destroy(StgHandle h)
     if (h->ev_fork) cudaEventDestroy(h->ev_fork);
     if (h->ev_join) cudaEventDestroy(h->ev_join);
     if (h->ev_order) cudaEventDestroy(h->ev_order);
+    if (h->ev_cut) cudaEventDestroy(h->ev_cut);
     if (h->aux_stream) cudaStreamDestroy(h->aux_stream);
     delete h;
     return STG_OK;

@@ -55,14 +55,15 @@ static_assert(sizeof(FlatRow) == 32, "FlatRow layout");
 //
 //   prep     history / bias overrides of the row -> a sorted (token, adjusted logit) list
 //   stream   HBM read: mask, overrides, 1/T -> x (stored), running max key
-//   exp      e = exp(x - max) (stored over x), sub-tile sums, exp-value histogram
-//   scan     fp64 prefix of the sub-tile sums -> guessed binade per sub-tile
-//   comp     composite increment of every sub-tile under its guess
+//   exp      e = exp(x - max) (stored over x), sub-tile sums, exp-value histogram; then, in the same
+//            CTA, the guessed binade of every sub-tile of the piece (fp64 prefix of the sub-tile sums:
+//            the pieces before it publish their totals, a bounded look-back collects them) and the
+//            composite increment of every sub-tile under its guess
 //   walk     exact softmax sum; min-p threshold; top-p plan (bound, bin starts, flagged bins)
 //   scatter  candidates above the bound into bin order (or fp64 partial sums without top-p)
 //   cut      dirty-bin sorts and the emulated sorted-order sum -> top-p threshold; normalise
-//   sums, scan, comp, draw   the same three steps over the final probabilities, then the walk that
-//            finds the token the uniform lands on
+//   sums     the same over the final probabilities (sub-tile sums, look-back, guesses, composites)
+//   draw     the walk that finds the token the uniform lands on
 //
 // A row the flat step cannot finish (its nucleus bound proved too tight) is flagged and redone by the
 // self-contained row kernel afterwards.
@@ -82,6 +83,12 @@ struct FullRow {
     uint32_t flags;                     // STG_ROW_* bits gathered on the way
     int32_t pad;
     double part[kFullMaxParts];         // rows without top-p: per-piece fp64 sums of the probabilities
+    // look-back between the CTAs of a per-piece phase kernel ([0]: exp values, [1]: final probabilities):
+    // every piece publishes the sum of its sub-tile sums and reads those of the pieces before it
+    double ptotal[2][kFullMaxParts];
+    uint32_t pflag[2][kFullMaxParts];   // 1: ptotal is there (cleared by k_full_prep)
+    int32_t n_cross[2];                 // crossing slots handed out (Emul2Work::xs)
+    int32_t pad2[2];
 };
 
 struct Emul2Work;
@@ -107,7 +114,7 @@ cudaError_t launch_flat_stream(const SampleArgs &a, FlatRow *fr, const FullWs &w
 cudaError_t launch_full_prep(const SampleArgs &a, const FullWs &ws, cudaStream_t stream);
 struct KernelTimer;
 cudaError_t launch_full_rest(const SampleArgs &a, const FullWs &ws, const WorkItem *full_items, int n_full, int *launches,
-                             KernelTimer *kt, cudaStream_t stream);
+                             KernelTimer *kt, cudaStream_t stream, int part);
 cudaError_t launch_flat_finish(const SampleArgs &a, FlatRow *fr, int n_rows, size_t smem, cudaStream_t stream);
 
 }  // namespace stg

@@ -43,7 +43,9 @@ __global__ void __launch_bounds__(kThreads, 1) k_full_prep(const __grid_constant
         fr->maxkey = 0ull; fr->rawkey = 0ull; fr->sum = 0.f; fr->surv = 0; fr->redo = 0; fr->flags = 0u;
         fr->c_lo = 0; fr->bound = 0; fr->n_ov = 0;
         for (int p = 0; p <= kFullMaxPieces; p++) fr->ov_piece[p] = 0;
+        fr->n_cross[0] = 0; fr->n_cross[1] = 0;
     }
+    if (tid < 2 * kFullMaxParts) fr->pflag[tid / kFullMaxParts][tid % kFullMaxParts] = 0u;
     if (row_wants_topp(rp) && !greedy) {
         unsigned long long *hist = ws.hist + (size_t)fi * kHistBins;
         uint32_t *cursor = ws.cursor + (size_t)fi * kHistBins;
@@ -97,6 +99,149 @@ __global__ void __launch_bounds__(kThreads, 1) k_full_prep(const __grid_constant
     if (tid == 0) fr->n_ov = cnt;
 }
 
+// ---- look-back over the pieces of a row; guesses and composites of a piece --------------------------------
+// A per-piece phase kernel needs, for every sub-tile, the binade the sequential running sum is in
+// when it gets there - a guess from the fp64 prefix of the sub-tile sums (stg_emul2.cuh, phase B).
+// Inside a piece that is a warp scan; across pieces every CTA publishes the total of its piece
+// (FullRow::ptotal, then the flag, release order) and collects the totals of the pieces before it.
+// Those belong to CTAs with a lower linear block index, which the hardware has dispatched before this
+// one, so they are running or done and none of them waits for a later piece.  The wait is bounded all
+// the same: when it runs out the row is flagged `redo` (the self-contained row kernel takes it) and
+// the CTA leaves.
+constexpr int kLookbackSpins = 100000;  // x 40 ns: a few milliseconds at most
+
+__device__ __forceinline__ uint32_t ld_acquire_u32(const uint32_t *p)
+{
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// Warp 0 of the CTA of piece `p` (k: 0 exp values, 1 final probabilities), given the sums of the
+// piece's sub-tiles in shared memory (s_sum[0..nloc)): publishes the piece total, looks back, and
+// leaves the guessed binade and the crossing slot of every sub-tile of the piece in shared memory
+// and in the row's Emul2Work.  Returns false (to every lane) when the look-back timed out.
+__device__ __forceinline__ bool piece_guesses(FullRow *fr, Emul2Work *ew, int k, int p, int t0, int nloc, int nsub,
+                                              const float *s_sum, unsigned char *s_guess, unsigned char *s_xslot)
+{
+    const int lane = threadIdx.x & 31;
+    const double mine = lane < nloc ? (double)s_sum[lane] : 0.0;
+    double tot = mine;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) tot += __shfl_xor_sync(0xFFFFFFFFu, tot, o);
+    if (lane == 0) {
+        __stcg(&fr->ptotal[k][p], tot);
+        __threadfence();
+        atomicExch(&fr->pflag[k][p], 1u);
+    }
+    bool ok = true;
+    double before = 0.0;
+    if (lane < p) {
+        int it = 0;
+        while (ld_acquire_u32(&fr->pflag[k][lane]) == 0u) {
+            if (++it > kLookbackSpins) { ok = false; break; }
+            __nanosleep(40);
+        }
+        if (ok) before = __ldcg(&fr->ptotal[k][lane]);
+    }
+    ok = __all_sync(0xFFFFFFFFu, ok);
+    // sum of the earlier pieces' totals in piece order (lane 0 adds them: a guess needs no more, but
+    // every CTA of the row must see the same prefix at a piece boundary whoever computes it)
+    double base = 0.0;
+    for (int q = 0; q < p; q++) base += __shfl_sync(0xFFFFFFFFu, before, q);
+    double inc = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const double t = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+        if (lane >= o) inc += t;
+    }
+    const int g = exp_of_double(base + (inc - mine));
+    const int gnext = exp_of_double(base + inc);  // the guess at the sub-tile behind this one
+    int xs = 0;
+    if (ok && lane < nloc && t0 + lane + 1 < nsub && gnext == g + 1 && s_sum[lane] > 0.f) {
+        // the sum should pass into the next binade inside this sub-tile: it gets a CrossSlot
+        const int slot = atomicAdd(&fr->n_cross[k], 1);
+        if (slot < kMaxCross) xs = slot + 1;
+    }
+    if (lane < nloc) {
+        s_guess[lane] = (unsigned char)g;
+        s_xslot[lane] = (unsigned char)xs;
+        ew->guess[t0 + lane] = (unsigned char)g;
+        ew->xslot[t0 + lane] = (unsigned char)xs;
+    }
+    if (!ok && lane == 0) fr->redo = 1;
+    return ok;
+}
+
+// Composite increment of every sub-tile of the piece under its guess (phase C), CrossSlots included.
+// FINAL: over the final probabilities, else over the exp values.  All threads of the CTA.
+template <bool FINAL>
+__device__ __forceinline__ void piece_composites(Emul2Work *ew, const float *e, const ProvFinal &pf, int begin, int n,
+                                                 const float *s_sum, const unsigned char *s_guess, const unsigned char *s_xslot)
+{
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    constexpr int W = kFullThreads / 32;
+    for (int st0 = warp; st0 < kPieceSubTiles; st0 += 2 * W) {
+        float x[2][8];
+        bool live[2];
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int st = st0 + h * W;
+            const int t = (begin >> 8) + st;
+            live[h] = st < kPieceSubTiles && t * kSub < n && !(s_sum[st] == 0.f);  // nothing to add: composite 0
+            const int base = t * kSub + lane * 8;
+            if (!live[h]) continue;
+            if (FINAL) {
+                pf.reload(base, n, x[h]);
+            } else {
+                SrcScratch sc{e, 1.f, false};
+                if (base < n) sc.get8(base, n, x[h]);
+#pragma unroll
+                for (int j = 0; j < 8; j++)
+                    if (base + j >= n) x[h][j] = 0.f;
+            }
+        }
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int st = st0 + h * W;
+            const int t = (begin >> 8) + st;
+            if (st >= kPieceSubTiles || t * kSub >= n) continue;
+            int a0 = 0, a1 = 0;
+            if (live[h]) {
+                const int g = s_guess[st];
+                subtile_composite<false>(x[h], g, a0, a1);
+                const int xsl = s_xslot[st];
+                if (xsl) {
+                    CrossSlot &cs = ew->xs[xsl - 1];
+                    int l0, l1, h0, h1;
+                    lane_composite(x[h], g, l0, l1);
+                    lane_composite(x[h], g + 1, h0, h1);
+                    cs.lo[lane][0] = l0; cs.lo[lane][1] = l1;
+                    cs.hi[lane][0] = h0; cs.hi[lane][1] = h1;
+                }
+            }
+            if (lane == 0) { ew->comp[t][0] = a0; ew->comp[t][1] = a1; }
+        }
+    }
+}
+
+// the tail both per-piece kernels share: look-back and guesses by warp 0, composites by everyone
+template <bool FINAL>
+__device__ __forceinline__ void piece_tail(FullRow *fr, Emul2Work *ew, const float *e, const ProvFinal &pf, int begin, int n,
+                                           float *s_sum, unsigned char *s_guess, unsigned char *s_xslot, int *s_ok)
+{
+    const int t0 = begin >> 8, nsub = (n + kSub - 1) / kSub;
+    const int nloc = min(kPieceSubTiles, nsub - t0);
+    __syncthreads();  // s_sum is complete
+    if (threadIdx.x < 32) {
+        const bool ok = piece_guesses(fr, ew, FINAL ? 1 : 0, begin / kPhasePiece, t0, nloc, nsub, s_sum, s_guess, s_xslot);
+        if (threadIdx.x == 0) *s_ok = ok ? 1 : 0;
+    }
+    __syncthreads();
+    if (!*s_ok) return;
+    piece_composites<FINAL>(ew, e, pf, begin, n, s_sum, s_guess, s_xslot);
+}
+
 // ---- exp: e = exp(x - max), sub-tile sums, histogram ----------------------------------------------------
 // grid (pieces, full rows), 256 threads: warp w takes sub-tiles w, w + 8, ... of the piece, lane l the
 // 8 consecutive elements 8l .. 8l+7 of a sub-tile (the element order the sequential-sum emulation
@@ -106,6 +251,9 @@ __global__ void __launch_bounds__(kFullThreads) k_full_exp(const __grid_constant
 {
     __shared__ unsigned hcnt[kHistBins];
     __shared__ unsigned hmass[kHistBins];
+    __shared__ float s_sum[kPieceSubTiles];
+    __shared__ unsigned char s_guess[kPieceSubTiles], s_xslot[kPieceSubTiles];
+    __shared__ int s_ok;
     const int fi = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int row = full_items[fi].row;
     const RowPlan *rpp = a.plans + row;
@@ -113,7 +261,7 @@ __global__ void __launch_bounds__(kFullThreads) k_full_exp(const __grid_constant
     const int n = a.vocab;
     const int begin = blockIdx.x * kPhasePiece;
     if (begin >= n) return;
-    const FullRow *fr = ws.rows + fi;
+    FullRow *fr = ws.rows + fi;
     const float top_p = __ldg(&rpp->top_p);
     const bool want_hist = top_p < 1.0f && top_p > 0.f;
     const unsigned long long mk = fr->maxkey;
@@ -169,7 +317,7 @@ __global__ void __launch_bounds__(kFullThreads) k_full_exp(const __grid_constant
             if (base < n) store8(e, base, n, x[h]);
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
-            if (lane == 0) ew->sums[(begin >> 8) + st] = acc;
+            if (lane == 0) { ew->sums[(begin >> 8) + st] = acc; s_sum[st] = acc; }
         }
     }
     if (want_hist) {
@@ -180,12 +328,18 @@ __global__ void __launch_bounds__(kFullThreads) k_full_exp(const __grid_constant
             if (c) atomicAdd(&hist[b], ((unsigned long long)c << 40) | (unsigned long long)hmass[b]);
         }
     }
+    // phases B and C of the softmax sum for this piece (the exp values just stored are read back from L2)
+    const ProvFinal none{e, RowDist{}, nullptr};
+    piece_tail<false>(fr, ew, e, none, begin, n, s_sum, s_guess, s_xslot, &s_ok);
 }
 
 // ---- sums of the final probabilities (the draw's phase A) ------------------------------------------------
 __global__ void __launch_bounds__(kFullThreads) k_full_psums(const __grid_constant__ SampleArgs a, const FullWs ws,
                                                              const WorkItem *full_items)
 {
+    __shared__ float s_sum[kPieceSubTiles];
+    __shared__ unsigned char s_guess[kPieceSubTiles], s_xslot[kPieceSubTiles];
+    __shared__ int s_ok;
     const int fi = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int row = full_items[fi].row;
     const RowPlan *rpp = a.plans + row;
@@ -193,7 +347,7 @@ __global__ void __launch_bounds__(kFullThreads) k_full_psums(const __grid_consta
     const int n = a.vocab;
     const int begin = blockIdx.x * kPhasePiece;
     if (begin >= n) return;
-    const FullRow *fr = ws.rows + fi;
+    FullRow *fr = ws.rows + fi;
     if (fr->redo) return;
     const ProvFinal pf{ws.e + (size_t)fi * ws.e_stride, fr->dist, nullptr};
     Emul2Work *ew = ws.ew + fi;
@@ -214,83 +368,10 @@ __global__ void __launch_bounds__(kFullThreads) k_full_psums(const __grid_consta
             for (int j = 0; j < 8; j++) acc += x[h][j] > 0.f ? x[h][j] : 0.f;
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
-            if (lane == 0) ew->sums[(begin >> 8) + st] = acc;
+            if (lane == 0) { ew->sums[(begin >> 8) + st] = acc; s_sum[st] = acc; }
         }
     }
-}
-
-// ---- scan: guessed binade of the running sum at every sub-tile (phase B) -------------------------------
-__global__ void __launch_bounds__(kThreads) k_full_scan(const __grid_constant__ SampleArgs a, const FullWs ws,
-                                                        const WorkItem *full_items)
-{
-    __shared__ Emul2Ctl ctl;
-    const int fi = blockIdx.x;
-    const int row = full_items[fi].row;
-    if (!(a.plans[row].temperature > 0.f) || ws.rows[fi].redo) return;
-    const int nsub = (a.vocab + kSub - 1) / kSub;
-    emul2_guess(&ctl, ws.ew + fi, nsub);
-}
-
-// ---- comp: composite increment of every sub-tile under its guessed binade (phase C) --------------------
-template <bool FINAL>
-__global__ void __launch_bounds__(kFullThreads) k_full_comp(const __grid_constant__ SampleArgs a, const FullWs ws,
-                                                            const WorkItem *full_items)
-{
-    const int fi = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int row = full_items[fi].row;
-    const RowPlan *rpp = a.plans + row;
-    if (!(__ldg(&rpp->temperature) > 0.f)) return;
-    const int n = a.vocab;
-    const int begin = blockIdx.x * kPhasePiece;
-    if (begin >= n) return;
-    const FullRow *fr = ws.rows + fi;
-    if (fr->redo) return;
-    const float *e = ws.e + (size_t)fi * ws.e_stride;
-    const ProvFinal pf{e, fr->dist, nullptr};
-    Emul2Work *ew = ws.ew + fi;
-    constexpr int W = kFullThreads / 32;
-    for (int st0 = warp; st0 < kPieceSubTiles; st0 += 2 * W) {
-        float x[2][8];
-        bool live[2];
-#pragma unroll
-        for (int h = 0; h < 2; h++) {
-            const int st = st0 + h * W;
-            const int t = (begin >> 8) + st;
-            live[h] = st < kPieceSubTiles && t * kSub < n && !(ew->sums[t] == 0.f);  // nothing to add: composite 0
-            const int base = t * kSub + lane * 8;
-            if (!live[h]) continue;
-            if (FINAL) {
-                pf.reload(base, n, x[h]);
-            } else {
-                SrcScratch sc{e, 1.f, false};
-                if (base < n) sc.get8(base, n, x[h]);
-#pragma unroll
-                for (int j = 0; j < 8; j++)
-                    if (base + j >= n) x[h][j] = 0.f;
-            }
-        }
-#pragma unroll
-        for (int h = 0; h < 2; h++) {
-            const int st = st0 + h * W;
-            const int t = (begin >> 8) + st;
-            if (st >= kPieceSubTiles || t * kSub >= n) continue;
-            int a0 = 0, a1 = 0;
-            if (live[h]) {
-                const int g = ew->guess[t];
-                subtile_composite<false>(x[h], g, a0, a1);
-                const int xsl = ew->xslot[t];
-                if (xsl) {
-                    CrossSlot &cs = ew->xs[xsl - 1];
-                    int l0, l1, h0, h1;
-                    lane_composite(x[h], g, l0, l1);
-                    lane_composite(x[h], g + 1, h0, h1);
-                    cs.lo[lane][0] = l0; cs.lo[lane][1] = l1;
-                    cs.hi[lane][0] = h0; cs.hi[lane][1] = h1;
-                }
-            }
-            if (lane == 0) { ew->comp[t][0] = a0; ew->comp[t][1] = a1; }
-        }
-    }
+    piece_tail<true>(fr, ew, pf.scratch, pf, begin, n, s_sum, s_guess, s_xslot, &s_ok);
 }
 
 // copies a row's sub-tile summaries from device memory into the shared-memory work area of the walk
@@ -942,38 +1023,33 @@ cudaError_t launch_full_prep(const SampleArgs &a, const FullWs &ws, cudaStream_t
 }
 
 // everything behind the HBM pass for the `n_full` full rows listed in `full_rows` (device array)
+// part 0: exp .. cut (after which the rows to redo are known); part 1: the draw's two kernels
 cudaError_t launch_full_rest(const SampleArgs &a, const FullWs &ws, const WorkItem *full_items, int n_full, int *launches,
-                             KernelTimer *kt, cudaStream_t stream)
+                             KernelTimer *kt, cudaStream_t stream, int part)
 {
     const dim3 pg = piece_grid(a, n_full);
+    if (part == 1) {
+        if (a.mode != 0) return cudaSuccess;
+        k_full_psums<<<pg, kFullThreads, 0, stream>>>(a, ws, full_items);
+        kt->mark("full_psums", stream);
+        k_full_draw<<<n_full, kThreads, kDrawSmem, stream>>>(a, ws, full_items);
+        kt->mark("full_draw", stream);
+        *launches += 2;
+        return cudaGetLastError();
+    }
     cudaError_t e = ensure_dynamic_smem((const void *)k_full_walk, kRowArenaBytes);
     if (e == cudaSuccess) e = ensure_dynamic_smem((const void *)k_full_cut, kRowArenaBytes);
     if (e == cudaSuccess) e = ensure_dynamic_smem((const void *)k_full_draw, kDrawSmem);
     if (e != cudaSuccess) return e;
     k_full_exp<<<pg, kFullThreads, 0, stream>>>(a, ws, full_items);
     kt->mark("full_exp", stream);
-    k_full_scan<<<n_full, kThreads, 0, stream>>>(a, ws, full_items);
-    kt->mark("full_scan", stream);
-    k_full_comp<false><<<pg, kFullThreads, 0, stream>>>(a, ws, full_items);
-    kt->mark("full_comp", stream);
     k_full_walk<<<n_full, kThreads, kRowArenaBytes, stream>>>(a, ws, full_items);
     kt->mark("full_walk", stream);
     k_full_scatter<<<pg, kFullThreads, 0, stream>>>(a, ws, full_items);
     kt->mark("full_scatter", stream);
     k_full_cut<<<n_full, kThreads, kRowArenaBytes, stream>>>(a, ws, full_items);
     kt->mark("full_cut", stream);
-    *launches += 6;
-    if (a.mode == 0) {
-        k_full_psums<<<pg, kFullThreads, 0, stream>>>(a, ws, full_items);
-        kt->mark("full_psums", stream);
-        k_full_scan<<<n_full, kThreads, 0, stream>>>(a, ws, full_items);
-        kt->mark("full_scan2", stream);
-        k_full_comp<true><<<pg, kFullThreads, 0, stream>>>(a, ws, full_items);
-        kt->mark("full_comp2", stream);
-        k_full_draw<<<n_full, kThreads, kDrawSmem, stream>>>(a, ws, full_items);
-        kt->mark("full_draw", stream);
-        *launches += 4;
-    }
+    *launches += 4;
     return cudaGetLastError();
 }
 

@@ -77,7 +77,7 @@ struct StgSampler_ {
     size_t cand_entries = 0;
     uint32_t work_base = 0, work_base_rows = 0;
     cudaStream_t aux_stream = nullptr;   // lowest priority: the chunked rows' finish runs here, beside the full rows' phases
-    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr, ev_cut = nullptr;
     cudaEvent_t ev_order = nullptr;      // orders a call behind the previous call's work when the stream changes
     cudaStream_t last_stream = nullptr;
     bool last_stream_valid = false;
