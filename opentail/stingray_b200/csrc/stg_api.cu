@@ -536,8 +536,8 @@ int run_batch(StgHandle h, const StgSampleBatch *b, const BatchExtra &x, void *s
     c.n_items = n_chunk_items;
     h->kt.begin(stream);
     if (flat_chunks || flat_full) {
-        if (flat_chunks) { e = launch_flat_prep(c, fr, stream); launches++; h->kt.mark("flat_prep", stream); }
-        if (e == cudaSuccess && flat_full) { e = launch_full_prep(a, ws, stream); launches++; h->kt.mark("full_prep", stream); }
+        if (flat_chunks && !flat_full) { e = launch_flat_prep(c, fr, stream); launches++; h->kt.mark("flat_prep", stream); }
+        if (e == cudaSuccess && flat_full) { e = launch_full_prep(a, ws, flat_chunks ? fr : nullptr, stream); launches++; h->kt.mark("full_prep", stream); }
         if (e == cudaSuccess) { e = launch_flat_stream(a, fr, ws, stream); launches++; h->kt.mark("flat_stream", stream); }
     }
     const bool flat_rows = flat_full && n_rows_items > 0;

@@ -5,6 +5,7 @@
 #include <stdint.h>
 
 #include "stg_flat.cuh"
+#include "stg_flat_prep.cuh"
 #include "stg_launch.h"
 #include "stg_select.cuh"
 #include "stg_types.h"
@@ -12,53 +13,17 @@
 namespace stg {
 
 // ---- k_flat_prep --------------------------------------------------------------------------------------
-// One 1024-thread CTA per row.  Top-k rows: the filter bound.  Thread t takes elements 4t .. 4t+3 of
-// the row's first 4096 (masked) logits and keeps their maximum; the 1024 maxima are cut into
-// `flat_groups` equal groups of consecutive threads, and the bound is the smallest of the groups'
-// maxima: at least flat_groups elements of the sample lie at or above it, about twice as many on
-// average, and the planner picks flat_groups so that about 3 N elements of the whole row should.
+// One 1024-thread CTA per row (flat_prep_row, stg_flat_prep.cuh).  Launched on its own only when the
+// step has no full-vocabulary rows in the flat form; otherwise k_full_prep, which has a CTA per row
+// anyway, does this for the rows that are not its own.
 template <bool BF16, bool CAP>
 __global__ void __launch_bounds__(kThreads) k_flat_prep(const __grid_constant__ SampleArgs a, FlatRow *fr)
 {
     __shared__ uint32_t red[32];
-    const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int row = blockIdx.x;
     const RowPlan rp = a.plans[row];
     if (rp.n_chunks == 0) return;  // not a row of the flat step
-    if (rp.path != kPathTopK) {
-        if (tid == 0) { fr[row].key = 0ull; fr[row].tau = 0.f; fr[row].cnt = 0; fr[row].cap = 0; }
-        return;
-    }
-    const int esz = BF16 ? 2 : 4;
-    const LogitRow rowp{(const char *)a.logits + (int64_t)row * a.row_stride * esz, CAP ? a.softcap : 0.f};
-    const uint32_t *mrow = (rp.use_mask && a.mask) ? a.mask + (int64_t)row * a.mask_stride : nullptr;
-    float v[4];
-    int idx[4];
-    load_items<4, BF16, false>(rowp, mrow, 0, 0, min(a.vocab, kFlatSample), v, idx);  // out of range reads -inf
-    uint32_t m = ord32(fmaxf(fmaxf(v[0], v[1]), fmaxf(v[2], v[3])));
-    const int ng = rp.flat_groups;          // power of two, 1 .. 1024
-    const int w = kThreads / ng;            // threads per group
-    // maximum over the thread's group
-    for (int o = 1; o < min(w, 32); o <<= 1) m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
-    if (w > 32) {
-        if (lane == 0) red[warp] = m;
-        __syncthreads();
-        const int wpg = w / 32;             // warps per group
-        const int g0 = (warp / wpg) * wpg;
-        m = 0u;
-        for (int k = 0; k < wpg; k++) m = max(m, red[g0 + k]);
-        __syncthreads();
-    }
-    // minimum over all groups (every thread holds its group's maximum)
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) m = min(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
-    if (lane == 0) red[warp] = m;
-    __syncthreads();
-    if (warp == 0) {
-        m = red[lane];
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) m = min(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
-        if (lane == 0) { fr[row].key = 0ull; fr[row].tau = unord32(m); fr[row].cnt = 0; fr[row].cap = rp.sel + kFlatSlack; }
-    }
+    flat_prep_row<BF16>(a, fr, row, rp, CAP ? a.softcap : 0.f, red);
 }
 
 // ---- k_flat_stream ------------------------------------------------------------------------------------

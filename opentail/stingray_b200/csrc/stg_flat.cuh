@@ -111,7 +111,8 @@ struct FullWs {
 
 cudaError_t launch_flat_prep(const SampleArgs &a, FlatRow *fr, cudaStream_t stream);
 cudaError_t launch_flat_stream(const SampleArgs &a, FlatRow *fr, const FullWs &ws, cudaStream_t stream);
-cudaError_t launch_full_prep(const SampleArgs &a, const FullWs &ws, cudaStream_t stream);
+// flat != null: also prepares the chunked rows of the flat step (then launch_flat_prep is not needed)
+cudaError_t launch_full_prep(const SampleArgs &a, const FullWs &ws, FlatRow *flat, cudaStream_t stream);
 struct KernelTimer;
 cudaError_t launch_full_rest(const SampleArgs &a, const FullWs &ws, const WorkItem *full_items, int n_full, int *launches,
                              KernelTimer *kt, cudaStream_t stream, int part);

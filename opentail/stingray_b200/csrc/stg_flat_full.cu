@@ -8,6 +8,7 @@
 #include <stdint.h>
 
 #include "stg_flat.cuh"
+#include "stg_flat_prep.cuh"
 #include "stg_launch.h"
 #include "stg_rowdist.cuh"
 
@@ -25,15 +26,20 @@ __device__ __forceinline__ bool row_wants_topp(const RowPlan &rp) { return rp.to
 // ApplyHistoryPenalties after the logit bias (Sampler.cs:50-56, :367-419) through build_overrides,
 // then the distinct tokens sorted by id with their adjusted logits, and where every piece starts
 // in that list.  Also clears the row's histogram and bin cursors.
+// `flat`: the step's chunked rows are in the flat form too; their CTAs of this kernel do k_flat_prep's work.
 template <bool BF16>
-__global__ void __launch_bounds__(kThreads, 1) k_full_prep(const __grid_constant__ SampleArgs a, const FullWs ws)
+__global__ void __launch_bounds__(kThreads, 1) k_full_prep(const __grid_constant__ SampleArgs a, const FullWs ws, FlatRow *flat)
 {
     extern __shared__ __align__(16) unsigned char arena[];
     __shared__ int n_ent;
+    __shared__ uint32_t red[32];
     const int row = blockIdx.x, tid = threadIdx.x;
     const RowPlan rp = a.plans[row];
     const int fi = rp.flat_full;
-    if (fi < 0) return;
+    if (fi < 0) {
+        if (flat != nullptr && rp.n_chunks != 0) flat_prep_row<BF16>(a, flat, row, rp, a.softcap, red);
+        return;
+    }
     FullRow *fr = ws.rows + fi;
     const int n = a.vocab;
     const bool greedy = rp.temperature <= 0.f;
@@ -1012,13 +1018,13 @@ constexpr size_t kDrawSmem = sizeof(Emul2Work) + (size_t)kXcEntries * kSub * 4;
 // ---- launchers ---------------------------------------------------------------------------------------------
 static dim3 piece_grid(const SampleArgs &a, int n_full) { return dim3((unsigned)((a.vocab + kPhasePiece - 1) / kPhasePiece), (unsigned)n_full); }
 
-cudaError_t launch_full_prep(const SampleArgs &a, const FullWs &ws, cudaStream_t stream)
+cudaError_t launch_full_prep(const SampleArgs &a, const FullWs &ws, FlatRow *flat, cudaStream_t stream)
 {
     const size_t smem = (size_t)kMaxOvSlots * 24 + 8192 + 1024 + (size_t)kMaxOverride * 16;
-    void (*fn)(const SampleArgs, const FullWs) = a.dtype == 1 ? k_full_prep<true> : k_full_prep<false>;
+    void (*fn)(const SampleArgs, const FullWs, FlatRow *) = a.dtype == 1 ? k_full_prep<true> : k_full_prep<false>;
     cudaError_t e = ensure_dynamic_smem((const void *)fn, smem);
     if (e != cudaSuccess) return e;
-    fn<<<a.rows, kThreads, smem, stream>>>(a, ws);
+    fn<<<a.rows, kThreads, smem, stream>>>(a, ws, flat);
     return cudaGetLastError();
 }
 
