@@ -54,7 +54,9 @@ template <bool BF16, bool CAP>
 __global__ void __launch_bounds__(kFlatThreads) k_flat_stream(const __grid_constant__ SampleArgs a, FlatRow *fr, const FullWs ws)
 {
     __shared__ unsigned long long red[kFlatThreads / 32];
-    const int row = blockIdx.y, tid = threadIdx.x, lane = tid & 31;
+    // grid.y runs over the step's item list, which names the full-vocabulary rows first: their CTAs do
+    // the most work per piece and so start first, and the light ones fill the tail of the grid
+    const int row = __ldg(&a.items[blockIdx.y].row), tid = threadIdx.x, lane = tid & 31;
     const RowPlan *rpp = a.plans + row;
     const int fi = __ldg(&rpp->flat_full);
     if (__ldg(&rpp->n_chunks) == 0 && fi < 0) return;  // not a row of the flat step
@@ -387,7 +389,7 @@ cudaError_t launch_flat_prep(const SampleArgs &a, FlatRow *fr, cudaStream_t stre
 
 cudaError_t launch_flat_stream(const SampleArgs &a, FlatRow *fr, const FullWs &ws, cudaStream_t stream)
 {
-    const dim3 grid((unsigned)((a.vocab + kFlatPiece - 1) / kFlatPiece), (unsigned)a.rows);
+    const dim3 grid((unsigned)((a.vocab + kFlatPiece - 1) / kFlatPiece), (unsigned)a.n_items);
     const bool cap = a.softcap != 0.f;
     if (a.dtype == 1) { if (cap) k_flat_stream<true, true><<<grid, kFlatThreads, 0, stream>>>(a, fr, ws); else k_flat_stream<true, false><<<grid, kFlatThreads, 0, stream>>>(a, fr, ws); }
     else { if (cap) k_flat_stream<false, true><<<grid, kFlatThreads, 0, stream>>>(a, fr, ws); else k_flat_stream<false, false><<<grid, kFlatThreads, 0, stream>>>(a, fr, ws); }
