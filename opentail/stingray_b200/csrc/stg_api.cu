@@ -148,6 +148,7 @@ int make_plan(StgHandle h, const StgSampleBatch *b, int mode, bool shard, int gl
         if (chunked) { n_chunk_rows++; max_sel = std::max(max_sel, rp.sel); }
         else pl.any_row_item = true;
         if (rp.path == kPathTopK) pl.n_topk++; else if (rp.path == kPathFull) pl.n_full++; else pl.n_greedy++;
+        if (rp.path == kPathFull && !(p.top_p < 1.0f && p.top_p > 0.f)) pl.n_full_without_top_p++;
     }
     pl.n_chunk_rows = n_chunk_rows;
     // The flat step needs long, aligned rows and a candidate list (N + kFlatSlack entries) that about 3 N
@@ -551,7 +552,10 @@ int run_batch(StgHandle h, const StgSampleBatch *b, const BatchExtra &x, void *s
         if (e != cudaSuccess || n_chunk_items == 0) return;
         cudaStream_t cs = fork ? h->aux_stream : stream;
         if (flat_chunks) {
-            e = launch_flat_finish(c, fr, n_chunk_items, pl.smem, cs);
+            // beside the full rows' one-SM-per-row kernels the finish must not take every SM
+            const int grid = flat_rows ? std::min(n_chunk_items, std::max(16, h->sm_count - std::min(n_rows_items, h->sm_count) - 4)) : n_chunk_items;
+            c.item_base = n_rows_items;  // diagnostic stamps: behind the full rows' slots
+            e = launch_flat_finish(c, fr, grid, pl.smem, cs);
             if (e == cudaSuccess) launches++;
             if (!fork) h->kt.mark("flat_finish", cs);
         } else {
@@ -563,15 +567,23 @@ int run_batch(StgHandle h, const StgSampleBatch *b, const BatchExtra &x, void *s
         }
     };
     if (flat_rows) {
-        // Main stream: the phases of the full rows.  Side stream: the finish of the chunked rows, and
-        // behind it - once the cut kernel has said which rows the flat form gave up - the row kernel
+        // Main stream: the phases of the full rows (their plan and scatter kernels on a stream of their
+        // own beside the walk).  Side stream: the finish of the chunked rows - held back until the scatter
+        // pass is through, because its one-SM CTAs would otherwise sit on the SMs that pass needs while
+        // the walk holds the others, whereas the cut that follows leaves two thirds of the GPU idle -
+        // and behind it, once the cut kernel has said which rows the flat form gave up, the row kernel
         // for exactly those (every other CTA of it leaves at once), beside the draw's two kernels.
-        launch_chunked();
-        if (e == cudaSuccess) e = launch_full_rest(a, ws, a.items, n_rows_items, &launches, &h->kt, stream, 0);
+        if (!flat_chunks) launch_chunked();
+        const FullSide side{h->plan_stream, h->ev_exp, h->ev_scatter, pl.n_full_without_top_p > 0};
+        if (e == cudaSuccess) e = launch_full_rest(a, ws, a.items, n_rows_items, &launches, &h->kt, stream, 0, side);
+        if (flat_chunks) {
+            if (e == cudaSuccess) e = cudaStreamWaitEvent(h->aux_stream, h->ev_scatter, 0);
+            launch_chunked();
+        }
         if (e == cudaSuccess) e = cudaEventRecord(h->ev_cut, stream);
         if (e == cudaSuccess) e = cudaStreamWaitEvent(h->aux_stream, h->ev_cut, 0);
         if (e == cudaSuccess) e = launch_rows_kernel(true, h->aux_stream);
-        if (e == cudaSuccess) e = launch_full_rest(a, ws, a.items, n_rows_items, &launches, &h->kt, stream, 1);
+        if (e == cudaSuccess) e = launch_full_rest(a, ws, a.items, n_rows_items, &launches, &h->kt, stream, 1, side);
     } else {
         if (e == cudaSuccess && n_rows_items > 0) {
             e = launch_rows_kernel(false, stream);
@@ -735,6 +747,9 @@ int stg_create(const StgConfig *cfg, StgHandle *out)
         if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->ev_join, cudaEventDisableTiming);
         if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->ev_order, cudaEventDisableTiming);
         if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->ev_cut, cudaEventDisableTiming);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->ev_exp, cudaEventDisableTiming);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->ev_scatter, cudaEventDisableTiming);
+        if (e == cudaSuccess) e = cudaStreamCreateWithPriority(&h->plan_stream, cudaStreamNonBlocking, hi);
         if (e != cudaSuccess) rc = cuda_fail(nullptr, e, "side stream");
     }
     for (int i = 0; i < 4 && rc == STG_OK; i++) {
@@ -769,6 +784,9 @@ int stg_destroy(StgHandle h)
     if (h->ev_join) cudaEventDestroy(h->ev_join);
     if (h->ev_order) cudaEventDestroy(h->ev_order);
     if (h->ev_cut) cudaEventDestroy(h->ev_cut);
+    if (h->ev_exp) cudaEventDestroy(h->ev_exp);
+    if (h->ev_scatter) cudaEventDestroy(h->ev_scatter);
+    if (h->plan_stream) cudaStreamDestroy(h->plan_stream);
     if (h->aux_stream) cudaStreamDestroy(h->aux_stream);
     delete h;
     return STG_OK;

@@ -280,7 +280,7 @@ struct FlatShared {
 // One row of the flat step by a 1024-thread CTA: any top_k, any penalties, and the second chance of
 // a row whose candidate list failed its check.
 template <bool BF16>
-__device__ void flat_finish_row(const SampleArgs &a, FlatRow *fr, int row, unsigned char *arena, SelCtl &ctl, FlatShared &fs)
+__device__ void flat_finish_row(const SampleArgs &a, FlatRow *fr, int row, int item, unsigned char *arena, SelCtl &ctl, FlatShared &fs)
 {
     const RowPlan rp = a.plans[row];
     const int esz = BF16 ? 2 : 4;
@@ -310,7 +310,7 @@ __device__ void flat_finish_row(const SampleArgs &a, FlatRow *fr, int row, unsig
         return;
     }
     const uint32_t *mrow = (rp.use_mask && a.mask) ? a.mask + (int64_t)row * a.mask_stride : nullptr;
-    unsigned long long *tk = a.phase_ticks ? a.phase_ticks + (int64_t)(a.item_base + blockIdx.x) * 32 : nullptr;
+    unsigned long long *tk = a.phase_ticks ? a.phase_ticks + (int64_t)(a.item_base + item) * 32 : nullptr;
     tick(tk, 0);
     Sel s;
     s.c = &ctl;
@@ -369,14 +369,22 @@ __device__ void flat_finish_row(const SampleArgs &a, FlatRow *fr, int row, unsig
     }
 }
 
-// One CTA per row of a.items.
-template <bool BF16>
+// The rows of a.items, shared between the CTAs of the grid (one row per CTA when the grid is as
+// large as the list; a smaller grid leaves SMs to the kernels of the full-vocabulary rows it runs beside).
+template <bool BF16, bool SHARED>
 __global__ void __launch_bounds__(kThreads, 1) k_flat_finish(const __grid_constant__ SampleArgs a, FlatRow *fr)
 {
     extern __shared__ __align__(16) unsigned char arena[];
     __shared__ SelCtl ctl;
     __shared__ FlatShared fs;
-    flat_finish_row<BF16>(a, fr, a.items[blockIdx.x].row, arena, ctl, fs);
+    if (!SHARED) {
+        flat_finish_row<BF16>(a, fr, a.items[blockIdx.x].row, blockIdx.x, arena, ctl, fs);
+        return;
+    }
+    for (int i = blockIdx.x; i < a.n_items; i += gridDim.x) {
+        flat_finish_row<BF16>(a, fr, a.items[i].row, i, arena, ctl, fs);
+        __syncthreads();
+    }
 }
 
 cudaError_t launch_flat_prep(const SampleArgs &a, FlatRow *fr, cudaStream_t stream)
@@ -396,12 +404,14 @@ cudaError_t launch_flat_stream(const SampleArgs &a, FlatRow *fr, const FullWs &w
     return cudaGetLastError();
 }
 
-cudaError_t launch_flat_finish(const SampleArgs &a, FlatRow *fr, int n_rows, size_t smem, cudaStream_t stream)
+cudaError_t launch_flat_finish(const SampleArgs &a, FlatRow *fr, int grid, size_t smem, cudaStream_t stream)
 {
-    void (*fn)(const SampleArgs, FlatRow *) = a.dtype == 1 ? k_flat_finish<true> : k_flat_finish<false>;
+    const bool shared = grid < a.n_items;
+    void (*fn)(const SampleArgs, FlatRow *) = a.dtype == 1 ? (shared ? k_flat_finish<true, true> : k_flat_finish<true, false>)
+                                                           : (shared ? k_flat_finish<false, true> : k_flat_finish<false, false>);
     cudaError_t e = ensure_dynamic_smem((const void *)fn, smem);
     if (e != cudaSuccess) return e;
-    fn<<<n_rows, kThreads, smem, stream>>>(a, fr);
+    fn<<<grid, kThreads, smem, stream>>>(a, fr);
     return cudaGetLastError();
 }
 

@@ -114,8 +114,15 @@ cudaError_t launch_flat_stream(const SampleArgs &a, FlatRow *fr, const FullWs &w
 // flat != null: also prepares the chunked rows of the flat step (then launch_flat_prep is not needed)
 cudaError_t launch_full_prep(const SampleArgs &a, const FullWs &ws, FlatRow *flat, cudaStream_t stream);
 struct KernelTimer;
+// the second stream of the full rows' phases (the plan and the scatter pass run beside the walk)
+struct FullSide {
+    cudaStream_t stream;
+    cudaEvent_t after_exp, after_scatter;
+    bool any_without_top_p;  // some full row has top-p off: its Normalize sum needs a pass of its own
+};
 cudaError_t launch_full_rest(const SampleArgs &a, const FullWs &ws, const WorkItem *full_items, int n_full, int *launches,
-                             KernelTimer *kt, cudaStream_t stream, int part);
-cudaError_t launch_flat_finish(const SampleArgs &a, FlatRow *fr, int n_rows, size_t smem, cudaStream_t stream);
+                             KernelTimer *kt, cudaStream_t stream, int part, const FullSide &side);
+// grid: CTAs that share the rows of a.items between them (at most a.n_items)
+cudaError_t launch_flat_finish(const SampleArgs &a, FlatRow *fr, int grid, size_t smem, cudaStream_t stream);
 
 }  // namespace stg

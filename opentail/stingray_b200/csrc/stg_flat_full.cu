@@ -528,13 +528,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_full_walk(const __grid_constant
         }
         return;
     }
-    unsigned *hcount = (unsigned *)(arena + kOffCount);
-    unsigned *hmass = (unsigned *)(arena + kOffMass);
-    unsigned *bstart = (unsigned *)(arena + kOffBinOff);
     Emul2Work *wk2 = (Emul2Work *)(arena + kOffEmul);
-    unsigned char *bin_exp = arena + kOffBinExp;
     const float *e = ws.e + (size_t)fi * ws.e_stride;
-    const bool want_topp = row_wants_topp(rp);
     const bool uniform = mk == 0ull;
     const float inv_t = rp.temperature != 1.0f ? __fdiv_rn(1.0f, rp.temperature) : 1.0f;
     RowDist d;
@@ -573,6 +568,47 @@ __global__ void __launch_bounds__(kThreads, 1) k_full_walk(const __grid_constant
         d.minp_thr = __fmul_rn(rp.min_p, pmax);
         d.flags |= kDistMinP;
     }
+    tick(tk, 4);
+    if (tid == 0) { fr->dist = d; fr->sum = sum; }
+}
+
+// ---- plan: where the nucleus ends in the histogram, where every bin starts in the candidate list ----------
+// Steps (1) to (3) of topp_cut.  They need the softmax sum only to turn histogram masses into
+// probabilities, and every use carries a margin (the bound of step 1, the binade guesses and flags of
+// step 3), so the fp64 sum of the sub-tile sums stands in for the exact sequential sum, which
+// k_full_walk is computing at the same time on another stream.  Should the bound come out too tight
+// all the same, k_full_cut notices (the sum never reaches top_p although survivors remain) and the
+// row is redone.
+__global__ void __launch_bounds__(kThreads, 1) k_full_plan(const __grid_constant__ SampleArgs a, const FullWs ws,
+                                                           const WorkItem *full_items)
+{
+    extern __shared__ __align__(16) unsigned char arena[];
+    __shared__ RowCtl rc;
+    const int fi = blockIdx.x, tid = threadIdx.x;
+    const int row = full_items[fi].row;
+    const RowPlan rp = a.plans[row];
+    if (!(rp.temperature > 0.f) || !row_wants_topp(rp)) return;
+    FullRow *fr = ws.rows + fi;
+    const int n = a.vocab;
+    const bool uniform = fr->maxkey == 0ull;
+    unsigned *hcount = (unsigned *)(arena + kOffCount);
+    unsigned *hmass = (unsigned *)(arena + kOffMass);
+    unsigned *bstart = (unsigned *)(arena + kOffBinOff);
+    unsigned char *bin_exp = arena + kOffBinExp;
+    struct { int flags; float inv1; float uniform_p; } d;
+    d.flags = 0; d.inv1 = 1.f; d.uniform_p = 0.f;
+    if (uniform) {
+        d.flags |= kDistUniform;
+        d.uniform_p = __fdiv_rn(1.0f, (float)n);
+    } else {
+        const int nsub = (n + kSub - 1) / kSub;
+        const float *sums = (ws.ew + fi)->sums;
+        double part = 0.0;
+        for (int t = tid; t < nsub; t += kThreads) part += (double)__ldcg(sums + t);
+        const double total = block_sum_double(part, rc.red_d);
+        if (total > 0.0 && total != 1.0) { d.flags |= kDistScale1; d.inv1 = (float)(1.0 / total); }
+    }
+    const bool want_topp = true;
     if (want_topp) {
         // histogram of the exp values as the exp pass left it
         const unsigned long long *hist = ws.hist + (size_t)fi * kHistBins;
@@ -679,89 +715,86 @@ __global__ void __launch_bounds__(kThreads, 1) k_full_walk(const __grid_constant
         for (int t = tid; t < kHistBins / 32; t += kThreads) g_flags[t] = rc.flag_bits[t];
         if (tid == 0) { fr->c_lo = c_lo; fr->bound = rc.bound; }
     }
-    tick(tk, 4);
-    if (tid == 0) { fr->dist = d; fr->sum = sum; }
 }
 
 // ---- scatter: candidates into bin order, survivors counted ---------------------------------------------
-// Step (4) of topp_cut over a piece.  Rows without top-p only need the fp64 sum of their
-// probabilities for Normalize (Sampler.cs:553-562).
+// Step (4) of topp_cut over a piece: every exp value at or above the plan's lowest bin goes to its
+// bin's range of the row's candidate list, AS AN EXP VALUE - the list is ordered by bins of exp
+// values, and the probability of a candidate (exp value times 1 / sum, then the min-p filter) is a
+// non-decreasing function of it, so k_full_cut turns the list into probabilities once the exact sum
+// is known.  That leaves this pass independent of the walk that computes the sum: the two run side by
+// side.  Rows without top-p are not touched (k_full_nosum).
 __global__ void __launch_bounds__(kFullThreads) k_full_scatter(const __grid_constant__ SampleArgs a, const FullWs ws,
                                                                const WorkItem *full_items)
 {
-    __shared__ double red_d[kFullThreads / 32];
+    // Positions are handed out in two levels: the CTA counts its candidates per bin in shared memory
+    // (a candidate's count at that moment is its rank inside the CTA's share of the bin), reserves the
+    // CTA's share of every bin it touched with ONE global atomicAdd per bin, and then writes.  The
+    // per-element global atomic with a returned value that this replaces cost a round trip to L2 each.
+    __shared__ unsigned s_cnt[kBins];
     __shared__ int red_i[kFullThreads / 32];
     const int fi = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int row = full_items[fi].row;
     const RowPlan *rpp = a.plans + row;
     if (!(__ldg(&rpp->temperature) > 0.f)) return;
+    const float top_p = __ldg(&rpp->top_p);
+    if (!(top_p < 1.0f && top_p > 0.f)) return;
     const int n = a.vocab;
     const int begin = blockIdx.x * kPhasePiece;
     if (begin >= n) return;
     FullRow *fr = ws.rows + fi;
-    const RowDist d = fr->dist;
-    const float top_p = __ldg(&rpp->top_p);
-    const bool want_topp = top_p < 1.0f && top_p > 0.f;
     const float *e = ws.e + (size_t)fi * ws.e_stride;
-    const int end = min(n, begin + kPhasePiece);
-    if (!want_topp) {
-        double part = 0.0;
-        for (int base = begin + tid * 8; base < end; base += kFullThreads * 8) {
-            float x[8];
-            SrcScratch sc{e, 1.f, false};
-            sc.get8(base, n, x);
-#pragma unroll
-            for (int j = 0; j < 8; j++)
-                if (base + j < n) part += (double)eval_p2(x[j], d);
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xFFFFFFFFu, part, o);
-        if (lane == 0) red_d[warp] = part;
-        __syncthreads();
-        if (tid == 0) {
-            double t = 0.0;
-            for (int w = 0; w < kFullThreads / 32; w++) t += red_d[w];
-            fr->part[blockIdx.x] = t;
-        }
-        return;
-    }
     const int c_lo = fr->c_lo;
     const uint32_t lo_bits = bin_floor_bits(c_lo);
-    const int cap = (int)ws.key_stride;
+    const unsigned cap = (unsigned)ws.key_stride;
     const uint32_t *bstart = ws.bstart + (size_t)fi * kHistBins;
-    const unsigned char *bin_exp = ws.bin_exp + (size_t)fi * kHistBins;
-    uint32_t *flag_bits = ws.flag_bits + (size_t)fi * (kHistBins / 32);
     uint32_t *cursor = ws.cursor + (size_t)fi * kHistBins;
     uint32_t *keys = ws.keys + (size_t)fi * ws.key_stride;
+    constexpr int R = kPhasePiece / (kFullThreads * 8);  // rounds of 8 consecutive elements per thread
+    float x[R][8];
+    unsigned short rank[R][8];
+    for (int b = tid; b < kBins; b += kFullThreads) s_cnt[b] = 0u;
+#pragma unroll
+    for (int r = 0; r < R; r++) {
+        const int base = begin + (r * kFullThreads + tid) * 8;
+        if (base < n) {
+            SrcScratch sc{e, 1.f, false};
+            sc.get8(base, n, x[r]);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; j++)
+            if (base + j >= n) x[r][j] = 0.f;
+    }
+    __syncthreads();
     int my_surv = 0;
-    for (int base = begin + tid * 8; base < end; base += kFullThreads * 8) {
-        float x[8];
-        SrcScratch sc{e, 1.f, false};
-        sc.get8(base, n, x);
+#pragma unroll
+    for (int r = 0; r < R; r++)
 #pragma unroll
         for (int j = 0; j < 8; j++) {
-            if (base + j >= n) continue;
-            const float ev = x[j];
-            const float p = eval_p2(ev, d);
-            if (p > 0.f) {
-                my_surv++;
+            const float ev = x[r][j];
+            rank[r][j] = 0xFFFFu;  // not a candidate
+            if (ev > 0.f) {
+                my_surv++;  // survives softmax; min-p may still drop it (k_full_cut errs on the safe side)
                 const uint32_t ebits = __float_as_uint(ev);
-                if (ebits >= lo_bits) {
-                    const unsigned bin = bin_of(ebits);
-                    const unsigned pos = __ldg(bstart + bin) + atomicAdd(&cursor[bin], 1u);
-                    const uint32_t pbits = __float_as_uint(p);
-                    if (pos < (unsigned)cap) keys[pos] = pbits;
-                    // a key whose addition would be an exact tie (the parity of the running sum then
-                    // decides the rounding, so the order inside its bin matters) flags its bin
-                    const int k = (int)__ldg(bin_exp + bin) - (int)((pbits >> 23) & 255u);
-                    if (k >= 1 && k <= 24) {
-                        const uint32_t m = (pbits & 0x7FFFFFu) | 0x800000u;
-                        if ((m & ((1u << k) - 1u)) == (1u << (k - 1))) atomicOr(&flag_bits[bin >> 5], 1u << (bin & 31));
-                    }
-                }
+                if (ebits >= lo_bits) rank[r][j] = (unsigned short)atomicAdd(&s_cnt[bin_of(ebits)], 1u);
             }
         }
+    __syncthreads();
+    // the CTA's share of every bin it touched: s_cnt turns from a count into the first position
+    for (int b = tid; b < kBins; b += kFullThreads) {
+        const unsigned c = s_cnt[b];
+        if (c) s_cnt[b] = __ldg(bstart + b) + atomicAdd(&cursor[b], c);
     }
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < R; r++)
+#pragma unroll
+        for (int j = 0; j < 8; j++)
+            if (rank[r][j] != 0xFFFFu) {
+                const uint32_t ebits = __float_as_uint(x[r][j]);
+                const unsigned pos = s_cnt[bin_of(ebits)] + rank[r][j];
+                if (pos < cap) keys[pos] = ebits;
+            }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) my_surv += __shfl_xor_sync(0xFFFFFFFFu, my_surv, o);
     if (lane == 0) red_i[warp] = my_surv;
@@ -772,6 +805,141 @@ __global__ void __launch_bounds__(kFullThreads) k_full_scatter(const __grid_cons
         if (t) atomicAdd(&fr->surv, t);
     }
 }
+
+// ---- rows without top-p: the fp64 sum of their probabilities for Normalize (Sampler.cs:553-562) ----------
+// Needs the exact distribution descriptor, so it runs behind k_full_walk; launched only when the step
+// has such rows.
+__global__ void __launch_bounds__(kFullThreads) k_full_nosum(const __grid_constant__ SampleArgs a, const FullWs ws,
+                                                             const WorkItem *full_items)
+{
+    __shared__ double red_d[kFullThreads / 32];
+    const int fi = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int row = full_items[fi].row;
+    const RowPlan *rpp = a.plans + row;
+    if (!(__ldg(&rpp->temperature) > 0.f)) return;
+    const float top_p = __ldg(&rpp->top_p);
+    if (top_p < 1.0f && top_p > 0.f) return;
+    const int n = a.vocab;
+    const int begin = blockIdx.x * kPhasePiece;
+    if (begin >= n) return;
+    FullRow *fr = ws.rows + fi;
+    const RowDist d = fr->dist;
+    const float *e = ws.e + (size_t)fi * ws.e_stride;
+    const int end = min(n, begin + kPhasePiece);
+    double part = 0.0;
+    for (int base = begin + tid * 8; base < end; base += kFullThreads * 8) {
+        float x[8];
+        SrcScratch sc{e, 1.f, false};
+        sc.get8(base, n, x);
+#pragma unroll
+        for (int j = 0; j < 8; j++)
+            if (base + j < n) part += (double)eval_p2(x[j], d);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xFFFFFFFFu, part, o);
+    if (lane == 0) red_d[warp] = part;
+    __syncthreads();
+    if (tid == 0) {
+        double t = 0.0;
+        for (int w = 0; w < kFullThreads / 32; w++) t += red_d[w];
+        fr->part[blockIdx.x] = t;
+    }
+}
+
+// ---- ties: candidates whose addition would be an exact tie flag their bin --------------------------------
+// With the exact sum known (k_full_walk) and the candidates in place (k_full_scatter): a candidate
+// whose probability falls exactly between two floats at the binade the sorted running sum has at its
+// bin makes the rounding depend on the parity of the sum, so the order inside that bin matters and
+// k_full_cut has to sort it.  One pass over the candidate lists, all SMs: grid (pieces of 8192
+// candidates, full rows).
+__global__ void __launch_bounds__(kFullThreads) k_full_ties(const __grid_constant__ SampleArgs a, const FullWs ws,
+                                                            const WorkItem *full_items)
+{
+    const int fi = blockIdx.y, tid = threadIdx.x;
+    const int row = full_items[fi].row;
+    const RowPlan *rpp = a.plans + row;
+    const float top_p = __ldg(&rpp->top_p);
+    if (!(__ldg(&rpp->temperature) > 0.f) || !(top_p < 1.0f && top_p > 0.f)) return;
+    const FullRow *fr = ws.rows + fi;
+    const int nc = min(fr->bound, (int)ws.key_stride);
+    const int begin = blockIdx.x * kPhasePiece;
+    if (begin >= nc) return;
+    const RowDist d = fr->dist;
+    const int scale = (d.flags & kDistScale1) ? 1 : 0, minp = (d.flags & kDistMinP) ? 1 : 0;
+    const unsigned char *bin_exp = ws.bin_exp + (size_t)fi * kHistBins;
+    uint32_t *flag_bits = ws.flag_bits + (size_t)fi * (kHistBins / 32);
+    const uint4 *g16 = (const uint4 *)(ws.keys + (size_t)fi * ws.key_stride);
+    const int q_end = (min(nc, begin + kPhasePiece) + 3) >> 2;
+    constexpr int U = kPhasePiece / (4 * kFullThreads);  // quads per thread
+    uint4 eb[U];
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+        const int q = (begin >> 2) + u * kFullThreads + tid;
+        eb[u] = q < q_end ? __ldcg(g16 + q) : make_uint4(0u, 0u, 0u, 0u);
+    }
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+        const int q = (begin >> 2) + u * kFullThreads + tid;
+        const uint32_t four[4] = {eb[u].x, eb[u].y, eb[u].z, eb[u].w};
+#pragma unroll
+        for (int c4 = 0; c4 < 4; c4++) {
+            if (q >= q_end || q * 4 + c4 >= nc) continue;
+            const uint32_t ebits = four[c4];
+            float p = __uint_as_float(ebits);
+            if (scale) p = __fmul_rn(p, d.inv1);
+            if (minp && p < d.minp_thr) p = 0.f;
+            const uint32_t pbits = __float_as_uint(p);
+            const unsigned bin = bin_of(ebits);
+            const int k = (int)__ldg(bin_exp + bin) - (int)((pbits >> 23) & 255u);
+            if (k >= 1 && k <= 24) {
+                const uint32_t m = (pbits & 0x7FFFFFu) | 0x800000u;
+                if ((m & ((1u << k) - 1u)) == (1u << (k - 1))) atomicOr(&flag_bits[bin >> 5], 1u << (bin & 31));
+            }
+        }
+    }
+}
+
+// The candidate list of the flat step holds exp values (k_full_scatter); every reader turns them into
+// the probabilities the reference sorts and sums - softmax scale, then the min-p filter (eval_p2; the
+// flat step has no rows with top-k on this path) - as it loads them.  The conversion is monotonic, so
+// the list's order by exp value is an order by probability.
+struct KeyConv {
+    int scale;        // multiply by inv1
+    float inv1;
+    int minp;         // apply the min-p threshold
+    float minp_thr;
+    __device__ __forceinline__ float operator()(uint32_t ebits) const
+    {
+        float p = __uint_as_float(ebits);
+        if (scale) p = __fmul_rn(p, inv1);
+        if (minp && p < minp_thr) p = 0.f;
+        return p;
+    }
+};
+struct ProvKeysE {
+    const uint32_t *keys;
+    bool global;  // the list sits in global memory (a nucleus too wide for shared memory): staged reads pay
+    KeyConv conv;
+    __device__ __forceinline__ void load(int base, int n, float x[8]) const
+    {
+#pragma unroll
+        for (int j = 0; j < 8; j++) x[j] = (base + j < n) ? conv(keys[base + j]) : 0.f;
+    }
+    __device__ __forceinline__ void reload(int base, int n, float x[8]) const { load(base, n, x); }
+    static constexpr int kQuadsLoad = 2, kQuadsReload = 2;
+    __device__ __forceinline__ bool stage_ok() const { return global; }
+    __device__ __forceinline__ const char *stage_src(int base, bool) const { return (const char *)(keys + base); }
+    __device__ __forceinline__ void load_from(int base, int n, const float4 *q, float x[8]) const
+    {
+        const uint32_t *u = (const uint32_t *)q;
+#pragma unroll
+        for (int j = 0; j < 8; j++) x[j] = conv(u[j]);
+    }
+    __device__ __forceinline__ void reload_from(int base, int n, const float4 *q, float x[8]) const
+    {
+        load_from(base, n, q, x);
+    }
+};
 
 // ---- cut: the top-p threshold from the bin-ordered candidates; Normalize ---------------------------------
 // Steps (5) onwards of topp_cut for a row whose candidates the scatter pass left in device memory.
@@ -829,8 +997,16 @@ __global__ void __launch_bounds__(kThreads, 1) k_full_cut(const __grid_constant_
         if (bound > kSortCap) { keys = gkeys; cap = (int)ws.key_stride; if (tid == 0) sh_flags |= (1u << 7); }
         const int nc = min(block_sum_int(mine, rc->red_i), cap);
         __syncthreads();
+        // The list holds exp values (k_full_scatter): a short one is copied to shared memory, a wide one
+        // stays where it is; every reader turns them into probabilities as it loads them (KeyConv).
+        const KeyConv conv{(d.flags & kDistScale1) ? 1 : 0, d.inv1, (d.flags & kDistMinP) ? 1 : 0, d.minp_thr};
         if (keys == skeys) {
-            for (int t = tid; t < nc; t += kThreads) skeys[t] = __ldcg(gkeys + t);
+            // 16-byte loads (the list starts on a 16-byte boundary and is read in whole quads: what lies
+            // behind its end is never used)
+            const uint4 *g16 = (const uint4 *)gkeys;
+            const int nq = (nc + 3) >> 2;
+            __syncthreads();
+            for (int q = tid; q < nq; q += kThreads) ((uint4 *)skeys)[q] = __ldcg(g16 + q);
             __syncthreads();
         }
         tick(tk, 9);
@@ -897,14 +1073,14 @@ __global__ void __launch_bounds__(kThreads, 1) k_full_cut(const __grid_constant_
                     }
                     __syncthreads();
                 }
-                ProvKeys pk{keys, keys != skeys};
+                ProvKeysE pk{keys, keys != skeys, conv};
                 if (nc <= kSub * kMaxSubTiles) {
-                    hit = emul_scan2<ProvKeys, false, true, 4>(&rc->em2, wk2, pk, nc, rp.top_p, true, &cum,
+                    hit = emul_scan2<ProvKeysE, false, true, 4>(&rc->em2, wk2, pk, nc, rp.top_p, true, &cum,
                                                             sorted_all ? nullptr : replay_ok, tk ? tk + 24 : nullptr,
                                                             keys != skeys ? arena + kOffKeys : nullptr, kSortCap * 4);
                 } else {
                     if (!sorted_all) { if (tid == 0) rc->give_up = 1; __syncthreads(); continue; }
-                    hit = emul_scan<ProvKeys, false>(&rc->em, pk, nc, rp.top_p, true, &cum);
+                    hit = emul_scan<ProvKeysE, false>(&rc->em, pk, nc, rp.top_p, true, &cum);
                 }
                 if (hit != -2) break;
                 const int t_abort = rc->em2.abort_at;
@@ -928,16 +1104,16 @@ __global__ void __launch_bounds__(kThreads, 1) k_full_cut(const __grid_constant_
                 return;
             }
             const int last = hit >= 0 ? hit : nc - 1;
-            const float tstar = hit >= 0 ? __uint_as_float(keys[last]) : 0.f;
+            const float tstar = hit >= 0 ? conv(keys[last]) : 0.f;
             if (hit >= 0 && nc <= kSub * kMaxSubTiles && tid == 0 &&
                 (cum - rp.top_p <= kNearTol || rp.top_p - rc->em2.hit_before <= kNearTol))
                 sh_flags |= kFlagNearCut;  // a last-bit difference in exp could move the cut by a token
             int keep = 0, all = 0;
             double part = 0.0;
             for (int t = tid; t < nc; t += kThreads) {
-                const uint32_t kb = keys[t];
-                if (kb == __float_as_uint(tstar)) { all++; keep += (t <= last) ? 1 : 0; }
-                if (t <= last) part += (double)__uint_as_float(kb);
+                const float p = conv(keys[t]);
+                if (p == tstar) { all++; keep += (t <= last) ? 1 : 0; }
+                if (t <= last) part += (double)p;
             }
             keep = block_sum_int(keep, rc->red_i);
             all = block_sum_int(all, rc->red_i);
@@ -1031,7 +1207,7 @@ cudaError_t launch_full_prep(const SampleArgs &a, const FullWs &ws, FlatRow *fla
 // everything behind the HBM pass for the `n_full` full rows listed in `full_rows` (device array)
 // part 0: exp .. cut (after which the rows to redo are known); part 1: the draw's two kernels
 cudaError_t launch_full_rest(const SampleArgs &a, const FullWs &ws, const WorkItem *full_items, int n_full, int *launches,
-                             KernelTimer *kt, cudaStream_t stream, int part)
+                             KernelTimer *kt, cudaStream_t stream, int part, const FullSide &side)
 {
     const dim3 pg = piece_grid(a, n_full);
     if (part == 1) {
@@ -1047,15 +1223,36 @@ cudaError_t launch_full_rest(const SampleArgs &a, const FullWs &ws, const WorkIt
     if (e == cudaSuccess) e = ensure_dynamic_smem((const void *)k_full_cut, kRowArenaBytes);
     if (e == cudaSuccess) e = ensure_dynamic_smem((const void *)k_full_draw, kDrawSmem);
     if (e != cudaSuccess) return e;
+    e = ensure_dynamic_smem((const void *)k_full_plan, kRowArenaBytes);
+    if (e != cudaSuccess) return e;
     k_full_exp<<<pg, kFullThreads, 0, stream>>>(a, ws, full_items);
     kt->mark("full_exp", stream);
+    // the plan and the scatter pass need the histogram and the sub-tile sums, not the exact sum: they
+    // run on the side stream beside the walk
+    e = cudaEventRecord(side.after_exp, stream);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(side.stream, side.after_exp, 0);
+    if (e != cudaSuccess) return e;
+    k_full_plan<<<n_full, kThreads, kRowArenaBytes, side.stream>>>(a, ws, full_items);
+    k_full_scatter<<<pg, kFullThreads, 0, side.stream>>>(a, ws, full_items);
+    e = cudaEventRecord(side.after_scatter, side.stream);
+    if (e != cudaSuccess) return e;
     k_full_walk<<<n_full, kThreads, kRowArenaBytes, stream>>>(a, ws, full_items);
     kt->mark("full_walk", stream);
-    k_full_scatter<<<pg, kFullThreads, 0, stream>>>(a, ws, full_items);
-    kt->mark("full_scatter", stream);
+    *launches += 4;
+    if (side.any_without_top_p) {
+        k_full_nosum<<<pg, kFullThreads, 0, stream>>>(a, ws, full_items);
+        kt->mark("full_nosum", stream);
+        *launches += 1;
+    }
+    e = cudaStreamWaitEvent(stream, side.after_scatter, 0);
+    if (e != cudaSuccess) return e;
+    kt->mark("wait_scatter", stream);
+    k_full_ties<<<pg, kFullThreads, 0, stream>>>(a, ws, full_items);
+    kt->mark("full_ties", stream);
+    *launches += 1;
     k_full_cut<<<n_full, kThreads, kRowArenaBytes, stream>>>(a, ws, full_items);
     kt->mark("full_cut", stream);
-    *launches += 4;
+    *launches += 1;
     return cudaGetLastError();
 }
 

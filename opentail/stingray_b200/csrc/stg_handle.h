@@ -38,6 +38,7 @@ struct Plan {
     bool flat = false;        // the chunked rows run as the flat step (stg_flat.cuh)
     bool flat_full = false;   // ... and so do the full-vocabulary rows
     int n_chunk_rows = 0;
+    int n_full_without_top_p = 0;  // sampled full-vocabulary rows with top-p off
 };
 
 }  // namespace stg
@@ -77,7 +78,8 @@ struct StgSampler_ {
     size_t cand_entries = 0;
     uint32_t work_base = 0, work_base_rows = 0;
     cudaStream_t aux_stream = nullptr;   // lowest priority: the chunked rows' finish runs here, beside the full rows' phases
-    cudaEvent_t ev_fork = nullptr, ev_join = nullptr, ev_cut = nullptr;
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr, ev_cut = nullptr, ev_exp = nullptr, ev_scatter = nullptr;
+    cudaStream_t plan_stream = nullptr;  // the plan and scatter kernels of the full rows, beside the walk
     cudaEvent_t ev_order = nullptr;      // orders a call behind the previous call's work when the stream changes
     cudaStream_t last_stream = nullptr;
     bool last_stream_valid = false;
