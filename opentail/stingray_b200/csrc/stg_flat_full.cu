@@ -33,7 +33,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_full_prep(const __grid_constant
     extern __shared__ __align__(16) unsigned char arena[];
     __shared__ int n_ent;
     __shared__ uint32_t red[32];
-    const int row = blockIdx.x, tid = threadIdx.x;
+    // grid over the step's item list: it names the full rows first, whose CTAs take longest
+    const int row = a.items[blockIdx.x].row, tid = threadIdx.x;
     const RowPlan rp = a.plans[row];
     const int fi = rp.flat_full;
     if (fi < 0) {
@@ -181,59 +182,40 @@ __device__ __forceinline__ bool piece_guesses(FullRow *fr, Emul2Work *ew, int k,
 
 // Composite increment of every sub-tile of the piece under its guess (phase C), CrossSlots included.
 // FINAL: over the final probabilities, else over the exp values.  All threads of the CTA.
-template <bool FINAL>
-__device__ __forceinline__ void piece_composites(Emul2Work *ew, const float *e, const ProvFinal &pf, int begin, int n,
+// The values come in registers: xs[i] holds the warp's i-th sub-tile of the piece (sub-tile warp + 8 i,
+// this lane's 8 elements, zeros beyond the row's end) as the first stage of the kernel left them.
+constexpr int kWarpSubTiles = kPieceSubTiles / (kFullThreads / 32);  // 4
+__device__ __forceinline__ void piece_composites(Emul2Work *ew, const float (&xs)[kWarpSubTiles][8], int begin, int n,
                                                  const float *s_sum, const unsigned char *s_guess, const unsigned char *s_xslot)
 {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     constexpr int W = kFullThreads / 32;
-    for (int st0 = warp; st0 < kPieceSubTiles; st0 += 2 * W) {
-        float x[2][8];
-        bool live[2];
 #pragma unroll
-        for (int h = 0; h < 2; h++) {
-            const int st = st0 + h * W;
-            const int t = (begin >> 8) + st;
-            live[h] = st < kPieceSubTiles && t * kSub < n && !(s_sum[st] == 0.f);  // nothing to add: composite 0
-            const int base = t * kSub + lane * 8;
-            if (!live[h]) continue;
-            if (FINAL) {
-                pf.reload(base, n, x[h]);
-            } else {
-                SrcScratch sc{e, 1.f, false};
-                if (base < n) sc.get8(base, n, x[h]);
-#pragma unroll
-                for (int j = 0; j < 8; j++)
-                    if (base + j >= n) x[h][j] = 0.f;
+    for (int i = 0; i < kWarpSubTiles; i++) {
+        const int st = warp + i * W;
+        const int t = (begin >> 8) + st;
+        if (t * kSub >= n) continue;
+        int a0 = 0, a1 = 0;
+        if (!(s_sum[st] == 0.f)) {  // else nothing to add: composite 0
+            const int g = s_guess[st];
+            subtile_composite<false>(xs[i], g, a0, a1);
+            const int xsl = s_xslot[st];
+            if (xsl) {
+                CrossSlot &cs = ew->xs[xsl - 1];
+                int l0, l1, h0, h1;
+                lane_composite(xs[i], g, l0, l1);
+                lane_composite(xs[i], g + 1, h0, h1);
+                cs.lo[lane][0] = l0; cs.lo[lane][1] = l1;
+                cs.hi[lane][0] = h0; cs.hi[lane][1] = h1;
             }
         }
-#pragma unroll
-        for (int h = 0; h < 2; h++) {
-            const int st = st0 + h * W;
-            const int t = (begin >> 8) + st;
-            if (st >= kPieceSubTiles || t * kSub >= n) continue;
-            int a0 = 0, a1 = 0;
-            if (live[h]) {
-                const int g = s_guess[st];
-                subtile_composite<false>(x[h], g, a0, a1);
-                const int xsl = s_xslot[st];
-                if (xsl) {
-                    CrossSlot &cs = ew->xs[xsl - 1];
-                    int l0, l1, h0, h1;
-                    lane_composite(x[h], g, l0, l1);
-                    lane_composite(x[h], g + 1, h0, h1);
-                    cs.lo[lane][0] = l0; cs.lo[lane][1] = l1;
-                    cs.hi[lane][0] = h0; cs.hi[lane][1] = h1;
-                }
-            }
-            if (lane == 0) { ew->comp[t][0] = a0; ew->comp[t][1] = a1; }
-        }
+        if (lane == 0) { ew->comp[t][0] = a0; ew->comp[t][1] = a1; }
     }
 }
 
 // the tail both per-piece kernels share: look-back and guesses by warp 0, composites by everyone
 template <bool FINAL>
-__device__ __forceinline__ void piece_tail(FullRow *fr, Emul2Work *ew, const float *e, const ProvFinal &pf, int begin, int n,
+__device__ __forceinline__ void piece_tail(FullRow *fr, Emul2Work *ew, const float (&xs)[kWarpSubTiles][8], int begin, int n,
                                            float *s_sum, unsigned char *s_guess, unsigned char *s_xslot, int *s_ok)
 {
     const int t0 = begin >> 8, nsub = (n + kSub - 1) / kSub;
@@ -245,7 +227,7 @@ __device__ __forceinline__ void piece_tail(FullRow *fr, Emul2Work *ew, const flo
     }
     __syncthreads();
     if (!*s_ok) return;
-    piece_composites<FINAL>(ew, e, pf, begin, n, s_sum, s_guess, s_xslot);
+    piece_composites(ew, xs, begin, n, s_sum, s_guess, s_xslot);
 }
 
 // ---- exp: e = exp(x - max), sub-tile sums, histogram ----------------------------------------------------
@@ -281,8 +263,11 @@ __global__ void __launch_bounds__(kFullThreads) k_full_exp(const __grid_constant
         __syncthreads();
     }
     constexpr int W = kFullThreads / 32;
-    for (int st0 = warp; st0 < kPieceSubTiles; st0 += 2 * W) {
-        float x[2][8];
+    float xs[kWarpSubTiles][8];
+#pragma unroll
+    for (int it = 0; it < kWarpSubTiles / 2; it++) {
+        const int st0 = warp + it * 2 * W;
+        float (&x)[2][8] = *reinterpret_cast<float (*)[2][8]>(&xs[it * 2]);
 #pragma unroll
         for (int h = 0; h < 2; h++) {
             const int st = st0 + h * W;
@@ -300,7 +285,11 @@ __global__ void __launch_bounds__(kFullThreads) k_full_exp(const __grid_constant
         for (int h = 0; h < 2; h++) {
             const int st = st0 + h * W;
             const int base = begin + st * kSub + lane * 8;
-            if (st >= kPieceSubTiles || begin + st * kSub >= n) continue;  // the same for the whole warp
+            if (st >= kPieceSubTiles || begin + st * kSub >= n) {  // the same for the whole warp
+#pragma unroll
+                for (int j = 0; j < 8; j++) x[h][j] = 0.f;
+                continue;
+            }
             float acc = 0.f;
             int low = 0;
 #pragma unroll
@@ -334,9 +323,8 @@ __global__ void __launch_bounds__(kFullThreads) k_full_exp(const __grid_constant
             if (c) atomicAdd(&hist[b], ((unsigned long long)c << 40) | (unsigned long long)hmass[b]);
         }
     }
-    // phases B and C of the softmax sum for this piece (the exp values just stored are read back from L2)
-    const ProvFinal none{e, RowDist{}, nullptr};
-    piece_tail<false>(fr, ew, e, none, begin, n, s_sum, s_guess, s_xslot, &s_ok);
+    // phases B and C of the softmax sum for this piece, on the exp values still in registers
+    piece_tail<false>(fr, ew, xs, begin, n, s_sum, s_guess, s_xslot, &s_ok);
 }
 
 // ---- sums of the final probabilities (the draw's phase A) ------------------------------------------------
@@ -358,12 +346,15 @@ __global__ void __launch_bounds__(kFullThreads) k_full_psums(const __grid_consta
     const ProvFinal pf{ws.e + (size_t)fi * ws.e_stride, fr->dist, nullptr};
     Emul2Work *ew = ws.ew + fi;
     constexpr int W = kFullThreads / 32;
-    for (int st0 = warp; st0 < kPieceSubTiles; st0 += 2 * W) {
-        float x[2][8];
+    float xs[kWarpSubTiles][8];
+#pragma unroll
+    for (int it = 0; it < kWarpSubTiles / 2; it++) {
+        const int st0 = warp + it * 2 * W;
+        float (&x)[2][8] = *reinterpret_cast<float (*)[2][8]>(&xs[it * 2]);
 #pragma unroll
         for (int h = 0; h < 2; h++) {
             const int st = st0 + h * W;
-            pf.reload(st < kPieceSubTiles ? begin + st * kSub + lane * 8 : n, n, x[h]);
+            pf.reload(st < kPieceSubTiles ? begin + st * kSub + lane * 8 : n, n, x[h]);  // zeros beyond the row
         }
 #pragma unroll
         for (int h = 0; h < 2; h++) {
@@ -377,7 +368,7 @@ __global__ void __launch_bounds__(kFullThreads) k_full_psums(const __grid_consta
             if (lane == 0) { ew->sums[(begin >> 8) + st] = acc; s_sum[st] = acc; }
         }
     }
-    piece_tail<true>(fr, ew, pf.scratch, pf, begin, n, s_sum, s_guess, s_xslot, &s_ok);
+    piece_tail<true>(fr, ew, xs, begin, n, s_sum, s_guess, s_xslot, &s_ok);
 }
 
 // copies a row's sub-tile summaries from device memory into the shared-memory work area of the walk
@@ -1200,7 +1191,7 @@ cudaError_t launch_full_prep(const SampleArgs &a, const FullWs &ws, FlatRow *fla
     void (*fn)(const SampleArgs, const FullWs, FlatRow *) = a.dtype == 1 ? k_full_prep<true> : k_full_prep<false>;
     cudaError_t e = ensure_dynamic_smem((const void *)fn, smem);
     if (e != cudaSuccess) return e;
-    fn<<<a.rows, kThreads, smem, stream>>>(a, ws, flat);
+    fn<<<a.n_items, kThreads, smem, stream>>>(a, ws, flat);
     return cudaGetLastError();
 }
 
