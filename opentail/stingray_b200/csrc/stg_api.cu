@@ -553,9 +553,18 @@ int run_batch(StgHandle h, const StgSampleBatch *b, const BatchExtra &x, void *s
         cudaStream_t cs = fork ? h->aux_stream : stream;
         if (flat_chunks) {
             // beside the full rows' one-SM-per-row kernels the finish must not take every SM
-            const int grid = flat_rows ? std::min(n_chunk_items, std::max(16, h->sm_count - std::min(n_rows_items, h->sm_count) - 4)) : n_chunk_items;
+            const int sms = flat_rows ? std::max(8, h->sm_count - std::min(n_rows_items, h->sm_count) - 4) : h->sm_count;
             c.item_base = n_rows_items;  // diagnostic stamps: behind the full rows' slots
-            e = launch_flat_finish(c, fr, grid, pl.smem, cs);
+            static const bool no_half = getenv("STG_NO_HALF_FINISH") != nullptr;
+            // 512-thread CTAs, two per SM, when their shorter buffers still hold a row's N best and one
+            // 4096-entry batch of its list; else one full-size CTA per row
+            constexpr int kHalfCap = 6912;  // 2 x (110,592 B + static) fit an SM's shared memory
+            if (!no_half && pl.max_sel + kSubTile + 512 <= kHalfCap) {
+                c.finish_cap = kHalfCap;
+                e = launch_flat_finish_half(c, fr, std::min(n_chunk_items, 2 * sms), cs);
+            } else {
+                e = launch_flat_finish(c, fr, std::min(n_chunk_items, flat_rows ? sms : n_chunk_items), pl.smem, cs);
+            }
             if (e == cudaSuccess) launches++;
             if (!fork) h->kt.mark("flat_finish", cs);
         } else {

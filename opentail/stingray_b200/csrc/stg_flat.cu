@@ -5,6 +5,7 @@
 #include <stdint.h>
 
 #include "stg_flat.cuh"
+#include "stg_flat_finish.cuh"
 #include "stg_flat_prep.cuh"
 #include "stg_launch.h"
 #include "stg_select.cuh"
@@ -272,105 +273,8 @@ __global__ void __launch_bounds__(kFlatThreads) k_flat_stream(const __grid_const
 }
 
 // ---- k_flat_finish ------------------------------------------------------------------------------------
-struct FlatShared {
-    FinishOut fout;
-    int ok;
-};
-
-// One row of the flat step by a 1024-thread CTA: any top_k, any penalties, and the second chance of
-// a row whose candidate list failed its check.
-template <bool BF16>
-__device__ void flat_finish_row(const SampleArgs &a, FlatRow *fr, int row, int item, unsigned char *arena, SelCtl &ctl, FlatShared &fs)
-{
-    const RowPlan rp = a.plans[row];
-    const int esz = BF16 ? 2 : 4;
-    const LogitRow rowp{(const char *)a.logits + (int64_t)row * a.row_stride * esz, a.softcap};
-    if (rp.path == kPathGreedy) {
-        if (threadIdx.x == 0) {
-            const unsigned long long key = fr[row].key;
-            int tok = 0;
-            float val;
-            uint32_t fl = kPathGreedy;
-            if (key != 0ull) {
-                tok = key_idx(key);
-                val = key_val(key);
-            } else {
-                val = load_one<BF16>(rowp, 0);  // Greedy of a row without a finite value: token 0
-                fl |= (1u << 6);
-            }
-            if (a.pairs_out) {
-                ((int32_t *)a.pairs_out)[2 * row] = tok;
-                ((float *)a.pairs_out)[2 * row + 1] = val;
-            }
-            if (a.tokens) a.tokens[row] = tok;
-            if (a.token_probs) a.token_probs[row] = 1.0f;
-            if (a.row_flags) a.row_flags[row] = fl;
-            count_row_flags(a.counters, fl);
-        }
-        return;
-    }
-    const uint32_t *mrow = (rp.use_mask && a.mask) ? a.mask + (int64_t)row * a.mask_stride : nullptr;
-    unsigned long long *tk = a.phase_ticks ? a.phase_ticks + (int64_t)(a.item_base + item) * 32 : nullptr;
-    tick(tk, 0);
-    Sel s;
-    s.c = &ctl;
-    s.buf[0] = (u64 *)arena;
-    s.buf[1] = s.buf[0] + a.cap;
-    s.cap = a.cap;
-    s.n = rp.sel;
-    s.idx_off = 0;
-    sel_reset(s);
-    if (threadIdx.x == 0) {
-        const FlatRow f = fr[row];
-        fs.ok = (f.cnt >= rp.sel && f.cnt <= f.cap && f.tau > -CUDART_INF_F) ? f.cnt : -1;
-    }
-    __syncthreads();
-    const int cnt = fs.ok;
-    if (cnt >= 0) {
-        // the list holds exactly the logits above the bound, N or more of them: a superset of the N best
-        // (when no penalty can promote a logit the finish works on the whole list, see finish_topk_select)
-        sel_append_keys(s, a.cand + rp.cand_off, cnt, !(rp.top_k <= kFastFinishK && penalties_only_demote(rp)));
-    } else {
-        // the bound was off (or dropped candidates): the row is read again by this CTA, with a generous
-        // bound first (about 8 N survivors, capacity permitting) and the exact selection behind it
-        const int over = (int)max(5ll, min(16ll, (long long)s.cap / max(s.n, 1)));
-        const FlatRow f = fr[row];
-        bool preset = false;
-        float bound = 0.f;
-        if (f.tau > -CUDART_INF_F && f.cnt > f.cap && f.cap > rp.sel && f.cap <= s.cap) {
-            // too many passed the first bound: the list kept f.cap of them, some subset.  The N-th best of a
-            // subset is no higher than the N-th best of the row, so everything at or above it is a superset of
-            // the row's best N - and a far smaller one than before
-            sel_append_keys(s, a.cand + rp.cand_off, f.cap, false);
-            sel_raise(s);
-            const uint32_t o = ord32(ctl.tau);
-            bound = unord32(o > 0u ? o - 1u : 0u);  // the next value below: the strict test then keeps ties with the bound
-            preset = true;
-            __syncthreads();
-            sel_reset(s);
-        }
-        sel_stream_generous<4, BF16>(s, rowp, mrow, 0, a.vocab, over, preset, bound);
-    }
-    tick(tk, 1);
-    if (tk && threadIdx.x == 0) { tk[8] = (unsigned long long)(long long)cnt; tk[9] = (unsigned long long)fr[row].cnt; tk[10] = (unsigned long long)fr[row].cap; }
-    const int32_t *hist = a.hist_ids ? a.hist_ids + rp.hist_off : nullptr;
-    const float *ptab = (a.pow_tab && rp.pow_off >= 0) ? a.pow_tab + rp.pow_off : nullptr;
-    const float u = a.uniforms ? __ldg(a.uniforms + row) : 0.5f;
-    const int64_t o = (int64_t)row * a.topk_stride;
-    finish_topk(s, rp, hist, ptab, u, &fs.fout, a.topk_ids ? a.topk_ids + o : nullptr,
-                a.topk_logits ? a.topk_logits + o : nullptr, a.topk_probs ? a.topk_probs + o : nullptr);
-    tick(tk, 3);
-    if (threadIdx.x == 0) {
-        a.tokens[row] = fs.fout.token;
-        if (a.token_probs) a.token_probs[row] = fs.fout.prob;
-        const uint32_t fl = fs.fout.flags | (cnt < 0 ? kFlagFlatRedo : 0u);
-        if (a.row_flags) a.row_flags[row] = fl;
-        count_row_flags(a.counters, fl);
-    }
-}
-
-// The rows of a.items, shared between the CTAs of the grid (one row per CTA when the grid is as
-// large as the list; a smaller grid leaves SMs to the kernels of the full-vocabulary rows it runs beside).
+// The rows of a.items: one per CTA, or (SHARED) shared between the CTAs of a smaller grid, which
+// leaves SMs to the kernels of the full-vocabulary rows it runs beside.
 template <bool BF16, bool SHARED>
 __global__ void __launch_bounds__(kThreads, 1) k_flat_finish(const __grid_constant__ SampleArgs a, FlatRow *fr)
 {
@@ -378,11 +282,11 @@ __global__ void __launch_bounds__(kThreads, 1) k_flat_finish(const __grid_consta
     __shared__ SelCtl ctl;
     __shared__ FlatShared fs;
     if (!SHARED) {
-        flat_finish_row<BF16>(a, fr, a.items[blockIdx.x].row, blockIdx.x, arena, ctl, fs);
+        flat_finish_row<BF16>(a, fr, a.items[blockIdx.x].row, blockIdx.x, a.cap, arena, ctl, fs);
         return;
     }
     for (int i = blockIdx.x; i < a.n_items; i += gridDim.x) {
-        flat_finish_row<BF16>(a, fr, a.items[i].row, i, arena, ctl, fs);
+        flat_finish_row<BF16>(a, fr, a.items[i].row, i, a.cap, arena, ctl, fs);
         __syncthreads();
     }
 }

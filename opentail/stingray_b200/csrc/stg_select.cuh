@@ -34,6 +34,9 @@ static __device__ __forceinline__ u64 make_key(float v, int idx)
 static __device__ __forceinline__ float key_val(u64 k) { return unord32((uint32_t)(k >> 32)); }
 static __device__ __forceinline__ int key_idx(u64 k) { return (int)(0xFFFFFFFFu - (uint32_t)k); }
 
+// elements one load_items call of the CTA covers (4 per thread): the sample the streaming select draws its first bound from
+constexpr int kSelTile = 4 * kThreads;
+
 // ---- element access --------------------------------------------------------------------------
 static __device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
 static __device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
@@ -271,7 +274,7 @@ static __device__ void sel_raise(Sel &s)
     if (tid < 256) c->hist[tid] = 0;
     __syncthreads();
     if (tid < 32) {
-        mx = c->red[tid];
+        mx = tid < kThreads / 32 ? c->red[tid] : 0u;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) mx = max(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
         if (tid == 0) {
@@ -454,7 +457,7 @@ static __device__ void sel_stream_pass(Sel &s, const LogitRow rowp, const uint32
 {
     SelCtl *c = s.c;
     constexpr int STEP = kThreads * 16;
-    const int first_end = min(end, begin + kSubTile);
+    const int first_end = min(end, begin + kSelTile);
     {
         float v[4];
         int idx[4];
@@ -465,7 +468,7 @@ static __device__ void sel_stream_pass(Sel &s, const LogitRow rowp, const uint32
             // about 2.5 N elements of the whole range should pass (the caller checks the outcome)
             const int n_saved = s.n;
             if (optimistic) {
-                const long long m = (5ll * s.n * kSubTile) / (2ll * (long long)(end - begin));
+                const long long m = (5ll * s.n * kSelTile) / (2ll * (long long)(end - begin));
                 s.n = (int)max(32ll, min((long long)s.n, m));
             }
             sel_raise(s);
@@ -502,7 +505,7 @@ static __device__ void sel_stream(Sel &s, const LogitRow rowp, const uint32_t *m
     // again.  The guess is checked: the survivors are exactly the elements above the final tau, so
     // N or more of them contain the best N; fewer (the first sub-tile was not representative) and
     // the range is streamed again with the safe bound, the N-th best seen so far.
-    const bool try_optimistic = end - begin >= 4 * kSubTile;
+    const bool try_optimistic = end - begin >= 4 * kSelTile;
     sel_stream_pass<VEC, BF16>(s, rowp, mrow, begin, end, try_optimistic);
     if (try_optimistic) {
         __syncthreads();
@@ -531,8 +534,8 @@ static __device__ void sel_stream_generous(Sel &s, const LogitRow rowp, const ui
 {
     SelCtl *c = s.c;
     constexpr int STEP = kThreads * 16;
-    int first_end = min(end, begin + kSubTile);
-    bool ok = preset || end - begin >= 4 * kSubTile;
+    int first_end = min(end, begin + kSelTile);
+    bool ok = preset || end - begin >= 4 * kSelTile;
     if (preset) {
         if (threadIdx.x == 0) c->tau = tau_preset;
         __syncthreads();
@@ -545,7 +548,7 @@ static __device__ void sel_stream_generous(Sel &s, const LogitRow rowp, const ui
         ok = c->cnt > s.n;
         if (ok) {
             const int n_saved = s.n;
-            const long long m = ((long long)over * s.n * kSubTile) / (2ll * (long long)(end - begin));
+            const long long m = ((long long)over * s.n * kSelTile) / (2ll * (long long)(end - begin));
             s.n = (int)max(32ll, min((long long)s.n, m));
             sel_raise(s);
             s.n = n_saved;

@@ -4,7 +4,11 @@
 
 namespace stg {
 
-constexpr int kThreads = 1024;          // threads per CTA of every kernel in this library
+#ifndef STG_KTHREADS
+#define STG_KTHREADS 1024
+#endif
+constexpr int kThreads = STG_KTHREADS;  // threads per CTA of the row-level kernels (one translation unit builds the
+                                        // top-k finish with 512, two CTAs per SM: stg_flat_finish_half.cu)
 constexpr int kSubTile = 4096;          // elements one CTA filters per exact-append step
 constexpr int kMaxSel = 8192;           // largest selection count (top_k + history length)
 constexpr int kPowTab = 32;             // host-computed powf(rep, occ) entries per distinct rep
@@ -118,6 +122,7 @@ struct SampleArgs {
     int32_t n_ranks;
     unsigned long long *counters;    // kCtr* event counters, never null
     float softcap;                   // != 0: every logit is read as tanh(x / softcap) * softcap
+    int32_t finish_cap;              // candidates per buffer of the half-size finish (stg_flat_finish_half.cu)
     const int32_t *redo_flags;       // row kernel as the flat step's second chance: only rows whose flag
     int32_t redo_stride;             // redo_flags[flat_full * redo_stride] is set are run; null: every row item
 };
