@@ -31,7 +31,7 @@ def sources():
 def _headers_mtime() -> float:
     t = os.path.getmtime(INCLUDE)
     for name in os.listdir(CSRC):
-        if name.endswith((".h", ".cuh")):
+        if name.endswith((".h", ".cuh", ".inc")):
             t = max(t, os.path.getmtime(os.path.join(CSRC, name)))
     return t
 

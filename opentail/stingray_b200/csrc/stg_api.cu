@@ -555,11 +555,16 @@ int run_batch(StgHandle h, const StgSampleBatch *b, const BatchExtra &x, void *s
             // beside the full rows' one-SM-per-row kernels the finish must not take every SM
             const int sms = flat_rows ? std::max(8, h->sm_count - std::min(n_rows_items, h->sm_count) - 4) : h->sm_count;
             c.item_base = n_rows_items;  // diagnostic stamps: behind the full rows' slots
-            static const bool no_half = getenv("STG_NO_HALF_FINISH") != nullptr;
-            // 512-thread CTAs, two per SM, when their shorter buffers still hold a row's N best and one
-            // 4096-entry batch of its list; else one full-size CTA per row
-            constexpr int kHalfCap = 6912;  // 2 x (110,592 B + static) fit an SM's shared memory
-            if (!no_half && pl.max_sel + kSubTile + 512 <= kHalfCap) {
+            static const bool no_small = getenv("STG_NO_SMALL_FINISH") != nullptr;
+            // Smaller CTAs, several per SM, when their shorter buffers still hold a row's N best and one
+            // batch of its list (4 entries per thread): 256 threads, four per SM, when the rows outnumber
+            // what the 512-thread form holds at once and no one-SM CTAs of full rows run beside; else 512
+            // threads, two per SM; else one full-size CTA per row.
+            constexpr int kHalfCap = 6912, kQuarterCap = 3456;  // 2 x 110,592 B, 4 x 55,296 B (+ static) fit an SM
+            if (!no_small && !flat_rows && n_chunk_items > 2 * sms && pl.max_sel + 1024 + 512 <= kQuarterCap) {
+                c.finish_cap = kQuarterCap;
+                e = launch_flat_finish_quarter(c, fr, std::min(n_chunk_items, 4 * sms), cs);
+            } else if (!no_small && pl.max_sel + 2048 + 512 <= kHalfCap) {
                 c.finish_cap = kHalfCap;
                 e = launch_flat_finish_half(c, fr, std::min(n_chunk_items, 2 * sms), cs);
             } else {

@@ -122,8 +122,9 @@ struct FullSide {
 };
 cudaError_t launch_full_rest(const SampleArgs &a, const FullWs &ws, const WorkItem *full_items, int n_full, int *launches,
                              KernelTimer *kt, cudaStream_t stream, int part, const FullSide &side);
-// the half-size finish (512 threads, two CTAs per SM, a.finish_cap entries per buffer)
+// the small-CTA finishes (512 threads, two CTAs per SM; 256 threads, four per SM; a.finish_cap entries per buffer)
 cudaError_t launch_flat_finish_half(const SampleArgs &a, FlatRow *fr, int grid, cudaStream_t stream);
+cudaError_t launch_flat_finish_quarter(const SampleArgs &a, FlatRow *fr, int grid, cudaStream_t stream);
 // grid: CTAs that share the rows of a.items between them (at most a.n_items)
 cudaError_t launch_flat_finish(const SampleArgs &a, FlatRow *fr, int grid, size_t smem, cudaStream_t stream);
 

@@ -603,8 +603,8 @@ static __device__ void sel_stream_generous(Sel &s, const LogitRow rowp, const ui
 static __device__ void sel_append_keys(Sel &s, const u64 *keys, int count, bool reduce = true)
 {
     SelCtl *c = s.c;
-    for (int base = 0; base < count; base += kSubTile) {
-        int m = min(kSubTile, count - base);
+    for (int base = 0; base < count; base += kSelTile) {
+        int m = min(kSelTile, count - base);
         __syncthreads();
         if (c->cnt + m > s.cap) sel_raise(s);
         u64 *b = s.buf[c->cur];
