@@ -7,10 +7,12 @@
 //   k_flat_stream  one small CTA per 16384-element piece of a row, every row of the batch in one
 //                  grid: the only kernel that reads the logits from HBM.  Greedy rows keep a running
 //                  arg-max key (64-bit atomicMax), top-k rows append every logit above the row's
-//                  bound to the row's candidate list (one atomicAdd per warp and step)
+//                  bound to the row's candidate list (staged in shared memory, one global atomicAdd
+//                  per CTA)
 //   k_flat_finish  one CTA per row   candidates only: the exact top-N selection, penalties, softmax
 //                                    over k, min-p, top-p and the draw of SampleTopK
-//                                    (src/OpenTail.Stingray.Engine/Sampler.cs:216-357)
+//                                    (src/OpenTail.Stingray.Engine/Sampler.cs:216-357); built for 1024,
+//                                    512 and 256 threads (one, two, four CTAs per SM)
 //
 // so that the HBM pass runs at copy speed on all SMs whatever the mix of rows - thousands of
 // 256-thread CTAs that the hardware scheduler balances, 16 independent 16-byte loads per thread in
@@ -20,7 +22,7 @@
 // when it holds between N = top_k + history length and its capacity entries - they are then exactly
 // the logits above the bound, hence a superset of the N best.  Otherwise (the first 4096 logits were
 // not representative: ties, masks, sorted rows) the finishing CTA streams the row again itself with
-// the exact selection of stg_select.cuh.  Nothing waits on another CTA anywhere.
+// the exact selection of stg_select.cuh.  No CTA of these kernels waits on another.
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
