@@ -149,6 +149,7 @@ int make_plan(StgHandle h, const StgSampleBatch *b, int mode, bool shard, int gl
         else pl.any_row_item = true;
         if (rp.path == kPathTopK) pl.n_topk++; else if (rp.path == kPathFull) pl.n_full++; else pl.n_greedy++;
         if (rp.path == kPathFull && !(p.top_p < 1.0f && p.top_p > 0.f)) pl.n_full_without_top_p++;
+        if (rp.path == kPathFull && p.top_p < 1.0f && p.top_p > 0.f) pl.n_full_with_top_p++;
     }
     pl.n_chunk_rows = n_chunk_rows;
     // The flat step needs long, aligned rows and a candidate list (N + kFlatSlack entries) that about 3 N
@@ -588,10 +589,10 @@ int run_batch(StgHandle h, const StgSampleBatch *b, const BatchExtra &x, void *s
         // and behind it, once the cut kernel has said which rows the flat form gave up, the row kernel
         // for exactly those (every other CTA of it leaves at once), beside the draw's two kernels.
         if (!flat_chunks) launch_chunked();
-        const FullSide side{h->plan_stream, h->ev_exp, h->ev_scatter, pl.n_full_without_top_p > 0};
+        const FullSide side{h->plan_stream, h->ev_exp, h->ev_scatter, pl.n_full_without_top_p > 0, pl.n_full_with_top_p > 0};
         if (e == cudaSuccess) e = launch_full_rest(a, ws, a.items, n_rows_items, &launches, &h->kt, stream, 0, side);
         if (flat_chunks) {
-            if (e == cudaSuccess) e = cudaStreamWaitEvent(h->aux_stream, h->ev_scatter, 0);
+            if (e == cudaSuccess && side.any_with_top_p) e = cudaStreamWaitEvent(h->aux_stream, h->ev_scatter, 0);
             launch_chunked();
         }
         if (e == cudaSuccess) e = cudaEventRecord(h->ev_cut, stream);
@@ -748,6 +749,7 @@ int stg_create(const StgConfig *cfg, StgHandle *out)
         A(h->sp_draft, R * L * 4); A(h->sp_uniforms, R * (L + 2) * 8);
         A(h->sp_accepted, R * 4); A(h->sp_correction, R * 4); A(h->sp_aprobs, R * L * 4); A(h->sp_flags, R * 4);
         A(h->dists, R * (2 * L + 1) * sizeof(RowDist));
+        A(h->sp_rowstats, R * 20);  // flat verification: 16 bytes of control and a fall-back flag per sequence
     }
     if (rc == STG_OK) {
         e = cudaHostAlloc((void **)&h->plan_host, h->plan_bytes_cap * 4, cudaHostAllocDefault);

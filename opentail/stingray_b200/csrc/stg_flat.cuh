@@ -116,11 +116,16 @@ cudaError_t launch_flat_stream(const SampleArgs &a, FlatRow *fr, const FullWs &w
 // flat != null: also prepares the chunked rows of the flat step (then launch_flat_prep is not needed)
 cudaError_t launch_full_prep(const SampleArgs &a, const FullWs &ws, FlatRow *flat, cudaStream_t stream);
 struct KernelTimer;
+// speculative verification in the flat form (stg_flat_full.cu): seq_ctl holds 16 bytes per sequence, fallback one
+// int per sequence (1: k_spec_finish must redo it)
+struct SpecArgs;
+cudaError_t launch_spec_flat(const SpecArgs &a, const FullWs &ws, void *seq_ctl, int32_t *fallback, cudaStream_t stream);
 // the second stream of the full rows' phases (the plan and the scatter pass run beside the walk)
 struct FullSide {
     cudaStream_t stream;
     cudaEvent_t after_exp, after_scatter;
     bool any_without_top_p;  // some full row has top-p off: its Normalize sum needs a pass of its own
+    bool any_with_top_p;     // some full row has top-p on: plan, scatter and tie kernels have work
 };
 cudaError_t launch_full_rest(const SampleArgs &a, const FullWs &ws, const WorkItem *full_items, int n_full, int *launches,
                              KernelTimer *kt, cudaStream_t stream, int part, const FullSide &side);

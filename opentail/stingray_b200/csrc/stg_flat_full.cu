@@ -9,6 +9,7 @@
 
 #include "stg_flat.cuh"
 #include "stg_flat_prep.cuh"
+#include "stg_spec_prov.cuh"
 #include "stg_launch.h"
 #include "stg_rowdist.cuh"
 
@@ -1183,6 +1184,221 @@ __global__ void __launch_bounds__(kThreads, 1) k_full_draw(const __grid_constant
 constexpr size_t kDrawSmem = sizeof(Emul2Work) + (size_t)kXcEntries * kSub * 4;
 
 // ---- launchers ---------------------------------------------------------------------------------------------
+// ---- speculative verification in the flat form ---------------------------------------------------------
+// What k_spec_finish (stg_spec_kernels.cu) does with one CTA per sequence - the accept chain, then one
+// or two emulated sums over V whose every phase recomputes p (and q) from the logits - as three
+// kernels: the accept chain (one warp per sequence, the draft positions evaluated side by side), ONE
+// flat pass that writes the values the draw runs over - the final probabilities of the target row
+// (bonus draw, or the looser rule's draw from p) or the residual max(p - q, 0) - into the sequence's
+// scratch row with their sub-tile sums, guesses and composites (the tail k_full_psums has), and a
+// per-sequence walk: for the residual first without a target (its sum), then to u * sum with the same
+// composites.  Sequences whose draw needs one of the rare fall-backs (an empty residual, a walk that
+// runs off the end, a look-back that ran out) are flagged, and k_spec_finish redoes exactly those.
+struct SpecSeq {
+    int32_t acc;       // accepted draft tokens
+    int32_t kind;      // 0: done (greedy), 1: draw from the target row `acc`, 2: residual of position `acc`
+    uint32_t flags;    // STG_SEQ_* gathered so far
+    int32_t pad;
+};
+
+template <bool BF16>
+__global__ void __launch_bounds__(256) k_spec_accept(const __grid_constant__ SpecArgs a, const FullWs ws, SpecSeq *seq,
+                                                     int32_t *fallback)
+{
+    const int lane = threadIdx.x & 31;
+    const int s = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (s >= a.n_seq) return;
+    const int L = a.n_draft, V = a.vocab;
+    const int esz = BF16 ? 2 : 4;
+    const RowDist *td = a.tdist + (int64_t)s * (L + 1);
+    const RowDist *dd = a.ddist ? a.ddist + (int64_t)s * L : nullptr;
+    const char *trows = (const char *)a.target + (int64_t)s * (L + 1) * V * esz;
+    const char *drows = a.draft ? (const char *)a.draft + (int64_t)s * L * V * esz : nullptr;
+    const double *u = a.uniforms + (int64_t)s * (L + 2);
+    const bool greedy = (td[0].flags & kDistOneHot) != 0;
+    bool ok = true, bad = false;
+    float shown = 0.f;
+    if (lane < L) {
+        const int i = lane;
+        const int tok = a.draft_tokens[(int64_t)s * L + i];
+        if ((unsigned)tok >= (unsigned)V) {
+            // a draft token outside the vocabulary (the reference's pDist[tokens[i]] throws,
+            // SpeculativeDecoder.cs:534): never read, rejected, and reported in the flags
+            ok = false;
+            bad = true;
+        } else if (greedy) {
+            ok = (tok == td[i].tie_idx_max);  // SpeculativeDecoder.Step, SpeculativeDecoder.cs:400-405
+            shown = ok ? 1.f : 0.f;
+        } else {
+            const float px = eval_point<BF16>(LogitRow{trows + (int64_t)i * V * esz, a.target_cap}, tok, td[i]);
+            if (a.mode == 0) {
+                const float qx = eval_point<BF16>(LogitRow{drows + (int64_t)i * V * esz, a.draft_cap}, tok, dd[i]);
+                const float r = qx > 0.f ? fminf(1.f, __fdiv_rn(px, qx)) : (px > 0.f ? 1.f : 0.f);
+                ok = u[i] < (double)r;
+                shown = r;
+            } else {
+                ok = px >= a.p_min || tok == td[i].argmax;
+                shown = px;
+            }
+        }
+    }
+    const unsigned rej = __ballot_sync(0xFFFFFFFFu, lane < L && !ok);
+    const int acc = rej ? __ffs(rej) - 1 : L;
+    // positions after the first rejection are not tested
+    if (a.accept_probs && lane < L) a.accept_probs[(int64_t)s * L + lane] = lane <= acc ? shown : 0.f;
+    const bool bad_draft = acc < L && __shfl_sync(0xFFFFFFFFu, bad ? 1 : 0, acc) != 0;
+    if (lane == 0) {
+        const uint32_t fl = bad_draft ? (1u << 9) : 0u;
+        SpecSeq q;
+        q.acc = acc;
+        q.flags = fl;
+        q.pad = 0;
+        q.kind = greedy ? 0 : ((acc == L || a.mode == 1) ? 1 : 2);
+        seq[s] = q;
+        fallback[s] = 0;
+        a.accepted[s] = acc;
+        if (greedy) {
+            a.correction[s] = td[acc].tie_idx_max;
+            if (a.seq_flags) a.seq_flags[s] = fl;
+        }
+        FullRow *fr = ws.rows + s;
+        fr->redo = 0;
+        fr->n_cross[1] = 0;
+    }
+    FullRow *fr = ws.rows + s;
+    for (int p = lane; p < kFullMaxParts; p += 32) fr->pflag[1][p] = 0u;
+}
+
+template <bool BF16>
+__global__ void __launch_bounds__(kFullThreads) k_spec_values(const __grid_constant__ SpecArgs a, const FullWs ws,
+                                                              const SpecSeq *seq)
+{
+    __shared__ float s_sum[kPieceSubTiles];
+    __shared__ unsigned char s_guess[kPieceSubTiles], s_xslot[kPieceSubTiles];
+    __shared__ int s_ok;
+    const int s = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const SpecSeq q = seq[s];
+    if (q.kind == 0) return;
+    const int L = a.n_draft, n = a.vocab;
+    const int begin = blockIdx.x * kPhasePiece;
+    if (begin >= n) return;
+    const int esz = BF16 ? 2 : 4;
+    const bool al = a.vec == 4;
+    const RowDist td = a.tdist[(int64_t)s * (L + 1) + q.acc];
+    const LogitRow prow{(const char *)a.target + ((int64_t)s * (L + 1) + q.acc) * n * esz, a.target_cap};
+    const ProvRow<BF16> pp{SrcLogits<BF16>{prow, nullptr, al, td.inv_t, td.inv_t != 1.0f}, td};
+    FullRow *fr = ws.rows + s;
+    Emul2Work *ew = ws.ew + s;
+    float *e = ws.e + (size_t)s * ws.e_stride;
+    constexpr int W = kFullThreads / 32;
+    float xs[kWarpSubTiles][8];
+    if (q.kind == 2) {
+        const RowDist dq = a.ddist[(int64_t)s * L + q.acc];
+        const LogitRow qrow{(const char *)a.draft + ((int64_t)s * L + q.acc) * n * esz, a.draft_cap};
+        const ProvRow<BF16> qq{SrcLogits<BF16>{qrow, nullptr, al, dq.inv_t, dq.inv_t != 1.0f}, dq};
+        const ProvResidual<BF16> rr{pp, qq};
+#pragma unroll
+        for (int i = 0; i < kWarpSubTiles; i++) {
+            const int st = warp + i * W;
+            rr.load(begin + st * kSub + lane * 8, n, xs[i]);  // zeros beyond the row
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < kWarpSubTiles; i++) {
+            const int st = warp + i * W;
+            pp.load(begin + st * kSub + lane * 8, n, xs[i]);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < kWarpSubTiles; i++) {
+        const int st = warp + i * W;
+        const int base = begin + st * kSub + lane * 8;
+        if (begin + st * kSub >= n) continue;  // the same for the whole warp
+        if (base < n) store8(e, base, n, xs[i]);
+        float acc = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; j++) acc += xs[i][j] > 0.f ? xs[i][j] : 0.f;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
+        if (lane == 0) { ew->sums[(begin >> 8) + st] = acc; s_sum[st] = acc; }
+    }
+    piece_tail<true>(fr, ew, xs, begin, n, s_sum, s_guess, s_xslot, &s_ok);
+}
+
+__global__ void __launch_bounds__(kThreads, 1) k_spec_draw(const __grid_constant__ SpecArgs a, const FullWs ws,
+                                                           const SpecSeq *seq, int32_t *fallback)
+{
+    extern __shared__ __align__(16) unsigned char arena[];
+    __shared__ Emul2Ctl ctl;
+    __shared__ XCache xcache;
+    const int s = blockIdx.x, tid = threadIdx.x;
+    const SpecSeq q = seq[s];
+    if (q.kind == 0) return;
+    const FullRow *fr = ws.rows + s;
+    if (fr->redo) {
+        if (tid == 0) fallback[s] = 1;
+        return;
+    }
+    const int L = a.n_draft, n = a.vocab;
+    const int nsub = (n + kSub - 1) / kSub;
+    Emul2Work *wk2 = (Emul2Work *)arena;
+    float *xdata = (float *)(arena + sizeof(Emul2Work));
+    load_work(wk2, ws.ew + s);
+    const ProvE pe{ws.e + (size_t)s * ws.e_stride};
+    const float u0 = __double2float_rn(a.uniforms[(int64_t)s * (L + 2) + L]);
+    float target = u0;
+    if (q.kind == 2) {
+        // ResampleResidual (Sampler.cs:587-618): the sum of the residual, then the draw to u * sum
+        build_xcache(&xcache, xdata, wk2, pe, n, nsub, 0.f, false);
+        if (tid < 32) {
+            const ProvCached<ProvE> pc{pe, xdata, xcache.of};
+            emul2_walk<ProvCached<ProvE>, false, false>(&ctl, wk2, pc, n, nsub, 0.f, false, nullptr, nullptr);
+        }
+        __syncthreads();
+        const float sum = ctl.s;
+        __syncthreads();
+        if (!(sum > 0.f)) {  // nothing left of p - q (or NaN): the draw from p with the spare uniform
+            if (tid == 0) fallback[s] = 1;
+            return;
+        }
+        target = __fmul_rn(u0, sum);
+    }
+    build_xcache(&xcache, xdata, wk2, pe, n, nsub, target, true);
+    if (tid < 32) {
+        const ProvCached<ProvE> pc{pe, xdata, xcache.of};
+        emul2_walk<ProvCached<ProvE>, false, false>(&ctl, wk2, pc, n, nsub, target, true, nullptr, nullptr);
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int corr = ctl.hit;
+        uint32_t fl = q.flags;
+        if (corr < 0) {
+            if (q.kind == 2) { fallback[s] = 1; return; }  // the rounding fall-back of the residual draw
+            corr = n - 1;
+            fl |= (1u << 5);
+        }
+        a.correction[s] = corr;
+        if (a.seq_flags) a.seq_flags[s] = fl;
+    }
+}
+
+cudaError_t launch_spec_flat(const SpecArgs &a, const FullWs &ws, void *seq_ctl, int32_t *fallback, cudaStream_t stream)
+{
+    SpecSeq *seq = (SpecSeq *)seq_ctl;
+    cudaError_t e = ensure_dynamic_smem((const void *)k_spec_draw, kDrawSmem);
+    if (e != cudaSuccess) return e;
+    const dim3 pg((unsigned)((a.vocab + kPhasePiece - 1) / kPhasePiece), (unsigned)a.n_seq);
+    if (a.dtype == 1) {
+        k_spec_accept<true><<<(a.n_seq + 7) / 8, 256, 0, stream>>>(a, ws, seq, fallback);
+        k_spec_values<true><<<pg, kFullThreads, 0, stream>>>(a, ws, seq);
+    } else {
+        k_spec_accept<false><<<(a.n_seq + 7) / 8, 256, 0, stream>>>(a, ws, seq, fallback);
+        k_spec_values<false><<<pg, kFullThreads, 0, stream>>>(a, ws, seq);
+    }
+    k_spec_draw<<<a.n_seq, kThreads, kDrawSmem, stream>>>(a, ws, seq, fallback);
+    return cudaGetLastError();
+}
+
 static dim3 piece_grid(const SampleArgs &a, int n_full) { return dim3((unsigned)((a.vocab + kPhasePiece - 1) / kPhasePiece), (unsigned)n_full); }
 
 cudaError_t launch_full_prep(const SampleArgs &a, const FullWs &ws, FlatRow *flat, cudaStream_t stream)
@@ -1219,28 +1435,33 @@ cudaError_t launch_full_rest(const SampleArgs &a, const FullWs &ws, const WorkIt
     k_full_exp<<<pg, kFullThreads, 0, stream>>>(a, ws, full_items);
     kt->mark("full_exp", stream);
     // the plan and the scatter pass need the histogram and the sub-tile sums, not the exact sum: they
-    // run on the side stream beside the walk
-    e = cudaEventRecord(side.after_exp, stream);
-    if (e == cudaSuccess) e = cudaStreamWaitEvent(side.stream, side.after_exp, 0);
-    if (e != cudaSuccess) return e;
-    k_full_plan<<<n_full, kThreads, kRowArenaBytes, side.stream>>>(a, ws, full_items);
-    k_full_scatter<<<pg, kFullThreads, 0, side.stream>>>(a, ws, full_items);
-    e = cudaEventRecord(side.after_scatter, side.stream);
-    if (e != cudaSuccess) return e;
+    // run on the side stream beside the walk (and have nothing to do when no row has top-p on)
+    if (side.any_with_top_p) {
+        e = cudaEventRecord(side.after_exp, stream);
+        if (e == cudaSuccess) e = cudaStreamWaitEvent(side.stream, side.after_exp, 0);
+        if (e != cudaSuccess) return e;
+        k_full_plan<<<n_full, kThreads, kRowArenaBytes, side.stream>>>(a, ws, full_items);
+        k_full_scatter<<<pg, kFullThreads, 0, side.stream>>>(a, ws, full_items);
+        e = cudaEventRecord(side.after_scatter, side.stream);
+        if (e != cudaSuccess) return e;
+        *launches += 2;
+    }
     k_full_walk<<<n_full, kThreads, kRowArenaBytes, stream>>>(a, ws, full_items);
     kt->mark("full_walk", stream);
-    *launches += 4;
+    *launches += 2;
     if (side.any_without_top_p) {
         k_full_nosum<<<pg, kFullThreads, 0, stream>>>(a, ws, full_items);
         kt->mark("full_nosum", stream);
         *launches += 1;
     }
-    e = cudaStreamWaitEvent(stream, side.after_scatter, 0);
-    if (e != cudaSuccess) return e;
-    kt->mark("wait_scatter", stream);
-    k_full_ties<<<pg, kFullThreads, 0, stream>>>(a, ws, full_items);
-    kt->mark("full_ties", stream);
-    *launches += 1;
+    if (side.any_with_top_p) {
+        e = cudaStreamWaitEvent(stream, side.after_scatter, 0);
+        if (e != cudaSuccess) return e;
+        kt->mark("wait_scatter", stream);
+        k_full_ties<<<pg, kFullThreads, 0, stream>>>(a, ws, full_items);
+        kt->mark("full_ties", stream);
+        *launches += 1;
+    }
     k_full_cut<<<n_full, kThreads, kRowArenaBytes, stream>>>(a, ws, full_items);
     kt->mark("full_cut", stream);
     *launches += 1;

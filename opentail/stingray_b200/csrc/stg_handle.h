@@ -39,6 +39,7 @@ struct Plan {
     bool flat_full = false;   // ... and so do the full-vocabulary rows
     int n_chunk_rows = 0;
     int n_full_without_top_p = 0;  // sampled full-vocabulary rows with top-p off
+    int n_full_with_top_p = 0;     // ... and on
 };
 
 }  // namespace stg

@@ -66,6 +66,7 @@ struct SpecArgs {
     uint32_t *seq_flags;
     float p_min;
     float target_cap, draft_cap;  // soft caps of the two models' logits, 0: none
+    const int32_t *only;          // k_spec_finish: when set, only the sequences whose entry is non-zero are done
     int32_t n_seq, n_draft, vocab, dtype, mode, vec;
 };
 cudaError_t launch_spec_finish(const SpecArgs &a, cudaStream_t stream);

@@ -7,6 +7,8 @@
 #include <vector>
 
 #include "stg_handle.h"
+#include "stg_flat.cuh"
+#include "stg_emul2.cuh"
 #include "stg_launch.h"
 
 using namespace stg;
@@ -163,7 +165,26 @@ int stg_spec_verify(StgHandle h, const StgSpecBatch *b, void *stream_)
     a.n_seq = S; a.n_draft = L; a.vocab = V; a.dtype = b->logits_dtype; a.mode = b->mode;
     a.vec = rows_aligned2(b->target_logits, V, b->logits_dtype) &&
             (!b->draft_logits || rows_aligned2(b->draft_logits, V, b->logits_dtype)) ? 4 : 1;
-    cudaError_t e = launch_spec_finish(a, stream);
+    // The flat form (stg_flat_full.cu) takes every sequence it can - up to 32 draft tokens, the handle's
+    // full-row workspace, rows the sub-tile machinery covers - and flags the few that need one of the
+    // draw's fall-backs; k_spec_finish then does exactly those (all of them when the flat form is off).
+    cudaError_t e = cudaSuccess;
+    static const bool no_flat_spec = getenv("STG_NO_FLAT_SPEC") != nullptr;
+    const bool rows_ok = rows_aligned2(b->target_logits, V, b->logits_dtype) &&
+                         (!b->draft_logits || rows_aligned2(b->draft_logits, V, b->logits_dtype));
+    if (!no_flat_spec && !getenv("STG_NO_FLAT") && S <= h->full_cap && h->fw_rows.p && L <= 32 && rows_ok && V >= 4096 &&
+        V <= kSub * kMaxSubTiles && h->sp_rowstats.p) {
+        FullWs ws;
+        memset(&ws, 0, sizeof(ws));
+        ws.rows = (FullRow *)h->fw_rows.p; ws.e = (float *)h->fw_e.p; ws.e_stride = h->escratch_stride;
+        ws.ew = (Emul2Work *)h->fw_ew.p;
+        int32_t *fallback = (int32_t *)((char *)h->sp_rowstats.p + (size_t)S * 16);
+        e = launch_spec_flat(a, ws, h->sp_rowstats.p, fallback, stream);
+        if (e != cudaSuccess) return cuda_fail(h, e, "flat verification launch");
+        h->stats.kernel_launches += 3;
+        a.only = fallback;
+    }
+    e = launch_spec_finish(a, stream);
     if (e != cudaSuccess) return cuda_fail(h, e, "k_spec_finish launch");
     h->stats.kernel_launches++;
     h->stats.sequences_verified += S;

@@ -12,68 +12,9 @@
 
 #include "stg_launch.h"
 #include "stg_rowdist.cuh"
+#include "stg_spec_prov.cuh"
 
 namespace stg {
-
-template <bool BF16>
-__device__ __forceinline__ float eval_point(const LogitRow rowp, int i, const RowDist &d)
-{
-    if (d.flags & kDistOneHot) return i == d.tie_idx_max ? 1.f : 0.f;
-    float e;
-    if (d.flags & kDistUniform) {
-        e = d.uniform_p;
-    } else {
-        float x = load_one<BF16>(rowp, i);
-        if (d.inv_t != 1.0f) x = __fmul_rn(x, d.inv_t);
-        e = expf(__fsub_rn(x, d.max_x));
-    }
-    return eval_p3(e, i, d);
-}
-
-// final probabilities of a row, recomputed from its logits
-template <bool BF16>
-struct ProvRow {
-    SrcLogits<BF16> src;
-    RowDist d;  // by value: lives in registers
-    __device__ __forceinline__ void load(int base, int n, float x[8]) const
-    {
-        if (base >= n) {
-#pragma unroll
-            for (int j = 0; j < 8; j++) x[j] = 0.f;
-            return;
-        }
-        if (d.flags & kDistOneHot) {
-#pragma unroll
-            for (int j = 0; j < 8; j++) x[j] = (base + j == d.tie_idx_max) ? 1.f : 0.f;
-            return;
-        }
-        src.get8(base, n, x);
-#pragma unroll
-        for (int j = 0; j < 8; j++) {
-            float e = (d.flags & kDistUniform) ? d.uniform_p : expf(__fsub_rn(x[j], d.max_x));
-            x[j] = (base + j < n) ? eval_p3(e, base + j, d) : 0.f;
-        }
-    }
-    __device__ __forceinline__ void reload(int base, int n, float x[8]) const { load(base, n, x); }
-};
-
-// positive part of p - q (ResampleResidual's terms)
-template <bool BF16>
-struct ProvResidual {
-    ProvRow<BF16> p, q;
-    __device__ __forceinline__ void load(int base, int n, float x[8]) const
-    {
-        float y[8];
-        p.load(base, n, x);
-        q.load(base, n, y);
-#pragma unroll
-        for (int j = 0; j < 8; j++) {
-            float r = __fsub_rn(x[j], y[j]);
-            x[j] = r > 0.f ? r : 0.f;
-        }
-    }
-    __device__ __forceinline__ void reload(int base, int n, float x[8]) const { load(base, n, x); }
-};
 
 struct SpecShared {
     EmulCtl em;
@@ -91,6 +32,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_spec_finish(const __grid_consta
     Emul2Work *wk2 = (Emul2Work *)spec_dyn;
     const int tid = threadIdx.x;
     const int s = blockIdx.x;
+    if (a.only != nullptr && a.only[s] == 0) return;  // the flat form has finished this sequence
     const int L = a.n_draft, V = a.vocab;
     const int esz = BF16 ? 2 : 4;
     const RowDist *td = a.tdist + (int64_t)s * (L + 1);
