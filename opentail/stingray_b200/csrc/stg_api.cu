@@ -354,7 +354,8 @@ int run_batch(StgHandle h, const StgSampleBatch *b, const BatchExtra &x, void *s
     const size_t esz0 = b->logits_dtype == STG_DTYPE_BF16 ? 2 : 4, need0 = b->logits_dtype == STG_DTYPE_BF16 ? 8 : 16;
     const bool aligned = ((size_t)b->row_stride * esz0) % need0 == 0 &&
                          ((b->mem_flags & STG_MEM_HOST_LOGITS) || ((uintptr_t)b->logits % need0) == 0);
-    const bool flat_ok = mode == 0 && x.shard_mode == 0 && aligned && !getenv("STG_NO_FLAT");
+    const bool flat_ok = mode == 0 && x.shard_mode != 2 && aligned && !getenv("STG_NO_FLAT") &&
+                         !(x.shard_mode == 1 && getenv("STG_NO_FLAT_SHARD"));
     const bool full_ok = (mode == 0 || mode == 2) && x.shard_mode == 0 && aligned && !getenv("STG_NO_FLAT") && !getenv("STG_NO_FLAT_FULL");
     // The plan depends on the batch description only (never on the logits): a decode loop that
     // repeats a description byte for byte reuses the plan of the previous call as it is.
@@ -557,17 +558,20 @@ int run_batch(StgHandle h, const StgSampleBatch *b, const BatchExtra &x, void *s
             const int sms = flat_rows ? std::max(8, h->sm_count - std::min(n_rows_items, h->sm_count) - 4) : h->sm_count;
             c.item_base = n_rows_items;  // diagnostic stamps: behind the full rows' slots
             static const bool no_small = getenv("STG_NO_SMALL_FINISH") != nullptr;
-            // Smaller CTAs, several per SM, when their shorter buffers still hold a row's N best and one
-            // batch of its list (4 entries per thread): 256 threads, four per SM, when the rows outnumber
-            // what the 512-thread form holds at once and no one-SM CTAs of full rows run beside; else 512
-            // threads, two per SM; else one full-size CTA per row.
+            // Smaller CTAs, several per SM, shorten the finish as long as all rows are in flight at once: the
+            // phases of a row are short and barrier-separated, so a 1024-thread CTA leaves most of its SM
+            // idle, but per row the smaller forms do more work (measured on 2048 rows: 577 us with 256
+            // threads against 304 us with 1024).  So: 512 threads, two per SM, up to 2 rows per SM; 256
+            // threads, four per SM, up to 4 rows per SM (not beside the one-SM CTAs of full rows, which
+            // need whole SMs to come free); beyond that one full-size CTA per row.  The smaller forms also
+            // need their shorter buffers to hold a row's N best and one batch of its list.
             constexpr int kHalfCap = 6912, kQuarterCap = 3456;  // 2 x 110,592 B, 4 x 55,296 B (+ static) fit an SM
-            if (!no_small && !flat_rows && n_chunk_items > 2 * sms && pl.max_sel + 1024 + 512 <= kQuarterCap) {
-                c.finish_cap = kQuarterCap;
-                e = launch_flat_finish_quarter(c, fr, std::min(n_chunk_items, 4 * sms), cs);
-            } else if (!no_small && pl.max_sel + 2048 + 512 <= kHalfCap) {
+            if (!no_small && n_chunk_items <= 2 * sms && pl.max_sel + 2048 + 512 <= kHalfCap) {
                 c.finish_cap = kHalfCap;
-                e = launch_flat_finish_half(c, fr, std::min(n_chunk_items, 2 * sms), cs);
+                e = launch_flat_finish_half(c, fr, n_chunk_items, cs);
+            } else if (!no_small && !flat_rows && n_chunk_items <= 4 * sms && pl.max_sel + 1024 + 512 <= kQuarterCap) {
+                c.finish_cap = kQuarterCap;
+                e = launch_flat_finish_quarter(c, fr, n_chunk_items, cs);
             } else {
                 e = launch_flat_finish(c, fr, std::min(n_chunk_items, flat_rows ? sms : n_chunk_items), pl.smem, cs);
             }

@@ -24,6 +24,17 @@ __device__ void flat_finish_row(const SampleArgs &a, FlatRow *fr, int row, int i
     const int esz = BF16 ? 2 : 4;
     const LogitRow rowp{(const char *)a.logits + (int64_t)row * a.row_stride * esz, a.softcap};
     if (rp.path == kPathGreedy) {
+        if (a.shard_mode == 1) {
+            // vocabulary-sharded mode: this rank's best (value, global token) goes to the exchange buffer
+            // (the streaming kernel numbers tokens by column; the global id is column + vocab_offset, and
+            // a key's low half holds ~token, so the offset is subtracted)
+            if (threadIdx.x == 0) {
+                const unsigned long long key = fr[row].key;
+                a.xchg_local[(int64_t)row * a.xchg_stride] = key ? key - (unsigned long long)a.vocab_offset : 0ull;
+                a.xchg_count[row] = key ? 1 : 0;
+            }
+            return;
+        }
         if (threadIdx.x == 0) {
             const unsigned long long key = fr[row].key;
             int tok = 0;
@@ -56,7 +67,7 @@ __device__ void flat_finish_row(const SampleArgs &a, FlatRow *fr, int row, int i
     s.buf[1] = s.buf[0] + cap;
     s.cap = cap;
     s.n = rp.sel;
-    s.idx_off = 0;
+    s.idx_off = a.vocab_offset;
     sel_reset(s);
     if (threadIdx.x == 0) {
         const FlatRow f = fr[row];
@@ -88,6 +99,19 @@ __device__ void flat_finish_row(const SampleArgs &a, FlatRow *fr, int row, int i
             sel_reset(s);
         }
         sel_stream_generous<4, BF16>(s, rowp, mrow, 0, a.vocab, over, preset, bound);
+    }
+    if (a.shard_mode == 1) {
+        // vocabulary-sharded mode: hand this rank's best `sel` survivors to the exchange buffer
+        __syncthreads();
+        if (ctl.cnt > rp.sel) sel_compact(s);
+        const int m = ctl.cnt;
+        const u64 *src = s.buf[ctl.cur];
+        u64 *dst = a.xchg_local + (int64_t)row * a.xchg_stride;
+        // keys from the streaming kernel's list carry column numbers, keys of a second pass global ids
+        const u64 shift = cnt >= 0 ? (u64)a.vocab_offset : 0ull;
+        for (int e = threadIdx.x; e < m; e += kThreads) dst[e] = src[e] - shift;
+        if (threadIdx.x == 0) a.xchg_count[row] = m;
+        return;
     }
     tick(tk, 1);
     if (tk && threadIdx.x == 0) { tk[8] = (unsigned long long)(long long)cnt; tk[9] = (unsigned long long)fr[row].cnt; tk[10] = (unsigned long long)fr[row].cap; }
