@@ -460,6 +460,7 @@ int run_batch(StgHandle h, const StgSampleBatch *b, const BatchExtra &x, void *s
     a.work_counter = (uint32_t *)h->work_counter.p;
     a.counters = (unsigned long long *)h->work_counter.p + 16;  // bytes 128..191 of the same small buffer
     a.softcap = b->logit_softcap;
+    a.lookback_drill = h->lookback_drill ? 1 : 0;
     a.phase_ticks = (unsigned long long *)h->ticks.p;
     h->ticks_items = (int)pl.items.size();
     a.escratch = (float *)h->escratch.p;
@@ -681,6 +682,7 @@ int stg_create(const StgConfig *cfg, StgHandle *out)
     h = new StgSampler_();
     h->cfg = *cfg;
     h->checked = getenv("STG_CHECKED") != nullptr && getenv("STG_CHECKED")[0] == '1';
+    h->lookback_drill = getenv("STG_LOOKBACK_DRILL") != nullptr && getenv("STG_LOOKBACK_DRILL")[0] == '1';
     h->sm_count = prop.multiProcessorCount;
     h->smem_optin = prop.sharedMemPerBlockOptin > 4096 ? prop.sharedMemPerBlockOptin - 4096 : 0;
     const size_t R = (size_t)cfg->max_rows, V = (size_t)cfg->max_vocab;

@@ -129,25 +129,28 @@ __device__ __forceinline__ uint32_t ld_acquire_u32(const uint32_t *p)
 // piece's sub-tiles in shared memory (s_sum[0..nloc)): publishes the piece total, looks back, and
 // leaves the guessed binade and the crossing slot of every sub-tile of the piece in shared memory
 // and in the row's Emul2Work.  Returns false (to every lane) when the look-back timed out.
+// `drill`: the wait-runs-out drill (SampleArgs::lookback_drill): piece 0 of the exp pass keeps its flag
+// to itself and the wait gives up after 64 polls, so every other piece of every row times out.
 __device__ __forceinline__ bool piece_guesses(FullRow *fr, Emul2Work *ew, int k, int p, int t0, int nloc, int nsub,
-                                              const float *s_sum, unsigned char *s_guess, unsigned char *s_xslot)
+                                              const float *s_sum, unsigned char *s_guess, unsigned char *s_xslot, bool drill)
 {
     const int lane = threadIdx.x & 31;
     const double mine = lane < nloc ? (double)s_sum[lane] : 0.0;
     double tot = mine;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) tot += __shfl_xor_sync(0xFFFFFFFFu, tot, o);
-    if (lane == 0) {
+    if (lane == 0 && !(drill && p == 0)) {
         __stcg(&fr->ptotal[k][p], tot);
         __threadfence();
         atomicExch(&fr->pflag[k][p], 1u);
     }
+    const int spins = drill ? 64 : kLookbackSpins;
     bool ok = true;
     double before = 0.0;
     if (lane < p) {
         int it = 0;
         while (ld_acquire_u32(&fr->pflag[k][lane]) == 0u) {
-            if (++it > kLookbackSpins) { ok = false; break; }
+            if (++it > spins) { ok = false; break; }
             __nanosleep(40);
         }
         if (ok) before = __ldcg(&fr->ptotal[k][lane]);
@@ -217,13 +220,14 @@ __device__ __forceinline__ void piece_composites(Emul2Work *ew, const float (&xs
 // the tail both per-piece kernels share: look-back and guesses by warp 0, composites by everyone
 template <bool FINAL>
 __device__ __forceinline__ void piece_tail(FullRow *fr, Emul2Work *ew, const float (&xs)[kWarpSubTiles][8], int begin, int n,
-                                           float *s_sum, unsigned char *s_guess, unsigned char *s_xslot, int *s_ok)
+                                           float *s_sum, unsigned char *s_guess, unsigned char *s_xslot, int *s_ok,
+                                           bool drill = false)
 {
     const int t0 = begin >> 8, nsub = (n + kSub - 1) / kSub;
     const int nloc = min(kPieceSubTiles, nsub - t0);
     __syncthreads();  // s_sum is complete
     if (threadIdx.x < 32) {
-        const bool ok = piece_guesses(fr, ew, FINAL ? 1 : 0, begin / kPhasePiece, t0, nloc, nsub, s_sum, s_guess, s_xslot);
+        const bool ok = piece_guesses(fr, ew, FINAL ? 1 : 0, begin / kPhasePiece, t0, nloc, nsub, s_sum, s_guess, s_xslot, drill);
         if (threadIdx.x == 0) *s_ok = ok ? 1 : 0;
     }
     __syncthreads();
@@ -325,7 +329,7 @@ __global__ void __launch_bounds__(kFullThreads) k_full_exp(const __grid_constant
         }
     }
     // phases B and C of the softmax sum for this piece, on the exp values still in registers
-    piece_tail<false>(fr, ew, xs, begin, n, s_sum, s_guess, s_xslot, &s_ok);
+    piece_tail<false>(fr, ew, xs, begin, n, s_sum, s_guess, s_xslot, &s_ok, a.lookback_drill != 0);
 }
 
 // ---- sums of the final probabilities (the draw's phase A) ------------------------------------------------

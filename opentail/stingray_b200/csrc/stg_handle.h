@@ -51,6 +51,7 @@ struct StgSampler_ {
     std::string err;
     StgStats stats{};
     bool checked = false;                // STG_CHECKED=1 at creation: guard words behind every device buffer
+    bool lookback_drill = false;         // STG_LOOKBACK_DRILL=1 at creation: see SampleArgs::lookback_drill
 
     // workspace (allocated once at creation)
     stg::DevBuf plan_dev;                // RowPlan[], WorkItem[], pow table

@@ -88,3 +88,31 @@ def test_unchecked_handles_carry_no_guards():
         assert _guards(bs) == (0, -1)
     finally:
         bs.close()
+
+
+def test_a_look_back_that_runs_out_costs_a_second_pass_not_the_result():
+    """The one wait between CTAs in the library - the look-back over the pieces of a row in the exp
+    pass - is bounded.  The drill makes it run out without any fault: piece 0 of every row withholds
+    its flag and the wait gives up after 64 polls, so every later piece times out, flags its row, and
+    the row kernel redoes the row.  Tokens and probabilities must still be the oracle's, every
+    full-vocabulary row must report the second pass, and the handle must keep working."""
+    from opentail.stingray_b200 import BatchSampler
+    from opentail.stingray_b200 import workloads as W
+    from tests import parity
+
+    w = W.config2(rows=24, seed=11)
+    os.environ["STG_LOOKBACK_DRILL"] = "1"
+    try:
+        bs = BatchSampler(max_rows=w.rows, max_vocab=w.vocab, max_history=512, max_top_k=128)
+    finally:
+        del os.environ["STG_LOOKBACK_DRILL"]
+    try:
+        for _ in range(2):
+            gpu = parity.run_gpu(bs, w, want_topk=int(w.params["top_k"].max()))
+            parity.compare(w, gpu)
+            flags = gpu["flags"].view(np.uint32)
+            full = (flags & 7) == 3
+            assert full.any() and ((flags[full] >> 8) & 1).all(), "every full-vocabulary row should have been redone"
+        assert bs.stats()["reread_rows"] >= int(full.sum())
+    finally:
+        bs.close()
