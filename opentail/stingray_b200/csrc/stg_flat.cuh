@@ -3,7 +3,7 @@
 //
 //   k_flat_prep    one CTA per row   what a row needs before it can be streamed: the filter bound of
 //                                    a top-k row (guessed from its first 4096 logits), zeroed
-//                                    counters
+//                                    counters (done by k_full_prep when the step has full rows too)
 //   k_flat_stream  one small CTA per 16384-element piece of a row, every row of the batch in one
 //                  grid: the only kernel that reads the logits from HBM.  Greedy rows keep a running
 //                  arg-max key (64-bit atomicMax), top-k rows append every logit above the row's
@@ -61,14 +61,18 @@ static_assert(sizeof(FlatRow) == 32, "FlatRow layout");
 //            CTA, the guessed binade of every sub-tile of the piece (fp64 prefix of the sub-tile sums:
 //            the pieces before it publish their totals, a bounded look-back collects them) and the
 //            composite increment of every sub-tile under its guess
-//   walk     exact softmax sum; min-p threshold; top-p plan (bound, bin starts, flagged bins)
-//   scatter  candidates above the bound into bin order (or fp64 partial sums without top-p)
-//   cut      dirty-bin sorts and the emulated sorted-order sum -> top-p threshold; normalise
+//   walk     exact softmax sum; min-p threshold
+//   plan     (beside the walk, on a stream of its own) top-p plan from the histogram and the fp64 sum
+//            of the sub-tile sums: nucleus bound, bin starts, flagged bins
+//   scatter  (behind the plan) exp values above the bound into bin order
+//   nosum    rows without top-p: fp64 partial sums of their probabilities
+//   ties     candidates whose addition would be an exact rounding tie flag their bin
+//   cut      flagged-bin sorts and the emulated sorted-order sum -> top-p threshold; normalise
 //   sums     the same over the final probabilities (sub-tile sums, look-back, guesses, composites)
 //   draw     the walk that finds the token the uniform lands on
 //
-// A row the flat step cannot finish (its nucleus bound proved too tight) is flagged and redone by the
-// self-contained row kernel afterwards.
+// A row the flat step cannot finish (its nucleus bound proved too tight, or a look-back ran out) is
+// flagged and redone by the self-contained row kernel, on the side stream beside the last two kernels.
 constexpr int kFullMaxPieces = 16;  // 262144 / kFlatPiece
 constexpr int kFullMaxParts = 32;   // per-piece partial sums of the phase kernels (8192-element pieces)
 
