@@ -21,6 +21,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 OUT_DIR = os.path.join(HERE, "_ref")
 SO = os.path.join(OUT_DIR, "libref_argmax.so")
 REL = os.path.join("src", "OpenTail.Stingray.Cuda", "CudaTextKernels.cs")
+# the reference checkout: STG_REFERENCE_ROOT, else a directory `reference` beside this repository
+DEFAULT_REFERENCE = os.environ.get("STG_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 
 
 def extract(cs_text: str) -> str:
@@ -33,7 +35,8 @@ def extract(cs_text: str) -> str:
     return (m.group(0) + "\n" + k.group(0)).replace('""', '"')
 
 
-def build(reference_root: str = "/root/reference") -> str | None:
+def build(reference_root: str | None = None) -> str | None:
+    reference_root = reference_root or DEFAULT_REFERENCE
     src = os.path.join(reference_root, REL)
     if not os.path.exists(src):
         return SO if os.path.exists(SO) else None
@@ -52,5 +55,5 @@ def build(reference_root: str = "/root/reference") -> str | None:
 
 
 if __name__ == "__main__":
-    out = build(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    out = build(sys.argv[1] if len(sys.argv) > 1 else None)
     print(out or "reference tree not present and no earlier build: nothing built")
