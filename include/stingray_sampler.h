@@ -23,6 +23,14 @@
  * stream than the previous one is put behind everything enqueued on the previous stream so far (an
  * event, no host wait), which must therefore still exist.  Inputs and outputs follow the usual
  * rule: they must be ready on, and are ready after, the stream of the call that uses them.
+ *
+ * Repeated steps: a decode loop calls stg_sample_batch with the same buffers and the same per-row
+ * parameters step after step, only the contents of the buffers change.  The second time the library
+ * sees such a call on a stream that can be captured (any stream but the legacy default stream, which
+ * CUDA cannot capture) it records the step's launches - a dozen kernels on three streams - as a CUDA
+ * graph, and from then on submits the step as one graph launch.  Nothing changes for the caller;
+ * StgStats.graph_replays counts those steps, and STG_NO_GRAPH=1 in the environment at stg_create turns
+ * the mechanism off.  Steps with host-memory inputs are never captured.
  */
 #ifndef STINGRAY_SAMPLER_H
 #define STINGRAY_SAMPLER_H
@@ -233,6 +241,7 @@ typedef struct StgStats {
     uint64_t reread_rows;        /* STG_ROW_READ_TWICE */
     uint64_t near_cut_rows;      /* STG_ROW_NEAR_CUT */
     uint64_t fully_masked_rows;  /* STG_ROW_FULLY_MASKED on a sampled row */
+    uint64_t graph_replays;      /* sampling steps submitted as one replay of a captured CUDA graph */
 } StgStats;
 
 /* ---- lifetime ---------------------------------------------------------------------------------- */

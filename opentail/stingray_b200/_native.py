@@ -79,7 +79,7 @@ class StgStats(C.Structure):
     _fields_ = [(n, C.c_uint64) for n in (
         "calls", "rows_sampled", "rows_greedy", "rows_topk_path", "rows_full_path",
         "sequences_verified", "kernel_launches", "plan_uploads", "boundary_draws", "tie_rows", "cdf_fallbacks",
-        "wide_nucleus_rows", "reread_rows", "near_cut_rows", "fully_masked_rows")]
+        "wide_nucleus_rows", "reread_rows", "near_cut_rows", "fully_masked_rows", "graph_replays")]
 
 
 _lib = None

@@ -384,6 +384,7 @@ int run_batch(StgHandle h, const StgSampleBatch *b, const BatchExtra &x, void *s
         if (rc) return rc;
         h->plan_key = key;
         h->plan_valid = true;
+        h->plan_version++;
     }
     const RowPlan *d_rows = h->d_rows; const WorkItem *d_items = h->d_items; const float *d_pow = h->d_pow;
 
@@ -529,16 +530,22 @@ int run_batch(StgHandle h, const StgSampleBatch *b, const BatchExtra &x, void *s
         r.item_base = 0;
         r.work_counter = (uint32_t *)h->work_counter.p + 1;
         r.work_base = h->work_base_rows;
-        if (redo_only) { r.redo_flags = &ws.rows[0].redo; r.redo_stride = (int32_t)(sizeof(FullRow) / 4); }
+        if (redo_only) { r.redo_flags = &ws.rows[0].redo; r.redo_stride = (int32_t)(sizeof(FullRow) / 4); r.static_items = 1; }
         row_grid = std::min(n_rows_items, h->sm_count);
         cudaError_t er = launch_sample_rows(r, row_grid, on);
-        if (er == cudaSuccess) { h->work_base_rows += (uint32_t)n_rows_items + (uint32_t)row_grid; launches++; }
+        if (er == cudaSuccess) { if (!redo_only) h->work_base_rows += (uint32_t)n_rows_items + (uint32_t)row_grid; launches++; }
         return er;
     };
     SampleArgs c = a;  // the chunked rows' view of the step
     c.items = a.items + n_rows_items;
     c.n_items = n_chunk_items;
-    h->kt.begin(stream);
+    // The launches of the step.  When this plan and these arguments (every pointer included) have been
+    // launched before, the whole sequence - three streams, their events - is captured once into a CUDA
+    // graph and replayed from then on: one submission instead of a dozen, and no host time between the
+    // kernels of the chain.  Only steps made of replayable launches qualify: the flat form (the
+    // persistent kernels of the first design draw work from counters whose base the host advances),
+    // inputs already on the device, no diagnostics.
+    auto issue = [&]() {
     if (flat_chunks || flat_full) {
         if (flat_chunks && !flat_full) { e = launch_flat_prep(c, fr, stream); launches++; h->kt.mark("flat_prep", stream); }
         if (e == cudaSuccess && flat_full) { e = launch_full_prep(a, ws, flat_chunks ? fr : nullptr, stream); launches++; h->kt.mark("full_prep", stream); }
@@ -614,6 +621,73 @@ int run_batch(StgHandle h, const StgSampleBatch *b, const BatchExtra &x, void *s
     if (e == cudaSuccess && fork) e = cudaEventRecord(h->ev_join, h->aux_stream);
     if (e == cudaSuccess && fork) e = cudaStreamWaitEvent(stream, h->ev_join, 0);
     h->kt.mark("join_side_stream", stream);
+    };
+    const uint32_t host_in = STG_MEM_HOST_LOGITS | STG_MEM_HOST_HISTORY | STG_MEM_HOST_MASK | STG_MEM_HOST_BIAS | STG_MEM_HOST_UNIFORMS;
+    const bool all_flat = (flat_chunks || n_chunk_items == 0) && (flat_full || n_rows_items == 0);
+    bool replayed = false;
+    cudaStreamCaptureStatus cap_status = cudaStreamCaptureStatusNone;
+    if (!h->graphs_off) cudaStreamIsCapturing(stream, &cap_status);  // never a capture inside a caller's capture
+    if (!h->graphs_off && cap_status == cudaStreamCaptureStatusNone && all_flat && x.shard_mode == 0 && (mf & host_in) == 0 &&
+        !h->kt.on && a.phase_ticks == nullptr) {
+        std::vector<unsigned char> &gk = h->plan_key_scratch;  // free again: the plan key has been compared
+        gk.assign((const unsigned char *)&a, (const unsigned char *)&a + sizeof(a));
+        const uint64_t extra[3] = {h->plan_version, (uint64_t)(uintptr_t)stream, (uint64_t)mode};
+        gk.insert(gk.end(), (const unsigned char *)extra, (const unsigned char *)extra + sizeof(extra));
+        uint64_t hash = 1469598103934665603ull;
+        for (unsigned char ch : gk) hash = (hash ^ ch) * 1099511628211ull;
+        StgSampler_::StepGraph *hit = nullptr;
+        for (auto &g : h->graphs)
+            if (g.exec && g.key == gk) hit = &g;
+        if (hit == nullptr && std::find(h->seen_keys.begin(), h->seen_keys.end(), hash) != h->seen_keys.end()) {
+            // second sighting: capture.  Nothing runs during a capture; a failed one is abandoned and the
+            // step launched directly, with graphs off for this handle from then on.
+            cudaGraph_t graph = nullptr;
+            cudaGraphExec_t exec = nullptr;
+            cudaError_t ce = cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal);
+            if (ce == cudaSuccess) {
+                issue();
+                const cudaError_t launch_e = e;
+                ce = cudaStreamEndCapture(stream, &graph);
+                if (ce == cudaSuccess && launch_e != cudaSuccess) ce = launch_e;
+            }
+            if (ce == cudaSuccess) ce = cudaGraphInstantiate(&exec, graph, 0);
+            if (graph) cudaGraphDestroy(graph);
+            if (ce == cudaSuccess) {
+                StgSampler_::StepGraph *slot = nullptr;
+                if (h->graphs.size() < 16) { h->graphs.emplace_back(); slot = &h->graphs.back(); }
+                else {
+                    slot = &h->graphs[0];
+                    for (auto &g : h->graphs) if (g.used < slot->used) slot = &g;
+                    if (slot->exec) cudaGraphExecDestroy(slot->exec);
+                }
+                slot->key = gk;
+                slot->exec = exec;
+                slot->launches = launches;
+                hit = slot;
+            } else {
+                cudaGetLastError();  // clear
+                h->graphs_off = true;
+                e = cudaSuccess;
+                launches = 0;
+            }
+        } else if (hit == nullptr) {
+            if (h->seen_keys.size() >= 8) h->seen_keys.erase(h->seen_keys.begin());
+            h->seen_keys.push_back(hash);
+        }
+        if (hit != nullptr) {
+            hit->used = ++h->graph_tick;
+            e = cudaGraphLaunch(hit->exec, stream);
+            replayed = true;
+            h->stats.graph_replays++;
+            launches = hit->launches;
+        }
+    }
+    if (!replayed) {
+        h->kt.begin(stream);
+        launches = 0;
+        e = cudaSuccess;
+        issue();
+    }
     if (e != cudaSuccess) {
         cudaMemsetAsync(h->work_counter.p, 0, 8, stream);
         cudaMemsetAsync(h->tickets.p, 0, h->tickets.bytes, stream);
@@ -683,6 +757,7 @@ int stg_create(const StgConfig *cfg, StgHandle *out)
     h->cfg = *cfg;
     h->checked = getenv("STG_CHECKED") != nullptr && getenv("STG_CHECKED")[0] == '1';
     h->lookback_drill = getenv("STG_LOOKBACK_DRILL") != nullptr && getenv("STG_LOOKBACK_DRILL")[0] == '1';
+    h->graphs_off = getenv("STG_NO_GRAPH") != nullptr;
     h->sm_count = prop.multiProcessorCount;
     h->smem_optin = prop.sharedMemPerBlockOptin > 4096 ? prop.sharedMemPerBlockOptin - 4096 : 0;
     const size_t R = (size_t)cfg->max_rows, V = (size_t)cfg->max_vocab;
@@ -799,6 +874,7 @@ int stg_destroy(StgHandle h)
     cudaSetDevice(h->cfg.device);
     cudaDeviceSynchronize();
     stg_comm_destroy(h);
+    for (auto &g : h->graphs) if (g.exec) cudaGraphExecDestroy(g.exec);
     for (DevBuf *b : all_buffers(h)) dev_free(*b);
     if (h->plan_host) cudaFreeHost(h->plan_host);
     for (auto &ev : h->plan_ev) if (ev) cudaEventDestroy(ev);

@@ -51,6 +51,19 @@ struct StgSampler_ {
     std::string err;
     StgStats stats{};
     bool checked = false;                // STG_CHECKED=1 at creation: guard words behind every device buffer
+    // replayable steps: the launches of a step whose plan and arguments have been seen before are
+    // captured once into a CUDA graph and replayed (stg_api.cu)
+    struct StepGraph {
+        std::vector<unsigned char> key;
+        cudaGraphExec_t exec = nullptr;
+        uint64_t used = 0;
+        int launches = 0;  // kernels in the graph
+    };
+    std::vector<StepGraph> graphs;
+    std::vector<uint64_t> seen_keys;       // hashes of the last few argument sets that were launched directly
+    uint64_t graph_tick = 0;
+    uint64_t plan_version = 0;             // bumped with every new plan
+    bool graphs_off = false;               // STG_NO_GRAPH=1, or a capture failed on this handle
     bool lookback_drill = false;         // STG_LOOKBACK_DRILL=1 at creation: see SampleArgs::lookback_drill
 
     // workspace (allocated once at creation)

@@ -235,11 +235,18 @@ __global__ void __launch_bounds__(kThreads, 1) k_sample_rows(const __grid_consta
     extern __shared__ __align__(16) unsigned char arena[];
     __shared__ SelCtl ctl;
     __shared__ int sh_item;
+    int next = blockIdx.x;
     for (;;) {
-        if (threadIdx.x == 0) sh_item = (int)(atomicAdd(a.work_counter, 1u) - a.work_base);
-        __syncthreads();
-        const int item = sh_item;
-        __syncthreads();
+        int item;
+        if (a.static_items) {
+            item = next;
+            next += gridDim.x;
+        } else {
+            if (threadIdx.x == 0) sh_item = (int)(atomicAdd(a.work_counter, 1u) - a.work_base);
+            __syncthreads();
+            item = sh_item;
+            __syncthreads();
+        }
         if ((unsigned)item >= (unsigned)a.n_items) break;
         const WorkItem w = a.items[item];
         run_row<BF16>(a, w.row, a.item_base + item, &ctl, arena);

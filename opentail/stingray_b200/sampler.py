@@ -242,30 +242,43 @@ class BatchSampler:
     def sample_rows(self, logits, params, *, history_ids=None, history_offsets=None, mask=None,
                     row_uses_mask=None, bias=None, uniforms=None, want_probs=False,
                     want_flags=False, want_topk=0, host_outputs: Optional[bool] = None, softcap: float = 0.0,
-                    history_ring: bool = False, stream=None):
+                    history_ring: bool = False, stream=None, out: Optional[dict] = None):
         """One sampling step (``stg_sample_rows``).  ``logits`` is a CUDA tensor (fp32/bf16) or a
         NumPy array (float32, or uint16 bf16 bit patterns); ``params`` a list of SamplingParams or
         a PARAMS_DTYPE array; histories/bias are CSR; ``uniforms`` one float per row.  Returns a
         dict with ``tokens`` and the optional outputs, on the device unless ``host_outputs``.
         ``softcap`` != 0 reads every logit as ``tanh(x / softcap) * softcap`` (the final-logit soft
         cap, ``CudaTextKernels.cs:374-383``) without rewriting the logits.  ``history_ring``: row r's
-        PreviousTokens are the handle's device-resident history of slot r (``history_append``)."""
+        PreviousTokens are the handle's device-resident history of slot r (``history_append``).
+        ``out``: the dict a previous call with the same shapes and options returned; its arrays are
+        written again instead of new ones (a decode loop's fixed output buffers - with the inputs in
+        place too, the step repeats exactly and the library replays it as a CUDA graph)."""
         b, keep = self._batch(logits, params, history_ids, history_offsets, mask, row_uses_mask,
                               bias, uniforms, softcap, history_ring)
         host = (not _is_torch(logits)) if host_outputs is None else host_outputs
         rows = b.rows
-        out = {"tokens": self._alloc((rows,), np.int32, host)}
+        prev = out
+
+        def take(name, shape, dtype):
+            if prev is not None:
+                arr = prev[name]
+                if tuple(arr.shape) != tuple(shape):
+                    raise ValueError(f"out[{name!r}] has shape {tuple(arr.shape)}, this call needs {tuple(shape)}")
+                return arr
+            return self._alloc(shape, dtype, host)
+
+        out = {"tokens": take("tokens", (rows,), np.int32)}
         b.tokens = _ptr(out["tokens"])
         if want_probs:
-            out["probs"] = self._alloc((rows,), np.float32, host)
+            out["probs"] = take("probs", (rows,), np.float32)
             b.token_probs = _ptr(out["probs"])
         if want_flags:
-            out["flags"] = self._alloc((rows,), np.uint32, host)
+            out["flags"] = take("flags", (rows,), np.uint32)
             b.row_flags = _ptr(out["flags"])
         if want_topk:
-            out["topk_ids"] = self._alloc((rows, want_topk), np.int32, host)
-            out["topk_logits"] = self._alloc((rows, want_topk), np.float32, host)
-            out["topk_probs"] = self._alloc((rows, want_topk), np.float32, host)
+            out["topk_ids"] = take("topk_ids", (rows, want_topk), np.int32)
+            out["topk_logits"] = take("topk_logits", (rows, want_topk), np.float32)
+            out["topk_probs"] = take("topk_probs", (rows, want_topk), np.float32)
             b.topk_ids, b.topk_logits = _ptr(out["topk_ids"]), _ptr(out["topk_logits"])
             b.topk_probs, b.topk_stride = _ptr(out["topk_probs"]), want_topk
         if host:

@@ -34,7 +34,7 @@ def test_struct_layouts_match_the_header():
     assert C.sizeof(N.StgRowParams) == 32
     assert C.sizeof(N.StgConfig) == 40
     assert C.sizeof(N.StgSampleBatch) == 176
-    assert C.sizeof(N.StgStats) == 120
+    assert C.sizeof(N.StgStats) == 128
     from opentail.stingray_b200.sampler import PARAMS_DTYPE
 
     assert PARAMS_DTYPE.itemsize == C.sizeof(N.StgRowParams)
