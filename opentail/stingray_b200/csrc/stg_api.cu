@@ -461,7 +461,7 @@ int run_batch(StgHandle h, const StgSampleBatch *b, const BatchExtra &x, void *s
     a.work_counter = (uint32_t *)h->work_counter.p;
     a.counters = (unsigned long long *)h->work_counter.p + 16;  // bytes 128..191 of the same small buffer
     a.softcap = b->logit_softcap;
-    a.lookback_drill = h->lookback_drill ? 1 : 0;
+    a.lookback_drill = h->lookback_drill;
     a.phase_ticks = (unsigned long long *)h->ticks.p;
     h->ticks_items = (int)pl.items.size();
     a.escratch = (float *)h->escratch.p;
@@ -598,8 +598,9 @@ int run_batch(StgHandle h, const StgSampleBatch *b, const BatchExtra &x, void *s
         // own beside the walk).  Side stream: the finish of the chunked rows - held back until the scatter
         // pass is through, because its one-SM CTAs would otherwise sit on the SMs that pass needs while
         // the walk holds the others, whereas the cut that follows leaves two thirds of the GPU idle -
-        // and behind it, once the cut kernel has said which rows the flat form gave up, the row kernel
-        // for exactly those (every other CTA of it leaves at once), beside the draw's two kernels.
+        // and behind it, once the last kernel that can give a row up (the draw's partial sums) is through,
+        // the row kernel for exactly the rows the flat form gave up (every other CTA of it leaves at
+        // once), beside the draw.
         if (!flat_chunks) launch_chunked();
         const FullSide side{h->plan_stream, h->ev_exp, h->ev_scatter, pl.n_full_without_top_p > 0, pl.n_full_with_top_p > 0};
         if (e == cudaSuccess) e = launch_full_rest(a, ws, a.items, n_rows_items, &launches, &h->kt, stream, 0, side);
@@ -607,10 +608,11 @@ int run_batch(StgHandle h, const StgSampleBatch *b, const BatchExtra &x, void *s
             if (e == cudaSuccess && side.any_with_top_p) e = cudaStreamWaitEvent(h->aux_stream, h->ev_scatter, 0);
             launch_chunked();
         }
+        if (e == cudaSuccess) e = launch_full_rest(a, ws, a.items, n_rows_items, &launches, &h->kt, stream, 1, side);
         if (e == cudaSuccess) e = cudaEventRecord(h->ev_cut, stream);
         if (e == cudaSuccess) e = cudaStreamWaitEvent(h->aux_stream, h->ev_cut, 0);
         if (e == cudaSuccess) e = launch_rows_kernel(true, h->aux_stream);
-        if (e == cudaSuccess) e = launch_full_rest(a, ws, a.items, n_rows_items, &launches, &h->kt, stream, 1, side);
+        if (e == cudaSuccess) e = launch_full_rest(a, ws, a.items, n_rows_items, &launches, &h->kt, stream, 2, side);
     } else {
         if (e == cudaSuccess && n_rows_items > 0) {
             e = launch_rows_kernel(false, stream);
@@ -756,7 +758,7 @@ int stg_create(const StgConfig *cfg, StgHandle *out)
     h = new StgSampler_();
     h->cfg = *cfg;
     h->checked = getenv("STG_CHECKED") != nullptr && getenv("STG_CHECKED")[0] == '1';
-    h->lookback_drill = getenv("STG_LOOKBACK_DRILL") != nullptr && getenv("STG_LOOKBACK_DRILL")[0] == '1';
+    if (const char *drill = getenv("STG_LOOKBACK_DRILL")) h->lookback_drill = drill[0] == '1' ? 1 : drill[0] == '2' ? 2 : 0;
     h->graphs_off = getenv("STG_NO_GRAPH") != nullptr;
     h->sm_count = prop.multiProcessorCount;
     h->smem_optin = prop.sharedMemPerBlockOptin > 4096 ? prop.sharedMemPerBlockOptin - 4096 : 0;

@@ -129,7 +129,7 @@ __device__ __forceinline__ uint32_t ld_acquire_u32(const uint32_t *p)
 // piece's sub-tiles in shared memory (s_sum[0..nloc)): publishes the piece total, looks back, and
 // leaves the guessed binade and the crossing slot of every sub-tile of the piece in shared memory
 // and in the row's Emul2Work.  Returns false (to every lane) when the look-back timed out.
-// `drill`: the wait-runs-out drill (SampleArgs::lookback_drill): piece 0 of the exp pass keeps its flag
+// `drill`: the wait-runs-out drill (SampleArgs::lookback_drill): piece 0 of the drilled pass keeps its flag
 // to itself and the wait gives up after 64 polls, so every other piece of every row times out.
 __device__ __forceinline__ bool piece_guesses(FullRow *fr, Emul2Work *ew, int k, int p, int t0, int nloc, int nsub,
                                               const float *s_sum, unsigned char *s_guess, unsigned char *s_xslot, bool drill)
@@ -329,7 +329,7 @@ __global__ void __launch_bounds__(kFullThreads) k_full_exp(const __grid_constant
         }
     }
     // phases B and C of the softmax sum for this piece, on the exp values still in registers
-    piece_tail<false>(fr, ew, xs, begin, n, s_sum, s_guess, s_xslot, &s_ok, a.lookback_drill != 0);
+    piece_tail<false>(fr, ew, xs, begin, n, s_sum, s_guess, s_xslot, &s_ok, a.lookback_drill == 1);
 }
 
 // ---- sums of the final probabilities (the draw's phase A) ------------------------------------------------
@@ -373,7 +373,7 @@ __global__ void __launch_bounds__(kFullThreads) k_full_psums(const __grid_consta
             if (lane == 0) { ew->sums[(begin >> 8) + st] = acc; s_sum[st] = acc; }
         }
     }
-    piece_tail<true>(fr, ew, xs, begin, n, s_sum, s_guess, s_xslot, &s_ok);
+    piece_tail<true>(fr, ew, xs, begin, n, s_sum, s_guess, s_xslot, &s_ok, a.lookback_drill == 2);
 }
 
 // copies a row's sub-tile summaries from device memory into the shared-memory work area of the walk
@@ -1416,7 +1416,8 @@ cudaError_t launch_full_prep(const SampleArgs &a, const FullWs &ws, FlatRow *fla
 }
 
 // everything behind the HBM pass for the `n_full` full rows listed in `full_rows` (device array)
-// part 0: exp .. cut (after which the rows to redo are known); part 1: the draw's two kernels
+// part 0: exp .. cut; part 1: the draw's partial sums (the last kernel that can give a row up: its
+// look-back is a bounded wait too), after which the rows to redo are known; part 2: the draw
 cudaError_t launch_full_rest(const SampleArgs &a, const FullWs &ws, const WorkItem *full_items, int n_full, int *launches,
                              KernelTimer *kt, cudaStream_t stream, int part, const FullSide &side)
 {
@@ -1425,9 +1426,14 @@ cudaError_t launch_full_rest(const SampleArgs &a, const FullWs &ws, const WorkIt
         if (a.mode != 0) return cudaSuccess;
         k_full_psums<<<pg, kFullThreads, 0, stream>>>(a, ws, full_items);
         kt->mark("full_psums", stream);
+        *launches += 1;
+        return cudaGetLastError();
+    }
+    if (part == 2) {
+        if (a.mode != 0) return cudaSuccess;
         k_full_draw<<<n_full, kThreads, kDrawSmem, stream>>>(a, ws, full_items);
         kt->mark("full_draw", stream);
-        *launches += 2;
+        *launches += 1;
         return cudaGetLastError();
     }
     cudaError_t e = ensure_dynamic_smem((const void *)k_full_walk, kRowArenaBytes);

@@ -64,7 +64,7 @@ struct StgSampler_ {
     uint64_t graph_tick = 0;
     uint64_t plan_version = 0;             // bumped with every new plan
     bool graphs_off = false;               // STG_NO_GRAPH=1, or a capture failed on this handle
-    bool lookback_drill = false;         // STG_LOOKBACK_DRILL=1 at creation: see SampleArgs::lookback_drill
+    int lookback_drill = 0;              // STG_LOOKBACK_DRILL=1 or 2 at creation: see SampleArgs::lookback_drill
 
     // workspace (allocated once at creation)
     stg::DevBuf plan_dev;                // RowPlan[], WorkItem[], pow table

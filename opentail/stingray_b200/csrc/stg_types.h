@@ -124,7 +124,7 @@ struct SampleArgs {
     float softcap;                   // != 0: every logit is read as tanh(x / softcap) * softcap
     int32_t finish_cap;              // candidates per buffer of the half-size finish (stg_flat_finish_half.cu)
     int32_t static_items;            // row kernel: CTA b takes items b, b + grid, ... (no work counter: the launch can be replayed)
-    int32_t lookback_drill;          // 1 (STG_LOOKBACK_DRILL=1 at stg_create): the exp pass's look-back is made to run out
+    int32_t lookback_drill;          // STG_LOOKBACK_DRILL at stg_create: 1 makes the exp pass's look-back run out, 2 that of the draw's partial sums
     const int32_t *redo_flags;       // row kernel as the flat step's second chance: only rows whose flag
     int32_t redo_stride;             // redo_flags[flat_full * redo_stride] is set are run; null: every row item
 };

@@ -90,18 +90,19 @@ def test_unchecked_handles_carry_no_guards():
         bs.close()
 
 
-def test_a_look_back_that_runs_out_costs_a_second_pass_not_the_result():
-    """The one wait between CTAs in the library - the look-back over the pieces of a row in the exp
-    pass - is bounded.  The drill makes it run out without any fault: piece 0 of every row withholds
-    its flag and the wait gives up after 64 polls, so every later piece times out, flags its row, and
-    the row kernel redoes the row.  Tokens and probabilities must still be the oracle's, every
+@pytest.mark.parametrize("drilled_pass", ["1", "2"])
+def test_a_look_back_that_runs_out_costs_a_second_pass_not_the_result(drilled_pass):
+    """The one wait between CTAs in the library - the look-back over the pieces of a row, in the exp
+    pass (1) and in the pass over the final probabilities (2) - is bounded.  The drill makes it run out
+    without any fault: piece 0 of every row withholds its flag in the drilled pass and the wait gives
+    up after 64 polls, so every later piece times out, flags its row, and the row kernel redoes the row.  Tokens and probabilities must still be the oracle's, every
     full-vocabulary row must report the second pass, and the handle must keep working."""
     from opentail.stingray_b200 import BatchSampler
     from opentail.stingray_b200 import workloads as W
     from tests import parity
 
     w = W.config2(rows=24, seed=11)
-    os.environ["STG_LOOKBACK_DRILL"] = "1"
+    os.environ["STG_LOOKBACK_DRILL"] = drilled_pass
     try:
         bs = BatchSampler(max_rows=w.rows, max_vocab=w.vocab, max_history=512, max_top_k=128)
     finally:
