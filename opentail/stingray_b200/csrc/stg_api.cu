@@ -545,7 +545,17 @@ int run_batch(StgHandle h, const StgSampleBatch *b, const BatchExtra &x, void *s
     // kernels of the chain.  Only steps made of replayable launches qualify: the flat form (the
     // persistent kernels of the first design draw work from counters whose base the host advances),
     // inputs already on the device, no diagnostics.
+    // every row a plain arg-max row of the flat form: one launch does the whole step (stg_flat_greedy.cu)
+    static const bool no_greedy_step = getenv("STG_NO_GREEDY_STEP") != nullptr;
+    const bool greedy_step = flat_chunks && n_rows_items == 0 && pl.n_greedy == (uint64_t)rows && n_chunk_items == rows &&
+                             x.shard_mode == 0 && a.phase_ticks == nullptr && !no_greedy_step;
     auto issue = [&]() {
+    if (greedy_step) {
+        e = launch_greedy_step(a, fr, stream);
+        launches++;
+        h->kt.mark("greedy_step", stream);
+        return;
+    }
     if (flat_chunks || flat_full) {
         if (flat_chunks && !flat_full) { e = launch_flat_prep(c, fr, stream); launches++; h->kt.mark("flat_prep", stream); }
         if (e == cudaSuccess && flat_full) { e = launch_full_prep(a, ws, flat_chunks ? fr : nullptr, stream); launches++; h->kt.mark("full_prep", stream); }
@@ -693,6 +703,7 @@ int run_batch(StgHandle h, const StgSampleBatch *b, const BatchExtra &x, void *s
     if (e != cudaSuccess) {
         cudaMemsetAsync(h->work_counter.p, 0, 8, stream);
         cudaMemsetAsync(h->tickets.p, 0, h->tickets.bytes, stream);
+        cudaMemsetAsync(h->flat_rows.p, 0, h->flat_rows.bytes, stream);
         h->work_base = 0;
         h->work_base_rows = 0;
         return cuda_fail(h, e, "sampling kernel launch");
@@ -859,6 +870,7 @@ int stg_create(const StgConfig *cfg, StgHandle *out)
         e = cudaMemset(h->work_counter.p, 0, 256);
         if (e == cudaSuccess) e = cudaMemset(h->tickets.p, 0, h->tickets.bytes);
         if (e == cudaSuccess) e = cudaMemset(h->ring_len_dev.p, 0, h->ring_len_dev.bytes);
+        if (e == cudaSuccess) e = cudaMemset(h->flat_rows.p, 0, h->flat_rows.bytes);  // keys and tickets are zero between steps
         if (e != cudaSuccess) rc = cuda_fail(nullptr, e, "cudaMemset");
     }
     if (rc != STG_OK) {

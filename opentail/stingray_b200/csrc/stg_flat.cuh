@@ -44,7 +44,8 @@ struct FlatRow {
     float tau;               // top-k: every logit > tau is a candidate
     int32_t cnt;             // top-k: candidates appended (may exceed the capacity: the excess was dropped)
     int32_t cap;             // top-k: capacity of the row's candidate list
-    int32_t pad[3];
+    int32_t ticket;          // all-greedy step (stg_flat_greedy.cu): pieces of the row that have arrived; 0 between steps
+    int32_t pad[2];
 };
 static_assert(sizeof(FlatRow) == 32, "FlatRow layout");
 
@@ -117,6 +118,8 @@ struct FullWs {
 
 cudaError_t launch_flat_prep(const SampleArgs &a, FlatRow *fr, cudaStream_t stream);
 cudaError_t launch_flat_stream(const SampleArgs &a, FlatRow *fr, const FullWs &ws, cudaStream_t stream);
+// a step of plain arg-max rows only, in one launch (stg_flat_greedy.cu); needs every row's key and ticket at zero
+cudaError_t launch_greedy_step(const SampleArgs &a, FlatRow *fr, cudaStream_t stream);
 // flat != null: also prepares the chunked rows of the flat step (then launch_flat_prep is not needed)
 cudaError_t launch_full_prep(const SampleArgs &a, const FullWs &ws, FlatRow *flat, cudaStream_t stream);
 struct KernelTimer;

@@ -30,6 +30,7 @@ __device__ void flat_finish_row(const SampleArgs &a, FlatRow *fr, int row, int i
             // a key's low half holds ~token, so the offset is subtracted)
             if (threadIdx.x == 0) {
                 const unsigned long long key = fr[row].key;
+                fr[row].key = 0ull;  // consumed: keys are zero between steps (stg_flat_greedy.cu starts from that)
                 a.xchg_local[(int64_t)row * a.xchg_stride] = key ? key - (unsigned long long)a.vocab_offset : 0ull;
                 a.xchg_count[row] = key ? 1 : 0;
             }
@@ -37,6 +38,7 @@ __device__ void flat_finish_row(const SampleArgs &a, FlatRow *fr, int row, int i
         }
         if (threadIdx.x == 0) {
             const unsigned long long key = fr[row].key;
+            fr[row].key = 0ull;  // consumed: keys are zero between steps (stg_flat_greedy.cu starts from that)
             int tok = 0;
             float val;
             uint32_t fl = kPathGreedy;
