@@ -559,7 +559,28 @@ int run_batch(StgHandle h, const StgSampleBatch *b, const BatchExtra &x, void *s
     if (flat_chunks || flat_full) {
         if (flat_chunks && !flat_full) { e = launch_flat_prep(c, fr, stream); launches++; h->kt.mark("flat_prep", stream); }
         if (e == cudaSuccess && flat_full) { e = launch_full_prep(a, ws, flat_chunks ? fr : nullptr, stream); launches++; h->kt.mark("full_prep", stream); }
-        if (e == cudaSuccess) { e = launch_flat_stream(a, fr, ws, stream); launches++; h->kt.mark("flat_stream", stream); }
+        // The HBM pass: the full-vocabulary rows (first in the item list) by the general kernel, the
+        // others by a kernel of their own that needs fewer registers and keeps more warps resident.
+        static const bool one_stream_pass = getenv("STG_ONE_STREAM_PASS") != nullptr;
+        if (one_stream_pass || x.shard_mode != 0) {
+            if (e == cudaSuccess) { e = launch_flat_stream(a, fr, ws, stream); launches++; h->kt.mark("flat_stream", stream); }
+        } else if (flat_full && flat_chunks) {
+            // both kinds: the full rows' pass on the caller's stream, where their phases follow at once; the
+            // others' pass on the side stream beside the first of those phases (the exp pass is bound by
+            // arithmetic, this one by HBM, and the full rows' chain is the longer one)
+            static const bool serial_passes = getenv("STG_SERIAL_PASSES") != nullptr;
+            cudaStream_t cs = serial_passes ? stream : h->aux_stream;
+            SampleArgs af = a;
+            af.n_items = n_rows_items;
+            if (e == cudaSuccess && !serial_passes) e = cudaEventRecord(h->ev_fork, stream);
+            if (e == cudaSuccess && !serial_passes) e = cudaStreamWaitEvent(h->aux_stream, h->ev_fork, 0);
+            if (e == cudaSuccess) { e = launch_flat_stream(af, fr, ws, stream); launches++; h->kt.mark("flat_stream_full_rows", stream); }
+            if (e == cudaSuccess) { e = launch_flat_stream_chunks(c, fr, cs); launches++; if (serial_passes) h->kt.mark("flat_stream_chunks", stream); }
+        } else if (flat_full) {
+            if (e == cudaSuccess) { e = launch_flat_stream(a, fr, ws, stream); launches++; h->kt.mark("flat_stream", stream); }
+        } else {
+            if (e == cudaSuccess) { e = launch_flat_stream_chunks(c, fr, stream); launches++; h->kt.mark("flat_stream_chunks", stream); }
+        }
     }
     const bool flat_rows = flat_full && n_rows_items > 0;
     const bool fork = both || flat_rows;  // the redo pass of the flat full rows runs on the side stream too

@@ -118,6 +118,8 @@ struct FullWs {
 
 cudaError_t launch_flat_prep(const SampleArgs &a, FlatRow *fr, cudaStream_t stream);
 cudaError_t launch_flat_stream(const SampleArgs &a, FlatRow *fr, const FullWs &ws, cudaStream_t stream);
+// the same pass over rows of the top-k path and plain arg-max rows only (stg_flat_chunks.cu)
+cudaError_t launch_flat_stream_chunks(const SampleArgs &a, FlatRow *fr, cudaStream_t stream);
 // a step of plain arg-max rows only, in one launch (stg_flat_greedy.cu); needs every row's key and ticket at zero
 cudaError_t launch_greedy_step(const SampleArgs &a, FlatRow *fr, cudaStream_t stream);
 // flat != null: also prepares the chunked rows of the flat step (then launch_flat_prep is not needed)

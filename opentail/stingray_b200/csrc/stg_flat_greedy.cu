@@ -33,13 +33,15 @@ __device__ __forceinline__ void greedy_load4(const LogitRow rowp, const uint32_t
     }
 }
 
-// grid (pieces of kFlatPiece elements, rows of a.items); 256 threads; thread t of sub-step q reads
-// elements 1024 q + 4 t .. + 3 of the piece, the next four sub-steps in flight behind the current four.
-// Measured against this form on the 256 x 151,936 batch (31.5 us): a grid resident all at once with
-// equal runs of 4096-element units per CTA was no faster, and deeper prefetch at fewer CTAs per SM
-// (3 x 3 units, 2 x 4 units in registers) was slower (39.7, 39.9 us).
+// grid (pieces of kFlatPiece elements, rows of a.items); 256 threads; in step s thread t reads elements
+// 4096 s + 1024 u + 4 t .. + 3 (u = 0..3) of the piece as four independent 16-byte loads.
+// Measured on the 256 x 151,936 batch, microseconds per step: this form 29.5 (launch bounds 256 x 5; the
+// same source under 256 x 6 or 256 x 8 gives 34.0 and 31.4, all at 31-40 registers - the difference is
+// the instruction schedule); the next four loads prefetched into a second register set (60 registers,
+// four CTAs per SM) 31.6; a grid resident all at once with equal runs of 4096-element units per CTA
+// 31.5; deeper prefetch at fewer CTAs per SM (3 x 3 units, 2 x 4 units in registers) 39.7 and 39.9.
 template <bool BF16, bool CAP>
-__global__ void __launch_bounds__(kFlatThreads) k_greedy_step(const __grid_constant__ SampleArgs a, FlatRow *fr)
+__global__ void __launch_bounds__(kFlatThreads, 5) k_greedy_step(const __grid_constant__ SampleArgs a, FlatRow *fr)
 {
     __shared__ unsigned long long red[kFlatThreads / 32];
     const int row = __ldg(&a.items[blockIdx.y].row), tid = threadIdx.x, lane = tid & 31;
@@ -51,26 +53,20 @@ __global__ void __launch_bounds__(kFlatThreads) k_greedy_step(const __grid_const
     const uint32_t *mrow = (__ldg(&rpp->use_mask) && a.mask) ? a.mask + (int64_t)row * a.mask_stride : nullptr;
     const int i0 = begin + tid * 4;
 
-    float cur[4][4], nxt[4][4];
-#pragma unroll
-    for (int u = 0; u < 4; u++) greedy_load4<BF16>(rowp, mrow, i0 + u * 1024, end, cur[u]);
+    // No register double-buffering: a thread has the four 16-byte loads of one step in flight and the
+    // other warps of the SM (40 registers: six CTAs) cover their latency.
     float best = -CUDART_INF_F;
     int best_i = -1;
+#pragma unroll 1
+    for (int s = 0; s < kFlatPiece / 4096; s++) {
+        float cur[4][4];
 #pragma unroll
-    for (int s = 0; s < kFlatSteps; s++) {
-        if (s + 1 < kFlatSteps) {
-#pragma unroll
-            for (int u = 0; u < 4; u++) greedy_load4<BF16>(rowp, mrow, i0 + ((s + 1) * 4 + u) * 1024, end, nxt[u]);
-        }
+        for (int u = 0; u < 4; u++) greedy_load4<BF16>(rowp, mrow, i0 + (s * 4 + u) * 1024, end, cur[u]);
 #pragma unroll
         for (int u = 0; u < 4; u++)
 #pragma unroll
             for (int e = 0; e < 4; e++)
                 if (cur[u][e] > best) { best = cur[u][e]; best_i = i0 + (s * 4 + u) * 1024 + e; }
-#pragma unroll
-        for (int u = 0; u < 4; u++)
-#pragma unroll
-            for (int e = 0; e < 4; e++) cur[u][e] = nxt[u][e];
     }
     // a thread visits ascending indices, so it holds its lowest index of the value; the key order
     // (value, then lower index) settles ties between threads, pieces and CTAs

@@ -284,6 +284,8 @@ static __device__ void sel_raise(Sel &s)
             c->shift = 18;
             c->cnt2 = 0;
             c->minkey = ~0ull;
+            c->cut = 0;   // no lane finds a boundary bin (fewer keys than wanted): the exact selection decides
+            c->want = 0;
         }
     }
     __syncthreads();
@@ -469,7 +471,10 @@ static __device__ void sel_stream_pass(Sel &s, const LogitRow rowp, const uint32
             const int n_saved = s.n;
             if (optimistic) {
                 const long long m = (5ll * s.n * kSelTile) / (2ll * (long long)(end - begin));
-                s.n = (int)max(32ll, min((long long)s.n, m));
+                const int target = (int)max(32ll, min((long long)s.n, m));
+                // the floor of 32 may exceed N: a sample with fewer keys than that (a sparse mask) keeps N,
+                // which it is known to exceed - the selection needs more keys than it is asked for
+                if (target < c->cnt) s.n = target;
             }
             sel_raise(s);
             s.n = n_saved;
@@ -509,7 +514,7 @@ static __device__ void sel_stream(Sel &s, const LogitRow rowp, const uint32_t *m
     sel_stream_pass<VEC, BF16>(s, rowp, mrow, begin, end, try_optimistic);
     if (try_optimistic) {
         __syncthreads();
-        const bool short_of = c->cnt < s.n && c->tau > -CUDART_INF_F;
+        const bool short_of = c->cnt < s.n && !(c->tau == -CUDART_INF_F);  // any bound but "none" may have been too high
         __syncthreads();
         if (short_of) {
             sel_reset(s);
@@ -549,7 +554,8 @@ static __device__ void sel_stream_generous(Sel &s, const LogitRow rowp, const ui
         if (ok) {
             const int n_saved = s.n;
             const long long m = ((long long)over * s.n * kSelTile) / (2ll * (long long)(end - begin));
-            s.n = (int)max(32ll, min((long long)s.n, m));
+            const int target = (int)max(32ll, min((long long)s.n, m));
+            if (target < c->cnt) s.n = target;  // as in sel_stream_pass: never more keys wanted than the sample holds
             sel_raise(s);
             s.n = n_saved;
         }

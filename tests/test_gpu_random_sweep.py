@@ -127,3 +127,43 @@ def test_bias_rows_and_distributions_match_oracle(it):
         else:
             np.testing.assert_allclose(dist[r], want, rtol=2e-5, atol=1e-30, err_msg=f"row {r}")
     assert near_cut_rows <= 2
+
+
+@pytest.mark.parametrize("vocab", [151936, 151937])
+def test_sparse_mask_with_tiny_top_k(vocab):
+    """Rows whose mask leaves so few tokens that the first tile of a row holds fewer finite logits than
+    the selection's floor of 32 keys, with top_k far below that: the bound must then come from the
+    row's own N, not from the floor (an earlier build asked the selection for 32 of 18 keys and,
+    depending on what the CTA had run before, returned token 0 for such a row).  Both forms of the
+    step: aligned rows (flat) and unaligned rows (the persistent kernels), repeated so that CTAs see
+    different predecessors."""
+    from opentail.stingray_b200 import BatchSampler, workloads as W
+
+    rng = np.random.default_rng(77)
+    rows = 64
+    logits = rng.normal(0, 2.0, (rows, vocab)).astype(np.float32)
+    p = W._params(rows)
+    p["temperature"] = rng.choice([0.7, 1.5], rows).astype(np.float32)
+    p["top_k"] = rng.choice([1, 2, 3, 40], rows)
+    p["top_p"] = rng.choice([1.0, 0.9], rows).astype(np.float32)
+    words = (vocab + 31) // 32
+    dens = rng.choice([0.002, 0.005, 0.01, 0.3], rows)
+    bits = rng.random((rows, words * 32)) < dens[:, None]
+    bits[:, :2] = True
+    mask = np.packbits(bits, axis=1, bitorder="little").view(np.uint32)
+    w = W.SampleWorkload("sparse", logits, p, W.uniforms24(rng, rows), None, None, mask)
+    bs = BatchSampler(max_rows=rows, max_vocab=vocab, max_history=8, max_top_k=64)
+    try:
+        dev = parity.to_device(w)
+        first = None
+        for rep in range(12):
+            gpu = parity.run_gpu(bs, w, dev, want_topk=64)
+            if first is None:
+                stats = parity.compare(w, gpu)
+                assert stats["mismatch"] == stats["boundary_draws"] <= 1
+                first = gpu
+            else:
+                np.testing.assert_array_equal(gpu["tokens"], first["tokens"], err_msg=f"repeat {rep}")
+                np.testing.assert_array_equal(gpu["flags"], first["flags"], err_msg=f"repeat {rep}")
+    finally:
+        bs.close()
