@@ -562,7 +562,7 @@ int run_batch(StgHandle h, const StgSampleBatch *b, const BatchExtra &x, void *s
         // The HBM pass: the full-vocabulary rows (first in the item list) by the general kernel, the
         // others by a kernel of their own that needs fewer registers and keeps more warps resident.
         static const bool one_stream_pass = getenv("STG_ONE_STREAM_PASS") != nullptr;
-        if (one_stream_pass || x.shard_mode != 0) {
+        if (one_stream_pass) {
             if (e == cudaSuccess) { e = launch_flat_stream(a, fr, ws, stream); launches++; h->kt.mark("flat_stream", stream); }
         } else if (flat_full && flat_chunks) {
             // both kinds: the full rows' pass on the caller's stream, where their phases follow at once; the
