@@ -103,7 +103,44 @@ class ClockSampler:
         self.proc = None
         self.index = device_index
 
+    def _nvml_loop(self):
+        # the same counters nvidia-smi prints, read through NVML every few milliseconds: the timed region
+        # of the headline run is a few tens of milliseconds, shorter than nvidia-smi's own sampling period
+        import pynvml as nv
+
+        R = {"hw_slowdown": nv.nvmlClocksEventReasonHwSlowdown, "hw_thermal_slowdown": nv.nvmlClocksEventReasonHwThermalSlowdown,
+             "sw_thermal_slowdown": nv.nvmlClocksEventReasonSwThermalSlowdown, "sw_power_cap": nv.nvmlClocksEventReasonSwPowerCap}
+        while not self.stop_flag:
+            try:
+                clock = nv.nvmlDeviceGetClockInfo(self.nvml_dev, nv.NVML_CLOCK_SM)
+                try:
+                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.nvml_dev)
+                except Exception:
+                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.nvml_dev)
+                self.nvml_rows.append((time.time(), float(clock), [n for n, bit in R.items() if mask & bit]))
+            except Exception:
+                break
+            time.sleep(0.004)
+
     def start(self):
+        self.nvml_rows, self.stop_flag, self.nvml_dev = [], False, None
+        try:
+            import pynvml as nv
+
+            nv.nvmlInit()
+            # NVML numbers devices like nvidia-smi; CUDA_VISIBLE_DEVICES may renumber CUDA's
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = self.index
+            if vis:
+                ids = [v.strip() for v in vis.split(",") if v.strip()]
+                if self.index < len(ids) and ids[self.index].isdigit():
+                    phys = int(ids[self.index])
+            self.nvml_dev = nv.nvmlDeviceGetHandleByIndex(phys)
+            self.nvml_max = float(nv.nvmlDeviceGetMaxClockInfo(self.nvml_dev, nv.NVML_CLOCK_SM))
+            self.nvml_thread = threading.Thread(target=self._nvml_loop, daemon=True)
+            self.nvml_thread.start()
+        except Exception:
+            self.nvml_dev = None
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
@@ -118,6 +155,15 @@ class ClockSampler:
             self.rows.append((time.time(), line.strip()))
 
     def stop(self, t0, t1):
+        self.stop_flag = True
+        if self.nvml_dev is not None:
+            inside = [r for r in self.nvml_rows if t0 <= r[0] <= t1]
+            if len(inside) >= 3:
+                if self.proc is not None:
+                    self.proc.terminate()
+                reasons = sorted({n for r in inside for n in r[2]})
+                return {"sm_mhz": statistics.median(r[1] for r in inside), "sm_max_mhz": self.nvml_max,
+                        "reasons": reasons, "samples": len(inside), "source": "NVML, every 4 ms during the timed region"}
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         time.sleep(0.15)
