@@ -832,6 +832,16 @@ def main():
     torch.cuda.synchronize()
     e2e_ms = e0.elapsed_time(e1) / e2e_steps
     e2e_tokens = np.asarray(out["tokens"])
+    # the bound of the end-to-end step: the same bytes as one plain pinned host-to-device copy, no compute
+    c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    devs[0]["logits"].view(torch.int16 if w.logits.dtype == np.uint16 else torch.float32).copy_(pin["logits"], non_blocking=True)
+    torch.cuda.synchronize()
+    c0.record()
+    for _ in range(3):
+        devs[0]["logits"].view(torch.int16 if w.logits.dtype == np.uint16 else torch.float32).copy_(pin["logits"], non_blocking=True)
+    c1.record()
+    torch.cuda.synchronize()
+    copy_ms = c0.elapsed_time(c1) / 3
 
     t = torch.tensor([ms_total, e2e_ms, launch_ms_mean], dtype=torch.float64, device="cuda")
     if world > 1:
@@ -884,7 +894,8 @@ def main():
                          "traffic": ncu_traffic(f"sample_step_{args.config}")},
             "e2e": {"value": total_rows / (e2e_ms / 1000.0), "unit": "rows/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": 4 * w.rows, "ms_per_step": e2e_ms,
-                    "h2d_gbs_per_rank": h2d / (e2e_ms / 1000.0) / 1e9},
+                    "h2d_gbs_per_rank": h2d / (e2e_ms / 1000.0) / 1e9,
+                    "pinned_copy_of_the_logits_alone_ms": copy_ms, "copy_share_of_step": copy_ms / e2e_ms},
             "gpu_launches": launches,
             "graph_replays": replays,
             "clocks": clock_info,
