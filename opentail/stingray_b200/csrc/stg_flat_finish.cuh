@@ -122,7 +122,7 @@ __device__ void flat_finish_row(const SampleArgs &a, FlatRow *fr, int row, int i
     const float u = a.uniforms ? __ldg(a.uniforms + row) : 0.5f;
     const int64_t o = (int64_t)row * a.topk_stride;
     finish_topk(s, rp, hist, ptab, u, &fs.fout, a.topk_ids ? a.topk_ids + o : nullptr,
-                a.topk_logits ? a.topk_logits + o : nullptr, a.topk_probs ? a.topk_probs + o : nullptr);
+                a.topk_logits ? a.topk_logits + o : nullptr, a.topk_probs ? a.topk_probs + o : nullptr, tk);
     tick(tk, 3);
     if (threadIdx.x == 0) {
         a.tokens[row] = fs.fout.token;

@@ -945,7 +945,7 @@ static __device__ void finish_topk_select(Sel &s, const RowPlan &rp, const int32
 // Sampler.cs:257-349.  `vals`/`ids`/`probs` views alias the inactive buffer.
 static __device__ void finish_topk(Sel &s, const RowPlan &rp, const int32_t *hist, const float *pow_tab,
                             float uniform, FinishOut *out_sh, int32_t *o_ids, float *o_vals,
-                            float *o_probs)
+                            float *o_probs, unsigned long long *tk = nullptr)
 {
     SelCtl *c = s.c;
     const int tid = threadIdx.x;
@@ -961,12 +961,15 @@ static __device__ void finish_topk(Sel &s, const RowPlan &rp, const int32_t *his
         __syncthreads();
         return;
     }
+    tick(tk, 20);
     if (k <= kFastFinishK) {
         finish_topk_select(s, rp, hist, pow_tab);
     } else {
         finish_topk_sort(s, rp, hist, pow_tab);
     }
+    tick(tk, 21);  // diagnostic stamps 20 .. 22: order the k best | softmax, filters, draw
     finish_topk_draw(s, rp, uniform, out_sh, o_ids, o_vals, o_probs);
+    tick(tk, 22);
 }
 
 // Candidate order by sorting everything (any k): leaves vals / ids of the first k in the buffer
