@@ -1136,24 +1136,27 @@ static __device__ void finish_topk_draw(Sel &s, const RowPlan &rp, float uniform
             for (int t = 0; t < count; t++)
                 if (probs[t] < thr) { count = t; break; }
         }
-        if (rp.top_p < 1.0f && rp.top_p > 0.f) {
-            float cum = 0.f;
-            for (int t = 0; t < count; t++) {
-                cum = __fadd_rn(cum, probs[t]);
-                if (cum >= rp.top_p) { count = t + 1; break; }
-            }
+        // The reference runs three sequential sums over the surviving probabilities - the top-p running
+        // sum, the kept mass, the CDF of the draw (Sampler.cs:318-349) - and all three add the same values
+        // in the same order from 0, so their partial sums are the same floats: one chain of additions,
+        // kept in `pre`, serves all three.
+        float *pre = (float *)s.buf[c->cur];  // the candidates' buffer: the selection is over, nobody reads it again
+        const bool cut = rp.top_p < 1.0f && rp.top_p > 0.f;
+        float acc = 0.f;
+        for (int t = 0; t < count; t++) {
+            acc = __fadd_rn(acc, probs[t]);
+            pre[t] = acc;
+            if (cut && acc >= rp.top_p) { count = t + 1; break; }
         }
-        float kept = 0.f;
-        for (int t = 0; t < count; t++) kept = __fadd_rn(kept, probs[t]);
+        const float kept = count > 0 ? pre[count - 1] : 0.f;
         float r = __fmul_rn(uniform, kept);
-        float cacc = 0.f;
         int tok = ids[0];
         float pr = probs[0];
         uint32_t fl = kPathTopK | (1u << 5);
         for (int t = 0; t < count; t++) {
-            const float prev = cacc;
-            cacc = __fadd_rn(cacc, probs[t]);
+            const float cacc = pre[t];
             if (r <= cacc && ids[t] >= 0) {
+                const float prev = t > 0 ? pre[t - 1] : 0.f;
                 tok = ids[t]; pr = probs[t]; fl = kPathTopK;
                 // the draw within 1e-6 (of the kept mass) of the step below or above the token
                 if (r - prev <= kNearTol * kept || cacc - r <= kNearTol * kept) fl |= kFlagNearBoundary;
