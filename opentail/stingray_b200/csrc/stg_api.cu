@@ -207,7 +207,41 @@ int make_plan(StgHandle h, const StgSampleBatch *b, int mode, bool shard, int gl
                         for (int i = g + 1; i <= 2 * g; i++) hn += 1.0 / i;
                     }
                     ng = best_ng;
+                    // The smallest of ng group maxima can also come out too high: the row then has fewer than
+                    // N logits above it and must be read again.  With x = N * sample / V (N counted in sample
+                    // elements) that happens with probability (1 - exp(-x / ng))^ng per row; more groups
+                    // until it is below 1e-7, the list's capacity permitting.
+                    const double x = (double)rp.sel / per;
+                    auto p_short = [&](int g) { return std::pow(1.0 - std::exp(-x / g), (double)g); };
+                    while (ng < 1024 && p_short(ng) > 1e-7) {
+                        double h2 = 0.0;
+                        for (int i = 1; i <= 2 * ng; i++) h2 += 1.0 / i;
+                        if (2 * ng * h2 * per > hi) break;
+                        ng *= 2;
+                    }
                     rp.flat_groups = ng;
+                    rp.flat_rank = 0;
+                    // Sharper, and what is used whenever it applies: the bound as an exact order statistic of
+                    // the sample.  The row's count above the sample's r-th largest logit is V / sample times a
+                    // Gamma(r) variable - mean r, spread sqrt(r), thin tails - where the smallest of g group
+                    // maxima scatters over a factor of three and comes in powers of two.  r: about `lo` logits
+                    // of the row above the bound, and large enough that fewer than N is a 1e-7 event
+                    // (P[Poisson(x) >= r]).  The groups' bound, with g >= r / 2 groups, then only fences off the
+                    // few dozen to few hundred sample elements among which the r-th largest is found by
+                    // ranking (flat_prep_row); should fewer than r lie above it, it stays the bound.
+                    static const bool no_rank = getenv("STG_NO_FLAT_RANK") != nullptr;
+                    int r = std::max(8, (int)std::ceil(lo / per));
+                    for (;; r++) {
+                        double term = std::exp(-x), cdf = 0.0;  // P[Poisson(x) <= r - 1]
+                        for (int i = 0; i < r; i++) { cdf += term; term *= x / (i + 1); }
+                        if (1.0 - cdf <= 1e-7 || r > 128) break;
+                    }
+                    if (!no_rank && r <= 128 && r * per <= hi) {
+                        int g = 8;
+                        while (2 * g < r) g *= 2;
+                        rp.flat_groups = g;
+                        rp.flat_rank = r;
+                    }
                 }
                 continue;
             }

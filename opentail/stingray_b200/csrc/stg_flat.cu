@@ -21,10 +21,11 @@ template <bool BF16, bool CAP>
 __global__ void __launch_bounds__(kThreads) k_flat_prep(const __grid_constant__ SampleArgs a, FlatRow *fr)
 {
     __shared__ uint32_t red[32];
+    __shared__ uint32_t list[kPrepList + 2];
     const int row = blockIdx.x;
     const RowPlan rp = a.plans[row];
     if (rp.n_chunks == 0) return;  // not a row of the flat step
-    flat_prep_row<BF16>(a, fr, row, rp, CAP ? a.softcap : 0.f, red);
+    flat_prep_row<BF16>(a, fr, row, rp, CAP ? a.softcap : 0.f, red, list);
 }
 
 // ---- k_flat_stream ------------------------------------------------------------------------------------

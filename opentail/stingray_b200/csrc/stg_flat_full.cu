@@ -39,7 +39,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_full_prep(const __grid_constant
     const RowPlan rp = a.plans[row];
     const int fi = rp.flat_full;
     if (fi < 0) {
-        if (flat != nullptr && rp.n_chunks != 0) flat_prep_row<BF16>(a, flat, row, rp, a.softcap, red);
+        if (flat != nullptr && rp.n_chunks != 0) flat_prep_row<BF16>(a, flat, row, rp, a.softcap, red, (uint32_t *)arena);
         return;
     }
     FullRow *fr = ws.rows + fi;

@@ -9,11 +9,15 @@ namespace stg {
 
 // One 1024-thread CTA for one chunked row.  Top-k rows: the filter bound.  Thread t takes elements
 // 4t .. 4t+3 of the row's first 4096 (masked) logits and keeps their maximum; the 1024 maxima are cut
-// into `flat_groups` equal groups of consecutive threads, and the bound is the smallest of the groups'
-// maxima: at least flat_groups elements of the sample lie at or above it, about twice as many on
-// average, and the planner picks flat_groups so that about 3 N elements of the whole row should.
+// into `flat_groups` equal groups of consecutive threads, and the smallest of the groups' maxima is a
+// first bound: at least flat_groups elements of the sample lie at or above it, two to five times as
+// many on average.  With flat_rank set (the planner's choice whenever it applies) the bound proper is
+// the sample's flat_rank-th largest logit, found among the elements above the first bound.
+constexpr int kPrepList = 1024;  // sample elements the exact bound is ranked among at most (list[] holds two more words)
+
 template <bool BF16>
-__device__ __forceinline__ void flat_prep_row(const SampleArgs &a, FlatRow *fr, int row, const RowPlan &rp, float softcap, uint32_t *red)
+__device__ __forceinline__ void flat_prep_row(const SampleArgs &a, FlatRow *fr, int row, const RowPlan &rp, float softcap, uint32_t *red,
+                                              uint32_t *list)
 {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (rp.path != kPathTopK) {
@@ -45,12 +49,56 @@ __device__ __forceinline__ void flat_prep_row(const SampleArgs &a, FlatRow *fr, 
     for (int o = 16; o > 0; o >>= 1) m = min(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
     if (lane == 0) red[warp] = m;
     __syncthreads();
-    if (warp == 0) {
-        m = red[lane];
+    if (rp.flat_rank == 0) {
+        if (warp == 0) {
+            m = red[lane];
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) m = min(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
-        if (lane == 0) { fr[row].key = 0ull; fr[row].tau = unord32(m); fr[row].cnt = 0; fr[row].cap = rp.sel + kFlatSlack; }
+            for (int o = 16; o > 0; o >>= 1) m = min(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+            if (lane == 0) { fr[row].key = 0ull; fr[row].tau = unord32(m); fr[row].cnt = 0; fr[row].cap = rp.sel + kFlatSlack; }
+        }
+        return;
     }
+    // The bound as the sample's flat_rank-th largest logit: the groups' bound tau0 fences off a short list
+    // of sample elements, and the element of that list with exactly flat_rank - 1 others ahead of it is the
+    // bound.  A list shorter than flat_rank, or one that does not fit (a sample full of equal values),
+    // leaves tau0 as the bound; every bound is checked by the kernel that consumes the row's candidates.
+    uint32_t t0 = red[lane];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t0 = min(t0, __shfl_xor_sync(0xFFFFFFFFu, t0, o));
+    __syncthreads();  // every warp has read red[]
+    if (tid == 0) { list[kPrepList] = 0u; list[kPrepList + 1] = t0; }
+    __syncthreads();
+    unsigned n_mine = 0;
+    uint32_t o4[4];
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+        o4[e] = ord32(v[e]);
+        n_mine += (o4[e] >= t0 && !(isinf(v[e]) && v[e] < 0.f)) ? 1u : 0u;
+    }
+    if (n_mine) {
+        unsigned slot = atomicAdd(&list[kPrepList], n_mine);
+#pragma unroll
+        for (int e = 0; e < 4; e++)
+            if (o4[e] >= t0 && !(isinf(v[e]) && v[e] < 0.f)) {
+                if (slot < (unsigned)kPrepList) list[slot] = o4[e];
+                slot++;
+            }
+    }
+    __syncthreads();
+    const int n = (int)list[kPrepList];
+    if (n >= rp.flat_rank && n <= kPrepList) {
+        for (int t = tid; t < n; t += kThreads) {
+            const uint32_t xv = list[t];
+            int rank = 0;
+            for (int j = 0; j < n; j++) {
+                const uint32_t y = list[j];
+                rank += (y > xv || (y == xv && j < t)) ? 1 : 0;
+            }
+            if (rank == rp.flat_rank - 1) list[kPrepList + 1] = xv;
+        }
+        __syncthreads();
+    }
+    if (tid == 0) { fr[row].key = 0ull; fr[row].tau = unord32(list[kPrepList + 1]); fr[row].cnt = 0; fr[row].cap = rp.sel + kFlatSlack; }
 }
 
 }  // namespace stg

@@ -46,6 +46,7 @@ struct RowPlan {
     int32_t use_mask, has_penalty, pow_off, slot;
     int32_t flat_groups; // flat step, top-k rows: groups of the sample whose maxima bound the filter (power of two)
     int32_t flat_full;   // flat step: index of a full-vocabulary row in the step's FullWs, -1 otherwise
+    int32_t flat_rank;   // flat step, top-k rows: the bound is the sample's flat_rank-th largest logit (0: the groups' bound itself)
 };
 
 struct WorkItem {
