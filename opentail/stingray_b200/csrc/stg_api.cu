@@ -179,6 +179,7 @@ int make_plan(StgHandle h, const StgSampleBatch *b, int mode, bool shard, int gl
         S = std::max(1, S / 2);
     }
     int cand_off = 0, slot = 0;
+    struct Memo { int sel = -1, groups = 0, rank = 0; } memo[64];
     for (int r = 0; r < rows; r++) {
         RowPlan &rp = pl.rows[r];
         if (mode == 0 && (rp.path == kPathGreedy || rp.path == kPathTopK)) {
@@ -188,6 +189,9 @@ int make_plan(StgHandle h, const StgSampleBatch *b, int mode, bool shard, int gl
                 rp.slot = slot++;
                 if (rp.path == kPathTopK) {
                     cand_off += rp.sel + kFlatSlack;
+                    // the choice below depends on the row's N alone (V is the step's): most rows of a step share it
+                    Memo &mm = memo[rp.sel & 63];
+                    if (rp.sel == mm.sel) { rp.flat_groups = mm.groups; rp.flat_rank = mm.rank; continue; }
                     // groups of the 4096-element sample: about 3 N survivors (at least 256) over the row
                     // The bound is the smallest of ng group maxima of the sample, above which about
                     // ng * H(ng) of the sample's elements lie (H the harmonic number), so about
@@ -242,6 +246,7 @@ int make_plan(StgHandle h, const StgSampleBatch *b, int mode, bool shard, int gl
                         rp.flat_groups = g;
                         rp.flat_rank = r;
                     }
+                    mm.sel = rp.sel; mm.groups = rp.flat_groups; mm.rank = rp.flat_rank;
                 }
                 continue;
             }
