@@ -2,21 +2,24 @@
 // large piece of one) from the first load to the last draw, the step is a short sequence of kernels
 //
 //   k_flat_prep    one CTA per row   what a row needs before it can be streamed: the filter bound of
-//                                    a top-k row (guessed from its first 4096 logits), zeroed
+//                                    a top-k row (an order statistic of its first 4096 logits), zeroed
 //                                    counters (done by k_full_prep when the step has full rows too)
-//   k_flat_stream  one small CTA per 16384-element piece of a row, every row of the batch in one
-//                  grid: the only kernel that reads the logits from HBM.  Greedy rows keep a running
-//                  arg-max key (64-bit atomicMax), top-k rows append every logit above the row's
-//                  bound to the row's candidate list (staged in shared memory, one global atomicAdd
-//                  per CTA)
+//   k_flat_stream, k_flat_stream_chunks
+//                  one small CTA per 16384-element piece of a row: the only kernels that read the
+//                  logits from HBM, each row once - the first over the full-vocabulary rows
+//                  (stg_flat.cu), the second over all others (stg_flat_chunks.cu: fewer registers,
+//                  more resident warps).  Greedy rows keep a running arg-max key (64-bit atomicMax),
+//                  top-k rows append every logit above the row's bound to the row's candidate list
+//                  (staged in shared memory, one global atomicAdd per CTA)
 //   k_flat_finish  one CTA per row   candidates only: the exact top-N selection, penalties, softmax
 //                                    over k, min-p, top-p and the draw of SampleTopK
 //                                    (src/OpenTail.Stingray.Engine/Sampler.cs:216-357); built for 1024,
 //                                    512 and 256 threads (one, two, four CTAs per SM)
+//   k_greedy_step  a step whose rows are all plain arg-max rows: the HBM pass with prep and finish
+//                  folded in, one launch (stg_flat_greedy.cu)
 //
-// so that the HBM pass runs at copy speed on all SMs whatever the mix of rows - thousands of
-// 256-thread CTAs that the hardware scheduler balances, 16 independent 16-byte loads per thread in
-// flight - and everything serial touches a few hundred candidates per row.
+// so that the HBM pass runs on all SMs whatever the mix of rows - thousands of 256-thread CTAs that
+// the hardware scheduler balances - and everything serial touches a few hundred candidates per row.
 //
 // The bound of a top-k row is optimistic, and checked: k_flat_finish accepts the candidate list only
 // when it holds between N = top_k + history length and its capacity entries - they are then exactly
